@@ -1,0 +1,249 @@
+"""Python wrappers over the extern "C" kernel launchers.
+
+Every wrapper takes CUDA torch tensors, checks what the kernel assumes (device,
+dtype, contiguity, sizes) and launches on the current torch stream.  There is no
+CPU or library fallback: a tensor that is not on a CUDA device, or a library that
+cannot be built and loaded, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported element type {t.dtype}; kernels take float32 and bfloat16") from None
+
+
+def _ptr(t):
+    return c_void_p(0) if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("rllm_b200 kernels run on a CUDA device only; got a tensor on "
+                              f"{t.device}. There is no CPU path.")
+
+
+def _need_contig(**ts):
+    for name, t in ts.items():
+        if t is not None and not t.is_contiguous():
+            raise KernelError(f"{name} must be contiguous")
+
+
+def _check(status: int, what: str):
+    if status != 0:
+        raise KernelError(f"{what}: CUDA error {status} "
+                          f"({torch.cuda.cudart().cudaGetErrorString(status) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else 'see cudaError_t'})")
+
+
+def core():
+    return build.load("core")
+
+
+# ------------------------------------------------------------------ elementwise
+
+def embed(table, tokens, out, err=None):
+    """out[t,:] = table[tokens[t],:] as float32.  table [V,d] f32/bf16, tokens int32 [n], out f32 [n,d]."""
+    _need_cuda(table, tokens, out)
+    _need_contig(table=table, tokens=tokens, out=out)
+    n, d = out.shape
+    assert tokens.dtype == torch.int32 and out.dtype == torch.float32 and table.shape[1] == d
+    _check(core().rllm_embed(_ptr(table), _code(table), _ptr(tokens), _ptr(out), c_int(n), c_int(d),
+                             c_int(table.shape[0]), _ptr(err), _stream()), "embed")
+    return out
+
+
+def add_rms_norm(x, delta, weight, out, eps, rows=None, write_x=True):
+    """out[r] = rmsnorm(x[src] (+ delta[src])) * weight with src = rows[r] if rows is given else r.
+    x is the float32 residual stream and receives the sum when write_x (and delta is given)."""
+    _need_cuda(x, delta, weight, out, rows)
+    _need_contig(x=x, delta=delta, weight=weight, out=out, rows=rows)
+    d = x.shape[-1]
+    n_rows = out.shape[0]
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == d
+    assert out.shape[-1] == d
+    if rows is None:
+        assert x.shape[0] == n_rows
+    else:
+        assert rows.dtype == torch.int32 and rows.numel() == n_rows
+    if delta is not None:
+        assert delta.shape == x.shape
+    _check(core().rllm_add_rms_norm(_ptr(x), _ptr(delta), c_int(_code(delta) if delta is not None else F32),
+                                    _ptr(rows), _ptr(weight), _ptr(out), c_int(_code(out)), c_int(n_rows),
+                                    c_int(d), c_float(eps), c_int(1 if write_x else 0), _stream()),
+           "add_rms_norm")
+    return out
+
+
+def add_inplace(x, delta):
+    _need_cuda(x, delta)
+    _need_contig(x=x, delta=delta)
+    assert x.dtype == torch.float32 and x.shape == delta.shape
+    _check(core().rllm_add_inplace(_ptr(x), _ptr(delta), c_int(_code(delta)), c_longlong(x.numel()),
+                                   _stream()), "add_inplace")
+    return x
+
+
+def silu_mul(gate_up, out):
+    """gate_up [n, 2F] (gate columns then up columns) -> out [n, F] = silu(gate) * up."""
+    _need_cuda(gate_up, out)
+    _need_contig(gate_up=gate_up, out=out)
+    n, F = out.shape
+    assert gate_up.shape == (n, 2 * F)
+    _check(core().rllm_silu_mul(_ptr(gate_up), c_int(_code(gate_up)), _ptr(out), c_int(_code(out)),
+                                c_int(n), c_int(F), _stream()), "silu_mul")
+    return out
+
+
+def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_out, k_cache, v_cache,
+                       H, K, hd, block_size, eps, write_kv=True):
+    """Fused per-head q/k RMSNorm, rotary embedding and paged K/V write; see elementwise.cu."""
+    _need_cuda(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_out, k_cache, v_cache)
+    _need_contig(qkv=qkv, q_out=q_out, k_cache=k_cache, v_cache=v_cache, positions=positions, slots=slots)
+    n = qkv.shape[0]
+    assert qkv.shape[1] == (H + 2 * K) * hd and q_out.shape == (n, H * hd)
+    assert positions.dtype == torch.int32 and slots.dtype == torch.int32
+    assert positions.numel() == n and slots.numel() == n
+    if hd % 2:
+        raise KernelError(f"head size {hd} must be even for the rotary embedding")
+    for w in (q_norm_w, k_norm_w):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == hd)
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == hd // 2)
+    assert k_cache.dtype == q_out.dtype == v_cache.dtype
+    _check(core().rllm_qk_norm_rope_store(
+        _ptr(qkv), c_int(_code(qkv)), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq), _ptr(positions),
+        _ptr(slots), _ptr(q_out), c_int(_code(q_out)), _ptr(k_cache), _ptr(v_cache), c_int(_code(k_cache)),
+        c_int(n), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(eps),
+        c_int(1 if write_kv else 0), _stream()), "qk_norm_rope_store")
+    return q_out
+
+
+# ------------------------------------------------------------------ attention
+
+def paged_attention_generic(q, k_cache, v_cache, out, positions, seq_ids, block_table, H, K, hd,
+                            block_size, scale, window=0):
+    """Plain paged causal attention; q/out [n, H*hd], caches [pages, K, block_size, hd]."""
+    _need_cuda(q, k_cache, v_cache, out, positions, seq_ids, block_table)
+    _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out, positions=positions, seq_ids=seq_ids)
+    n = q.shape[0]
+    assert q.shape == (n, H * hd) and out.shape == (n, H * hd)
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.stride(1) == 1
+    assert positions.dtype == torch.int32 and seq_ids.dtype == torch.int32
+    if hd > 512:
+        raise KernelError(f"head size {hd} exceeds the attention kernel's limit of 512")
+    if H % K:
+        raise KernelError(f"{H} query heads are not a multiple of {K} key/value heads")
+    _check(core().rllm_paged_attention_generic(
+        _ptr(q), c_int(_code(q)), _ptr(k_cache), _ptr(v_cache), c_int(_code(k_cache)), _ptr(out),
+        c_int(_code(out)), _ptr(positions), _ptr(seq_ids), _ptr(block_table), c_int(block_table.stride(0)),
+        c_int(n), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
+        _stream()), "paged_attention_generic")
+    return out
+
+
+# ------------------------------------------------------------------ matrix products
+
+def gemm_plain(a, w, out, accumulate=False):
+    """out[m,n] (+)= a[m,k] . w[n,k]^T with float32 multiply-add on the CUDA cores."""
+    _need_cuda(a, w, out)
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and out.shape == (m, n)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if accumulate and out.dtype != torch.float32:
+        raise KernelError("accumulating product needs a float32 output")
+    _check(core().rllm_gemm_plain(_ptr(a), c_int(_code(a)), _ptr(w), c_int(_code(w)), _ptr(out),
+                                  c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
+                                  c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if accumulate else 0),
+                                  _stream()), "gemm_plain")
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+
+def sample_rows(logits, out_ids, temperature=None, top_k=None, top_p=None, seed=None, counter=None):
+    """One token id per row of float32 logits [rows, vocab]; all parameter arrays are per row
+    (float32, int32, float32, int64, int64) or None (greedy)."""
+    _need_cuda(logits, out_ids, temperature, top_k, top_p, seed, counter)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert out_ids.dtype == torch.int32 and out_ids.numel() == rows
+    for t, dt in ((temperature, torch.float32), (top_k, torch.int32), (top_p, torch.float32),
+                  (seed, torch.int64), (counter, torch.int64)):
+        assert t is None or (t.dtype == dt and t.numel() == rows and t.is_contiguous())
+    if vocab >= 1 << 24:
+        raise KernelError(f"vocabulary {vocab} exceeds the sampler's limit of 2^24 - 1")
+    _check(core().rllm_sample_rows(_ptr(logits), c_longlong(logits.stride(0)), c_int(rows), c_int(vocab),
+                                   _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(counter),
+                                   _ptr(out_ids), _stream()), "sample_rows")
+    return out_ids
+
+
+# ------------------------------------------------------------------ library product and dispatch
+
+def gemm_lib(a, w, out, accumulate=False):
+    """out[m,n] (+)= a[m,k] . w[n,k]^T through cuBLAS: bfloat16 operands, float32 accumulation."""
+    _need_cuda(a, w, out)
+    m, k = a.shape
+    n = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert w.shape[1] == k and out.shape == (m, n)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    st = build.load("blas").rllm_gemm_lib(_ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(m), c_int(n),
+                                          c_int(k), c_int(a.stride(0)), c_int(w.stride(0)),
+                                          c_int(out.stride(0)), c_int(1 if accumulate else 0), _stream())
+    if st >= 10000:
+        raise KernelError(f"gemm_lib: cuBLAS status {st - 10000} for m={m} n={n} k={k}")
+    _check(st, "gemm_lib")
+    return out
+
+
+def linear(a, w, out=None, out_dtype=None, accumulate=False):
+    """out (+)= a . w^T, choosing the kernel by element type and shape.
+
+    float32 operands always take the plain CUDA-core product (the true 32-bit path).
+    bfloat16 operands take the library product; shapes it cannot take (a row stride that is
+    not a multiple of 8 elements) take the plain product with the same operand types."""
+    m, k = a.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or a.dtype, device=a.device)
+    if m == 0:
+        return out
+    if a.dtype == torch.float32 or w.dtype == torch.float32:
+        if a.dtype != w.dtype:
+            raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
+        return gemm_plain(a, w, out, accumulate)
+    aligned = (a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+               and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+               and out.stride(0) % (4 if out.dtype == torch.float32 else 8) == 0)
+    if aligned:
+        return gemm_lib(a, w, out, accumulate)
+    return gemm_plain(a, w, out, accumulate)
+
+
+def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_size, scale, window=0):
+    """Attention of the step's tokens over the paged cache; chooses the kernel by element type,
+    head size and the shape of the step (`ctx`: the step's StepContext)."""
+    return paged_attention_generic(q, k_cache, v_cache, out, ctx.positions, ctx.seq_ids, block_table,
+                                   H, K, hd, block_size, scale, window)

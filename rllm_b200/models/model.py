@@ -1,0 +1,120 @@
+"""A decoder put together from a :class:`~rllm_b200.config.base.ModelSpec`: embedding, layers
+(blocks of parts), final norm, LM head, and the run order as data.  This file knows no
+architecture; AxiomOperator/rllm's counterpart is the layer loop of
+crates/rllm-model/src/qwen3.rs:162-234, written once per architecture there.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from ..config import ModelConfig, ModelSpec, load_config
+from ..parts import Runtime, build_part, part_class
+from ..weights.loader import load_checked
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, runtime: Runtime):
+        self.spec, self.runtime = spec, runtime
+        self.embedding = build_part("embedding", spec.embedding, runtime)
+        self.blocks = [part_class("block", ls.block)(ls, runtime) for ls in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, runtime)
+        self.lm_head = build_part("lm_head", spec.lm_head, runtime)
+        self.run_order = list(spec.run_order)
+        for i, e in enumerate(self.run_order):
+            if not 0 <= e.layer < len(self.blocks):
+                raise ValueError(f"run entry {i} names layer {e.layer}, but there are {len(self.blocks)}")
+        self.loaded = False
+
+    # ------------------------------------------------------------------ tensors
+    def _weighted_parts(self):
+        ps = [self.embedding]
+        for b in self.blocks:
+            ps.extend(b.parts())
+        ps += [self.final_norm, self.lm_head]
+        return ps
+
+    def expected_tensors(self) -> dict:
+        out = {}
+        for p in self._weighted_parts():
+            out.update(p.expected_tensors())
+        return out
+
+    def ignorable_tensors(self) -> set:
+        out = set()
+        for p in self._weighted_parts():
+            if hasattr(p, "ignorable_tensors"):
+                out |= p.ignorable_tensors()
+        return out
+
+    def load_tensors(self, tensors: dict) -> None:
+        """`tensors`: name -> tensor (CPU or device), already checked against expected_tensors()."""
+        shared = {}
+        for p in self._weighted_parts():
+            if p is self.lm_head:
+                continue
+            p.load(tensors)
+        shared[self.embedding.prefix + "weight"] = self.embedding.weight
+        self.lm_head.load(tensors, shared=shared)
+        self.loaded = True
+
+    def load_dir(self, model_dir) -> None:
+        exp = {n: shape for n, (shape, _) in self.expected_tensors().items()}
+        self.load_tensors(load_checked(model_dir, exp, self.ignorable_tensors()))
+
+    # ------------------------------------------------------------------ cache needs
+    def cache_needs(self):
+        """(needs, cache_of) per run entry, for the cache manager."""
+        needs = [self.blocks[e.layer].mixer.cache_need() for e in self.run_order]
+        return needs, [e.cache_of for e in self.run_order]
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ctx, views):
+        """Runs the step's tokens through the run order; returns float32 logits [wanted, vocab]
+        (None when no row is wanted).  `views[i]` is run entry i's cache view."""
+        x = self.embedding.forward(ctx.tokens)
+        pending = None
+        for i, e in enumerate(self.run_order):
+            pending = self.blocks[e.layer].forward(x, pending, ctx, views[i])
+        if ctx.logit_rows is None or ctx.logit_rows.numel() == 0:
+            return None
+        h = self.final_norm.forward(x, pending, rows=ctx.logit_rows, write_x=False)
+        return self.lm_head.forward(h)
+
+
+def expected_tensors(spec: ModelSpec) -> dict:
+    """name -> (shape, role) of every tensor a model of `spec` reads (no device needed)."""
+    return DecoderModel(spec, Runtime(torch.device("cpu"), torch.float32)).expected_tensors()
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype in (torch.bfloat16, torch.float32):
+            return dtype
+    elif str(dtype).lower() in ("bfloat16", "bf16"):
+        return torch.bfloat16
+    elif str(dtype).lower() in ("float32", "fp32", "f32"):
+        return torch.float32
+    raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}")
+
+
+def load_model(model_dir, dtype="bfloat16", device="cuda:0"):
+    """config.json chooses the model class (through the architecture registry); weights come from
+    model.safetensors.  Returns (config, DecoderModel)."""
+    config = load_config(model_dir)
+    model = DecoderModel(config.model_spec(), Runtime(torch.device(device), parse_dtype(dtype)))
+    model.load_dir(Path(model_dir))
+    return config, model
+
+
+def random_model(config: ModelConfig, seed=0, dtype="bfloat16", device="cuda:0", std=0.02, norm_std=0.1,
+                 generate_on_device=False):
+    """A model with random weights without going through a file (large benchmarks)."""
+    from ..weights.random_init import random_tensors
+    rt = Runtime(torch.device(device), parse_dtype(dtype))
+    model = DecoderModel(config.model_spec(), rt)
+    tensors = random_tensors(model.expected_tensors(), seed, rt.dtype, std, norm_std,
+                             device=device if generate_on_device else "cpu")
+    model.load_tensors(tensors)
+    return model

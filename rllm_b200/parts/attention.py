@@ -1,0 +1,73 @@
+"""Grouped-query causal attention over the paged cache.
+
+q/k/v projections without bias, optional per-head RMSNorm on queries and keys (one weight of
+head_dim entries shared by all heads, applied before the rotation), position encoding on
+queries and keys, keys and values written to the cache at the step's slots, softmax(q.k *
+scale) over keys pos+1-window..pos (window 0: all), output projection
+(AxiomOperator/rllm: crates/rllm-model/src/qwen3.rs:195-201; attention formula
+crates/rllm-cpu/src/lib.rs:389-425; q/k norm crates/rllm-core/src/lib.rs:459-476).
+
+Parameters: hidden_size, num_heads, num_kv_heads, head_dim, qk_norm, qk_norm_eps, window,
+scale.  Tensors: <prefix>{q,k,v,o}_proj.weight and, with qk_norm, <prefix>{q,k}_norm.weight.
+Load-time transform: q, k and v are stacked into one [(H + 2K) * head_dim, hidden] matrix.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import Mixer, PagedKVNeed, PartError, register_part
+
+
+@register_part("mixer", "attention")
+class Attention(Mixer):
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        p = params
+        self.hidden_size = int(p["hidden_size"])
+        self.H = int(p["num_heads"])
+        self.K = int(p["num_kv_heads"])
+        self.hd = int(p["head_dim"])
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
+        self.window = int(p.get("window", 0) or 0)
+        self.scale = float(p["scale"])
+        if self.H % self.K:
+            raise PartError(f"attention: {self.H} heads are not a multiple of {self.K} key/value heads")
+        if self.hd % 16:
+            raise PartError(f"attention: head_dim {self.hd} must be a multiple of 16")
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    def cache_need(self):
+        return PagedKVNeed(self.K, self.hd, self.window)
+
+    def expected_tensors(self):
+        d, H, K, hd, p = self.hidden_size, self.H, self.K, self.hd, self.prefix
+        t = {p + "q_proj.weight": ((H * hd, d), "matrix"), p + "k_proj.weight": ((K * hd, d), "matrix"),
+             p + "v_proj.weight": ((K * hd, d), "matrix"), p + "o_proj.weight": ((d, H * hd), "matrix")}
+        if self.qk_norm:
+            t[p + "q_norm.weight"] = ((hd,), "norm")
+            t[p + "k_norm.weight"] = ((hd,), "norm")
+        return t
+
+    def load(self, tensors):
+        p, dt = self.prefix, self.runtime.dtype
+        self.w_qkv = self._to_device(torch.cat([tensors[p + f"{n}_proj.weight"].to(dt) for n in "qkv"], 0))
+        self.w_o = self._to_device(tensors[p + "o_proj.weight"])
+        if self.qk_norm:
+            self.q_norm_w = self._to_device(tensors[p + "q_norm.weight"], torch.float32)
+            self.k_norm_w = self._to_device(tensors[p + "k_norm.weight"], torch.float32)
+
+    def forward(self, h, ctx, cache, position):
+        n = h.shape[0]
+        dt = self.runtime.dtype
+        qkv = ops.linear(h, self.w_qkv, out_dtype=torch.float32)
+        q = torch.empty((n, self.H * self.hd), dtype=dt, device=h.device)
+        ops.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w,
+                               position.table() if position is not None else None, ctx.positions,
+                               cache.slots, q, cache.k, cache.v, self.H, self.K, self.hd,
+                               cache.block_size, self.qk_norm_eps, write_kv=cache.write)
+        attn = torch.empty_like(q)
+        ops.paged_attention(q, cache.k, cache.v, attn, ctx, cache.block_table, self.H, self.K, self.hd,
+                            cache.block_size, self.scale, self.window)
+        return ops.linear(attn, self.w_o, out_dtype=torch.float32)
