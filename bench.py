@@ -1,0 +1,230 @@
+"""Benchmark of the engine on one B200: decode tokens per second at the layer sizes of
+Qwen3-8B (random bf16 weights, batch 8, 2,048-token prompts in a 4,096-token context), plus
+prefill of 2,048 tokens, decode at batch 1 and 64, the same decode end to end through the
+Python entry point, and the roofline fractions.  Prints ONE JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  Timing: CUDA events on the launching stream,
+synchronize on both sides, W >= 3 warm-up steps; every step streams all weights (16 GB at full
+depth, far above the 126 MB L2), so no L2 flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                max_position_embeddings=40960, use_sliding_window=False)
+FULL_LAYERS = 36
+CTX, PROMPT, PREFILL_TOKENS = 4096, 2048, 2048
+METRIC = "decode tok/s at batch 8 (Qwen3-8B bf16, 2,048-token prompts, ctx 4,096)"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+        sm = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples if len(s) >= 6 for n, v in zip(names, s[2:6]) if v == "Active"})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def reference_arm():
+    """AxiomOperator/rllm is a Rust workspace (Cargo.toml, no setup.py / pyproject.toml): pip has
+    nothing to install, and neither cargo nor rustc exist in this image."""
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "AxiomOperator/rllm is a Rust workspace without a Python package; "
+                                     "pip cannot install it and cargo/rustc are not in this image"}))
+    return 0
+
+
+def weight_bytes(model):
+    """Bytes of every weight a decode step reads once: all layer matrices and norms, the final
+    norm and the LM head (the embedding table only gives one row per token)."""
+    seen, total = set(), 0
+    parts = [p for b in model.blocks for p in b.parts()] + [model.final_norm, model.lm_head]
+    for p in parts:
+        for v in vars(p).values():
+            if hasattr(v, "data_ptr") and hasattr(v, "numel") and v.is_cuda and v.data_ptr() not in seen:
+                seen.add(v.data_ptr())
+                total += v.numel() * v.element_size()
+    return total
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return reference_arm()
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    a.warmup = max(a.warmup, 3)
+
+    import torch
+    from rllm_b200.config import config_from_dict
+    from rllm_b200.csrc import ops
+    from rllm_b200.engine import Engine, StepItem
+    from rllm_b200.models.model import random_model
+    from rllm_b200.sampling.device import sample_rows
+    from rllm_b200.sampling.params import SamplingParams
+
+    pk = peaks()
+    cfg_d = dict(QWEN3_8B, num_hidden_layers=a.layers)
+    config = config_from_dict(cfg_d)
+    torch.cuda.set_device(0)
+    model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0", generate_on_device=True)
+    V = config.vocab_size
+    wbytes = weight_bytes(model)
+    g = torch.Generator().manual_seed(1)
+    greedy = SamplingParams()
+
+    def decode_run(batch, steps, warmup, e2e=False):
+        """Prefills `batch` prompts of PROMPT tokens, then times `steps` decode steps."""
+        eng = Engine(model, block_size=16, max_tokens=batch * CTX, max_requests=batch)
+        prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(batch)]
+        for b in range(batch):                       # prefill in portions of 512, one request at a time
+            for c in range(0, PROMPT, 512):
+                eng.step([StepItem(b, prompts[b][c:c + 512], [])])
+        nxt = [torch.randint(0, V, (steps + warmup,), generator=g).tolist() for _ in range(batch)]
+        cur = [int(n[0]) for n in nxt]
+        launches0 = ops.launch_count()
+        h2d = 0
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(steps + warmup):
+            if i == warmup:
+                torch.cuda.synchronize()
+                launches0 = ops.launch_count()
+                start.record()
+            items = [StepItem(b, [cur[b]], [0]) for b in range(batch)]
+            logits = eng.step(items)
+            ids = sample_rows(logits, [greedy] * batch, [0] * batch)
+            if e2e:
+                cur = ids.tolist()                   # device -> host: the step's result
+            else:
+                cur = [int(n[i + 1]) if i + 1 < len(n) else 0 for n in nxt]
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / steps
+        kv_tokens = sum(eng.cache.length(b) for b in range(batch)) - batch * steps / 2.0
+        kv_bytes = kv_tokens * eng.cache.bytes_per_token(2)
+        launches = (ops.launch_count() - launches0)
+        staging = eng.last_upload_bytes
+        for b in range(batch):
+            eng.finish(b)
+        del eng
+        torch.cuda.empty_cache()
+        return {"ms": ms, "tok_s": batch * 1000.0 / ms, "bytes": wbytes + kv_bytes, "launches": launches,
+                "h2d": staging, "d2h": 4 * batch}
+
+    clocks = ClockSampler()
+    clocks.start()
+    main_run = decode_run(a.batch, a.steps, a.warmup)
+    clk = clocks.stop()
+    e2e_run = decode_run(a.batch, a.steps, a.warmup, e2e=True)
+
+    out = {
+        "metric": METRIC, "value": round(main_run["tok_s"], 2), "unit": "tok/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(main_run["ms"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
+        "config": {"model": "Qwen3-8B-shaped", "layers": a.layers, "layers_full_model": FULL_LAYERS,
+                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
+                   "vocab": V, "global_batch": a.batch, "seq_len": CTX, "prompt_len": PROMPT,
+                   "kv_block": 16, "parallelism": "single GPU",
+                   "l2": "no flush: each step streams %.1f GB of weights (> 126 MB L2)" % (wbytes / 1e9),
+                   "peaks": pk["source"]},
+        "clocks": clk,
+        "e2e": {"value": round(e2e_run["tok_s"], 2), "unit": "tok/s", "h2d_bytes_per_step": e2e_run["h2d"],
+                "d2h_bytes_per_step": e2e_run["d2h"]},
+        "gpu_launches": main_run["launches"],
+        "roofline": {"bound": "hbm", "achieved": round(main_run["bytes"] / main_run["ms"] / 1e6, 1),
+                     "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(main_run["bytes"] / main_run["ms"] / 1e6 / pk["hbm_gbs"], 4)},
+    }
+    if not a.skip_points:
+        # prefill of 2,048 tokens in one step
+        eng = Engine(model, block_size=16, max_tokens=CTX, max_requests=1)
+        toks = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
+        times = []
+        for rep in range(4):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
+            eng.step([StepItem("p", toks, [PREFILL_TOKENS - 1])])
+            e.record()
+            torch.cuda.synchronize()
+            eng.finish("p")
+            if rep:
+                times.append(s.elapsed_time(e))
+        ms = min(times)
+        c = config
+        per_tok = 2 * a.layers * (c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
+                                  + c.num_attention_heads * c.head_dim * c.hidden_size
+                                  + 3 * c.hidden_size * c.intermediate_size)
+        attn = a.layers * 4 * c.num_attention_heads * c.head_dim * PREFILL_TOKENS * PREFILL_TOKENS / 2
+        flops = per_tok * PREFILL_TOKENS + attn + 2 * c.hidden_size * V
+        out["prefill"] = {"value": round(PREFILL_TOKENS * 1000.0 / ms, 1), "tokens": PREFILL_TOKENS,
+                          "ms": round(ms, 3), "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
+                          "peak_tflops": pk["bf16_tflops_sustained"]}
+        del eng
+        torch.cuda.empty_cache()
+        steps = max(8, a.steps // 2)
+        out["points"] = {"decode_b1": round(decode_run(1, steps, a.warmup)["tok_s"], 2),
+                         "decode_b64": round(decode_run(64, steps, a.warmup)["tok_s"], 2)}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,201 @@
+"""Command line in the manner of AxiomOperator/rllm's ``rllm`` (crates/rllm-cli/src/main.rs:24-237):
+
+  rllm run MODEL PROMPT [-n/--max-tokens 256] [-t/--temperature 0] [--top-k 0] [--top-p 1.0]
+                        [--seed 0] [--ctx 4096] [--block-size 16] [--prefill-chunk 512]
+                        [--kv-type bf16|f32] [--show-ids]
+  rllm bench MODEL [-p/--n-prompt 512] [-n/--n-gen 128] [-r/--reps 3] [--depth 0] [-b/--batch 1]
+  rllm compare MODEL PROMPT [-n/--steps 32]      engine float32 against engine bfloat16, same tokens
+  rllm inspect MODEL                              configuration and tensor list
+  rllm random-model OUT --config FILE [--seed 0] [--dtype bfloat16]
+  rllm replay ...                                 same as bin/trace_run
+
+The engine has no tokenizer: PROMPT is token ids separated by commas or spaces, or @FILE holding
+them.  MODEL is a folder with config.json and model.safetensors.  ``--kv-type`` chooses the
+precision of the whole engine (bf16 serving path, f32 true 32-bit path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from pathlib import Path
+
+
+def _ids(text: str) -> list:
+    if text.startswith("@"):
+        text = Path(text[1:]).read_text()
+    return [int(t) for t in text.replace(",", " ").split()]
+
+
+def _dtype(kv_type: str) -> str:
+    return {"bf16": "bfloat16", "bfloat16": "bfloat16", "f32": "float32", "float32": "float32"}[kv_type]
+
+
+def cmd_run(a) -> int:
+    from .llm import LLM
+    prompt = _ids(a.prompt)
+    if len(prompt) + a.max_tokens > a.ctx:
+        print(f"prompt ({len(prompt)}) + max tokens ({a.max_tokens}) exceed --ctx {a.ctx}", file=sys.stderr)
+        return 2
+    t0 = time.time()
+    llm = LLM(a.model, dtype=_dtype(a.kv_type), device=a.device, ctx=a.ctx, block_size=a.block_size,
+              prefill_chunk=a.prefill_chunk, parallel=1, host_sampling=a.host_sampling)
+    print(f"[rllm] loaded in {time.time() - t0:.2f} s", file=sys.stderr)
+    t0 = time.time()
+    out = llm.generate([prompt], max_tokens=a.max_tokens, temperature=a.temperature, top_k=a.top_k,
+                       top_p=a.top_p, seed=a.seed, stop_ids=a.stop_id or ())[0]
+    dt = time.time() - t0
+    print(" ".join(map(str, out)))
+    if a.show_ids:
+        print(f"[rllm] prompt ids: {prompt}", file=sys.stderr)
+    print(f"[rllm] {len(prompt)} prompt + {len(out)} generated tokens in {dt:.3f} s "
+          f"({len(out) / dt:.1f} tok/s overall)", file=sys.stderr)
+    return 0
+
+
+def cmd_bench(a) -> int:
+    import torch
+    from .engine import Engine, StepItem
+    from .models.model import load_model
+    _, model = load_model(a.model, _dtype(a.kv_type), a.device)
+    V = model.spec.vocab_size
+    per_req = max(a.depth, 0) + a.n_prompt + a.n_gen
+    eng = Engine(model, block_size=a.block_size, max_tokens=(per_req + 64) * a.batch, max_requests=a.batch)
+    g = torch.Generator().manual_seed(1)
+    res = {"pp": [], "tg": []}
+    for rep in range(a.reps + 1):                     # first repetition is the warm-up
+        ids = [torch.randint(0, V, (per_req,), generator=g).tolist() for _ in range(a.batch)]
+        if a.depth > 0:
+            eng.step([StepItem(b, ids[b][:a.depth], []) for b in range(a.batch)])
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.step([StepItem(b, ids[b][a.depth:a.depth + a.n_prompt], [a.n_prompt - 1]) for b in range(a.batch)])
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        for i in range(a.n_gen):
+            p = a.depth + a.n_prompt + i
+            logits = eng.step([StepItem(b, [ids[b][p]], [0]) for b in range(a.batch)])
+            logits.argmax(-1)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        for b in range(a.batch):
+            eng.finish(b)
+        if rep:
+            res["pp"].append(a.batch * a.n_prompt / (t1 - t0))
+            res["tg"].append(a.batch * a.n_gen / (t2 - t1) if a.n_gen else 0.0)
+    mean = lambda v: sum(v) / len(v)
+    print(json.dumps({"pp": a.n_prompt, "tg": a.n_gen, "batch": a.batch, "depth": a.depth,
+                      "pp_tok_s": mean(res["pp"]), "tg_tok_s": mean(res["tg"])}))
+    return 0
+
+
+def cmd_compare(a) -> int:
+    """Feeds the same tokens through the float32 and the bfloat16 engine; both continue from the
+    float32 argmax so that errors do not compound (crates/rllm-cli/src/main.rs:465-508)."""
+    import torch
+    from .engine import Engine, StepItem
+    from .models.model import load_model
+    prompt = _ids(a.prompt)
+    engines = []
+    for dt in ("float32", "bfloat16"):
+        _, m = load_model(a.model, dt, a.device)
+        engines.append(Engine(m, block_size=a.block_size, max_tokens=len(prompt) + a.steps + 64, max_requests=1))
+    feed, worst, mism = prompt, 0.0, 0
+    for i in range(a.steps + 1):
+        rows = []
+        for e in engines:
+            if len(feed) > 1:
+                for c in range(0, len(feed) - 1, a.prefill_chunk):
+                    e.step([StepItem(0, feed[c:min(c + a.prefill_chunk, len(feed) - 1)], [])])
+            rows.append(e.step([StepItem(0, feed[-1:], [0])])[0].float().cpu())
+        diff = float((rows[0] - rows[1]).abs().max())
+        rel = diff / float(rows[0].abs().max())
+        worst = max(worst, rel)
+        mism += int(rows[0].argmax()) != int(rows[1].argmax())
+        feed = [int(rows[0].argmax())]
+    print(f"max relative logit diff {worst:.3e}; argmax mismatches {mism}/{a.steps + 1}")
+    return 0
+
+
+def cmd_inspect(a) -> int:
+    from .config import load_config
+    from .weights import SafetensorsFile
+    cfg = load_config(a.model)
+    print(cfg)
+    with SafetensorsFile(Path(a.model) / "model.safetensors") as f:
+        for n in sorted(f.names()):
+            print(f"{n:60s} {str(f.dtype(n)):16s} {list(f.shape(n))}")
+    return 0
+
+
+def cmd_random_model(a) -> int:
+    import torch
+    from .config import config_from_dict
+    from .weights import write_random_model
+    cfg = config_from_dict(json.loads(Path(a.config).read_text()))
+    write_random_model(cfg, a.out, seed=a.seed,
+                       dtype={"bfloat16": torch.bfloat16, "float32": torch.float32}[a.dtype])
+    print(a.out)
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="rllm", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    def common(p):
+        p.add_argument("model")
+        p.add_argument("-d", "--device", default="cuda:0")
+        p.add_argument("--block-size", type=int, default=16)
+        p.add_argument("--kv-type", default="bf16", choices=["bf16", "f32", "bfloat16", "float32"])
+
+    p = sub.add_parser("run"); common(p)
+    p.add_argument("prompt")
+    p.add_argument("-n", "--max-tokens", type=int, default=256)
+    p.add_argument("-t", "--temperature", type=float, default=0.0)
+    p.add_argument("--top-k", type=int, default=0)
+    p.add_argument("--top-p", type=float, default=1.0)
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--ctx", type=int, default=4096)
+    p.add_argument("--prefill-chunk", type=int, default=512)
+    p.add_argument("--show-ids", action="store_true")
+    p.add_argument("--host-sampling", action="store_true")
+    p.add_argument("--stop-id", type=int, action="append")
+    p.set_defaults(fn=cmd_run)
+
+    p = sub.add_parser("bench"); common(p)
+    p.add_argument("-p", "--n-prompt", type=int, default=512)
+    p.add_argument("-n", "--n-gen", type=int, default=128)
+    p.add_argument("-r", "--reps", type=int, default=3)
+    p.add_argument("--depth", type=int, default=0)
+    p.add_argument("-b", "--batch", type=int, default=1)
+    p.set_defaults(fn=cmd_bench)
+
+    p = sub.add_parser("compare"); common(p)
+    p.add_argument("prompt")
+    p.add_argument("-n", "--steps", type=int, default=32)
+    p.add_argument("--prefill-chunk", type=int, default=512)
+    p.set_defaults(fn=cmd_compare)
+
+    p = sub.add_parser("inspect"); p.add_argument("model"); p.set_defaults(fn=cmd_inspect)
+
+    p = sub.add_parser("random-model")
+    p.add_argument("out"); p.add_argument("--config", required=True)
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    p.set_defaults(fn=cmd_random_model)
+
+    p = sub.add_parser("replay", add_help=False)
+    p.set_defaults(fn=None)
+    argv = sys.argv[1:] if argv is None else argv
+    if argv and argv[0] == "replay":
+        from .replay import main as replay_main
+        return replay_main(argv[1:])
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

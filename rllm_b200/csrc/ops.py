@@ -50,10 +50,20 @@ def _need_contig(**ts):
             raise KernelError(f"{name} must be contiguous")
 
 
-def _check(status: int, what: str):
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of this package's own kernels launched so far (library products not counted)."""
+    return _launches
+
+
+def _check(status: int, what: str, own: bool = True):
+    global _launches
     if status != 0:
-        raise KernelError(f"{what}: CUDA error {status} "
-                          f"({torch.cuda.cudart().cudaGetErrorString(status) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else 'see cudaError_t'})")
+        raise KernelError(f"{what}: CUDA error {status} (cudaError_t)")
+    if own:
+        _launches += 1
 
 
 def core():
@@ -214,7 +224,7 @@ def gemm_lib(a, w, out, accumulate=False):
                                           c_int(out.stride(0)), c_int(1 if accumulate else 0), _stream())
     if st >= 10000:
         raise KernelError(f"gemm_lib: cuBLAS status {st - 10000} for m={m} n={n} k={k}")
-    _check(st, "gemm_lib")
+    _check(st, "gemm_lib", own=False)
     return out
 
 

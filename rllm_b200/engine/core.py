@@ -43,6 +43,7 @@ class Engine:
         self._staging_events = []
         self._staging_next = 0
         self.stats = {"steps": 0, "step_tokens": 0}
+        self.last_upload_bytes = 0
 
     # ------------------------------------------------------------------ staging
     def _upload(self, arrays: Sequence[np.ndarray]):
@@ -68,6 +69,7 @@ class Engine:
             hv[o:o + a.size] = a.reshape(-1)
         dev = torch.empty(total, dtype=torch.int32, device=self.runtime.device)
         dev.copy_(host[:total], non_blocking=True)
+        self.last_upload_bytes = 4 * total
         self._staging_events[i].record()
         return [dev[o:o + a.size].view(a.shape) for a, o in zip(arrays, offs)]
 
