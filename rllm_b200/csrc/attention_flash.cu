@@ -1,0 +1,355 @@
+// Paged causal flash attention on the tensor cores (bfloat16 in, float32 softmax and accumulation),
+// for prompt portions and for decode, over the same paged cache.
+//
+// Rows of a tile are (token, query head of one key/value head) pairs: the GQA group shares every
+// key/value tile that is staged in shared memory (AxiomOperator/rllm lays its prefill tiles out the
+// same way: crates/rllm-cuda/kernels/kernels.cu:3022-3309, attn_fa; its decode kernel is the
+// split-context attn_decode, 2786-3011, with attn_decode_combine, 2964-2984).
+//
+//   S = Q K^T  : mma.sync m16n8k16, A = Q fragments kept in registers, B = K rows via ldmatrix
+//   softmax    : online, float32, exp2 with the scale folded in, masks for causality and window
+//   O += P V   : P re-used from the S accumulators as A fragments, B = V via ldmatrix.trans
+//
+// One template, two shapes:
+//   prefill: NW = 4 warps x 16 rows, key tiles of 64, whole key range, writes normalized output
+//   decode : NW = 1 warp  x 16 rows, key tiles of 32, the key range cut into splits of
+//            `split_keys` keys (a function of the position only, never of the batch), writes
+//            unnormalized partials (o, m, l) that paged_flash_combine merges in split order.
+// K/V tiles come in through cp.async (16-byte chunks, zero-filled beyond the context) into a
+// double buffer with an XOR swizzle on the chunk index, so ldmatrix is free of bank conflicts.
+// Any page size; head size 64 or 128 (other sizes take the plain kernel).
+#include "common.cuh"
+#include <math.h>
+
+struct FlashParams {
+    const bf16* q;            // [n, H, HD]
+    const bf16* k_cache;      // [pages, K, bs, HD]
+    const bf16* v_cache;
+    bf16* out;                // [n, H, HD]
+    float* part_o;            // [tile, kvh*chunks, split, rows, HD]   (decode)
+    float* part_ml;           // [tile, kvh*chunks, split, rows, 2]
+    const int* positions;     // [n]
+    const int* cu_q;          // [R+1]
+    const int* block_table;   // [R, table_stride]
+    const int* tile_req;      // [tiles] request row of each tile
+    const int* tile_tok0;     // [tiles] first flat token of each tile
+    int table_stride;
+    int H, K, bs, window;
+    int TT, GH, head_chunks;  // tokens per tile, heads per token in a tile, chunks of the GQA group
+    int split_keys;           // 0: no split
+    int part_rows;            // rows kept per partial (TT * GH)
+    float scale_log2;         // softmax scale * log2(e)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD, int NW, int BN>
+__global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const FlashParams p) {
+    constexpr int CH = HD / 8;                    // 16-byte chunks per key row
+    constexpr int TILE_BYTES = BN * HD * 2;
+    constexpr int NT_S = BN / 8;                  // score n-tiles
+    constexpr int NT_O = HD / 8;                  // output n-tiles
+    extern __shared__ __align__(128) unsigned char smem[];   // [2 stages][K tile, V tile]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+
+    const int tile = blockIdx.x;
+    const int req = p.tile_req[tile], tok0 = p.tile_tok0[tile];
+    const int nt = min(p.TT, p.cu_q[req + 1] - tok0);
+    const int grp = p.H / p.K;
+    const int kvh = blockIdx.y / p.head_chunks, hc = blockIdx.y % p.head_chunks;
+    const int head0 = kvh * grp + hc * p.GH;
+    const int nh = min(p.GH, grp - hc * p.GH);
+    const int pos_first = p.positions[tok0], pos_last = p.positions[tok0 + nt - 1];
+    int lo = p.window > 0 ? max(0, pos_first + 1 - p.window) : 0;
+    lo = lo / BN * BN;
+    int kb = lo, ke = pos_last + 1;
+    if (p.split_keys > 0) {
+        kb = lo + blockIdx.z * p.split_keys;
+        ke = min(ke, kb + p.split_keys);
+    }
+    const size_t part_base = (((size_t)tile * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z) * p.part_rows;
+
+    // this thread's two rows: (token, head) pairs
+    const int R0 = warp * 16 + g, R1 = R0 + 8;
+    const int tl0 = R0 / p.GH, hl0 = R0 % p.GH, tl1 = R1 / p.GH, hl1 = R1 % p.GH;
+    const bool valid0 = tl0 < nt && hl0 < nh, valid1 = tl1 < nt && hl1 < nh;
+    const int pos0 = valid0 ? p.positions[tok0 + tl0] : -1, pos1 = valid1 ? p.positions[tok0 + tl1] : -1;
+    const int first0 = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;
+    const int first1 = p.window > 0 ? max(0, pos1 + 1 - p.window) : 0;
+    const int hi0 = min(pos0 + 1, ke), hi1 = min(pos1 + 1, ke);
+
+    if (kb >= ke) {                                // an empty split: mark it so
+        if (p.split_keys > 0 && t == 0) {
+            if (R0 < p.part_rows) { p.part_ml[(part_base + R0) * 2] = -INFINITY; p.part_ml[(part_base + R0) * 2 + 1] = 0.f; }
+            if (R1 < p.part_rows) { p.part_ml[(part_base + R1) * 2] = -INFINITY; p.part_ml[(part_base + R1) * 2 + 1] = 0.f; }
+        }
+        return;
+    }
+
+    // Q fragments
+    uint32_t qf[HD / 16][4];
+    {
+        const bf16* q0 = p.q + ((size_t)(tok0 + (valid0 ? tl0 : 0)) * p.H + head0 + (valid0 ? hl0 : 0)) * HD;
+        const bf16* q1 = p.q + ((size_t)(tok0 + (valid1 ? tl1 : 0)) * p.H + head0 + (valid1 ? hl1 : 0)) * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            qf[ks][0] = valid0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t) : 0u;
+            qf[ks][1] = valid1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t) : 0u;
+            qf[ks][2] = valid0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t) : 0u;
+            qf[ks][3] = valid1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+
+    const int* table = p.block_table + (size_t)req * p.table_stride;
+    auto load_tile = [&](int stage, int kt) {
+        unsigned char* sk = smem + (size_t)stage * 2 * TILE_BYTES;
+        unsigned char* sv = sk + TILE_BYTES;
+        for (int idx = tid; idx < BN * CH; idx += NW * 32) {
+            const int row = idx / CH, c = idx % CH;
+            const int key = kt + row;
+            const bool ok = key < ke;              // beyond the range: zero fill
+            const int kk = ok ? key : kb;
+            const int page = table[kk / p.bs], off = kk % p.bs;
+            const size_t src = (((size_t)page * p.K + kvh) * p.bs + off) * HD + c * 8;
+            const uint32_t dst = row * (HD * 2) + ((c ^ (row & 7)) << 4);
+            cp_async16(smem_u32(sk + dst), p.k_cache + src, ok ? 16 : 0);
+            cp_async16(smem_u32(sv + dst), p.v_cache + src, ok ? 16 : 0);
+        }
+    };
+
+    float o[NT_O][4];
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    const int n_tiles = (ke - kb + BN - 1) / BN;
+    load_tile(0, kb);
+    cp_async_commit();
+    const int mi = lane >> 3, ri = lane & 7;
+    for (int it = 0; it < n_tiles; ++it) {
+        const int kt = kb + it * BN;
+        if (it + 1 < n_tiles) load_tile((it + 1) & 1, kt + BN);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const unsigned char* sk = smem + (size_t)(it & 1) * 2 * TILE_BYTES;
+        const unsigned char* sv = sk + TILE_BYTES;
+
+        // ---- S = Q K^T
+        float s[NT_S][4];
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < BN / 16; ++np) {
+                const int row = np * 16 + (mi >> 1) * 8 + ri;
+                const int chunk = ks * 2 + (mi & 1);
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(smem_u32(sk + row * (HD * 2) + ((chunk ^ ri) << 4)), b0, b1, b2, b3);
+                mma_bf16(s[2 * np], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+                mma_bf16(s[2 * np + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+            }
+        }
+        // ---- scale, mask, online softmax
+        const bool need_mask = (kt + BN > min(hi0, hi1)) || (kt < max(first0, first1));
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = s[j][e] * p.scale_log2;
+                if (need_mask) {
+                    const int key = kt + 8 * j + 2 * t + (e & 1);
+                    const bool vis = (e < 2) ? (key >= first0 && key < hi0) : (key >= first1 && key < hi1);
+                    if (!vis) v = -INFINITY;
+                }
+                s[j][e] = v;
+            }
+            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float al0 = exp2f(m0 - ms0), al1 = exp2f(m1 - ms1);      // exp2(-inf) = 0
+        m0 = mn0; m1 = mn1;
+        float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < NT_S; ++j) {
+            s[j][0] = exp2f(s[j][0] - ms0); s[j][1] = exp2f(s[j][1] - ms0);
+            s[j][2] = exp2f(s[j][2] - ms1); s[j][3] = exp2f(s[j][3] - ms1);
+            rs0 += s[j][0] + s[j][1];
+            rs1 += s[j][2] + s[j][3];
+        }
+        l0 = l0 * al0 + rs0;
+        l1 = l1 * al1 + rs1;
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) { o[j][0] *= al0; o[j][1] *= al0; o[j][2] *= al1; o[j][3] *= al1; }
+        // ---- O += P V
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+            const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {
+                const int row = kk * 16 + (mi & 1) * 8 + ri;
+                const int chunk = dp * 2 + (mi >> 1);
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_t(smem_u32(sv + row * (HD * 2) + ((chunk ^ ri) << 4)), b0, b1, b2, b3);
+                mma_bf16(o[2 * dp], a0, a1, a2, a3, b0, b1);
+                mma_bf16(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        __syncthreads();                           // the stage may be overwritten from here on
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    if (p.split_keys > 0) {
+        if (R0 < p.part_rows) {
+            float* po = p.part_o + (part_base + R0) * HD;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) *reinterpret_cast<float2*>(po + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
+            if (t == 0) { p.part_ml[(part_base + R0) * 2] = m0; p.part_ml[(part_base + R0) * 2 + 1] = valid0 ? l0 : 0.f; }
+        }
+        if (R1 < p.part_rows) {
+            float* po = p.part_o + (part_base + R1) * HD;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) *reinterpret_cast<float2*>(po + 8 * j + 2 * t) = make_float2(o[j][2], o[j][3]);
+            if (t == 0) { p.part_ml[(part_base + R1) * 2] = m1; p.part_ml[(part_base + R1) * 2 + 1] = valid1 ? l1 : 0.f; }
+        }
+    } else {
+        if (valid0) {
+            const float inv = l0 > 0.f ? 1.0f / l0 : 0.f;
+            bf16* po = p.out + ((size_t)(tok0 + tl0) * p.H + head0 + hl0) * HD;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j)
+                *reinterpret_cast<uint32_t*>(po + 8 * j + 2 * t) = pack_bf16(o[j][0] * inv, o[j][1] * inv);
+        }
+        if (valid1) {
+            const float inv = l1 > 0.f ? 1.0f / l1 : 0.f;
+            bf16* po = p.out + ((size_t)(tok0 + tl1) * p.H + head0 + hl1) * HD;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j)
+                *reinterpret_cast<uint32_t*>(po + 8 * j + 2 * t) = pack_bf16(o[j][2] * inv, o[j][3] * inv);
+        }
+    }
+}
+
+// Merges the partials of the decode shape in split order (fixed order: the result is reproducible)
+// and writes the normalized output.  grid (tiles, K * head_chunks), one thread per output dim.
+template <int HD>
+__global__ void __launch_bounds__(HD) paged_flash_combine_kernel(const FlashParams p, int n_splits) {
+    const int tile = blockIdx.x;
+    const int req = p.tile_req[tile], tok0 = p.tile_tok0[tile];
+    const int nt = min(p.TT, p.cu_q[req + 1] - tok0);
+    const int grp = p.H / p.K;
+    const int kvh = blockIdx.y / p.head_chunks, hc = blockIdx.y % p.head_chunks;
+    const int head0 = kvh * grp + hc * p.GH;
+    const int nh = min(p.GH, grp - hc * p.GH);
+    const int d = threadIdx.x;
+    const size_t base = ((size_t)tile * gridDim.y + blockIdx.y) * n_splits;
+    for (int R = 0; R < p.part_rows; ++R) {
+        const int tl = R / p.GH, hl = R % p.GH;
+        if (tl >= nt || hl >= nh) continue;
+        float M = -INFINITY;
+        for (int z = 0; z < n_splits; ++z) {
+            const float* ml = p.part_ml + ((base + z) * p.part_rows + R) * 2;
+            if (ml[1] > 0.f) M = fmaxf(M, ml[0]);
+        }
+        float num = 0.f, den = 0.f;
+        for (int z = 0; z < n_splits; ++z) {
+            const size_t row = (base + z) * p.part_rows + R;
+            const float l = p.part_ml[row * 2 + 1];
+            if (l > 0.f) {
+                const float w = exp2f(p.part_ml[row * 2] - M);
+                num += p.part_o[row * HD + d] * w;
+                den += l * w;
+            }
+        }
+        p.out[((size_t)(tok0 + tl) * p.H + head0 + hl) * HD + d] = from_f<bf16>(den > 0.f ? num / den : 0.f);
+    }
+}
+
+template <int HD>
+static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_splits, cudaStream_t stream) {
+    dim3 grid(n_tiles, p.K * p.head_chunks, mode == 0 ? 1 : n_splits);
+    if (mode == 0) {
+        constexpr int NW = 4, BN = 64;
+        const int smem = 2 * 2 * BN * HD * 2;
+        auto kern = paged_flash_attention_kernel<HD, NW, BN>;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, NW * 32, smem, stream>>>(p);
+        return RLLM_LAUNCH_STATUS();
+    }
+    constexpr int NW = 1, BN = 32;
+    const int smem = 2 * 2 * BN * HD * 2;
+    auto kern = paged_flash_attention_kernel<HD, NW, BN>;
+    kern<<<grid, NW * 32, smem, stream>>>(p);
+    int st = RLLM_LAUNCH_STATUS();
+    if (st) return st;
+    paged_flash_combine_kernel<HD><<<dim3(n_tiles, p.K * p.head_chunks), HD, 0, stream>>>(p, n_splits);
+    return RLLM_LAUNCH_STATUS();
+}
+
+// mode 0: prefill shape (64-row tiles, no split; part_* unused).  mode 1: decode shape (16-row tiles,
+// n_splits splits of split_keys keys; part_o needs tiles*K*head_chunks*n_splits*part_rows*hd floats,
+// part_ml the same with 2 in place of hd).  TT * GH must not exceed the tile's rows; split_keys must be
+// a multiple of 32.  Returns cudaErrorInvalidValue for a head size other than 64 or 128.
+RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        float* part_o, float* part_ml, const int* positions, const int* cu_q,
+                                        const int* block_table, int table_stride, const int* tile_req,
+                                        const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
+                                        float scale, int window, int mode, int TT, int GH, int head_chunks,
+                                        int split_keys, int n_splits, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    const int rows = mode == 0 ? 64 : 16;
+    if (K <= 0 || H % K || TT <= 0 || GH <= 0 || TT * GH > rows || head_chunks * GH < H / K || bs <= 0)
+        return (int)cudaErrorInvalidValue;
+    if (mode == 1 && (split_keys <= 0 || split_keys % 32 || n_splits <= 0 || !part_o || !part_ml))
+        return (int)cudaErrorInvalidValue;
+    FlashParams p;
+    p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache; p.out = (bf16*)out;
+    p.part_o = part_o; p.part_ml = part_ml; p.positions = positions; p.cu_q = cu_q; p.block_table = block_table;
+    p.tile_req = tile_req; p.tile_tok0 = tile_tok0; p.table_stride = table_stride;
+    p.H = H; p.K = K; p.bs = bs; p.window = window; p.TT = TT; p.GH = GH; p.head_chunks = head_chunks;
+    p.split_keys = mode == 0 ? 0 : split_keys; p.part_rows = TT * GH;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    if (hd == 128) return launch_flash<128>(p, mode, n_tiles, n_splits, stream);
+    if (hd == 64) return launch_flash<64>(p, mode, n_tiles, n_splits, stream);
+    return (int)cudaErrorInvalidValue;
+}

@@ -33,6 +33,8 @@ NVCC_FLAGS = [
 LIBRARIES = {
     "core": (["elementwise.cu", "attention_generic.cu", "gemm_plain.cu", "sampling.cu"], []),
     "blas": (["gemm_lib.cu"], ["-lcublas"]),
+    "fast": (["skinny_gemm.cu"], []),
+    "attn": (["attention_flash.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -228,15 +228,50 @@ def gemm_lib(a, w, out, accumulate=False):
     return out
 
 
+EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
+SKINNY_MAX_ROWS = 64
+
+
+def _skinny_ok(a, w) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= SKINNY_MAX_ROWS
+            and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def skinny_gemm(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
+    """out (+)= a . w^T for at most 64 rows of a, streaming w once (tensor-core kernel for decode).
+    epilogue EPI_SWIGLU: w holds gate rows then (from up_row_offset) up rows; out[b, j] =
+    silu(gate_j) * up_j with out [m, n], n = number of gate rows."""
+    _need_cuda(a, w, out)
+    if not _skinny_ok(a, w):
+        raise KernelError("skinny_gemm needs bfloat16 operands, at most 64 rows, k a multiple of 8 and "
+                          "16-byte aligned rows")
+    m, k = a.shape
+    n = out.shape[1]
+    assert out.shape[0] == m and out.stride(1) == 1
+    if epilogue == EPI_SWIGLU:
+        assert w.shape[0] >= up_row_offset + n
+    else:
+        assert w.shape[0] == n
+    _check(build.load("fast").rllm_skinny_gemm(
+        _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
+        c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), _stream()),
+        "skinny_gemm")
+    return out
+
+
 def linear(a, w, out=None, out_dtype=None, accumulate=False):
     """out (+)= a . w^T, choosing the kernel by element type and shape.
 
     float32 operands always take the plain CUDA-core product (the true 32-bit path).
-    bfloat16 operands take the library product; shapes it cannot take (a row stride that is
-    not a multiple of 8 elements) take the plain product with the same operand types."""
+    bfloat16 operands: up to 64 rows take the weight-streaming tensor-core kernel, more rows the
+    library product; shapes neither can take (a row length that is not a multiple of 8
+    elements) take the plain product with the same operand types."""
     m, k = a.shape
     n = w.shape[0]
     if out is None:
+        if accumulate:
+            raise KernelError("linear: accumulate needs an output to add to")
         out = torch.empty((m, n), dtype=out_dtype or a.dtype, device=a.device)
     if m == 0:
         return out
@@ -244,6 +279,8 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False):
         if a.dtype != w.dtype:
             raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
         return gemm_plain(a, w, out, accumulate)
+    if _skinny_ok(a, w):
+        return skinny_gemm(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
     aligned = (a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
                and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
                and out.stride(0) % (4 if out.dtype == torch.float32 else 8) == 0)
@@ -252,8 +289,106 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False):
     return gemm_plain(a, w, out, accumulate)
 
 
+def gate_up_swiglu(h, w_gate_up, out):
+    """out[m, F] = silu(h . Wg^T) * (h . Wu^T) with w_gate_up = [Wg; Wu] stacked ([2F, k]).
+    At most 64 rows in bfloat16: one kernel; otherwise a product followed by the activation."""
+    m = h.shape[0]
+    F = out.shape[1]
+    if _skinny_ok(h, w_gate_up):
+        return skinny_gemm(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
+    gu = linear(h, w_gate_up, out_dtype=torch.float32)     # same rounding points as the fused kernel
+    return silu_mul(gu, out)
+
+
+FLASH_HEAD_DIMS = (64, 128)
+DECODE_SPLIT_KEYS = 128        # keys per split of the decode shape: a constant, so that a request's
+                               # result never depends on the batch around it
+DECODE_MAX_Q = 8               # requests with at most this many tokens in the step take the decode shape
+
+
+class AttentionPlan:
+    """Tiles of one step for one attention geometry (query heads per key/value head, window):
+    which requests take the decode shape (16-row tiles, split keys) and which the prefill shape
+    (64-row tiles).  Built once per step on the host and shared by every layer of that geometry."""
+
+    def __init__(self, ctx, H, K, window, device):
+        g = H // K
+        self.GHd = min(g, 16)
+        self.chunks_d = -(-g // self.GHd)
+        self.GHp = min(g, 64)
+        self.chunks_p = -(-g // self.GHp)
+        self.TTp = 64 // self.GHp
+        dec = [r for r in range(ctx.n_requests) if ctx.q_lens[r] <= DECODE_MAX_Q]
+        pre = [r for r in range(ctx.n_requests) if ctx.q_lens[r] > DECODE_MAX_Q]
+        self.TTd = 1 if all(ctx.q_lens[r] == 1 for r in dec) else max(1, 16 // self.GHd)
+        cu = [0]
+        for ql in ctx.q_lens:
+            cu.append(cu[-1] + ql)
+        d_req, d_tok, p_req, p_tok = [], [], [], []
+        n_splits = 1
+        for r in dec:
+            for t0 in range(0, ctx.q_lens[r], self.TTd):
+                d_req.append(r)
+                d_tok.append(cu[r] + t0)
+                pos_first = ctx.start_pos[r] + t0
+                pos_last = ctx.start_pos[r] + min(t0 + self.TTd, ctx.q_lens[r]) - 1
+                lo = (max(0, pos_first + 1 - window) if window > 0 else 0) // 32 * 32
+                n_splits = max(n_splits, -(-(pos_last + 1 - lo) // DECODE_SPLIT_KEYS))
+        for r in pre:
+            for t0 in range(0, ctx.q_lens[r], self.TTp):
+                p_req.append(r)
+                p_tok.append(cu[r] + t0)
+        self.n_dec, self.n_pre, self.n_splits = len(d_req), len(p_req), n_splits
+        flat = torch.tensor(d_req + d_tok + p_req + p_tok + [0], dtype=torch.int32).to(device)
+        nd, np_ = self.n_dec, self.n_pre
+        self.d_req, self.d_tok = flat[:nd], flat[nd:2 * nd]
+        self.p_req, self.p_tok = flat[2 * nd:2 * nd + np_], flat[2 * nd + np_:2 * nd + 2 * np_]
+
+
+def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0,
+                          n_tiles, H, K, hd, block_size, scale, window, mode, TT, GH, head_chunks,
+                          split_keys=DECODE_SPLIT_KEYS, n_splits=1):
+    """Tensor-core paged attention; mode 0: prefill shape, mode 1: decode shape with split keys
+    (allocates the partials as scratch).  See attention_flash.cu."""
+    _need_cuda(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0)
+    _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out)
+    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS:
+        raise KernelError(f"paged_flash_attention takes bfloat16 and a head size of 64 or 128, got {q.dtype}, {hd}")
+    assert block_table.stride(1) == 1
+    part_o = part_ml = None
+    if mode == 1:
+        rows = n_tiles * K * head_chunks * n_splits * TT * GH
+        part_o = torch.empty(rows * hd, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
+    _check(build.load("attn").rllm_paged_flash_attention(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(positions),
+        _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req), _ptr(tile_tok0),
+        c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
+        c_int(mode), c_int(TT), c_int(GH), c_int(head_chunks), c_int(split_keys), c_int(n_splits),
+        _stream()), "paged_flash_attention")
+    global _launches
+    if mode == 1:
+        _launches += 1                         # the combine kernel
+    return out
+
+
 def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_size, scale, window=0):
     """Attention of the step's tokens over the paged cache; chooses the kernel by element type,
-    head size and the shape of the step (`ctx`: the step's StepContext)."""
-    return paged_attention_generic(q, k_cache, v_cache, out, ctx.positions, ctx.seq_ids, block_table,
-                                   H, K, hd, block_size, scale, window)
+    head size and the shape of the step (`ctx`: the step's StepContext).  float32, and head sizes
+    other than 64 and 128, take the plain kernel."""
+    if q.dtype != torch.bfloat16 or hd not in FLASH_HEAD_DIMS:
+        return paged_attention_generic(q, k_cache, v_cache, out, ctx.positions, ctx.seq_ids, block_table,
+                                       H, K, hd, block_size, scale, window)
+    key = (H // K, window)
+    plan = ctx.plans.get(key)
+    if plan is None:
+        plan = ctx.plans[key] = AttentionPlan(ctx, H, K, window, q.device)
+    if plan.n_pre:
+        paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.p_req,
+                              plan.p_tok, plan.n_pre, H, K, hd, block_size, scale, window, 0, plan.TTp,
+                              plan.GHp, plan.chunks_p)
+    if plan.n_dec:
+        paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.d_req,
+                              plan.d_tok, plan.n_dec, H, K, hd, block_size, scale, window, 1, plan.TTd,
+                              plan.GHd, plan.chunks_d, DECODE_SPLIT_KEYS, plan.n_splits)
+    return out

@@ -1,0 +1,188 @@
+// Weight-streaming product for decode: C[m,n] = X[m,k] . W[n,k]^T with few rows (m <= 64),
+// bfloat16 operands, float32 accumulation on the tensor cores (mma.sync m16n8k16).
+// The step is bound by reading W once from HBM, so the kernel is organised around the weight
+// stream: a CTA owns 16 weight rows (32 for the fused SwiGLU form: 16 gate rows and the 16 up
+// rows with the same index), its 8 warps interleave over k in steps of 32 elements, every thread
+// fetches 16 contiguous bytes of two weight rows straight from global memory into the
+// registers the MMA wants, and the batch rows X come through L1.  Partial sums of the 8 warps
+// are added in warp order, so a column's value never depends on the other columns (requests)
+// of the batch.
+//
+// Trick: for D = A.B the k index may be permuted as long as A and B use the same permutation.
+// Lane (g = lane/4, t = lane%4) holds elements [8t, 8t+8) of a 32-wide k step of row g for both
+// operands; elements 0-3 feed one MMA (as its k slots 2t,2t+1,2t+8,2t+9), elements 4-7 the next.
+//
+// Epilogues: store (float32 / bfloat16), accumulate into a float32 C (residual stream), or
+// SwiGLU: C[b, j] = silu(gate_j) * up_j.
+//
+// Counterparts in AxiomOperator/rllm: matvec_f (crates/rllm-cuda/kernels/kernels.cu:608-651) and
+// matvec_glu_f (1288-1356), CUDA-core kernels for m <= 8; above that it calls cuBLAS.
+#include "common.cuh"
+
+#define SG_WARPS 8
+#define SG_THREADS (SG_WARPS * 32)
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg_cached(const void* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+
+// NT: batch columns / 8.  RT: weight row tiles per CTA (2 for SwiGLU).  U: k steps fetched ahead.
+template <int NT, int EPI, typename TC, int U>
+__global__ void __launch_bounds__(SG_THREADS)
+skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, TC* __restrict__ C, int m,
+                   int n, int k, int ldw, int ldx, int ldc, int up_row_offset) {
+    constexpr int RT = (EPI == EPI_SWIGLU) ? 2 : 1;
+    extern __shared__ float red[];          // [SG_WARPS][RT][16][NT*8]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = blockIdx.x * 16;
+    // rows beyond n are clamped for loading and dropped at the store
+    const bf16* wrow[RT][2];
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt) {
+        const int base = r0 + rt * up_row_offset;
+        const int lim = (rt == 0 ? n : n + up_row_offset) - 1;
+        wrow[rt][0] = W + (size_t)min(base + g, lim) * ldw + 8 * t;
+        wrow[rt][1] = W + (size_t)min(base + g + 8, lim) * ldw + 8 * t;
+    }
+    const bf16* xrow[NT];
+    bool xok[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        xok[j] = 8 * j + g < m;
+        xrow[j] = X + (size_t)(xok[j] ? 8 * j + g : 0) * ldx + 8 * t;
+    }
+    float acc[RT][NT][4];
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[rt][j][e] = 0.f;
+
+    const int steps = (k + 31) >> 5;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int s0 = warp; s0 < steps; s0 += SG_WARPS * U) {
+        uint4 a[U][RT][2];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int kk = (s0 + u * SG_WARPS) << 5;
+            const bool ok = kk + 8 * t + 8 <= k;       // k % 8 == 0: a 16-byte chunk is whole or absent
+#pragma unroll
+            for (int rt = 0; rt < RT; ++rt) {
+                a[u][rt][0] = ok ? ldg_stream(wrow[rt][0] + kk) : zero;
+                a[u][rt][1] = ok ? ldg_stream(wrow[rt][1] + kk) : zero;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int kk = (s0 + u * SG_WARPS) << 5;
+            const bool ok = kk + 8 * t + 8 <= k;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const uint4 b = (ok && xok[j]) ? ldg_cached(xrow[j] + kk) : zero;
+#pragma unroll
+                for (int rt = 0; rt < RT; ++rt) {
+                    mma16816(acc[rt][j], a[u][rt][0].x, a[u][rt][1].x, a[u][rt][0].y, a[u][rt][1].y, b.x, b.y);
+                    mma16816(acc[rt][j], a[u][rt][0].z, a[u][rt][1].z, a[u][rt][0].w, a[u][rt][1].w, b.z, b.w);
+                }
+            }
+        }
+    }
+    // partial sums -> shared memory [warp][rt][row 0..15][batch 0..NT*8)
+    constexpr int NB = NT * 8;
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            float* base = red + ((size_t)(warp * RT + rt) * 16) * NB;
+            base[(g)*NB + 8 * j + 2 * t] = acc[rt][j][0];
+            base[(g)*NB + 8 * j + 2 * t + 1] = acc[rt][j][1];
+            base[(g + 8) * NB + 8 * j + 2 * t] = acc[rt][j][2];
+            base[(g + 8) * NB + 8 * j + 2 * t + 1] = acc[rt][j][3];
+        }
+    __syncthreads();
+    // outputs: 16 rows x NB batch columns; consecutive threads take consecutive rows (contiguous in C)
+    for (int o = threadIdx.x; o < 16 * NB; o += SG_THREADS) {
+        const int row = o & 15, b = o >> 4;
+        if (b >= m || r0 + row >= n) continue;
+        float v[RT];
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < SG_WARPS; ++w) s += red[((size_t)(w * RT + rt) * 16 + row) * NB + b];
+            v[rt] = s;
+        }
+        TC* c = C + (size_t)b * ldc + r0 + row;
+        if (EPI == EPI_STORE) *c = from_f<TC>(v[0]);
+        else if (EPI == EPI_ACCUM) *c = from_f<TC>(to_f<TC>(*c) + v[0]);
+        else *c = from_f<TC>(v[0] / (1.0f + expf(-v[0])) * v[RT - 1]);
+    }
+}
+
+template <int NT, int EPI, typename TC>
+static int launch_sg(const bf16* W, const bf16* X, void* C, int m, int n, int k, int ldw, int ldx, int ldc,
+                     int up_row_offset, cudaStream_t stream) {
+    constexpr int RT = (EPI == EPI_SWIGLU) ? 2 : 1;
+    constexpr int U = (NT * RT >= 8) ? 2 : 4;
+    const size_t smem = (size_t)SG_WARPS * RT * 16 * NT * 8 * sizeof(float);
+    auto kern = skinny_gemm_kernel<NT, EPI, TC, U>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kern<<<(n + 15) / 16, SG_THREADS, smem, stream>>>(W, X, (TC*)C, m, n, k, ldw, ldx, ldc, up_row_offset);
+    return RLLM_LAUNCH_STATUS();
+}
+
+template <int EPI, typename TC>
+static int dispatch_nt(const bf16* W, const bf16* X, void* C, int m, int n, int k, int ldw, int ldx, int ldc,
+                       int up, cudaStream_t s) {
+    if (m <= 8) return launch_sg<1, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, s);
+    if (m <= 16) return launch_sg<2, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, s);
+    if (m <= 32) return launch_sg<4, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, s);
+    return launch_sg<8, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, s);
+}
+
+// epilogue: 0 store, 1 accumulate into float32 C, 2 SwiGLU (W holds n gate rows then, from row
+// up_row_offset on, n up rows; C is [m, n]).  Requires m <= 64, k % 8 == 0, ldw % 8 == 0,
+// ldx % 8 == 0 and 16-byte aligned W and X; returns cudaErrorInvalidValue otherwise.
+RLLM_API int rllm_skinny_gemm(const void* W, const void* X, void* C, int c_dtype, int m, int n, int k,
+                              int ldw, int ldx, int ldc, int epilogue, int up_row_offset,
+                              cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (m > 64 || k <= 0 || (k & 7) || (ldw & 7) || (ldx & 7) || ((uintptr_t)W & 15) || ((uintptr_t)X & 15))
+        return (int)cudaErrorInvalidValue;
+    if (epilogue == EPI_ACCUM && c_dtype != RLLM_F32) return (int)cudaErrorInvalidValue;
+    const bf16* w = (const bf16*)W;
+    const bf16* x = (const bf16*)X;
+    if (epilogue == EPI_STORE) {
+        return c_dtype == RLLM_F32 ? dispatch_nt<EPI_STORE, float>(w, x, C, m, n, k, ldw, ldx, ldc, 0, stream)
+                                   : dispatch_nt<EPI_STORE, bf16>(w, x, C, m, n, k, ldw, ldx, ldc, 0, stream);
+    } else if (epilogue == EPI_ACCUM) {
+        return dispatch_nt<EPI_ACCUM, float>(w, x, C, m, n, k, ldw, ldx, ldc, 0, stream);
+    } else if (epilogue == EPI_SWIGLU) {
+        return c_dtype == RLLM_F32
+                   ? dispatch_nt<EPI_SWIGLU, float>(w, x, C, m, n, k, ldw, ldx, ldc, up_row_offset, stream)
+                   : dispatch_nt<EPI_SWIGLU, bf16>(w, x, C, m, n, k, ldw, ldx, ldc, up_row_offset, stream);
+    }
+    return (int)cudaErrorInvalidValue;
+}

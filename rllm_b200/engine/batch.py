@@ -40,3 +40,4 @@ class StepContext:
     max_q_len: int = 0
     max_ctx_len: int = 0
     state_slots: Optional[torch.Tensor] = None   # [R] slot of each request's fixed-size state
+    plans: dict = field(default_factory=dict)    # per-step scratch of the kernels' dispatchers

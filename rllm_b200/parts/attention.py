@@ -58,7 +58,7 @@ class Attention(Mixer):
             self.q_norm_w = self._to_device(tensors[p + "q_norm.weight"], torch.float32)
             self.k_norm_w = self._to_device(tensors[p + "k_norm.weight"], torch.float32)
 
-    def forward(self, h, ctx, cache, position):
+    def forward(self, h, ctx, cache, position, residual=None):
         n = h.shape[0]
         dt = self.runtime.dtype
         qkv = ops.linear(h, self.w_qkv, out_dtype=torch.float32)
@@ -70,4 +70,7 @@ class Attention(Mixer):
         attn = torch.empty_like(q)
         ops.paged_attention(q, cache.k, cache.v, attn, ctx, cache.block_table, self.H, self.K, self.hd,
                             cache.block_size, self.scale, self.window)
+        if residual is not None:
+            ops.linear(attn, self.w_o, out=residual, accumulate=True)
+            return None
         return ops.linear(attn, self.w_o, out_dtype=torch.float32)

@@ -103,20 +103,23 @@ class Mixer(Part):
     ``forward(h, ctx, cache, position)``: `h` [n, hidden] normed activations in the runtime's
     dtype, `ctx` the step's :class:`~rllm_b200.engine.batch.StepContext`, `cache` the view of
     this run entry's cache (:class:`~rllm_b200.cache.views.PagedKVView` or ``StateView``; None
-    if it needs none), `position` the layer's position-encoding part or None.  Returns the
-    mixer's output [n, hidden] (any float type); the block adds it to the residual stream."""
+    if it needs none), `position` the layer's position-encoding part or None, `residual` the
+    float32 residual stream [n, hidden].  Returns the mixer's output [n, hidden] (float32 or the
+    runtime's dtype), which the block adds to the residual stream; or adds it into `residual`
+    itself and returns None."""
 
     def cache_need(self):
         return None
 
-    def forward(self, h, ctx, cache, position):
+    def forward(self, h, ctx, cache, position, residual=None):
         raise NotImplementedError
 
 
 class FeedForward(Part):
-    """``forward(h, ctx)`` -> [n, hidden]."""
+    """``forward(h, ctx, residual=None)`` -> [n, hidden] or None.  As for mixers, a part may add
+    its output into the float32 `residual` itself and return None."""
 
-    def forward(self, h, ctx):
+    def forward(self, h, ctx, residual=None):
         raise NotImplementedError
 
 

@@ -2,10 +2,11 @@
 
     x += pending;  a = mixer(norm_mixer(x));  x += a;  f = ffn(norm_ffn(x));  pending = f
 
-The output of the feed-forward is handed on as `pending` instead of being added at once, so that
-the next layer's (or the final) norm adds it in the same kernel that normalizes
-(AxiomOperator/rllm: crates/rllm-model/src/qwen3.rs:192-208 fuses the next layer's norm into
-the residual add in the same way).
+A mixer or feed-forward is handed the float32 residual stream as `residual`; it may add its
+output into it itself (its last product accumulates into x) and return None, or ignore it and
+return its output, which the next norm then adds in the same kernel that normalizes
+(AxiomOperator/rllm fuses the next layer's norm into the residual add:
+crates/rllm-model/src/qwen3.rs:192-208).
 
 A block's interface: ``__init__(layer_spec, runtime)`` builds its parts from the registries;
 ``parts()`` lists them; ``forward(x, pending, ctx, cache) -> pending``.
@@ -33,6 +34,6 @@ class PreNormBlock:
 
     def forward(self, x, pending, ctx, cache):
         h = self.norm_mixer.forward(x, pending)
-        a = self.mixer.forward(h, ctx, cache, self.position)
+        a = self.mixer.forward(h, ctx, cache, self.position, residual=x)
         h = self.norm_ffn.forward(x, a)
-        return self.ffn.forward(h, ctx)
+        return self.ffn.forward(h, ctx, residual=x)

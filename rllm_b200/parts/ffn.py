@@ -33,9 +33,11 @@ class SwiGLU(FeedForward):
         self.w_gate_up = self._to_device(torch.cat([g.to(self.runtime.dtype), u.to(self.runtime.dtype)], 0))
         self.w_down = self._to_device(tensors[self.prefix + "down_proj.weight"])
 
-    def forward(self, h, ctx=None):
+    def forward(self, h, ctx=None, residual=None):
         n = h.shape[0]
-        gu = ops.linear(h, self.w_gate_up, out_dtype=self.runtime.dtype)
         act = torch.empty((n, self.intermediate_size), dtype=self.runtime.dtype, device=h.device)
-        ops.silu_mul(gu, act)
+        ops.gate_up_swiglu(h, self.w_gate_up, act)
+        if residual is not None:
+            ops.linear(act, self.w_down, out=residual, accumulate=True)
+            return None
         return ops.linear(act, self.w_down, out_dtype=torch.float32)

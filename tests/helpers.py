@@ -24,7 +24,17 @@ TINY_W = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_si
               vocab_size=311, rope_theta=50000.0, rms_norm_eps=3e-6, tie_word_embeddings=False,
               max_position_embeddings=1024, hidden_act="silu", attention_bias=False,
               use_sliding_window=True, sliding_window=24, max_window_layers=1)
-TINY = {"A": TINY_A, "B": TINY_B, "W": TINY_W}
+# head sizes 64 and 128: the tensor-core attention kernels (groups of 4 and 1, one with a window)
+TINY_F = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=128,
+              num_attention_heads=4, num_key_value_heads=1, head_dim=64, intermediate_size=192,
+              vocab_size=500, rope_theta=20000.0, rms_norm_eps=2e-6, tie_word_embeddings=True,
+              max_position_embeddings=1024, hidden_act="silu", attention_bias=False)
+TINY_G = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=72,
+              num_attention_heads=3, num_key_value_heads=3, head_dim=128, intermediate_size=136,
+              vocab_size=277, rope_theta=300000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+              max_position_embeddings=1024, hidden_act="silu", attention_bias=False,
+              sliding_window=40, layer_types=["sliding_attention", "full_attention"])
+TINY = {"A": TINY_A, "B": TINY_B, "W": TINY_W, "F": TINY_F, "G": TINY_G}
 
 
 def make_model_dir(path, cfg: dict, seed: int, dtype=torch.float32, std=0.02, norm_std=0.1, scale_attn=1.0):

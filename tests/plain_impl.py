@@ -50,6 +50,16 @@ def load_model(model_dir, dtype=torch.float32):
     return cfg, w
 
 
+# ---------------------------------------------------------------- storage rounding
+# The engine's bfloat16 mode stores activations between kernels and the cache in bfloat16 while
+# every sum, norm, softmax and the residual stream stay float32.  `storage` names that type; the
+# functions below round at exactly those hand-over points (norm outputs, rotated queries and keys,
+# values, attention output, the SwiGLU activation) and nowhere else.  None: no rounding.
+
+def _store(x, storage):
+    return x if storage is None else x.to(storage).to(torch.float32)
+
+
 # ---------------------------------------------------------------- parts
 
 def embed(table, tokens):
@@ -109,16 +119,16 @@ def attention(q, k, v, scale, window=0):
     return out
 
 
-def swiglu(x, w_gate, w_up, w_down):
+def swiglu(x, w_gate, w_up, w_down, storage=None):
     """act = gate/(1+exp(-gate)) * up; out = act . Wd^T.
     crates/rllm-core/src/lib.rs:247-262, crates/rllm-cpu/src/lib.rs:292-298"""
     gate = linear(x, w_gate)
     up = linear(x, w_up)
-    act = gate / (1.0 + torch.exp(-gate)) * up
+    act = _store(gate / (1.0 + torch.exp(-gate)) * up, storage)
     return linear(act, w_down)
 
 
-def attention_block(h, positions, w, prefix, cfg, window):
+def attention_block(h, positions, w, prefix, cfg, window, storage=None):
     """q/k/v projections, per-head q/k RMSNorm (weight of hd entries shared by all
     heads, same eps as the layer norms, before RoPE), RoPE on q and k, attention,
     output projection.  crates/rllm-model/src/qwen3.rs:195-201,
@@ -133,9 +143,10 @@ def attention_block(h, positions, w, prefix, cfg, window):
     v = linear(h, w[prefix + "self_attn.v_proj.weight"]).view(n, K, hd)
     q = rms_norm(q, w[prefix + "self_attn.q_norm.weight"], eps)
     k = rms_norm(k, w[prefix + "self_attn.k_norm.weight"], eps)
-    q = rope_neox(q, positions, theta)
-    k = rope_neox(k, positions, theta)
-    a = attention(q, k, v, 1.0 / math.sqrt(hd), window)
+    q = _store(rope_neox(q, positions, theta), storage)
+    k = _store(rope_neox(k, positions, theta), storage)
+    v = _store(v, storage)
+    a = _store(attention(q, k, v, 1.0 / math.sqrt(hd), window), storage)
     return linear(a.reshape(n, H * hd), w[prefix + "self_attn.o_proj.weight"])
 
 
@@ -162,7 +173,7 @@ def layer_windows(cfg):
     return [0] * L
 
 
-def forward(cfg, w, tokens):
+def forward(cfg, w, tokens, storage=None):
     """Logits [n, vocab] for one whole sequence; pre-norm decoder:
     x += attn(norm1(x)); x += ffn(norm2(x)); logits = lm_head(final_norm(x)),
     lm_head tied to the embedding when the tensor is absent.
@@ -174,12 +185,12 @@ def forward(cfg, w, tokens):
     x = embed(w["model.embed_tokens.weight"], tokens)
     for li in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{li}."
-        h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-        x = x + attention_block(h, positions, w, p, cfg, windows[li])
-        h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+        h = _store(rms_norm(x, w[p + "input_layernorm.weight"], eps), storage)
+        x = x + attention_block(h, positions, w, p, cfg, windows[li], storage)
+        h = _store(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps), storage)
         x = x + swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
-                       w[p + "mlp.down_proj.weight"])
-    x = rms_norm(x, w["model.norm.weight"], eps)
+                       w[p + "mlp.down_proj.weight"], storage)
+    x = _store(rms_norm(x, w["model.norm.weight"], eps), storage)
     head = w.get("lm_head.weight")
     if head is None:
         head = w["model.embed_tokens.weight"]

@@ -1,0 +1,299 @@
+"""Each kernel alone against a plain float32 torch reference of the same op, at sizes other than
+the engine's tiny configurations (widths and vocabularies that are no power of two, odd row
+counts, head sizes in steps of 16, scattered page tables).  In the manner of
+AxiomOperator/rllm's parity tests (crates/rllm-cuda/tests/common/parity.rs:130-652).
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_impl
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from rllm_b200.csrc import ops as o
+    return o
+
+
+def rnd(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    V, d = 311, 200
+    table = rnd(V, d, seed=1).to(dtype)
+    toks = torch.tensor([0, 310, 5, 5, 77], dtype=torch.int32)
+    out = torch.empty(5, d, device=DEV)
+    ops().embed(table.to(DEV), toks.to(DEV), out)
+    assert torch.equal(out.cpu(), table.float()[toks.long()])
+
+
+@pytest.mark.parametrize("d", [64, 200, 4096, 5000])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rms_norm(d, out_dtype):
+    n, eps = 7, 3e-6
+    x, delta, w = rnd(n, d, seed=2), rnd(n, d, seed=3), 1 + 0.1 * rnd(d, seed=4)
+    ref = plain_impl.rms_norm(x + delta, w, eps)
+    xd = x.to(DEV)
+    out = torch.empty(n, d, dtype=out_dtype, device=DEV)
+    ops().add_rms_norm(xd, delta.to(DEV), w.to(DEV), out, eps)
+    tol = 1e-5 if out_dtype == torch.float32 else 5e-3
+    assert rel_err(out.float().cpu(), ref) < tol
+    assert torch.equal(xd.cpu(), x + delta)                      # residual stream received the sum
+    # gathered rows, no write-back, no delta
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    out2 = torch.empty(3, d, dtype=out_dtype, device=DEV)
+    x2 = x.to(DEV)
+    ops().add_rms_norm(x2, None, w.to(DEV), out2, eps, rows=rows.to(DEV), write_x=False)
+    assert rel_err(out2.float().cpu(), plain_impl.rms_norm(x[rows.long()], w, eps)) < tol
+    assert torch.equal(x2.cpu(), x)
+
+
+def test_silu_mul():
+    n, F = 5, 333
+    gu = rnd(n, 2 * F, seed=5, scale=3.0)
+    g, u = gu[:, :F], gu[:, F:]
+    ref = g / (1 + torch.exp(-g)) * u
+    out = torch.empty(n, F, device=DEV)
+    ops().silu_mul(gu.to(DEV), out)
+    assert rel_err(out.cpu(), ref) < 1e-6
+
+
+@pytest.mark.parametrize("hd,H,K", [(16, 4, 2), (48, 5, 1), (128, 8, 2), (80, 3, 3)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_store(hd, H, K, dtype):
+    n, bs, pages, theta, eps = 9, 8, 6, 50000.0, 1e-5
+    qkv = rnd(n, (H + 2 * K) * hd, seed=6)
+    qw, kw = 1 + 0.1 * rnd(hd, seed=7), 1 + 0.1 * rnd(hd, seed=8)
+    positions = torch.tensor([0, 1, 17, 300, 4095, 2, 3, 4, 5], dtype=torch.int32)
+    slots = torch.tensor([40, 3, 17, 9, 8, 47, 0, 25, 31], dtype=torch.int32)
+    q = qkv[:, :H * hd].view(n, H, hd)
+    k = qkv[:, H * hd:(H + K) * hd].view(n, K, hd)
+    v = qkv[:, (H + K) * hd:].view(n, K, hd)
+    q_ref = plain_impl.rope_neox(plain_impl.rms_norm(q, qw, eps), positions.tolist(), theta)
+    k_ref = plain_impl.rope_neox(plain_impl.rms_norm(k, kw, eps), positions.tolist(), theta)
+    inv = 1.0 / torch.pow(torch.tensor(theta), torch.arange(0, hd, 2).float() / hd)
+    kc = torch.zeros(pages, K, bs, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(n, H * hd, dtype=dtype, device=DEV)
+    ops().qk_norm_rope_store(qkv.to(DEV), qw.to(DEV), kw.to(DEV), inv.to(DEV), positions.to(DEV),
+                             slots.to(DEV), q_out, kc, vc, H, K, hd, bs, eps)
+    # rotation angles at position 4095 differ by a few float32 ulps between sin/cos implementations
+    tol = 2e-4 if dtype == torch.float32 else 1e-2
+    assert rel_err(q_out.float().cpu().view(n, H, hd), q_ref) < tol
+    for t in range(n):
+        s = int(slots[t])
+        assert rel_err(kc[s // bs, :, s % bs].float().cpu(), k_ref[t]) < tol
+        assert rel_err(vc[s // bs, :, s % bs].float().cpu(), v[t]) < (1e-7 if dtype == torch.float32 else 1e-2)
+    used = {int(s) for s in slots}
+    for s in range(pages * bs):
+        if s not in used:
+            assert float(kc[s // bs, :, s % bs].abs().max()) == 0.0
+
+
+def paged_case(hd, H, K, bs, lens, q_lens, seed, dtype, window=0, spike=False):
+    """Builds a scattered paged cache for requests of `lens` tokens whose last `q_lens` tokens are
+    the step's queries; returns kernel inputs and the plain reference output."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(lens)
+    n_pages = sum(-(-L // bs) for L in lens) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kc = torch.zeros(n_pages, K, bs, hd)
+    vc = torch.zeros(n_pages, K, bs, hd)
+    width = max(-(-L // bs) for L in lens)
+    table = torch.zeros(R, width, dtype=torch.int32)
+    qs, pos, sid, refs = [], [], [], []
+    for r, (L, ql) in enumerate(zip(lens, q_lens)):
+        k = torch.randn(L, K, hd, generator=g)
+        v = torch.randn(L, K, hd, generator=g)
+        q = torch.randn(L, H, hd, generator=g)
+        if spike:
+            # one far key stands out: a fault that drops or misplaces it shows at once
+            far = L // 7
+            k[far] *= 0.0
+            k[far, :, 0] = 6.0
+            q[:, :, 0] = 6.0
+        k, v, q = k.to(dtype).float(), v.to(dtype).float(), q.to(dtype).float()
+        for b in range(-(-L // bs)):
+            page = perm.pop()
+            table[r, b] = page
+            m = min(bs, L - b * bs)
+            kc[page, :, :m] = k[b * bs:b * bs + m].transpose(0, 1)
+            vc[page, :, :m] = v[b * bs:b * bs + m].transpose(0, 1)
+        full = plain_impl.attention(q, k, v, 1.0 / math.sqrt(hd), window)
+        refs.append(full[L - ql:].reshape(ql, H * hd))
+        qs.append(q[L - ql:].reshape(ql, H * hd))
+        pos += list(range(L - ql, L))
+        sid += [r] * ql
+    return dict(q=torch.cat(qs).to(dtype).to(DEV), kc=kc.to(dtype).to(DEV), vc=vc.to(dtype).to(DEV),
+                table=table.to(DEV), pos=torch.tensor(pos, dtype=torch.int32, device=DEV),
+                sid=torch.tensor(sid, dtype=torch.int32, device=DEV), ref=torch.cat(refs),
+                q_lens=q_lens, lens=lens)
+
+
+@pytest.mark.parametrize("hd,H,K,bs", [(16, 4, 2, 4), (64, 6, 2, 16), (128, 8, 2, 16), (48, 5, 5, 8), (256, 2, 1, 32)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 37])
+def test_paged_attention_generic(hd, H, K, bs, dtype, window):
+    c = paged_case(hd, H, K, bs, lens=[300, 1, 77, 129], q_lens=[3, 1, 77, 1], seed=9, dtype=dtype,
+                   window=window, spike=True)
+    out = torch.empty_like(c["q"])
+    ops().paged_attention_generic(c["q"], c["kc"], c["vc"], out, c["pos"], c["sid"], c["table"], H, K, hd,
+                                  bs, 1.0 / math.sqrt(hd), window)
+    assert rel_err(out.float().cpu(), c["ref"]) < (2e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 96, 512), (3, 37, 100), (33, 130, 257), (64, 64, 64), (200, 311, 96)])
+def test_gemm_plain(m, n, k):
+    a, w = rnd(m, k, seed=10), rnd(n, k, seed=11)
+    ref = (a.double() @ w.double().t()).float()
+    out = torch.empty(m, n, device=DEV)
+    ops().gemm_plain(a.to(DEV), w.to(DEV), out)
+    assert rel_err(out.cpu(), ref) < 2e-6
+    base = rnd(m, n, seed=12)
+    acc = base.to(DEV)
+    ops().gemm_plain(a.to(DEV), w.to(DEV), acc, accumulate=True)
+    assert rel_err(acc.cpu(), ref + base) < 2e-6
+    # a row's result does not depend on the rows around it: bit-identical alone and in the batch
+    alone = torch.empty(1, n, device=DEV)
+    ops().gemm_plain(a[m - 1:m].to(DEV), w.to(DEV), alone)
+    assert torch.equal(alone[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m,n,k", [(9, 96, 512), (70, 1000, 264), (256, 384, 4096)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_lib(m, n, k, out_dtype):
+    a, w = rnd(m, k, seed=13, dtype=torch.bfloat16), rnd(n, k, seed=14, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    out = torch.empty(m, n, dtype=out_dtype, device=DEV)
+    ops().gemm_lib(a.to(DEV), w.to(DEV), out)
+    assert rel_err(out.float().cpu(), ref) < (1e-5 if out_dtype == torch.float32 else 5e-3)
+    if out_dtype == torch.float32:
+        base = rnd(m, n, seed=15)
+        acc = base.to(DEV)
+        ops().gemm_lib(a.to(DEV), w.to(DEV), acc, accumulate=True)
+        assert rel_err(acc.cpu(), ref + base) < 1e-5
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("n,k", [(96, 512), (37, 264), (4096, 4096), (1000, 12288), (50, 8)])
+def test_skinny_gemm(m, n, k):
+    a, w = rnd(m, k, seed=16, dtype=torch.bfloat16), rnd(n, k, seed=17, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    out = torch.empty(m, n, device=DEV)
+    o = ops()
+    o.skinny_gemm(a.to(DEV), w.to(DEV), out)
+    assert rel_err(out.cpu(), ref) < 1e-5
+    out16 = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    o.skinny_gemm(a.to(DEV), w.to(DEV), out16)
+    assert rel_err(out16.float().cpu(), ref) < 5e-3
+    base = rnd(m, n, seed=18)
+    acc = base.to(DEV)
+    o.skinny_gemm(a.to(DEV), w.to(DEV), acc, epilogue=o.EPI_ACCUM)
+    assert rel_err(acc.cpu(), ref + base) < 1e-5
+    # a request's column does not depend on its batch-mates
+    alone = torch.empty(1, n, device=DEV)
+    o.skinny_gemm(a[m - 1:m].to(DEV), w.to(DEV), alone)
+    assert torch.equal(alone[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m", [1, 8, 20, 64])
+@pytest.mark.parametrize("F,k", [(224, 96), (1000, 264), (12288, 4096), (37, 64)])
+def test_skinny_gemm_swiglu(m, F, k):
+    a = rnd(m, k, seed=19, dtype=torch.bfloat16)
+    w = rnd(2 * F, k, seed=20, scale=0.2, dtype=torch.bfloat16)
+    g, u = a.float() @ w[:F].float().t(), a.float() @ w[F:].float().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    out = torch.empty(m, F, dtype=torch.bfloat16, device=DEV)
+    ops().gate_up_swiglu(a.to(DEV), w.to(DEV), out)
+    assert rel_err(out.float().cpu(), ref) < 5e-3
+    out32 = torch.empty(m, F, device=DEV)
+    ops().gate_up_swiglu(a.to(DEV), w.to(DEV), out32)
+    assert rel_err(out32.cpu(), ref) < 1e-5
+
+
+def test_sample_rows_matches_plain():
+    rows, V = 12, 1531
+    logits = rnd(rows, V, seed=21, scale=3.0)
+    logits[3, 7] = logits[3].max() + 1
+    logits[3, 900] = logits[3, 7]                    # tie: the lower index wins
+    logits[4, 11] = float("nan")                     # NaNs never win
+    o = ops()
+    ids = torch.empty(rows, dtype=torch.int32, device=DEV)
+    o.sample_rows(logits.to(DEV), ids)
+    want = [plain_impl.sample_row(torch.nan_to_num(logits[r], nan=-1e30).numpy(), 0, 0, 1.0, 0, 0) for r in range(rows)]
+    assert ids.tolist() == want
+    assert ids[3].item() == 7
+    clean = torch.nan_to_num(logits, nan=-1e30)
+    T = torch.tensor([0.8, 1.0, 0.5, 1.3] * 3)
+    tk = torch.tensor([0, 5, 0, 40] * 3, dtype=torch.int32)
+    tp = torch.tensor([1.0, 1.0, 0.9, 0.7] * 3)
+    seed = torch.arange(rows, dtype=torch.int64) * 7919 + 4
+    ctr = torch.arange(rows, dtype=torch.int64) + 100
+    o.sample_rows(clean.to(DEV), ids, T.to(DEV), tk.to(DEV), tp.to(DEV), seed.to(DEV), ctr.to(DEV))
+    want = [plain_impl.sample_row(clean[r].numpy(), float(T[r]), int(tk[r]), float(tp[r]), int(seed[r]), int(ctr[r]))
+            for r in range(rows)]
+    same = sum(int(a == b) for a, b in zip(ids.tolist(), want))
+    assert same >= rows - 1, (ids.tolist(), want)     # float rounding of log/exp may flip a near tie
+
+
+def test_sample_rows_frequencies():
+    """Draws follow softmax(logits / T) (crates/rllm-core/src/sample.rs:133-161)."""
+    V, N = 6, 20000
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 1.5, -3.0]]).repeat(N, 1)
+    ids = torch.empty(N, dtype=torch.int32, device=DEV)
+    T = torch.full((N,), 0.7)
+    ops().sample_rows(logits.to(DEV), ids, T.to(DEV), torch.zeros(N, dtype=torch.int32, device=DEV),
+                      torch.ones(N, device=DEV), torch.full((N,), 5, dtype=torch.int64, device=DEV),
+                      torch.arange(N, dtype=torch.int64, device=DEV))
+    freq = torch.bincount(ids.cpu().long(), minlength=V).float() / N
+    p = torch.softmax(logits[0] / 0.7, 0)
+    assert float((freq - p).abs().max()) < 0.015
+
+
+class FakeCtx:
+    """The part of a StepContext the attention dispatcher reads."""
+
+    def __init__(self, case):
+        self.n_requests = len(case["lens"])
+        self.q_lens = list(case["q_lens"])
+        self.start_pos = [L - q for L, q in zip(case["lens"], case["q_lens"])]
+        self.positions, self.seq_ids = case["pos"], case["sid"]
+        cu = [0]
+        for q in self.q_lens:
+            cu.append(cu[-1] + q)
+        self.cu_q = torch.tensor(cu, dtype=torch.int32, device=DEV)
+        self.plans = {}
+
+
+@pytest.mark.parametrize("hd,H,K,bs", [(64, 4, 1, 16), (64, 6, 2, 4), (128, 8, 2, 16), (128, 5, 5, 8),
+                                       (128, 8, 1, 32), (64, 40, 2, 16), (128, 3, 1, 1)])
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("lens,q_lens", [
+    ([300, 1, 77, 129], [1, 1, 1, 1]),             # pure decode, several splits
+    ([300, 2, 77, 129], [3, 2, 1, 4]),             # short portions: decode shape, several tokens per tile
+    ([300, 64, 77, 200], [300, 9, 77, 65]),        # prefill shape, whole prompts and portions
+    ([520, 5, 90, 130], [130, 1, 17, 2]),          # mixed: both shapes in one step
+])
+def test_paged_flash_attention(hd, H, K, bs, window, lens, q_lens):
+    c = paged_case(hd, H, K, bs, lens=lens, q_lens=q_lens, seed=23, dtype=torch.bfloat16, window=window,
+                   spike=True)
+    out = torch.full_like(c["q"], float("nan"))
+    ctx = FakeCtx(c)
+    ops().paged_attention(c["q"], c["kc"], c["vc"], out, ctx, c["table"], H, K, hd, bs, 1.0 / math.sqrt(hd), window)
+    assert ctx.plans, "the tensor-core path was not taken"
+    assert torch.isfinite(out.float()).all()
+    # the probabilities are rounded to bfloat16 before P.V: errors of a few bfloat16 ulps of the output
+    assert rel_err(out.float().cpu(), c["ref"]) < 1.5e-2
+    plain = torch.empty_like(c["q"])
+    ops().paged_attention_generic(c["q"], c["kc"], c["vc"], plain, c["pos"], c["sid"], c["table"], H, K, hd,
+                                  bs, 1.0 / math.sqrt(hd), window)
+    assert rel_err(out.float().cpu(), plain.float().cpu()) < 1.5e-2

@@ -15,18 +15,30 @@ from helpers import TINY, rel_err
 
 pytestmark = pytest.mark.gpu
 
-# max |engine - plain| / max |plain| over a logits row
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# max |engine - plain| / max |plain| over a logits row.  float32: the engine against the plain
+# implementation.  bfloat16: against the plain implementation in float32 (TOL), and, sharper,
+# against the plain implementation rounding to bfloat16 at the engine's storage points (TOL_STORAGE);
+# The bfloat16 errors are not smooth: where no stored value lands on the other side of a rounding
+# boundary the engine matches the storage-rounding implementation to 1e-5; one flipped bfloat16
+# ulp moves a logits row by about 5e-3.  Measured over 4 seeds x 5 configurations x 428 rows:
+# float32 worst 1.8e-6; bfloat16 against plain worst 2.2e-2 (mean 7e-3); against the
+# storage-rounding implementation worst 1.3e-2, mean over a test's rows at most 5.7e-3.
+TOL = {"float32": 5e-6, "bfloat16": 3e-2}
+TOL_STORAGE = 2e-2
+TOL_STORAGE_MEAN = 8e-3
 STD = 0.08
 
 
 @pytest.fixture(scope="module")
 def model_dirs(tmp_path_factory):
+    """One folder per configuration and stored type: the bfloat16 engine reads bfloat16 files, so
+    that engine and plain implementation start from identical weights."""
     out = {}
-    for name, cfg in TINY.items():
-        d = tmp_path_factory.mktemp(f"tiny_{name}")
-        helpers.make_model_dir(d, cfg, seed=11 + len(out), dtype=torch.float32, std=STD)
-        out[name] = d
+    for i, (name, cfg) in enumerate(TINY.items()):
+        for dtype in ("float32", "bfloat16"):
+            d = tmp_path_factory.mktemp(f"tiny_{name}_{dtype}")
+            helpers.make_model_dir(d, cfg, seed=11 + i, dtype=getattr(torch, dtype), std=STD)
+            out[name, dtype] = d
     return out
 
 
@@ -38,24 +50,34 @@ def make_engine(model_dir, dtype, max_tokens, block_size=16, max_requests=8):
 
 
 def reference(model_dir, dtype, tokens):
-    """Plain float32 logits; for the bfloat16 engine the weights are rounded to bfloat16 first
-    (that rounding is the engine's storage format, not an error of its kernels)."""
+    """(plain float32 logits, plain logits with the engine's storage rounding) from the folder's
+    weights converted exactly to float32."""
     import plain_impl
     cfg, w = plain_impl.load_model(model_dir, torch.float32)
+    plain = plain_impl.forward(cfg, w, tokens)
     if dtype == "bfloat16":
-        w = {k: v.to(torch.bfloat16).to(torch.float32) for k, v in w.items()}
-    return plain_impl.forward(cfg, w, tokens)
+        return plain, plain_impl.forward(cfg, w, tokens, storage=torch.bfloat16)
+    return plain, plain
 
 
 def check(out, refs, dtype, what):
     worst = 0.0
+    storage_errs = []
     for (rid, pos), row in out.items():
-        ref = refs[rid][pos]
+        ref, ref_storage = refs[rid][0][pos], refs[rid][1][pos]
         e = rel_err(row, ref)
         worst = max(worst, e)
         assert e <= TOL[dtype], f"{what}: request {rid} position {pos}: rel err {e:.3e} > {TOL[dtype]}"
         if dtype == "float32":
             assert int(row.argmax()) == int(ref.argmax()), f"{what}: request {rid} position {pos}: argmax differs"
+        else:
+            e = rel_err(row, ref_storage)
+            storage_errs.append(e)
+            assert e <= TOL_STORAGE, (f"{what}: request {rid} position {pos}: rel err {e:.3e} against the "
+                                      f"storage-rounding plain implementation > {TOL_STORAGE}")
+    if storage_errs:
+        mean = sum(storage_errs) / len(storage_errs)
+        assert mean <= TOL_STORAGE_MEAN, f"{what}: mean rel err {mean:.3e} > {TOL_STORAGE_MEAN}"
     return worst
 
 
@@ -68,12 +90,12 @@ def requests_for(cfg, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", list(TINY))
 def test_whole(model_dirs, name, dtype):
     cfg = TINY[name]
     reqs = requests_for(cfg, 100)
-    refs = {rid: reference(model_dirs[name], dtype, t) for rid, t in reqs.items()}
-    eng = make_engine(model_dirs[name], dtype, max_tokens=128)
+    refs = {rid: reference(model_dirs[name, dtype], dtype, t) for rid, t in reqs.items()}
+    eng = make_engine(model_dirs[name, dtype], dtype, max_tokens=128)
     for rid, toks in reqs.items():
         steps = [{"entries": [{"id": rid, "tokens": toks, "want": list(range(len(toks)))}], "end": [rid]}]
         out = helpers.run_steps(eng, steps)
@@ -84,12 +106,12 @@ def test_whole(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", list(TINY))
 def test_tail_decoded_one_by_one(model_dirs, name, dtype):
     cfg = TINY[name]
     reqs = requests_for(cfg, 200)
-    refs = {rid: reference(model_dirs[name], dtype, t) for rid, t in reqs.items()}
-    eng = make_engine(model_dirs[name], dtype, max_tokens=128)
+    refs = {rid: reference(model_dirs[name, dtype], dtype, t) for rid, t in reqs.items()}
+    eng = make_engine(model_dirs[name, dtype], dtype, max_tokens=128)
     for rid, toks in reqs.items():
         head = max(1, len(toks) - 32)
         steps = [{"entries": [{"id": rid, "tokens": toks[:head], "want": [head - 1]}]}]
@@ -102,12 +124,12 @@ def test_tail_decoded_one_by_one(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", list(TINY))
 def test_portions_of_changing_size(model_dirs, name, dtype):
     cfg = TINY[name]
     reqs = requests_for(cfg, 300)
-    refs = {rid: reference(model_dirs[name], dtype, t) for rid, t in reqs.items()}
-    eng = make_engine(model_dirs[name], dtype, max_tokens=128)
+    refs = {rid: reference(model_dirs[name, dtype], dtype, t) for rid, t in reqs.items()}
+    eng = make_engine(model_dirs[name, dtype], dtype, max_tokens=128)
     sizes = [7, 2, 16, 3, 2, 17, 1, 5, 32, 2, 9]
     for rid, toks in reqs.items():
         steps, i, si = [], 0, 0
@@ -153,17 +175,17 @@ def mixed_schedule(reqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", list(TINY))
 def test_mixed_with_page_reuse(model_dirs, name, dtype):
     cfg = TINY[name]
     reqs = requests_for(cfg, 400)
     refs = {}
     for rid, t in reqs.items():
-        refs[rid] = reference(model_dirs[name], dtype, t)
+        refs[rid] = reference(model_dirs[name, dtype], dtype, t)
         refs[rid + "2"] = refs[rid]
     # four live requests of at most 97 tokens, each rounded up to 64: 4 * 128 = 512 would always fit;
     # 256 forces pages to be handed out again while other requests are still live.
-    eng = make_engine(model_dirs[name], dtype, max_tokens=256)
+    eng = make_engine(model_dirs[name, dtype], dtype, max_tokens=256)
     steps = mixed_schedule(reqs)
     assert max(len(s["entries"]) for s in steps) >= 3
     out = helpers.run_steps(eng, steps)
