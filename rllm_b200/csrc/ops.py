@@ -58,6 +58,12 @@ def launch_count() -> int:
     return _launches
 
 
+def add_launches(n: int) -> None:
+    """Counts kernels that ran from a replayed CUDA graph."""
+    global _launches
+    _launches += n
+
+
 def _check(status: int, what: str, own: bool = True):
     global _launches
     if status != 0:
@@ -332,8 +338,13 @@ class AttentionPlan:
                 d_tok.append(cu[r] + t0)
                 pos_first = ctx.start_pos[r] + t0
                 pos_last = ctx.start_pos[r] + min(t0 + self.TTd, ctx.q_lens[r]) - 1
-                lo = (max(0, pos_first + 1 - window) if window > 0 else 0) // 32 * 32
-                n_splits = max(n_splits, -(-(pos_last + 1 - lo) // DECODE_SPLIT_KEYS))
+                # an upper bound of the keys the tile reads (the kernel rounds the window's start
+                # down to a multiple of 32); a function of the padded shape only, so that a graph
+                # captured for a padded context covers every real one
+                span = pos_last + 1
+                if window > 0:
+                    span = min(span, window + self.TTd + 30)
+                n_splits = max(n_splits, -(-span // DECODE_SPLIT_KEYS))
         for r in pre:
             for t0 in range(0, ctx.q_lens[r], self.TTp):
                 p_req.append(r)

@@ -7,8 +7,13 @@ model over exactly the given tokens and returns float32 logits ``[wanted, vocab]
 device, in the order of the items and of their `want`.  Pages that a window has passed are
 given back after the step; `finish(request)` gives back everything a request holds.
 
+Steps that hold one token per request (decode) are replayed from CUDA graphs: one graph per
+(padded number of requests, padded context length), captured the second time a shape is seen,
+with the step's index arrays copied into the graph's fixed input buffer before each replay.
+
 AxiomOperator/rllm: ``KvPool::step_sampled`` (crates/rllm-model/src/generate.rs:85-139) with
-the same pre-checks before any mutation (86-100).
+the same pre-checks before any mutation (86-100); graph replay keyed by the step's shape
+(crates/rllm-model/src/lib.rs:78-95, crates/rllm-cuda/src/backend.rs:1394-1430).
 """
 from __future__ import annotations
 
@@ -17,7 +22,8 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
-from ..cache import CacheManager, OutOfPages, PagedKVView, StateView
+from ..cache import CacheManager, PagedKVView, StateView
+from ..csrc import ops
 from .batch import StepContext, StepItem
 
 
@@ -25,8 +31,46 @@ class StepError(ValueError):
     """A step that cannot run as given (empty item, bad token id, bad `want`, unknown request)."""
 
 
+GRAPH_MAX_REQUESTS = 64
+GRAPH_CTX_QUANTUM = 256          # context lengths are padded to a multiple of this many tokens
+
+
+def _bucket(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+class _Layout:
+    """Where each int32 array of a step lies in the flat upload buffer (16-byte aligned starts)."""
+
+    def __init__(self, shapes: Sequence[tuple]):
+        self.shapes, self.offsets, total = list(shapes), [], 0
+        for shp in self.shapes:
+            self.offsets.append(total)
+            total += (int(np.prod(shp)) + 3) // 4 * 4
+        self.total = max(total, 4)
+
+    def views(self, flat: torch.Tensor):
+        return [flat[o:o + int(np.prod(s))].view(s) for s, o in zip(self.shapes, self.offsets)]
+
+
+class _DecodeGraph:
+    def __init__(self):
+        self.uses = 0
+        self.static = None       # device int32 buffer the graph reads
+        self.layout = None
+        self.ctx = None
+        self.views = None
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+
+
 class Engine:
-    def __init__(self, model, block_size: int = 16, max_tokens: int = 4096, max_requests: int = 64):
+    def __init__(self, model, block_size: int = 16, max_tokens: int = 4096, max_requests: int = 64,
+                 use_graphs: bool = True):
         if not model.loaded:
             raise ValueError("the model has no weights loaded")
         self.model = model
@@ -39,21 +83,19 @@ class Engine:
         self.cache = CacheManager(needs, cache_of, block_size, max_tokens, max_requests)
         self.cache.allocate_device(self.runtime.device, self.runtime.dtype)
         self.block_size = block_size
+        self.use_graphs = use_graphs
+        self._graphs: dict = {}
         self._staging = []
         self._staging_events = []
         self._staging_next = 0
-        self.stats = {"steps": 0, "step_tokens": 0}
+        self.stats = {"steps": 0, "step_tokens": 0, "graph_replays": 0, "graphs_captured": 0}
         self.last_upload_bytes = 0
 
     # ------------------------------------------------------------------ staging
-    def _upload(self, arrays: Sequence[np.ndarray]):
-        """Copies int32 arrays to the device through one pinned buffer; returns device views.
-        Each array starts on a 16-byte boundary."""
-        offs, total = [], 0
-        for a in arrays:
-            offs.append(total)
-            total += (a.size + 3) // 4 * 4
-        total = max(total, 4)
+    def _stage(self, arrays: Sequence[np.ndarray], layout: _Layout) -> torch.Tensor:
+        """Packs the arrays into a pinned buffer (a ring of four, each reused only after its last
+        copy has finished) and returns the pinned slice to copy from."""
+        total = layout.total
         if not self._staging or self._staging[0].numel() < total:
             cap = max(4096, 1 << (total - 1).bit_length())
             for ev in self._staging_events:
@@ -63,25 +105,19 @@ class Engine:
         i = self._staging_next
         self._staging_next = (i + 1) % len(self._staging)
         self._staging_events[i].synchronize()
-        host = self._staging[i]
-        hv = host.numpy()
-        for a, o in zip(arrays, offs):
+        hv = self._staging[i].numpy()
+        for a, o in zip(arrays, layout.offsets):
             hv[o:o + a.size] = a.reshape(-1)
-        dev = torch.empty(total, dtype=torch.int32, device=self.runtime.device)
-        dev.copy_(host[:total], non_blocking=True)
+        self._staged = i
         self.last_upload_bytes = 4 * total
-        self._staging_events[i].record()
-        return [dev[o:o + a.size].view(a.shape) for a, o in zip(arrays, offs)]
+        return self._staging[i][:total]
 
-    # ------------------------------------------------------------------ the step
-    def step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
-        ctx, views = self.prepare(items)
-        logits = self.model.forward(ctx, views)
-        self.after_step(items)
-        return logits
+    def _copy_in(self, dev: torch.Tensor, host: torch.Tensor) -> None:
+        dev.copy_(host, non_blocking=True)
+        self._staging_events[self._staged].record()
 
-    def prepare(self, items: Sequence[StepItem]):
-        """Validates, appends to the cache and builds the step's context and cache views."""
+    # ------------------------------------------------------------------ validation + cache append
+    def _check_items(self, items: Sequence[StepItem]) -> None:
         if not items:
             raise StepError("a step needs at least one item")
         seen = set()
@@ -100,19 +136,25 @@ class Engine:
                 if not 0 <= int(w) < k:
                     raise StepError(f"request {it.request_id!r}: wanted place {w} is outside its "
                                     f"{k} tokens")
-        cache = self.cache
-        cache.check_append([(it.request_id, len(it.tokens)) for it in items])   # raises OutOfPages
+        self.cache.check_append([(it.request_id, len(it.tokens)) for it in items])   # raises OutOfPages
 
-        n = sum(len(it.tokens) for it in items)
-        R = len(items)
-        tokens = np.empty(n, np.int32)
-        positions = np.empty(n, np.int32)
-        seq_ids = np.empty(n, np.int32)
+    def _arrays(self, items: Sequence[StepItem], pad_requests: int = 0, pad_width: int = 0):
+        """Appends to the cache and builds the step's int32 arrays.  With `pad_requests`, the
+        arrays are padded to that many one-token requests (padding rows write nothing: slot -1)
+        and block tables to `pad_width` columns."""
+        cache = self.cache
+        R_real = len(items)
+        n_real = sum(len(it.tokens) for it in items)
+        R = max(R_real, pad_requests)
+        n = n_real + (R - R_real)
+        tokens = np.zeros(n, np.int32)
+        positions = np.zeros(n, np.int32)
+        seq_ids = np.arange(n, dtype=np.int32) if pad_requests else np.zeros(n, np.int32)
         cu_q = np.zeros(R + 1, np.int32)
-        ctx_lens = np.empty(R, np.int32)
-        state_slots = np.empty(R, np.int32)
+        ctx_lens = np.ones(R, np.int32)
+        state_slots = np.zeros(R, np.int32)
         rows = []
-        group_slots = [np.empty(n, np.int32) for _ in cache.paged]
+        group_slots = [np.full(n, -1, np.int32) for _ in cache.paged]
         q_lens, start_pos = [], []
         base = 0
         for r, it in enumerate(items):
@@ -131,23 +173,32 @@ class Engine:
             q_lens.append(k)
             start_pos.append(start)
             base += k
+        for r in range(R_real, R):
+            cu_q[r + 1] = cu_q[r] + 1
+            q_lens.append(1)
+            start_pos.append(0)
         tables = []
         for g in range(len(cache.paged)):
             tl = [cache.block_table(it.request_id, g) for it in items]
-            width = max(1, max(len(t) for t in tl))
+            width = max(1, pad_width, max(len(t) for t in tl))
             tab = np.zeros((R, width), np.int32)
             for r, t in enumerate(tl):
                 tab[r, :len(t)] = t
             tables.append(tab)
-        logit_rows = np.asarray(rows, np.int32)
+        logit_rows = np.arange(n, dtype=np.int32) if pad_requests else np.asarray(rows, np.int32)
         arrays = [tokens, positions, seq_ids, cu_q, ctx_lens, state_slots, logit_rows, *group_slots, *tables]
-        dev = self._upload(arrays)
+        meta = dict(n=n, R=R, q_lens=q_lens, start_pos=start_pos, rows=rows,
+                    ctx_lens=[int(c) for c in ctx_lens])
+        return arrays, meta
+
+    def _context(self, dev: Sequence[torch.Tensor], meta: dict, has_rows: bool):
+        cache = self.cache
         G = len(cache.paged)
         ctx = StepContext(
-            n_tokens=n, n_requests=R, tokens=dev[0], positions=dev[1], seq_ids=dev[2], cu_q=dev[3],
-            ctx_lens=dev[4], state_slots=dev[5], logit_rows=dev[6] if len(rows) else None,
-            q_lens=q_lens, start_pos=start_pos, ctx_lens_host=[int(c) for c in ctx_lens],
-            max_q_len=max(q_lens), max_ctx_len=int(ctx_lens.max()))
+            n_tokens=meta["n"], n_requests=meta["R"], tokens=dev[0], positions=dev[1], seq_ids=dev[2],
+            cu_q=dev[3], ctx_lens=dev[4], state_slots=dev[5], logit_rows=dev[6] if has_rows else None,
+            q_lens=meta["q_lens"], start_pos=meta["start_pos"], ctx_lens_host=meta["ctx_lens"],
+            max_q_len=max(meta["q_lens"]), max_ctx_len=max(meta["ctx_lens"]))
         dev_slots, dev_tables = dev[7:7 + G], dev[7 + G:7 + 2 * G]
         views = []
         for i, place in enumerate(cache.entry_place):
@@ -162,13 +213,69 @@ class Engine:
                 _, g, plane = place
                 views.append(StateView(cache.stateful[g].state[plane], ctx.state_slots,
                                        write=cache.cache_of[i] is None))
-        self.stats["steps"] += 1
-        self.stats["step_tokens"] += n
         return ctx, views
 
-    def after_step(self, items: Sequence[StepItem]) -> None:
+    # ------------------------------------------------------------------ the step
+    def step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
+        self._check_items(items)
+        self.stats["steps"] += 1
+        self.stats["step_tokens"] += sum(len(it.tokens) for it in items)
+        if (self.use_graphs and len(items) <= GRAPH_MAX_REQUESTS and not self.cache.stateful
+                and all(len(it.tokens) == 1 for it in items)):
+            logits = self._graph_step(items)
+        else:
+            arrays, meta = self._arrays(items)
+            layout = _Layout([a.shape for a in arrays])
+            host = self._stage(arrays, layout)
+            dev = torch.empty(layout.total, dtype=torch.int32, device=self.runtime.device)
+            self._copy_in(dev, host)
+            ctx, views = self._context(layout.views(dev), meta, bool(meta["rows"]))
+            logits = self.model.forward(ctx, views)
         for it in items:
             self.cache.release_passed(it.request_id)
+        return logits
+
+    def _graph_step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
+        R = len(items)
+        B = _bucket(R)
+        longest = max((self.cache.length(it.request_id) if self.cache.has(it.request_id) else 0) + 1
+                      for it in items)
+        ctx_pad = -(-longest // GRAPH_CTX_QUANTUM) * GRAPH_CTX_QUANTUM
+        width = -(-ctx_pad // self.block_size)
+        key = (B, ctx_pad)
+        arrays, meta = self._arrays(items, pad_requests=B, pad_width=width)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = _DecodeGraph()
+            g.layout = _Layout([a.shape for a in arrays])
+            g.static = torch.zeros(g.layout.total, dtype=torch.int32, device=self.runtime.device)
+            # host-side shape of the step as the graph sees it: every request at the padded length
+            meta_pad = dict(meta, start_pos=[ctx_pad - 1] * B, ctx_lens=[ctx_pad] * B, q_lens=[1] * B)
+            g.ctx, g.views = self._context(g.layout.views(g.static), meta_pad, True)
+        host = self._stage(arrays, g.layout)
+        self._copy_in(g.static, host)
+        g.uses += 1
+        if g.uses == 1:
+            # first time: run the padded step eagerly (loads kernels, builds the dispatch plans)
+            g.logits = self.model.forward(g.ctx, g.views)
+        else:
+            if g.graph is None:
+                before = ops.launch_count()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    g.logits = self.model.forward(g.ctx, g.views)
+                g.graph, g.launches = graph, ops.launch_count() - before
+                self.stats["graphs_captured"] += 1
+            else:
+                ops.add_launches(g.launches)
+            g.graph.replay()
+            self.stats["graph_replays"] += 1
+        rows = meta["rows"]
+        if not rows:
+            return None
+        if rows == list(range(R)):
+            return g.logits[:R]
+        return g.logits[torch.tensor(rows, dtype=torch.long, device=self.runtime.device)]
 
     def finish(self, request_id) -> None:
         """Gives back what a finished request holds.  Freed pages may be handed out again at once:
