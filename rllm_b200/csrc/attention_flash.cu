@@ -353,3 +353,57 @@ RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, cons
     if (hd == 64) return launch_flash<64>(p, mode, n_tiles, n_splits, stream);
     return (int)cudaErrorInvalidValue;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free entry point for callers that cannot allocate device memory (see
+// attention_flash_static.h for who they are and for the rules of use).  The partials of the decode
+// shape live in the file-scope array below instead of caller-provided scratch.
+#include "attention_flash_static.h"
+#include <stdio.h>
+
+// [rows][128 + 2] floats: per row the unnormalized output (head size <= 128) and (max, sum).
+static __device__ __align__(256) float g_static_scratch[(size_t)RLLM_FLASH_STATIC_SCRATCH_ROWS * (128 + 2)];
+
+#define RLLM_STATIC_MAX_DEVICES 64
+// Device address of g_static_scratch per device.  In host code the array's name is only a handle
+// for the runtime, never a pointer a kernel could use: the address comes from cudaGetSymbolAddress.
+static float* g_static_scratch_addr[RLLM_STATIC_MAX_DEVICES];
+static thread_local char g_static_error[256] = "";
+
+RLLM_API const char* rllm_paged_flash_decode_static_error(void) { return g_static_error; }
+
+RLLM_API int rllm_paged_flash_decode_static(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                            const int* positions, const int* cu_q, const int* block_table,
+                                            int table_stride, const int* tile_req, const int* tile_tok0,
+                                            int n_tiles, int H, int K, int hd, int bs, float scale, int window,
+                                            int TT, int GH, int head_chunks, int split_keys, int n_splits,
+                                            cudaStream_t stream) {
+    g_static_error[0] = 0;
+    if (n_tiles <= 0) return 0;
+    if (K <= 0 || head_chunks <= 0 || n_splits <= 0 || TT <= 0 || GH <= 0) return (int)cudaErrorInvalidValue;
+    const long long rows = (long long)n_tiles * K * head_chunks * n_splits * TT * GH;
+    if (rows > RLLM_FLASH_STATIC_SCRATCH_ROWS || hd > 128) {
+        snprintf(g_static_error, sizeof g_static_error,
+                 "rllm_paged_flash_decode_static: %lld partial rows of head size %d requested "
+                 "(tiles %d x kv heads %d x head chunks %d x splits %d x rows %d); the static scratch holds "
+                 "%d rows of head size <= 128",
+                 rows, hd, n_tiles, K, head_chunks, n_splits, TT * GH, RLLM_FLASH_STATIC_SCRATCH_ROWS);
+        return RLLM_FLASH_STATIC_TOO_LARGE;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= RLLM_STATIC_MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+    if (!g_static_scratch_addr[dev]) {
+        // set-up, once per device, with that device current
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_static_scratch_addr[dev] = ptr;
+    }
+    float* part_o = g_static_scratch_addr[dev];
+    float* part_ml = part_o + (size_t)RLLM_FLASH_STATIC_SCRATCH_ROWS * 128;
+    return rllm_paged_flash_attention(q, k_cache, v_cache, out, part_o, part_ml, positions, cu_q, block_table,
+                                      table_stride, tile_req, tile_tok0, n_tiles, H, K, hd, bs, scale, window,
+                                      /*mode=*/1, TT, GH, head_chunks, split_keys, n_splits, stream);
+}
