@@ -67,8 +67,10 @@ class Qwen3Config(ModelConfig):
         act = optional(d, "hidden_act", str, "silu")
         if act != "silu":
             raise ConfigError(f"config.json: 'hidden_act' = {act!r} is not supported (silu only)")
-        sw = optional(d, "sliding_window", int, 0)
+        # A window applies only when `use_sliding_window` is true: checkpoints carry a
+        # `sliding_window` number beside `use_sliding_window: false`, which means no window.
         use_sw = optional(d, "use_sliding_window", bool, False)
+        sw = optional(d, "sliding_window", int, 0) if use_sw else 0
         mwl = optional(d, "max_window_layers", int, L)
         types = d.get("layer_types")
         if types is not None:
@@ -79,13 +81,10 @@ class Qwen3Config(ModelConfig):
                 if t == "full_attention":
                     windows.append(0)
                 elif t == "sliding_attention":
-                    if sw <= 0:
-                        raise ConfigError("config.json: 'layer_types' names sliding_attention but "
-                                          "'sliding_window' is absent")
-                    windows.append(sw)
+                    windows.append(sw)          # 0 when windows are switched off
                 else:
                     raise ConfigError(f"config.json: 'layer_types[{i}]' = {t!r} is not supported")
-        elif use_sw and sw > 0:
+        elif sw > 0:
             windows = [sw if i >= mwl else 0 for i in range(L)]
         else:
             windows = [0] * L

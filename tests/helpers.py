@@ -33,7 +33,8 @@ TINY_G = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_si
               num_attention_heads=3, num_key_value_heads=3, head_dim=128, intermediate_size=136,
               vocab_size=277, rope_theta=300000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
               max_position_embeddings=1024, hidden_act="silu", attention_bias=False,
-              sliding_window=40, layer_types=["sliding_attention", "full_attention"])
+              use_sliding_window=True, sliding_window=40,
+              layer_types=["sliding_attention", "full_attention"])
 TINY = {"A": TINY_A, "B": TINY_B, "W": TINY_W, "F": TINY_F, "G": TINY_G}
 
 

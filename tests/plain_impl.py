@@ -158,16 +158,17 @@ def _rope_theta(cfg):
 
 
 def layer_windows(cfg):
-    """Window per layer (0 = all keys).  A layer attends through a window of
-    `sliding_window` keys when `layer_types[i] == "sliding_attention"`, or, without
-    that list, when `use_sliding_window` is true and i >= `max_window_layers`.
+    """Window per layer (0 = all keys).  Windows exist only when `use_sliding_window` is
+    true; then a layer attends through a window of `sliding_window` keys when
+    `layer_types[i] == "sliding_attention"`, or, without that list, when
+    i >= `max_window_layers`.
     The window rule itself (keys pos+1-window..pos) is crates/rllm-cpu/src/lib.rs:402."""
     L = cfg["num_hidden_layers"]
-    sw = cfg.get("sliding_window") or 0
+    sw = (cfg.get("sliding_window") or 0) if cfg.get("use_sliding_window") else 0
     types = cfg.get("layer_types")
     if types is not None:
         return [sw if t == "sliding_attention" else 0 for t in types]
-    if cfg.get("use_sliding_window") and sw:
+    if sw:
         mwl = cfg.get("max_window_layers", L)
         return [sw if i >= mwl else 0 for i in range(L)]
     return [0] * L

@@ -1,0 +1,413 @@
+"""The engine above the kernels: trace replay as a program, generation through the Python entry
+point, long decoding, the first tokens of a sequence, preemption, sampling, each part alone, and a
+toy architecture with a stateful mixer that is registered here, without touching the package.
+"""
+import json
+import math
+import os
+import subprocess
+import sys
+from dataclasses import dataclass
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_impl
+from helpers import TINY, rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ROOT = Path(__file__).resolve().parent.parent
+STD = 0.08
+
+
+@pytest.fixture(scope="module")
+def dirs(tmp_path_factory):
+    out = {}
+    for i, (name, cfg) in enumerate(TINY.items()):
+        for dtype in ("float32", "bfloat16"):
+            d = tmp_path_factory.mktemp(f"m_{name}_{dtype}")
+            helpers.make_model_dir(d, cfg, seed=21 + i, dtype=getattr(torch, dtype), std=STD)
+            out[name, dtype] = d
+    return out
+
+
+def engine(model_dir, dtype, **kw):
+    from rllm_b200.engine import Engine
+    from rllm_b200.models.model import load_model
+    _, model = load_model(model_dir, dtype, DEV)
+    return Engine(model, **kw)
+
+
+# ---------------------------------------------------------------- bin/trace_run
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dirs, tmp_path, dtype):
+    name = "B"
+    cfg, w = plain_impl.load_model(dirs[name, dtype])
+    a = helpers.random_tokens(40, cfg["vocab_size"], 1)
+    b = helpers.random_tokens(23, cfg["vocab_size"], 2)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:17], "want": [0, 16]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[17:19], "want": []},
+                                {"id": "b", "tokens": b[:20], "want": [19]}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[20:21], "want": [0]}], "end": []},   # a sits out
+        {"step": 3, "entries": [{"id": "a", "tokens": a[19:], "want": [20]},
+                                {"id": "b", "tokens": b[21:], "want": [0, 1]}], "end": ["a", "b"]},
+        {"step": 4, "entries": [{"id": "c", "tokens": a[:5], "want": [4]}], "end": ["c"]},
+    ]
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(dirs[name, dtype]),
+                           "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(5)]
+    la, lb = plain_impl.forward(cfg, w, a), plain_impl.forward(cfg, w, b)
+    want = {0: [la[0], la[16]], 1: [lb[19]], 2: [lb[20]], 3: [la[39], lb[21], lb[22]], 4: [la[4]]}
+    tol = 5e-6 if dtype == "float32" else 3e-2
+    for step, rows in want.items():
+        got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(rows), cfg["vocab_size"])
+        for g_, r in zip(got, rows):
+            assert rel_err(torch.from_numpy(g_.copy()), r) <= tol
+
+
+def test_trace_run_rejects_bad_model(tmp_path):
+    d = helpers.make_model_dir(tmp_path / "m", TINY["A"], seed=1)
+    cfgp = d / "config.json"
+    c = json.loads(cfgp.read_text()); c["architectures"] = ["NopeForCausalLM"]; cfgp.write_text(json.dumps(c))
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(d), "--dtype", "float32",
+                           "--out", str(tmp_path / "o"), "--max-tokens", "64"], input="", capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode != 0 and "unsupported architecture" in proc.stderr
+
+
+# ---------------------------------------------------------------- generation through the entry point
+
+@pytest.mark.parametrize("name", ["A", "B", "W", "F"])
+def test_greedy_generation_matches_plain(dirs, name):
+    from rllm_b200 import LLM
+    cfg, w = plain_impl.load_model(dirs[name, "float32"])
+    prompts = [helpers.random_tokens(n, cfg["vocab_size"], 50 + n) for n in (5, 11, 24, 1)]
+    want = [plain_impl.greedy_generate(cfg, w, p, 8) for p in prompts]
+    llm = LLM(dirs[name, "float32"], dtype="float32", device=DEV, ctx=128, parallel=3, prefill_chunk=8)
+    assert llm.generate(prompts, max_tokens=8) == want
+    assert llm.engine.cache.n_free_pages(0) == llm.engine.cache.n_blocks
+
+
+def test_bfloat16_generation_follows_plain_argmax(dirs):
+    """bfloat16 greedy tokens agree with the plain implementation wherever its top two logits are
+    further apart than the bfloat16 error bound."""
+    from rllm_b200.engine import StepItem
+    name = "F"
+    cfg, w = plain_impl.load_model(dirs[name, "bfloat16"])
+    toks = helpers.random_tokens(60, cfg["vocab_size"], 77)
+    ref = plain_impl.forward(cfg, w, toks)
+    eng = engine(dirs[name, "bfloat16"], "bfloat16", max_tokens=128)
+    got = eng.step([StepItem(0, toks, list(range(60)))]).float().cpu()
+    checked = 0
+    for p in range(60):
+        top = torch.topk(ref[p], 2).values
+        if float(top[0] - top[1]) > 2 * 3e-2 * float(ref[p].abs().max()):
+            assert int(got[p].argmax()) == int(ref[p].argmax())
+            checked += 1
+    assert checked >= 20
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "W", "F"])
+def test_long_decoding_and_first_tokens(dirs, name, dtype):
+    """A one-token prompt, then 330 tokens decoded one by one: crosses many page edges, the decode
+    graphs' context paddings (256) and, for W, runs far past the window."""
+    from rllm_b200.engine import StepItem
+    cfg, w = plain_impl.load_model(dirs[name, dtype])
+    toks = helpers.random_tokens(331, cfg["vocab_size"], 5)
+    ref = plain_impl.forward(cfg, w, toks)
+    eng = engine(dirs[name, dtype], dtype, max_tokens=384, max_requests=2)
+    tol = 5e-6 if dtype == "float32" else 3e-2
+    worst = 0.0
+    for i, t in enumerate(toks):
+        row = eng.step([StepItem("r", [t], [0])])[0].float().cpu()
+        e = rel_err(row, ref[i])
+        worst = max(worst, e)
+        assert e <= tol, f"position {i}: {e:.3e}"
+    assert eng.stats["graph_replays"] >= 300
+    if name == "W":
+        assert eng.cache.n_free_pages(1) > eng.cache.n_free_pages(0)     # the window gave pages back
+    eng.finish("r")
+    eng.cache.check_invariants()
+
+
+def test_preemption_gives_the_same_tokens(dirs):
+    from rllm_b200 import LLM
+    cfg, _ = plain_impl.load_model(dirs["B", "float32"])
+    prompts = [helpers.random_tokens(30, cfg["vocab_size"], 90 + i) for i in range(4)]
+    roomy = LLM(dirs["B", "float32"], dtype="float32", device=DEV, ctx=256, parallel=4, kv_tokens=4096)
+    want = roomy.generate(prompts, max_tokens=100)
+    assert roomy.last_stats["preemptions"] == 0
+    tight = LLM(dirs["B", "float32"], dtype="float32", device=DEV, ctx=256, parallel=4, kv_tokens=320)
+    got = tight.generate(prompts, max_tokens=100)
+    assert tight.last_stats["preemptions"] >= 1
+    assert got == want
+
+
+def test_sampling_is_reproducible_whatever_the_batch(dirs):
+    from rllm_b200 import LLM
+    cfg, w = plain_impl.load_model(dirs["B", "float32"])
+    prompts = [helpers.random_tokens(n, cfg["vocab_size"], 30 + n) for n in (1, 9, 40, 63)]
+    kw = dict(max_tokens=12, temperature=0.8, top_p=0.95, top_k=50, seed=4)
+    together = LLM(dirs["B", "float32"], dtype="float32", device=DEV, ctx=256, parallel=4, prefill_chunk=16,
+                   block_size=8).generate(prompts, **kw)
+    alone = LLM(dirs["B", "float32"], dtype="float32", device=DEV, ctx=256, parallel=1, block_size=8)
+    for i, p in enumerate(prompts):
+        assert alone.generate([p], **dict(kw, seed=4 + i))[0] == together[i]
+    # and they are the plain sampler's draws from the plain implementation's logits
+    seq = list(prompts[1])
+    for _ in range(12):
+        logits = plain_impl.forward(cfg, w, seq)[-1].numpy()
+        seq.append(plain_impl.sample_row(logits, 0.8, 50, 0.95, 4 + 1, len(seq)))
+    agree = next((j for j, (a, b) in enumerate(zip(seq[9:], together[1])) if a != b), 12)
+    assert agree >= 8                # equal draws; only a rounding-level near tie could end the agreement
+    host = LLM(dirs["B", "float32"], dtype="float32", device=DEV, ctx=256, parallel=2, host_sampling=True)
+    h1 = host.generate(prompts[:2], **kw)
+    assert h1 == host.generate(prompts[:2], **kw) and all(len(t) == 12 for t in h1)
+
+
+def test_step_errors_change_nothing(dirs):
+    from rllm_b200.cache import OutOfPages
+    from rllm_b200.engine import StepError, StepItem
+    eng = engine(dirs["A", "float32"], "float32", max_tokens=32, max_requests=2)
+    eng.step([StepItem("a", [1, 2, 3], [2])])
+    free = eng.cache.n_free_pages(0)
+    for bad in ([StepItem("a", [], [])], [StepItem("a", [999], [0])], [StepItem("a", [1], [1])],
+                [StepItem("a", [1], []), StepItem("a", [2], [])], []):
+        with pytest.raises(StepError):
+            eng.step(bad)
+    with pytest.raises(OutOfPages):
+        eng.step([StepItem("a", [1], [0]), StepItem("b", list(range(40)), [])])
+    assert eng.cache.n_free_pages(0) == free and eng.cache.length("a") == 3 and not eng.cache.has("b")
+    with pytest.raises(Exception, match="CUDA device only"):
+        from rllm_b200.csrc import ops
+        ops.silu_mul(torch.zeros(1, 4), torch.zeros(1, 2))
+
+
+# ---------------------------------------------------------------- each part alone
+
+def rt(dtype=torch.float32):
+    from rllm_b200.parts import Runtime
+    return Runtime(torch.device(DEV), dtype)
+
+
+def test_part_norm_and_rotary_alone():
+    from rllm_b200.config import PartSpec
+    from rllm_b200.parts import build_part
+    norm = build_part("norm", PartSpec("rms_norm", {"size": 200, "eps": 1e-5}, "n."), rt())
+    w = 1 + 0.1 * torch.randn(200)
+    norm.load({"n.weight": w})
+    assert list(norm.expected_tensors()) == ["n.weight"]
+    x, d = torch.randn(9, 200), torch.randn(9, 200)
+    xd = x.to(DEV)
+    out = norm.forward(xd, d.to(DEV))
+    assert rel_err(out.cpu(), plain_impl.rms_norm(x + d, w, 1e-5)) < 1e-5 and torch.equal(xd.cpu(), x + d)
+    rot = build_part("position", PartSpec("rotary_neox", {"head_dim": 48, "theta": 50000.0}), rt())
+    inv = 1.0 / torch.pow(torch.tensor(50000.0), torch.arange(0, 48, 2).float() / 48)
+    assert torch.equal(rot.table().cpu(), inv)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_part_ffn_and_head_alone(dtype):
+    from rllm_b200.config import PartSpec
+    from rllm_b200.parts import build_part
+    d, F, V = 96, 224, 311
+    ffn = build_part("ffn", PartSpec("swiglu", {"hidden_size": d, "intermediate_size": F}, "m."), rt(dtype))
+    g = torch.Generator().manual_seed(3)
+    ws = {"m.gate_proj.weight": torch.randn(F, d, generator=g) * 0.1, "m.up_proj.weight": torch.randn(F, d, generator=g) * 0.1,
+          "m.down_proj.weight": torch.randn(d, F, generator=g) * 0.1}
+    ws = {k: v.to(dtype) for k, v in ws.items()}
+    ffn.load(ws)
+    for n in (3, 70):                                   # the few-rows kernel and the library product
+        h = torch.randn(n, d, generator=g).to(dtype)
+        ref = plain_impl.swiglu(h.float(), *(ws[f"m.{p}_proj.weight"].float() for p in ("gate", "up", "down")),
+                                storage=None if dtype == torch.float32 else dtype)
+        out = ffn.forward(h.to(DEV))
+        assert out.dtype == torch.float32 and rel_err(out.cpu(), ref) < (2e-6 if dtype == torch.float32 else 5e-3)
+        res = torch.ones(n, d, device=DEV)
+        assert ffn.forward(h.to(DEV), residual=res) is None
+        assert rel_err(res.cpu(), ref + 1) < (2e-6 if dtype == torch.float32 else 5e-3)
+    emb = build_part("embedding", PartSpec("embedding", {"vocab_size": V, "hidden_size": d}, "e."), rt(dtype))
+    table = (torch.randn(V, d, generator=g) * 0.1).to(dtype)
+    emb.load({"e.weight": table})
+    toks = torch.tensor([0, 310, 17], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(toks).cpu(), table.float()[[0, 310, 17]])
+    head = build_part("lm_head", PartSpec("lm_head", {"vocab_size": V, "hidden_size": d, "tied_to": "e.weight"}, "h."), rt(dtype))
+    assert head.expected_tensors() == {}
+    head.load({}, shared={"e.weight": emb.weight})
+    h = torch.randn(4, d, generator=g).to(dtype)
+    assert rel_err(head.forward(h.to(DEV)).cpu(), h.float() @ table.float().t()) < (2e-6 if dtype == torch.float32 else 1e-5)
+
+
+@pytest.mark.parametrize("dtype,hd,H,K,window", [(torch.float32, 32, 6, 2, 0), (torch.bfloat16, 64, 4, 2, 0),
+                                                  (torch.float32, 16, 4, 4, 9), (torch.bfloat16, 128, 4, 1, 21)])
+def test_part_attention_alone(dtype, hd, H, K, window):
+    """The attention part with its own cache pages, fed in two portions and one decoded token,
+    against the plain attention block over the whole sequence."""
+    from rllm_b200.cache import CacheManager, PagedKVView
+    from rllm_b200.config import PartSpec
+    from rllm_b200.engine.batch import StepContext
+    from rllm_b200.parts import build_part
+    d, eps, theta, bs, n = 80, 1e-5, 30000.0, 8, 45
+    att = build_part("mixer", PartSpec("attention", {"hidden_size": d, "num_heads": H, "num_kv_heads": K,
+                     "head_dim": hd, "qk_norm": True, "qk_norm_eps": eps, "window": window, "scale": hd ** -0.5}, "a."), rt(dtype))
+    rot = build_part("position", PartSpec("rotary_neox", {"head_dim": hd, "theta": theta}), rt(dtype))
+    g = torch.Generator().manual_seed(11)
+    ws = {n_: ((torch.randn(s, generator=g) * 0.15) if r != "norm" else 1 + 0.1 * torch.randn(s, generator=g)).to(dtype)
+          for n_, (s, r) in att.expected_tensors().items()}
+    att.load(ws)
+    h = torch.randn(n, d, generator=g).to(dtype)
+    cfg = dict(num_attention_heads=H, num_key_value_heads=K, head_dim=hd, hidden_size=d, rms_norm_eps=eps, rope_theta=theta)
+    pw = {"x.self_attn." + k[2:]: v.float() for k, v in ws.items()}
+    ref = plain_impl.attention_block(h.float(), list(range(n)), pw, "x.", cfg, window,
+                                     storage=None if dtype == torch.float32 else dtype)
+    cm = CacheManager([att.cache_need()], [None], bs, 64, 1)
+    cm.allocate_device(torch.device(DEV), dtype)
+    outs, start = [], 0
+    for k in (30, 14, 1):
+        slots = cm.append("r", k)[0]
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        ctx = StepContext(n_tokens=k, n_requests=1, tokens=i32([0] * k), positions=i32(list(range(start, start + k))),
+                          seq_ids=i32([0] * k), cu_q=i32([0, k]), ctx_lens=i32([start + k]), logit_rows=None,
+                          q_lens=[k], start_pos=[start], ctx_lens_host=[start + k], max_q_len=k, max_ctx_len=start + k)
+        pool = cm.paged[0].pool
+        view = PagedKVView(pool[0, 0], pool[0, 1], i32([cm.block_table("r", 0)]), i32(slots), bs)
+        outs.append(att.forward(h[start:start + k].to(DEV), ctx, view, rot).cpu())
+        cm.release_passed("r")
+        start += k
+    got = torch.cat(outs)
+    assert rel_err(got, ref) < (5e-6 if dtype == torch.float32 else 1.5e-2)
+
+
+# ---------------------------------------------------------------- a toy architecture, defined here
+
+def test_toy_stateful_mixer_registers_and_steps(tmp_path):
+    """A mixer with a fixed-size state of its own (a decaying running sum of a projection), a toy
+    architecture using it in every other layer beside attention layers that share one cache, and
+    a layer that runs twice: all registered from this test, built and stepped by the package
+    without any change to its files; checked against a whole-sequence computation."""
+    from rllm_b200.config import (LayerSpec, ModelConfig, ModelSpec, PartSpec, RunEntry, load_config,
+                                  register_architecture)
+    from rllm_b200.engine import Engine, StepItem
+    from rllm_b200.models.model import load_model
+    from rllm_b200.parts import Mixer, StateNeed, register_part
+    from rllm_b200.weights import write_safetensors
+
+    @register_part("mixer", "toy_decay_sum")
+    class ToyDecaySum(Mixer):
+        """state_t = decay * state_{t-1} + W_in x_t;  y_t = W_out state_t   (plain torch: a toy)."""
+
+        def __init__(self, params, prefix, runtime):
+            super().__init__(params, prefix, runtime)
+            self.d, self.s, self.decay = params["hidden_size"], params["state_size"], params["decay"]
+
+        def cache_need(self):
+            return StateNeed((self.s,), torch.float32)
+
+        def expected_tensors(self):
+            return {self.prefix + "in.weight": ((self.s, self.d), "matrix"),
+                    self.prefix + "out.weight": ((self.d, self.s), "matrix")}
+
+        def load(self, tensors):
+            self.w_in = self._to_device(tensors[self.prefix + "in.weight"], torch.float32)
+            self.w_out = self._to_device(tensors[self.prefix + "out.weight"], torch.float32)
+
+        def forward(self, h, ctx, cache, position, residual=None):
+            u = h.float() @ self.w_in.t()
+            out = torch.empty(h.shape[0], self.d, device=h.device)
+            for r in range(ctx.n_requests):
+                slot = int(cache.slots[r])
+                lo = sum(ctx.q_lens[:r])
+                st = cache.state[slot].clone()
+                for t in range(lo, lo + ctx.q_lens[r]):
+                    st = self.decay * st + u[t]
+                    out[t] = self.w_out @ st
+                cache.state[slot] = st
+            return out
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        hidden: int
+        vocab: int
+        state: int
+        decay: float
+        architecture: str = "ToyForCausalLM"
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["hidden"], d["vocab"], d["state"], d["decay"])
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], hidden=self.hidden, vocab=self.vocab,
+                        state=self.state, decay=self.decay)
+
+        def model_spec(self):
+            norm = lambda p: PartSpec("rms_norm", {"size": self.hidden, "eps": 1e-6}, p)
+            ffn = lambda p: PartSpec("swiglu", {"hidden_size": self.hidden, "intermediate_size": 2 * self.hidden}, p)
+            attn = lambda p: PartSpec("attention", {"hidden_size": self.hidden, "num_heads": 2, "num_kv_heads": 1,
+                                                    "head_dim": 16, "qk_norm": False, "window": 0, "scale": 0.25}, p)
+            toy = lambda p: PartSpec("toy_decay_sum", {"hidden_size": self.hidden, "state_size": self.state,
+                                                       "decay": self.decay}, p)
+            layers = []
+            for i, mixer in enumerate([attn, toy, attn]):
+                p = f"l.{i}."
+                layers.append(LayerSpec("pre_norm", mixer(p + "mix."), ffn(p + "mlp."),
+                                        {"mixer": norm(p + "n1."), "ffn": norm(p + "n2.")},
+                                        PartSpec("rotary_neox", {"head_dim": 16, "theta": 1e4}) if mixer is attn else None))
+            # layer 1 (the stateful one) runs twice; entry 3 (layer 2) reads the cache entry 0 wrote
+            order = (RunEntry(0), RunEntry(1), RunEntry(1), RunEntry(2, cache_of=0))
+            return ModelSpec(self.vocab, self.hidden, PartSpec("embedding", {"vocab_size": self.vocab, "hidden_size": self.hidden}, "emb."),
+                             tuple(layers), order, norm("fn."),
+                             PartSpec("lm_head", {"vocab_size": self.vocab, "hidden_size": self.hidden, "tied_to": "emb.weight"}, "head."),
+                             512)
+
+    register_architecture("ToyForCausalLM", ToyConfig)
+    cfg = ToyConfig(hidden=32, vocab=50, state=6, decay=0.9)
+    d = tmp_path / "toy"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg.to_dict()))
+    from rllm_b200.models.model import expected_tensors
+    g = torch.Generator().manual_seed(2)
+    tensors = {n: (1 + 0.1 * torch.randn(s, generator=g)) if r == "norm" else 0.2 * torch.randn(s, generator=g)
+               for n, (s, r) in expected_tensors(cfg.model_spec()).items()}
+    write_safetensors(d / "model.safetensors", tensors)
+    assert isinstance(load_config(d), ToyConfig)
+
+    _, model = load_model(d, "float32", DEV)
+    needs, cache_of = model.cache_needs()
+    assert cache_of == [None, None, None, 0] and isinstance(needs[1], StateNeed)
+    toks = {"a": helpers.random_tokens(21, 50, 1), "b": helpers.random_tokens(9, 50, 2)}
+
+    def run(schedule):
+        eng = Engine(model, block_size=4, max_tokens=64, max_requests=2)
+        assert len(eng.cache.paged) == 1 and len(eng.cache.paged[0].entries) == 1     # one shared plane
+        assert eng.cache.stateful[0].state.shape == (2, 2, 6)                          # two entries, two slots
+        return helpers.run_steps(eng, schedule)
+
+    whole = run([{"entries": [{"id": r, "tokens": t, "want": list(range(len(t)))}], "end": [r]} for r, t in toks.items()])
+    a, b = toks["a"], toks["b"]
+    cut = run([
+        {"entries": [{"id": "a", "tokens": a[:7], "want": list(range(7))}]},
+        {"entries": [{"id": "a", "tokens": a[7:9], "want": [0, 1]}, {"id": "b", "tokens": b[:8], "want": list(range(8))}]},
+        {"entries": [{"id": "b", "tokens": b[8:], "want": [0]}], "end": ["b"]},
+        {"entries": [{"id": "a", "tokens": a[9:20], "want": list(range(11))}]},
+        {"entries": [{"id": "a", "tokens": a[20:], "want": [0]}], "end": ["a"]},
+    ])
+    assert set(whole) == set(cut)
+    for key in whole:
+        assert rel_err(cut[key], whole[key]) < 1e-5
+    # and the state really matters: a request that starts in a used slot starts from zero
+    eng = Engine(model, block_size=4, max_tokens=64, max_requests=1)
+    first = helpers.run_steps(eng, [{"entries": [{"id": "x", "tokens": a, "want": [20]}], "end": ["x"]}])
+    again = helpers.run_steps(eng, [{"entries": [{"id": "y", "tokens": a, "want": [20]}], "end": ["y"]}])
+    assert rel_err(again["y", 20], first["x", 20]) < 1e-6

@@ -1,0 +1,453 @@
+"""Host-side tests that need no GPU: configuration, weight files and their errors, the cache
+manager under random orders of requests, the scheduler's decisions, and the plain implementation
+itself.  In the manner of AxiomOperator/rllm's host unit tests (crates/rllm-kv/src/lib.rs:454-719,
+crates/rllm-model/src/sampler.rs:460-569, crates/rllm-core/src/sample.rs:111-161).
+"""
+import json
+import random
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_impl
+from rllm_b200.cache import BlockAllocator, CacheManager, OutOfPages
+from rllm_b200.config import ConfigError, Qwen3Config, config_from_dict, load_config, supported_architectures
+from rllm_b200.engine.scheduler import Request, Scheduler
+from rllm_b200.parts import PagedKVNeed, StateNeed
+from rllm_b200.sampling import HostSampler, SamplingParams, SplitMix64
+from rllm_b200.weights import (SafetensorsFile, WeightFileError, WeightMismatchError, load_checked,
+                               write_random_model, write_safetensors)
+
+
+# ---------------------------------------------------------------- configuration
+
+def test_config_reads_every_key():
+    for name, d in helpers.TINY.items():
+        c = config_from_dict(d)
+        assert isinstance(c, Qwen3Config)
+        assert (c.num_hidden_layers, c.hidden_size, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
+                c.intermediate_size, c.vocab_size) == tuple(d[k] for k in (
+                    "num_hidden_layers", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
+                    "intermediate_size", "vocab_size"))
+        assert c.rms_norm_eps == d["rms_norm_eps"] and c.rope_theta == d["rope_theta"]
+        assert c.tie_word_embeddings == d["tie_word_embeddings"]
+        assert list(c.layer_windows) == plain_impl.layer_windows(d)
+        # what it writes reads back to the same configuration
+        assert config_from_dict(json.loads(json.dumps(c.to_dict()))) == c
+    w = config_from_dict(helpers.TINY_W)
+    assert w.layer_windows == (0, 24, 24)
+    g = config_from_dict(helpers.TINY_G)
+    assert g.layer_windows == (40, 0)
+
+
+def test_config_defaults_and_rope_parameters():
+    d = dict(helpers.TINY_A)
+    del d["head_dim"], d["rope_theta"], d["rms_norm_eps"]
+    d["rope_parameters"] = {"rope_theta": 12345.0, "rope_type": "default"}
+    c = config_from_dict(d)
+    assert c.head_dim == 64 // 4 and c.rope_theta == 12345.0 and c.rms_norm_eps == 1e-6
+    # a window that is configured but switched off is no window
+    d2 = dict(helpers.TINY_A, sliding_window=32, use_sliding_window=False, max_window_layers=0)
+    assert config_from_dict(d2).layer_windows == (0, 0)
+    d3 = dict(helpers.TINY_G, use_sliding_window=False)
+    assert config_from_dict(d3).layer_windows == (0, 0) == tuple(plain_impl.layer_windows(d3))
+
+
+@pytest.mark.parametrize("change,needle", [
+    ({"architectures": ["GPT2LMHeadModel"]}, "unsupported architecture"),
+    ({"hidden_size": None}, "'hidden_size'"),
+    ({"num_hidden_layers": "two"}, "'num_hidden_layers'"),
+    ({"num_key_value_heads": 3}, "num_key_value_heads"),
+    ({"head_dim": 20}, "'head_dim'"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 4.0}}, "rope_scaling"),
+    ({"attention_bias": True}, "'attention_bias'"),
+    ({"hidden_act": "gelu"}, "'hidden_act'"),
+    ({"layer_types": ["full_attention"]}, "'layer_types'"),
+    ({"vocab_size": 0}, "'vocab_size'"),
+])
+def test_config_errors_name_the_key(change, needle):
+    d = dict(helpers.TINY_A, **change)
+    with pytest.raises(ConfigError) as e:
+        config_from_dict(d)
+    assert needle in str(e.value)
+    if "unsupported" in needle:
+        assert "Qwen3ForCausalLM" in str(e.value) and "Qwen3ForCausalLM" in supported_architectures()
+
+
+def test_model_spec_is_data():
+    spec = config_from_dict(helpers.TINY_W).model_spec()
+    assert [e.layer for e in spec.run_order] == [0, 1, 2]
+    assert [l.mixer.params["window"] for l in spec.layers] == [0, 24, 24]
+    assert spec.layers[0].mixer.kind == "attention" and spec.layers[0].ffn.kind == "swiglu"
+    assert spec.layers[1].mixer.params["scale"] == 48 ** -0.5
+    assert spec.lm_head.params["tied_to"] is None
+    assert config_from_dict(helpers.TINY_A).model_spec().lm_head.params["tied_to"] == "model.embed_tokens.weight"
+
+
+# ---------------------------------------------------------------- weights
+
+def test_random_model_roundtrip_and_seed(tmp_path):
+    cfg = config_from_dict(helpers.TINY_B)
+    a = write_random_model(cfg, tmp_path / "a", seed=3, dtype=torch.bfloat16)
+    b = write_random_model(cfg, tmp_path / "b", seed=3, dtype=torch.bfloat16)
+    c = write_random_model(cfg, tmp_path / "c", seed=4, dtype=torch.float32)
+    assert (a / "model.safetensors").read_bytes() == (b / "model.safetensors").read_bytes()
+    assert load_config(a) == cfg
+    fa, fc = SafetensorsFile(a / "model.safetensors"), SafetensorsFile(c / "model.safetensors")
+    assert set(fa.names()) == set(fc.names())
+    assert "lm_head.weight" in fa.names()                       # untied
+    assert fa.dtype("model.embed_tokens.weight") == torch.bfloat16 and fc.dtype("model.norm.weight") == torch.float32
+    assert fa.shape("model.layers.2.self_attn.q_proj.weight") == (6 * 32, 96)
+    assert fa.shape("model.layers.0.self_attn.k_norm.weight") == (32,)
+    assert not torch.equal(fa.tensor("model.norm.weight").float(), fc.tensor("model.norm.weight"))
+    # the plain implementation's own reader sees the same values
+    mine = plain_impl.read_safetensors(a / "model.safetensors")
+    for n in fa.names():
+        assert torch.equal(mine[n], fa.tensor(n))
+    tied = write_random_model(config_from_dict(helpers.TINY_A), tmp_path / "t", seed=0)
+    assert "lm_head.weight" not in SafetensorsFile(tied / "model.safetensors").names()
+
+
+def test_loader_lists_missing_unexpected_and_wrong_shapes(tmp_path):
+    from rllm_b200.models.model import expected_tensors
+    cfg = config_from_dict(helpers.TINY_A)
+    exp = {n: s for n, (s, _) in expected_tensors(cfg.model_spec()).items()}
+    d = write_random_model(cfg, tmp_path / "m", seed=0, dtype=torch.float32)
+    good = load_checked(d, exp)
+    assert set(good) == set(exp) and good["model.norm.weight"].dtype == torch.float32
+    tensors = dict(good)
+    del tensors["model.layers.1.mlp.up_proj.weight"]
+    del tensors["model.norm.weight"]
+    tensors["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(64, 63)
+    tensors["model.layers.7.extra.weight"] = torch.zeros(3)
+    write_safetensors(d / "model.safetensors", tensors)
+    with pytest.raises(WeightMismatchError) as e:
+        load_checked(d, exp)
+    err = e.value
+    assert err.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
+    assert err.unexpected == ["model.layers.7.extra.weight"]
+    assert [w[0] for w in err.wrong_shape] == ["model.layers.0.self_attn.q_proj.weight"]
+    msg = str(err)
+    for needle in ("missing (2)", "unexpected (1)", "wrong shape (1)", "is [64, 63], expected [64, 64]"):
+        assert needle in msg
+    # a tied model may still carry an lm_head: tolerated, not read
+    tensors = dict(good, **{"lm_head.weight": torch.zeros(256, 64)})
+    write_safetensors(d / "model.safetensors", tensors)
+    assert set(load_checked(d, exp, ignorable={"lm_head.weight"})) == set(exp)
+
+
+def test_loader_dtypes(tmp_path):
+    t = {"a": torch.ones(2, 2, dtype=torch.float16), "b": torch.ones(2, dtype=torch.float32),
+         "c": torch.arange(4, dtype=torch.int64), "d": torch.ones(3, dtype=torch.bfloat16)}
+    (tmp_path / "m").mkdir()
+    write_safetensors(tmp_path / "m" / "model.safetensors", t)
+    got = load_checked(tmp_path / "m", {k: tuple(v.shape) for k, v in t.items()})
+    assert [got[k].dtype for k in "abcd"] == [torch.bfloat16, torch.float32, torch.int32, torch.bfloat16]
+
+
+def test_malformed_weight_files(tmp_path):
+    p = tmp_path / "x.safetensors"
+    write_safetensors(p, {"w": torch.arange(6, dtype=torch.float32).reshape(2, 3)})
+    raw = p.read_bytes()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + hlen])
+
+    def rewrite(h, data=raw[8 + hlen:]):
+        hj = json.dumps(h).encode()
+        p.write_bytes(struct.pack("<Q", len(hj)) + hj + data)
+
+    p.write_bytes(raw[:-4])
+    with pytest.raises(WeightFileError, match="truncated"):
+        SafetensorsFile(p)
+    p.write_bytes(struct.pack("<Q", 1 << 40) + raw[8:])
+    with pytest.raises(WeightFileError, match="header length"):
+        SafetensorsFile(p)
+    p.write_bytes(struct.pack("<Q", 5) + b"{nope" + raw[8 + hlen:])
+    with pytest.raises(WeightFileError, match="not valid JSON"):
+        SafetensorsFile(p)
+    bad = json.loads(json.dumps(header)); bad["w"]["data_offsets"] = [0, 20]
+    rewrite(bad)
+    with pytest.raises(WeightFileError, match="do not hold 24 bytes"):
+        SafetensorsFile(p)
+    bad = json.loads(json.dumps(header)); bad["w"]["dtype"] = "F8_E4M3"
+    rewrite(bad)
+    with pytest.raises(WeightFileError, match="not supported"):
+        SafetensorsFile(p)
+    bad = json.loads(json.dumps(header)); bad["v"] = {"dtype": "F32", "shape": [2], "data_offsets": [16, 24]}
+    rewrite(bad)
+    with pytest.raises(WeightFileError, match="overlap"):
+        SafetensorsFile(p)
+    with pytest.raises(WeightFileError, match="no such file"):
+        SafetensorsFile(tmp_path / "absent.safetensors")
+
+
+# ---------------------------------------------------------------- cache manager
+
+def test_block_allocator_all_or_nothing_and_double_free():
+    a = BlockAllocator(4)
+    assert a.alloc(2) == [0, 1]                               # lowest ids first
+    with pytest.raises(OutOfPages) as e:
+        a.alloc(3)
+    assert (e.value.need, e.value.free) == (3, 2) and a.n_free == 2
+    a.release(0)
+    with pytest.raises(ValueError):
+        a.release(0)
+    assert a.alloc(1) == [0]                                  # a freed page is handed out again
+    a.share(1); a.release(1)
+    assert a.refcount(1) == 1 and a.n_free == 2
+
+
+def test_cache_manager_slots_and_tables():
+    cm = CacheManager([PagedKVNeed(2, 16)], [None], block_size=4, max_tokens=32, max_requests=2)
+    assert cm.append("a", 5)[0] == [0, 1, 2, 3, 4]
+    assert cm.append("b", 3)[0] == [8, 9, 10]
+    assert cm.append("a", 4)[0] == [5, 6, 7, 12]              # a's third page comes after b's first
+    assert cm.block_table("a", 0) == [0, 1, 3] and cm.length("a") == 9
+    with pytest.raises(OutOfPages):
+        cm.append("c", 1)                                     # no state slot left
+    before = (cm.n_free_pages(0), cm.length("b"))
+    with pytest.raises(OutOfPages):
+        cm.append("b", 100)
+    assert (cm.n_free_pages(0), cm.length("b")) == before     # nothing taken
+    cm.truncate("a", 4)
+    assert cm.block_table("a", 0) == [0] and cm.length("a") == 4
+    cm.free("a"); cm.free("b")
+    assert cm.n_free_pages(0) == 8
+    cm.check_invariants()
+
+
+def test_cache_groups_window_and_shared_cache():
+    full, win = PagedKVNeed(2, 16, 0), PagedKVNeed(2, 16, 6)
+    cm = CacheManager([full, win, win, win, StateNeed((3,)), None], [None, None, None, 1, None, None],
+                      block_size=4, max_tokens=64, max_requests=3)
+    assert len(cm.paged) == 2 and len(cm.stateful) == 1
+    assert cm.entry_place[3] == cm.entry_place[1]             # entry 3 reads entry 1's cache
+    assert cm.entry_place[5] is None
+    assert [len(g.entries) for g in cm.paged] == [1, 2]
+    cm.append("r", 10)
+    assert cm.release_passed("r") == 1                        # keys 0..3 are behind the window of position 10
+    cm.append("r", 1)
+    cm.release_passed("r")
+    assert cm.block_table("r", 0) == [0, 1, 2]
+    assert cm.requests["r"].tables[1] == [None, 1, 2]
+    # a long portion needs pages for all of its tokens at once, and gives most back after the step
+    free_before = cm.n_free_pages(1)
+    cm.append("r", 21)
+    assert cm.n_free_pages(1) == free_before - 5
+    assert cm.release_passed("r") == 5
+    cm.check_invariants()
+    with pytest.raises(ValueError):
+        CacheManager([full, win], [None, 0], 4, 64, 2)        # reading a cache of another kind
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_cache_manager_random_orders(seed):
+    rng = random.Random(seed)
+    needs = [PagedKVNeed(1, 16, 0), PagedKVNeed(1, 16, 9), PagedKVNeed(1, 16, 0), StateNeed((2,))]
+    cm = CacheManager(needs, [None] * 4, block_size=rng.choice([1, 4, 16]), max_tokens=200, max_requests=5)
+    live, nxt = {}, 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.25 and len(live) < 5:
+            live[nxt] = 0
+            nxt += 1
+        elif op < 0.85 and live:
+            rid = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 7, 30])
+            state = (cm.n_free_pages(0), cm.n_free_pages(1), cm.slots.n_free)
+            try:
+                slots = cm.append(rid, n)
+            except OutOfPages:
+                assert state == (cm.n_free_pages(0), cm.n_free_pages(1), cm.slots.n_free)
+                victim = rng.choice(list(live))
+                if cm.has(victim):
+                    cm.free(victim)
+                del live[victim]
+            else:
+                assert all(len(s) == n for s in slots)
+                live[rid] += n
+                assert cm.length(rid) == live[rid]
+                cm.release_passed(rid)
+        elif live:
+            rid = rng.choice(list(live))
+            if cm.has(rid):
+                cm.free(rid)
+                with pytest.raises(KeyError):
+                    cm.free(rid)
+            del live[rid]
+        cm.check_invariants()
+    for rid in list(live):
+        if cm.has(rid):
+            cm.free(rid)
+    cm.check_invariants()
+    assert all(cm.n_free_pages(g) == cm.n_blocks for g in range(2)) and cm.slots.n_free == 5
+
+
+# ---------------------------------------------------------------- scheduler
+
+def drive(sched, cache, pick=lambda seq_tokens: 7, max_steps=10000):
+    """Runs the scheduler against the host cache manager with a fake model."""
+    log = []
+    while sched.has_work() and max_steps:
+        max_steps -= 1
+        plan = sched.plan()
+        if not plan:
+            continue
+        assert cache.can_append([(p.seq.rid, p.take) for p in plan])
+        for p in plan:
+            cache.append(p.seq.rid, p.take)
+        log.append([(p.seq.rid, p.take, p.want_last) for p in plan])
+        sched.commit(plan, [pick(p.seq.tokens) for p in plan if p.want_last])
+        cache.check_invariants()
+    return log
+
+
+def test_scheduler_portions_budget_and_order():
+    cache = CacheManager([PagedKVNeed(1, 16)], [None], 16, 4096, 8)
+    s = Scheduler(cache, ctx=512, max_num_seqs=4, prefill_chunk=32)
+    for i, n in enumerate([50, 20, 5]):
+        s.add(Request(i, list(range(n)), max_tokens=3))
+    log = drive(s, cache)
+    assert log[0] == [(0, 32, False)]                          # the first prompt takes the whole budget
+    assert log[1] == [(0, 18, True), (1, 14, False)]           # the rest is shared in admission order
+    assert log[2] == [(0, 1, True), (1, 6, True), (2, 5, True)]   # decoders first, one token each
+    done = {f.request_id: f for f in s.collect()}
+    assert all(f.reason == "length" and len(f.tokens) == 3 for f in done.values())
+    assert not cache.requests and cache.n_free_pages(0) == cache.n_blocks
+    assert s.stats["prompt_tokens"] == 75 and s.stats["generated_tokens"] == 9
+
+
+def test_scheduler_accept_and_stop():
+    cache = CacheManager([PagedKVNeed(1, 16)], [None], 16, 4096, 8)
+    s = Scheduler(cache, ctx=64, max_num_seqs=2, prefill_chunk=512)
+    with pytest.raises(ValueError, match="empty prompt"):
+        s.add(Request("e", []))
+    with pytest.raises(ValueError, match="does not fit"):
+        s.add(Request("l", list(range(64))))
+    s.add(Request("z", list(range(5)), max_tokens=0))
+    assert s.collect()[0].reason == "length"
+    s.add(Request("a", list(range(60)), max_tokens=100))       # budget = ctx - prompt = 4
+    s.add(Request("b", [1, 2, 3], max_tokens=100, stop_ids=frozenset([9])))
+    toks = iter([1, 2, 3, 9, 5, 6, 7, 8])
+    drive(s, cache, pick=lambda t: 9 if len(t) == 6 and t[:3] == [1, 2, 3] else 4)
+    done = {f.request_id: f for f in s.collect()}
+    assert done["a"].reason == "length" and len(done["a"].tokens) == 4
+    assert done["b"].reason == "stop" and done["b"].tokens[-1] == 9 and len(done["b"].tokens) == 4
+
+
+def test_scheduler_preempts_newest_and_results_do_not_change():
+    def run(max_tokens_pool):
+        cache = CacheManager([PagedKVNeed(1, 16)], [None], 16, max_tokens_pool, 8)
+        s = Scheduler(cache, ctx=400, max_num_seqs=4, prefill_chunk=64)
+        for i in range(4):
+            s.add(Request(i, [i] * 30, max_tokens=120))
+        # the fake model's token depends on the request's whole history: a recomputed request must
+        # continue exactly where it was
+        drive(s, cache, pick=lambda t: (sum(t) * 31 + len(t)) % 1000)
+        return {f.request_id: f.tokens for f in s.collect()}, s.stats["preemptions"]
+    roomy, p0 = run(4096)
+    tight, p1 = run(384)             # 4 x 150 tokens do not fit 384: somebody must wait
+    assert p0 == 0 and p1 >= 1
+    assert roomy == tight
+
+
+def test_scheduler_never_fits():
+    cache = CacheManager([PagedKVNeed(1, 16)], [None], 16, 64, 4)
+    s = Scheduler(cache, ctx=4096, max_num_seqs=2, prefill_chunk=512)
+    s.add(Request("big", list(range(200)), max_tokens=4))      # the prompt alone exceeds the pool
+    s.add(Request("grow", list(range(40)), max_tokens=100))    # fits at first, outgrows the pool alone
+    s.add(Request("ok", list(range(10)), max_tokens=2))
+    drive(s, cache)
+    done = {f.request_id: f for f in s.collect()}
+    assert done["big"].reason == "error" and "more KV cache than the pool" in done["big"].error
+    assert done["grow"].reason == "error" and len(done["grow"].tokens) > 0
+    assert done["ok"].reason == "length"
+    assert not cache.requests and cache.n_free_pages(0) == cache.n_blocks
+
+
+def test_scheduler_failed_step_frees_running():
+    cache = CacheManager([PagedKVNeed(1, 16)], [None], 16, 1024, 4)
+    s = Scheduler(cache, ctx=256, max_num_seqs=2, prefill_chunk=512)
+    for i in range(3):
+        s.add(Request(i, [1] * 20, max_tokens=5))
+    plan = s.plan()
+    for p in plan:
+        cache.append(p.seq.rid, p.take)
+    failed = s.fail_running("device fault (injected on the host)")
+    assert sorted(f.request_id for f in failed) == [0, 1] and all(f.reason == "error" for f in failed)
+    assert not cache.requests
+    drive(s, cache)                                            # the queue goes on
+    assert [f.request_id for f in s.collect() if f.reason == "length"] == [2]
+
+
+# ---------------------------------------------------------------- samplers and the plain implementation
+
+def test_host_sampler():
+    logits = np.array([0.1, 3.0, 3.0, -1.0, np.nan], dtype=np.float32)
+    assert HostSampler(SamplingParams()).sample(logits) == 1          # first index on ties, NaN never wins
+    r = SplitMix64(1)
+    assert [r.next_u64() for _ in range(2)] == [0x910A2DEC89025CC1, 0xBEEB8DA1658EEC67]
+    s = HostSampler(SamplingParams(temperature=1.0, top_k=2, seed=3))
+    assert {s.sample(logits) for _ in range(50)} <= {1, 2}
+    ids, probs = HostSampler(SamplingParams(temperature=1.0, top_p=0.5)).candidates(
+        np.array([2.0, 1.0, 0.0, -1.0], dtype=np.float32))
+    assert list(ids) == [0]
+    x = np.array([2.0, 1.0, 0.0, -1.0, 1.5], dtype=np.float32)
+    s = HostSampler(SamplingParams(temperature=0.7, seed=11))
+    n = 20000
+    freq = np.bincount([s.sample(x) for _ in range(n)], minlength=5) / n
+    p = np.exp(x / 0.7) / np.exp(x / 0.7).sum()
+    assert np.abs(freq - p).max() < 0.012
+
+
+def test_plain_sampler_reference():
+    x = np.array([2.0, 1.0, 0.0, -1.0, 1.5, -3.0], dtype=np.float32)
+    assert plain_impl.sample_row(x, 0, 0, 1.0, 0, 0) == 0
+    assert abs(float(plain_impl.threshold(x, 2, 1.0)) - 1.5) < 1e-5
+    thr = plain_impl.threshold(x, 0, 0.6)
+    assert int((x >= thr).sum()) == 2                       # 0.47 + 0.29 >= 0.6
+    u = [float(plain_impl.uniform(5, c, 3)) for c in range(2000)]
+    assert 0 < min(u) and max(u) < 1 and abs(sum(u) / len(u) - 0.5) < 0.02
+    draws = [plain_impl.sample_row(x, 0.7, 0, 1.0, 5, c) for c in range(4000)]
+    freq = np.bincount(draws, minlength=6) / 4000
+    p = np.exp(x / 0.7) / np.exp(x / 0.7).sum()
+    assert np.abs(freq - p).max() < 0.03
+
+
+def test_plain_implementation_parts():
+    torch.manual_seed(0)
+    x = torch.randn(5, 8)
+    w = torch.rand(8) + 0.5
+    ref = x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * w
+    assert torch.allclose(plain_impl.rms_norm(x, w, 1e-5), ref, atol=1e-6)
+    # rotary: position 0 is the identity, norms are kept, and q.k depends on the distance only
+    q, k = torch.randn(1, 1, 16), torch.randn(1, 1, 16)
+    assert torch.allclose(plain_impl.rope_neox(q, [0], 1e4), q)
+    d1 = (plain_impl.rope_neox(q, [7], 1e4) * plain_impl.rope_neox(k, [3], 1e4)).sum()
+    d2 = (plain_impl.rope_neox(q, [104], 1e4) * plain_impl.rope_neox(k, [100], 1e4)).sum()
+    assert abs(float(d1 - d2)) < 1e-4
+    assert torch.allclose(plain_impl.rope_neox(q, [9], 1e4).norm(), q.norm(), atol=1e-5)
+    # attention: the first token sees itself only; a window of 1 returns v; GQA maps heads h // g
+    qq, kk, vv = torch.randn(6, 4, 8), torch.randn(6, 2, 8), torch.randn(6, 2, 8)
+    a = plain_impl.attention(qq, kk, vv, 0.3)
+    assert torch.allclose(a[0, 3], vv[0, 1], atol=1e-6)
+    a1 = plain_impl.attention(qq, kk, vv, 0.3, window=1)
+    assert torch.allclose(a1[:, 0], vv[:, 0], atol=1e-6) and torch.allclose(a1[:, 2], vv[:, 1], atol=1e-6)
+    aw = plain_impl.attention(qq, kk, vv, 0.3, window=3)
+    assert torch.allclose(aw[:3], a[:3], atol=1e-6) and not torch.allclose(aw[5], a[5], atol=1e-4)
+
+
+def test_plain_forward_is_causal_and_windows_matter(tmp_path):
+    d = helpers.make_model_dir(tmp_path / "w", helpers.TINY_W, seed=5, std=0.08)
+    cfg, w = plain_impl.load_model(d)
+    toks = helpers.random_tokens(40, cfg["vocab_size"], 1)
+    full = plain_impl.forward(cfg, w, toks)
+    assert torch.allclose(plain_impl.forward(cfg, w, toks[:17]), full[:17], atol=1e-5)
+    nowin = dict(cfg, use_sliding_window=False)
+    other = plain_impl.forward(nowin, w, toks)
+    assert torch.allclose(other[:24], full[:24], atol=1e-5)            # within the window nothing changes
+    assert not torch.allclose(other[30:], full[30:], atol=1e-3)
+    assert plain_impl.greedy_generate(cfg, w, toks[:5], 3) == plain_impl.greedy_generate(cfg, w, toks[:5], 3)
