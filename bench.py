@@ -103,6 +103,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
+    ap.add_argument("--profile", choices=["decode", "prefill"],
+                    help="run only that step between cudaProfilerStart/Stop (for ncu --profile-from-start off) "
+                         "and print no benchmark line")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
@@ -166,6 +169,30 @@ def main():
         torch.cuda.empty_cache()
         return {"ms": ms, "tok_s": batch * 1000.0 / ms, "bytes": wbytes + kv_bytes, "launches": launches,
                 "h2d": staging, "d2h": 4 * batch}
+
+    if a.profile:
+        eng = Engine(model, block_size=16, max_tokens=a.batch * CTX, max_requests=a.batch)
+        prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(a.batch)]
+        if a.profile == "prefill":
+            eng.step([StepItem(0, prompts[0], [PROMPT - 1])])          # warm-up
+            eng.finish(0)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            eng.step([StepItem(0, prompts[0], [PROMPT - 1])])
+        else:
+            for b in range(a.batch):
+                for c in range(0, PROMPT, 512):
+                    eng.step([StepItem(b, prompts[b][c:c + 512], [])])
+            for i in range(3):                                         # eager, capture, replay
+                eng.step([StepItem(b, [1 + i], [0]) for b in range(a.batch)])
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            logits = eng.step([StepItem(b, [7], [0]) for b in range(a.batch)])
+            sample_rows(logits, [greedy] * a.batch, [0] * a.batch)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(f"profiled one {a.profile} step: layers {a.layers}, batch {a.batch}")
+        return 0
 
     clocks = ClockSampler()
     clocks.start()

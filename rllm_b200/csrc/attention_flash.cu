@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     constexpr int NT_O = HD / 8;                  // output n-tiles
     extern __shared__ __align__(128) unsigned char smem[];   // [2 stages][K tile, V tile]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    pdl_wait();          // queries, positions and this step's keys come from the kernels before
 
     const int tile = blockIdx.x;
     const int req = p.tile_req[tile], tok0 = p.tile_tok0[tile];
@@ -235,6 +236,7 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
         }
         __syncthreads();                           // the stage may be overwritten from here on
     }
+    pdl_launch_dependents();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
@@ -270,38 +272,44 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
 }
 
 // Merges the partials of the decode shape in split order (fixed order: the result is reproducible)
-// and writes the normalized output.  grid (tiles, K * head_chunks), one thread per output dim.
+// and writes the normalized output.  grid (tiles, K * head_chunks, rows), one thread per output dim.
 template <int HD>
 __global__ void __launch_bounds__(HD) paged_flash_combine_kernel(const FlashParams p, int n_splits) {
-    const int tile = blockIdx.x;
+    extern __shared__ float wgt[];               // [n_splits] weight of each split, then the sum
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tile = blockIdx.x, R = blockIdx.z;
     const int req = p.tile_req[tile], tok0 = p.tile_tok0[tile];
     const int nt = min(p.TT, p.cu_q[req + 1] - tok0);
     const int grp = p.H / p.K;
     const int kvh = blockIdx.y / p.head_chunks, hc = blockIdx.y % p.head_chunks;
     const int head0 = kvh * grp + hc * p.GH;
     const int nh = min(p.GH, grp - hc * p.GH);
+    const int tl = R / p.GH, hl = R % p.GH;
+    if (tl >= nt || hl >= nh) return;
     const int d = threadIdx.x;
     const size_t base = ((size_t)tile * gridDim.y + blockIdx.y) * n_splits;
-    for (int R = 0; R < p.part_rows; ++R) {
-        const int tl = R / p.GH, hl = R % p.GH;
-        if (tl >= nt || hl >= nh) continue;
-        float M = -INFINITY;
-        for (int z = 0; z < n_splits; ++z) {
-            const float* ml = p.part_ml + ((base + z) * p.part_rows + R) * 2;
-            if (ml[1] > 0.f) M = fmaxf(M, ml[0]);
-        }
-        float num = 0.f, den = 0.f;
-        for (int z = 0; z < n_splits; ++z) {
-            const size_t row = (base + z) * p.part_rows + R;
-            const float l = p.part_ml[row * 2 + 1];
-            if (l > 0.f) {
-                const float w = exp2f(p.part_ml[row * 2] - M);
-                num += p.part_o[row * HD + d] * w;
-                den += l * w;
-            }
-        }
-        p.out[((size_t)(tok0 + tl) * p.H + head0 + hl) * HD + d] = from_f<bf16>(den > 0.f ? num / den : 0.f);
+    // weights exp2(m_z - M) * [l_z > 0], computed once per block
+    float M = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) {
+        const float* ml = p.part_ml + ((base + z) * p.part_rows + R) * 2;
+        if (ml[1] > 0.f) M = fmaxf(M, ml[0]);
     }
+    for (int z = d; z < n_splits; z += HD) {
+        const float* ml = p.part_ml + ((base + z) * p.part_rows + R) * 2;
+        wgt[z] = ml[1] > 0.f ? exp2f(ml[0] - M) : 0.f;
+    }
+    __syncthreads();
+    float num = 0.f, den = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+        const float w = wgt[z];
+        if (w > 0.f) {
+            const size_t row = (base + z) * p.part_rows + R;
+            num += p.part_o[row * HD + d] * w;
+            den += p.part_ml[row * 2 + 1] * w;
+        }
+    }
+    p.out[((size_t)(tok0 + tl) * p.H + head0 + hl) * HD + d] = from_f<bf16>(den > 0.f ? num / den : 0.f);
 }
 
 template <int HD>
@@ -313,17 +321,15 @@ static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_split
         auto kern = paged_flash_attention_kernel<HD, NW, BN>;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, NW * 32, smem, stream>>>(p);
-        return RLLM_LAUNCH_STATUS();
+        return rllm_launch(kern, grid, dim3(NW * 32), smem, stream, p);
     }
     constexpr int NW = 1, BN = 32;
     const int smem = 2 * 2 * BN * HD * 2;
     auto kern = paged_flash_attention_kernel<HD, NW, BN>;
-    kern<<<grid, NW * 32, smem, stream>>>(p);
-    int st = RLLM_LAUNCH_STATUS();
+    int st = rllm_launch(kern, grid, dim3(NW * 32), smem, stream, p);
     if (st) return st;
-    paged_flash_combine_kernel<HD><<<dim3(n_tiles, p.K * p.head_chunks), HD, 0, stream>>>(p, n_splits);
-    return RLLM_LAUNCH_STATUS();
+    return rllm_launch(paged_flash_combine_kernel<HD>, dim3(n_tiles, p.K * p.head_chunks, p.part_rows), dim3(HD),
+                       n_splits * sizeof(float), stream, p, n_splits);
 }
 
 // mode 0: prefill shape (64-row tiles, no split; part_* unused).  mode 1: decode shape (16-row tiles,

@@ -26,6 +26,8 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ 
                                const int* __restrict__ block_table, int table_stride, int H, int K,
                                int hd, int bs, float scale, int window) {
     extern __shared__ float smem[];
+    pdl_wait();
+    pdl_launch_dependents();
     float* qs = smem;                    // [hd]
     float* pr = smem + hd;               // [ATT_THREADS] probabilities of the chunk
     int* rowoff = (int*)(pr + ATT_THREADS);  // [ATT_THREADS] element offset / hd of each key row
@@ -100,12 +102,10 @@ RLLM_API int rllm_paged_attention_generic(const void* q, int q_dtype, const void
     const size_t smem = (size_t)(hd + 2 * ATT_THREADS) * sizeof(float);
     dim3 grid(n, H);
     if (q_dtype == RLLM_F32)
-        paged_attention_generic_kernel<float, float, float><<<grid, ATT_THREADS, smem, stream>>>(
-            (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, positions,
-            seq_ids, block_table, table_stride, H, K, hd, bs, scale, window);
-    else
-        paged_attention_generic_kernel<bf16, bf16, bf16><<<grid, ATT_THREADS, smem, stream>>>(
-            (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions,
-            seq_ids, block_table, table_stride, H, K, hd, bs, scale, window);
-    return RLLM_LAUNCH_STATUS();
+        return rllm_launch(paged_attention_generic_kernel<float, float, float>, grid, dim3(ATT_THREADS), smem,
+                           stream, (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out,
+                           positions, seq_ids, block_table, table_stride, H, K, hd, bs, scale, window);
+    return rllm_launch(paged_attention_generic_kernel<bf16, bf16, bf16>, grid, dim3(ATT_THREADS), smem, stream,
+                       (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions,
+                       seq_ids, block_table, table_stride, H, K, hd, bs, scale, window);
 }

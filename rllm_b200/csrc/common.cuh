@@ -64,4 +64,41 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return red[32];
 }
 
+// Programmatic dependent launch (griddepcontrol): `pdl_wait` blocks until the kernels this one
+// depends on have completed and their writes are visible (a no-op for an ordinary launch);
+// `pdl_launch_dependents` lets the next kernel of the stream begin to launch early.  A kernel
+// launched with the attribute may only touch memory that earlier kernels write after its wait.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" :::); }
+
+// Host side: every kernel of this package is launched through rllm_launch.  With the switch on
+// (RLLM_B200_PDL=0 in the environment turns it off) kernels carry the programmatic stream
+// serialization attribute, so a kernel's launch and its loads of data that no kernel writes
+// (weights) overlap the tail of the kernel before it.  Every kernel therefore calls pdl_wait()
+// before it reads or writes anything an earlier kernel may have written, and before it exits.
+#include <stdlib.h>
+static inline int rllm_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("RLLM_B200_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on;
+}
+template <typename... KArgs, typename... Args>
+static inline int rllm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = rllm_pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 #define RLLM_LAUNCH_STATUS() ((int)cudaGetLastError())

@@ -14,6 +14,8 @@
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int d, int vocab, int* err) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     int tok = tokens[t];
     if (tok < 0 || tok >= vocab) {
@@ -30,10 +32,8 @@ RLLM_API int rllm_embed(const void* table, int table_dtype, const int* tokens, f
     if (n <= 0) return 0;
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == RLLM_F32)
-        embed_kernel<float><<<n, threads, 0, stream>>>((const float*)table, tokens, out, d, vocab, err);
-    else
-        embed_kernel<bf16><<<n, threads, 0, stream>>>((const bf16*)table, tokens, out, d, vocab, err);
-    return RLLM_LAUNCH_STATUS();
+        return rllm_launch(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, out, d, vocab, err);
+    return rllm_launch(embed_kernel<bf16>, dim3(n), dim3(threads), 0, stream, (const bf16*)table, tokens, out, d, vocab, err);
 }
 
 // ------------------------------------------------------------------ add + RMSNorm
@@ -45,6 +45,9 @@ __global__ void add_rms_norm_kernel(float* __restrict__ x, const TD* __restrict_
                                     const int* __restrict__ rows, const float* __restrict__ w,
                                     TO* __restrict__ out, int d, float eps, int write_x) {
     __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* xr = x + (size_t)src * d;
@@ -74,20 +77,21 @@ RLLM_API int rllm_add_rms_norm(float* x, const void* delta, int delta_dtype, con
     if (n_rows <= 0) return 0;
     int threads = 32;
     while (threads < d / 4 && threads < 1024) threads <<= 1;
-#define LAUNCH(TD, TO)                                                                         \
-    add_rms_norm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(x, (const TD*)delta, rows, w,   \
-                                                                 (TO*)out, d, eps, write_x)
+#define LAUNCH(TD, TO)                                                                           \
+    return rllm_launch(add_rms_norm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, x,    \
+                       (const TD*)delta, rows, w, (TO*)out, d, eps, write_x)
     if (delta_dtype == RLLM_F32 && out_dtype == RLLM_F32) LAUNCH(float, float);
     else if (delta_dtype == RLLM_F32 && out_dtype == RLLM_BF16) LAUNCH(float, bf16);
     else if (delta_dtype == RLLM_BF16 && out_dtype == RLLM_F32) LAUNCH(bf16, float);
     else LAUNCH(bf16, bf16);
 #undef LAUNCH
-    return RLLM_LAUNCH_STATUS();
 }
 
 // Plain residual add x += delta (used after the last layer when no norm follows).
 template <typename TD>
 __global__ void add_inplace_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += to_f<TD>(delta[i]);
 }
@@ -97,16 +101,16 @@ RLLM_API int rllm_add_inplace(float* x, const void* delta, int delta_dtype, long
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (delta_dtype == RLLM_F32)
-        add_inplace_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)delta, (size_t)n);
-    else
-        add_inplace_kernel<bf16><<<blocks, threads, 0, stream>>>(x, (const bf16*)delta, (size_t)n);
-    return RLLM_LAUNCH_STATUS();
+        return rllm_launch(add_inplace_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x, (const float*)delta, (size_t)n);
+    return rllm_launch(add_inplace_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, x, (const bf16*)delta, (size_t)n);
 }
 
 // ------------------------------------------------------------------ SwiGLU
 // in [n, 2F] holds gate in columns [0,F) and up in [F,2F); out[t,j] = gate/(1+exp(-gate)) * up.
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out, int F, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t t = i / F;
@@ -121,13 +125,13 @@ RLLM_API int rllm_silu_mul(const void* in, int in_dtype, void* out, int out_dtyp
     if (total == 0) return 0;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-#define LAUNCH(TI, TO) silu_mul_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)in, (TO*)out, F, total)
+#define LAUNCH(TI, TO) \
+    return rllm_launch(silu_mul_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)in, (TO*)out, F, total)
     if (in_dtype == RLLM_F32 && out_dtype == RLLM_F32) LAUNCH(float, float);
     else if (in_dtype == RLLM_F32 && out_dtype == RLLM_BF16) LAUNCH(float, bf16);
     else if (in_dtype == RLLM_BF16 && out_dtype == RLLM_F32) LAUNCH(bf16, float);
     else LAUNCH(bf16, bf16);
 #undef LAUNCH
-    return RLLM_LAUNCH_STATUS();
 }
 
 // ------------------------------------------------------------------ q/k norm + rotary + paged KV write
@@ -147,6 +151,9 @@ __global__ void qk_norm_rope_store_kernel(const TI* __restrict__ qkv, const floa
                                           TC* __restrict__ v_cache, int H, int K, int hd, int bs,
                                           float eps, int write_kv) {
     __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+
     const int t = blockIdx.x, hx = blockIdx.y;
     const int half = hd >> 1;
     const int i = threadIdx.x;
@@ -197,15 +204,14 @@ RLLM_API int rllm_qk_norm_rope_store(const void* qkv, int in_dtype, const float*
     if (hd % 2 != 0 || hd > 2048) return (int)cudaErrorInvalidValue;
     const int threads = ((hd / 2 + 31) / 32) * 32;
     dim3 grid(n, H + 2 * K);
-#define LAUNCH(TI, TO, TC)                                                                      \
-    qk_norm_rope_store_kernel<TI, TO, TC><<<grid, threads, 0, stream>>>(                        \
-        (const TI*)qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, (TO*)q_out,        \
-        (TC*)k_cache, (TC*)v_cache, H, K, hd, bs, eps, write_kv)
+#define LAUNCH(TI, TO, TC)                                                                        \
+    return rllm_launch(qk_norm_rope_store_kernel<TI, TO, TC>, grid, dim3(threads), 0, stream,     \
+                       (const TI*)qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, (TO*)q_out, \
+                       (TC*)k_cache, (TC*)v_cache, H, K, hd, bs, eps, write_kv)
     if (q_dtype != cache_dtype) return (int)cudaErrorInvalidValue;
     if (in_dtype == RLLM_F32 && q_dtype == RLLM_F32) LAUNCH(float, float, float);
     else if (in_dtype == RLLM_F32 && q_dtype == RLLM_BF16) LAUNCH(float, bf16, bf16);
     else if (in_dtype == RLLM_BF16 && q_dtype == RLLM_BF16) LAUNCH(bf16, bf16, bf16);
     else LAUNCH(bf16, float, float);
 #undef LAUNCH
-    return RLLM_LAUNCH_STATUS();
 }

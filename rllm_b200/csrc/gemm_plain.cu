@@ -23,6 +23,8 @@ gemm_plain_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __rest
                   int n, int k, int lda, int ldw, int ldc, int accumulate) {
     __shared__ float As[TK][TM + 1];
     __shared__ float Ws[TK][TN + 1];
+    pdl_wait();
+    pdl_launch_dependents();
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;        // 16 x 16 threads, 4 x 4 outputs each
     const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
@@ -80,9 +82,9 @@ RLLM_API int rllm_gemm_plain(const void* A, int a_dtype, const void* W, int w_dt
     if (k <= 0) return (int)cudaErrorInvalidValue;
     if (accumulate && c_dtype != RLLM_F32) return (int)cudaErrorInvalidValue;
     dim3 grid((n + TN - 1) / TN, (m + TM - 1) / TM);
-#define LAUNCH(TA, TW, TC)                                                                     \
-    gemm_plain_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (TC*)C, \
-                                                            m, n, k, lda, ldw, ldc, accumulate)
+#define LAUNCH(TA, TW, TC)                                                                        \
+    return rllm_launch(gemm_plain_kernel<TA, TW, TC>, grid, dim3(256), 0, stream, (const TA*)A,    \
+                       (const TW*)W, (TC*)C, m, n, k, lda, ldw, ldc, accumulate)
     const int key = a_dtype * 4 + w_dtype * 2 + c_dtype;
     switch (key) {
         case 0: LAUNCH(float, float, float); break;
@@ -96,5 +98,5 @@ RLLM_API int rllm_gemm_plain(const void* A, int a_dtype, const void* W, int w_dt
         default: return (int)cudaErrorInvalidValue;
     }
 #undef LAUNCH
-    return RLLM_LAUNCH_STATUS();
+    return 0;
 }

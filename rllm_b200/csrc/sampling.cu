@@ -60,6 +60,8 @@ sample_rows_kernel(const float* __restrict__ logits, long long row_stride, int v
                    const unsigned long long* __restrict__ counter, int* __restrict__ out) {
     __shared__ float red[33];
     __shared__ KeyIdx best_sh[33];
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* x = logits + (size_t)r * row_stride;
     const float T = temperature ? temperature[r] : 0.f;
@@ -137,7 +139,6 @@ RLLM_API int rllm_sample_rows(const float* logits, long long row_stride, int row
                               int* out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0 || vocab >= (1 << 24)) return (int)cudaErrorInvalidValue;
-    sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature,
-                                                            top_k, top_p, seed, counter, out);
-    return RLLM_LAUNCH_STATUS();
+    return rllm_launch(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride, vocab,
+                       temperature, top_k, top_p, seed, counter, out);
 }

@@ -43,6 +43,7 @@ __device__ __forceinline__ uint4 ldg_cached(const void* p) {
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 
+
 // NT: batch columns / 8.  RT: weight row tiles per CTA (2 for SwiGLU).  U: k steps fetched ahead.
 template <int NT, int EPI, typename TC, int U>
 __global__ void __launch_bounds__(SG_THREADS)
@@ -91,6 +92,10 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, TC* _
                 a[u][rt][1] = ok ? ldg_stream(wrow[rt][1] + kk) : zero;
             }
         }
+        // The weights do not depend on the kernel before this one, the activations do: with a
+        // programmatic dependent launch the first weight loads are already in flight while the
+        // previous kernel drains.  (Without that launch attribute the wait returns at once.)
+        if (s0 == warp) pdl_wait();
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int kk = (s0 + u * SG_WARPS) << 5;
@@ -106,6 +111,8 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, TC* _
             }
         }
     }
+    pdl_wait();                 // warps that had no k step still have to wait before they write
+    pdl_launch_dependents();    // the next kernel may start to fill the SMs that this one leaves
     // partial sums -> shared memory [warp][rt][row 0..15][batch 0..NT*8)
     constexpr int NB = NT * 8;
 #pragma unroll
@@ -142,15 +149,16 @@ template <int NT, int EPI, typename TC>
 static int launch_sg(const bf16* W, const bf16* X, void* C, int m, int n, int k, int ldw, int ldx, int ldc,
                      int up_row_offset, cudaStream_t stream) {
     constexpr int RT = (EPI == EPI_SWIGLU) ? 2 : 1;
-    constexpr int U = (NT * RT >= 8) ? 2 : 4;
+    // k steps fetched ahead: 16 weight loads of 16 bytes in flight per thread where registers allow
+    constexpr int U = (NT * RT >= 8) ? 2 : (NT >= 2 ? 4 : 8 / RT);
     const size_t smem = (size_t)SG_WARPS * RT * 16 * NT * 8 * sizeof(float);
     auto kern = skinny_gemm_kernel<NT, EPI, TC, U>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kern<<<(n + 15) / 16, SG_THREADS, smem, stream>>>(W, X, (TC*)C, m, n, k, ldw, ldx, ldc, up_row_offset);
-    return RLLM_LAUNCH_STATUS();
+    return rllm_launch(kern, dim3((n + 15) / 16), dim3(SG_THREADS), smem, stream, W, X, (TC*)C, m, n, k, ldw, ldx,
+                       ldc, up_row_offset);
 }
 
 template <int EPI, typename TC>
