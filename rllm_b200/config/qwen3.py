@@ -108,9 +108,9 @@ class Qwen3Config(ModelConfig):
         if self.num_attention_heads % self.num_key_value_heads:
             raise ConfigError(f"config.json: num_attention_heads {self.num_attention_heads} is not a "
                               f"multiple of num_key_value_heads {self.num_key_value_heads}")
-        if self.head_dim % 16:
-            raise ConfigError(f"config.json: 'head_dim' {self.head_dim} must be a multiple of 16 "
-                              f"(the kernels take head sizes in steps of 16)")
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise ConfigError(f"config.json: 'head_dim' {self.head_dim} must be a multiple of 16 and at most 256 "
+                              f"(the kernels take head sizes from 16 to 256 in steps of 16)")
         if not self.rms_norm_eps > 0:
             raise ConfigError("config.json: 'rms_norm_eps' must be positive")
         if not self.rope_theta > 0:

@@ -131,17 +131,26 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     }
 
     const int* table = p.block_table + (size_t)req * p.table_stride;
+    // Each thread copies the same 16-byte chunk column of several rows: the chunk index is fixed,
+    // the page of a row is looked up once per row (a shift when the page size is a power of two).
+    static_assert((NW * 32) % CH == 0, "threads must cover whole rows of chunks");
+    constexpr int ROWS_PER_PASS = NW * 32 / CH;
+    const int my_chunk = tid % CH, my_row0 = tid / CH;
+    const int bs_shift = (p.bs & (p.bs - 1)) == 0 ? __ffs(p.bs) - 1 : -1;
     auto load_tile = [&](int stage, int kt) {
         unsigned char* sk = smem + (size_t)stage * 2 * TILE_BYTES;
         unsigned char* sv = sk + TILE_BYTES;
-        for (int idx = tid; idx < BN * CH; idx += NW * 32) {
-            const int row = idx / CH, c = idx % CH;
+#pragma unroll 4
+        for (int row = my_row0; row < BN; row += ROWS_PER_PASS) {
             const int key = kt + row;
             const bool ok = key < ke;              // beyond the range: zero fill
             const int kk = ok ? key : kb;
-            const int page = table[kk / p.bs], off = kk % p.bs;
-            const size_t src = (((size_t)page * p.K + kvh) * p.bs + off) * HD + c * 8;
-            const uint32_t dst = row * (HD * 2) + ((c ^ (row & 7)) << 4);
+            int blk, off;
+            if (bs_shift >= 0) { blk = kk >> bs_shift; off = kk & (p.bs - 1); }
+            else { blk = kk / p.bs; off = kk - blk * p.bs; }
+            const int page = table[blk];
+            const size_t src = (((size_t)page * p.K + kvh) * p.bs + off) * HD + my_chunk * 8;
+            const uint32_t dst = row * (HD * 2) + ((my_chunk ^ (row & 7)) << 4);
             cp_async16(smem_u32(sk + dst), p.k_cache + src, ok ? 16 : 0);
             cp_async16(smem_u32(sv + dst), p.v_cache + src, ok ? 16 : 0);
         }

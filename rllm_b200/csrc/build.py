@@ -35,6 +35,7 @@ LIBRARIES = {
     "blas": (["gemm_lib.cu"], ["-lcublas"]),
     "fast": (["skinny_gemm.cu"], []),
     "attn": (["attention_flash.cu"], []),
+    "tc": (["gemm_tc.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -71,20 +71,86 @@ __global__ void add_rms_norm_kernel(float* __restrict__ x, const TD* __restrict_
     }
 }
 
+template <typename T> __device__ __forceinline__ void store2(T* p, float a, float b);
+template <> __device__ __forceinline__ void store2<float>(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+template <> __device__ __forceinline__ void store2<bf16>(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// Same operation for d a multiple of 4 and at most 256 * 4 * NV: one pass over global memory, the row
+// lives in registers between the sum of squares and the scaling (float4 loads, 256 threads a row).
+template <typename TD, typename TO, int NV>
+__global__ void __launch_bounds__(256)
+add_rms_norm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, const int* __restrict__ rows,
+                        const float* __restrict__ w, TO* __restrict__ out, int d, float eps, int write_x) {
+    __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* xr = x + (size_t)src * d;
+    const TD* dr = delta ? delta + (size_t)src * d : nullptr;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < NV; ++it) {
+        const int i = (it * 256 + threadIdx.x) * 4;
+        v[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < d) {
+            v[it] = *reinterpret_cast<const float4*>(xr + i);
+            if (dr) {
+                v[it].x += to_f<TD>(dr[i]); v[it].y += to_f<TD>(dr[i + 1]);
+                v[it].z += to_f<TD>(dr[i + 2]); v[it].w += to_f<TD>(dr[i + 3]);
+                if (write_x) *reinterpret_cast<float4*>(xr + i) = v[it];
+            }
+            ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
+        }
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = out + (size_t)r * d;
+#pragma unroll
+    for (int it = 0; it < NV; ++it) {
+        const int i = (it * 256 + threadIdx.x) * 4;
+        if (i < d) {
+            const float4 ww = *reinterpret_cast<const float4*>(w + i);
+            store2<TO>(o + i, v[it].x * rs * ww.x, v[it].y * rs * ww.y);
+            store2<TO>(o + i + 2, v[it].z * rs * ww.z, v[it].w * rs * ww.w);
+        }
+    }
+}
+
+template <typename TD, typename TO>
+static int launch_norm(float* x, const void* delta, const int* rows, const float* w, void* out, int n_rows, int d,
+                       float eps, int write_x, cudaStream_t stream) {
+    const bool vec = d % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
+#define VEC(NV)                                                                                        \
+    return rllm_launch(add_rms_norm_vec_kernel<TD, TO, NV>, dim3(n_rows), dim3(256), 0, stream, x,     \
+                       (const TD*)delta, rows, w, (TO*)out, d, eps, write_x)
+    if (vec && d <= 1024) VEC(1);
+    if (vec && d <= 2048) VEC(2);
+    if (vec && d <= 4096) VEC(4);
+    if (vec && d <= 8192) VEC(8);
+#undef VEC
+    int threads = 32;
+    while (threads < d / 4 && threads < 1024) threads <<= 1;
+    return rllm_launch(add_rms_norm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, x, (const TD*)delta,
+                       rows, w, (TO*)out, d, eps, write_x);
+}
+
 RLLM_API int rllm_add_rms_norm(float* x, const void* delta, int delta_dtype, const int* rows,
                                const float* w, void* out, int out_dtype, int n_rows, int d,
                                float eps, int write_x, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    int threads = 32;
-    while (threads < d / 4 && threads < 1024) threads <<= 1;
-#define LAUNCH(TD, TO)                                                                           \
-    return rllm_launch(add_rms_norm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, x,    \
-                       (const TD*)delta, rows, w, (TO*)out, d, eps, write_x)
-    if (delta_dtype == RLLM_F32 && out_dtype == RLLM_F32) LAUNCH(float, float);
-    else if (delta_dtype == RLLM_F32 && out_dtype == RLLM_BF16) LAUNCH(float, bf16);
-    else if (delta_dtype == RLLM_BF16 && out_dtype == RLLM_F32) LAUNCH(bf16, float);
-    else LAUNCH(bf16, bf16);
-#undef LAUNCH
+    if (delta_dtype == RLLM_F32 && out_dtype == RLLM_F32)
+        return launch_norm<float, float>(x, delta, rows, w, out, n_rows, d, eps, write_x, stream);
+    if (delta_dtype == RLLM_F32 && out_dtype == RLLM_BF16)
+        return launch_norm<float, bf16>(x, delta, rows, w, out, n_rows, d, eps, write_x, stream);
+    if (delta_dtype == RLLM_BF16 && out_dtype == RLLM_F32)
+        return launch_norm<bf16, float>(x, delta, rows, w, out, n_rows, d, eps, write_x, stream);
+    return launch_norm<bf16, bf16>(x, delta, rows, w, out, n_rows, d, eps, write_x, stream);
 }
 
 // Plain residual add x += delta (used after the last layer when no norm follows).
@@ -119,79 +185,124 @@ __global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out,
     const float u = to_f<TI>(in[t * 2 * F + F + j]);
     out[i] = from_f<TO>(g / (1.0f + expf(-g)) * u);
 }
+template <typename TI, typename TO>
+__global__ void silu_mul_vec2_kernel(const TI* __restrict__ in, TO* __restrict__ out, int F, size_t total2) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i2 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // pairs of outputs
+    if (i2 >= total2) return;
+    const size_t i = i2 * 2;
+    const size_t t = i / F;
+    const int j = (int)(i - t * F);
+    const TI* g = in + t * 2 * F + j;
+    const TI* u = g + F;
+    const float g0 = to_f<TI>(g[0]), g1 = to_f<TI>(g[1]);
+    store2<TO>(out + i, g0 / (1.0f + expf(-g0)) * to_f<TI>(u[0]), g1 / (1.0f + expf(-g1)) * to_f<TI>(u[1]));
+}
+
 RLLM_API int rllm_silu_mul(const void* in, int in_dtype, void* out, int out_dtype, int n, int F,
                            cudaStream_t stream) {
     const size_t total = (size_t)n * F;
     if (total == 0) return 0;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-#define LAUNCH(TI, TO) \
+    const bool vec = F % 2 == 0 && ((uintptr_t)out & 7) == 0;
+    const unsigned blocks2 = (unsigned)((total / 2 + threads - 1) / threads);
+#define LAUNCH(TI, TO)                                                                                       \
+    if (vec)                                                                                                 \
+        return rllm_launch(silu_mul_vec2_kernel<TI, TO>, dim3(blocks2), dim3(threads), 0, stream, (const TI*)in, \
+                           (TO*)out, F, total / 2);                                                          \
     return rllm_launch(silu_mul_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)in, (TO*)out, F, total)
-    if (in_dtype == RLLM_F32 && out_dtype == RLLM_F32) LAUNCH(float, float);
-    else if (in_dtype == RLLM_F32 && out_dtype == RLLM_BF16) LAUNCH(float, bf16);
-    else if (in_dtype == RLLM_BF16 && out_dtype == RLLM_F32) LAUNCH(bf16, float);
-    else LAUNCH(bf16, bf16);
+    if (in_dtype == RLLM_F32 && out_dtype == RLLM_F32) { LAUNCH(float, float); }
+    if (in_dtype == RLLM_F32 && out_dtype == RLLM_BF16) { LAUNCH(float, bf16); }
+    if (in_dtype == RLLM_BF16 && out_dtype == RLLM_F32) { LAUNCH(bf16, float); }
+    LAUNCH(bf16, bf16);
 #undef LAUNCH
 }
 
 // ------------------------------------------------------------------ q/k norm + rotary + paged KV write
-// One block per (token, head) over the fused projection row qkv[t] = [q (H*hd) | k (K*hd) | v (K*hd)].
+// Over the fused projection row qkv[t] = [q (H*hd) | k (K*hd) | v (K*hd)]:
 //   q, k heads: optional RMSNorm over the head (weight of hd entries shared by all heads),
 //               then rotate-half rotary with angle = position * inv_freq[i] on pairs (i, i+hd/2)
 //               (inv_freq has hd/2 entries; a null inv_freq means no rotation);
 //   q -> q_out[t, h, :];  k, v -> the paged cache at slot = slots[t]
 //   (page = slot / bs, offset = slot % bs, layout [page][kv_head][bs][hd]); slot < 0 writes nothing.
 // write_kv == 0 skips the cache (a layer that reads another layer's cache).
+//
+// One block per token and group of 8 heads (head size a multiple of 4, at most 256): the
+// token's cos/sin table is computed once in shared memory, each warp then takes one head,
+// a lane holding two neighbouring pairs (j, j + hd/2), (j + 1, j + 1 + hd/2) so that loads and
+// stores are 8 and 4 bytes wide.
 template <typename TI, typename TO, typename TC>
-__global__ void qk_norm_rope_store_kernel(const TI* __restrict__ qkv, const float* __restrict__ q_norm_w,
-                                          const float* __restrict__ k_norm_w,
-                                          const float* __restrict__ inv_freq,
-                                          const int* __restrict__ positions, const int* __restrict__ slots,
-                                          TO* __restrict__ q_out, TC* __restrict__ k_cache,
-                                          TC* __restrict__ v_cache, int H, int K, int hd, int bs,
-                                          float eps, int write_kv) {
-    __shared__ float red[33];
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_token_kernel(const TI* __restrict__ qkv, const float* __restrict__ q_norm_w,
+                                const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
+                                const int* __restrict__ positions, const int* __restrict__ slots,
+                                TO* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache, int H,
+                                int K, int hd, int bs, float eps, int write_kv) {
+    __shared__ float2 cs[128];                    // (cos, sin) of pair j at this token's position
     pdl_wait();
     pdl_launch_dependents();
-
-    const int t = blockIdx.x, hx = blockIdx.y;
+    const int t = blockIdx.x;
     const int half = hd >> 1;
-    const int i = threadIdx.x;
-    const bool active = i < half;
-    const int width = (H + 2 * K) * hd;
-    const int kind = hx < H ? 0 : (hx < H + K ? 1 : 2);     // 0 q, 1 k, 2 v
-    if (kind != 0 && !write_kv) return;
-    const TI* src = qkv + (size_t)t * width + (size_t)hx * hd;
-    float a = 0.f, b = 0.f;
-    if (active) { a = to_f<TI>(src[i]); b = to_f<TI>(src[i + half]); }
-    if (kind != 2) {
-        const float* nw = kind == 0 ? q_norm_w : k_norm_w;
-        if (nw) {
-            const float ss = block_sum(a * a + b * b, red);
-            const float rs = 1.0f / sqrtf(ss / (float)hd + eps);
-            if (active) { a = a * rs * nw[i]; b = b * rs * nw[i + half]; }
-        }
-        // rotary over the whole head: pairs (i, i + hd/2)
-        if (inv_freq && active) {
-            float s, c;
-            sincosf((float)positions[t] * inv_freq[i], &s, &c);
-            const float a2 = a * c - b * s, b2 = a * s + b * c;
-            a = a2; b = b2;
-        }
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < half) {
+        float sn = 0.f, c = 1.f;
+        if (inv_freq) sincosf((float)positions[t] * inv_freq[tid], &sn, &c);
+        cs[tid] = make_float2(c, sn);
     }
-    if (!active) return;
-    if (kind == 0) {
-        TO* dst = q_out + ((size_t)t * H + hx) * hd;
-        dst[i] = from_f<TO>(a);
-        dst[i + half] = from_f<TO>(b);
-    } else {
-        const int slot = slots[t];
-        if (slot < 0) return;
-        const int kvh = kind == 1 ? hx - H : hx - H - K;
-        TC* base = kind == 1 ? k_cache : v_cache;
-        TC* dst = base + (((size_t)(slot / bs) * K + kvh) * bs + (slot % bs)) * hd;
-        dst[i] = from_f<TC>(a);
-        dst[i + half] = from_f<TC>(b);
+    __syncthreads();
+    const int n_heads = write_kv ? H + 2 * K : H;
+    const int slot = slots[t];
+    const size_t width = (size_t)(H + 2 * K) * hd;
+    const int units = half >> 1;                  // float2 units per half head
+    const int hx = blockIdx.y * 8 + warp;          // one head per warp
+    if (hx < n_heads) {
+        const int kind = hx < H ? 0 : (hx < H + K ? 1 : 2);
+        const TI* src = qkv + (size_t)t * width + (size_t)hx * hd;
+        TO* qdst = nullptr;
+        TC* cdst = nullptr;
+        if (kind == 0) {
+            qdst = q_out + ((size_t)t * H + hx) * hd;
+        } else if (slot >= 0) {
+            const int kvh = kind == 1 ? hx - H : hx - H - K;
+            cdst = (kind == 1 ? k_cache : v_cache) + (((size_t)(slot / bs) * K + kvh) * bs + (slot % bs)) * hd;
+        }
+        float a[2][2], b[2][2];
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int j = (lane + 32 * u) * 2;
+            a[u][0] = a[u][1] = b[u][0] = b[u][1] = 0.f;
+            if (lane + 32 * u < units) {
+                a[u][0] = to_f<TI>(src[j]); a[u][1] = to_f<TI>(src[j + 1]);
+                b[u][0] = to_f<TI>(src[j + half]); b[u][1] = to_f<TI>(src[j + half + 1]);
+                ss += a[u][0] * a[u][0] + a[u][1] * a[u][1] + b[u][0] * b[u][0] + b[u][1] * b[u][1];
+            }
+        }
+        const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+        float rs = 1.f;
+        if (nw) rs = 1.0f / sqrtf(warp_sum(ss) / (float)hd + eps);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int j = (lane + 32 * u) * 2;
+            if (lane + 32 * u < units) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float av = a[u][e], bv = b[u][e];
+                if (nw) { av = av * rs * nw[j + e]; bv = bv * rs * nw[j + e + half]; }
+                if (kind != 2) {
+                    const float2 c = cs[j + e];
+                    const float a2 = av * c.x - bv * c.y, b2 = av * c.y + bv * c.x;
+                    av = a2; bv = b2;
+                }
+                o[e] = av; o[2 + e] = bv;
+            }
+            if (qdst) { store2<TO>(qdst + j, o[0], o[1]); store2<TO>(qdst + j + half, o[2], o[3]); }
+            if (cdst) { store2<TC>(cdst + j, o[0], o[1]); store2<TC>(cdst + j + half, o[2], o[3]); }
+            }
+        }
     }
 }
 
@@ -201,17 +312,18 @@ RLLM_API int rllm_qk_norm_rope_store(const void* qkv, int in_dtype, const float*
                                      void* k_cache, void* v_cache, int cache_dtype, int n, int H, int K,
                                      int hd, int bs, float eps, int write_kv, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (hd % 2 != 0 || hd > 2048) return (int)cudaErrorInvalidValue;
-    const int threads = ((hd / 2 + 31) / 32) * 32;
-    dim3 grid(n, H + 2 * K);
-#define LAUNCH(TI, TO, TC)                                                                        \
-    return rllm_launch(qk_norm_rope_store_kernel<TI, TO, TC>, grid, dim3(threads), 0, stream,     \
-                       (const TI*)qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, (TO*)q_out, \
+    if (hd % 4 != 0 || hd > 256 || ((uintptr_t)qkv & 7) || ((uintptr_t)q_out & 7) || ((uintptr_t)k_cache & 7) ||
+        ((uintptr_t)v_cache & 7))
+        return (int)cudaErrorInvalidValue;
+    const dim3 grid(n, ((write_kv ? H + 2 * K : H) + 7) / 8);
+#define LAUNCH(TI, TO, TC)                                                                            \
+    return rllm_launch(qk_norm_rope_store_token_kernel<TI, TO, TC>, grid, dim3(256), 0, stream,       \
+                       (const TI*)qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, (TO*)q_out,    \
                        (TC*)k_cache, (TC*)v_cache, H, K, hd, bs, eps, write_kv)
     if (q_dtype != cache_dtype) return (int)cudaErrorInvalidValue;
-    if (in_dtype == RLLM_F32 && q_dtype == RLLM_F32) LAUNCH(float, float, float);
-    else if (in_dtype == RLLM_F32 && q_dtype == RLLM_BF16) LAUNCH(float, bf16, bf16);
-    else if (in_dtype == RLLM_BF16 && q_dtype == RLLM_BF16) LAUNCH(bf16, bf16, bf16);
-    else LAUNCH(bf16, float, float);
+    if (in_dtype == RLLM_F32 && q_dtype == RLLM_F32) { LAUNCH(float, float, float); }
+    if (in_dtype == RLLM_F32 && q_dtype == RLLM_BF16) { LAUNCH(float, bf16, bf16); }
+    if (in_dtype == RLLM_BF16 && q_dtype == RLLM_BF16) { LAUNCH(bf16, bf16, bf16); }
+    LAUNCH(bf16, float, float);
 #undef LAUNCH
 }

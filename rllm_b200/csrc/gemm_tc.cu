@@ -1,0 +1,357 @@
+// Blackwell tensor-core product for many rows: D[M,N] = A[M,K] . B[N,K]^T, bfloat16 operands,
+// float32 accumulation in tensor memory (TMEM), operands staged in shared memory by TMA.
+//
+//   * one CTA computes a 128 x BN tile (BN = 128 or 256); K is walked in blocks of 64 elements
+//     through a ring of shared-memory stages, each holding a [128 x 64] A tile and a [BN x 64]
+//     B tile in the 128-byte-swizzled K-major layout that both TMA writes and tcgen05.mma reads;
+//   * warp 0 (one elected lane) issues the TMA loads (cp.async.bulk.tensor.2d) and arms the
+//     stage's "full" mbarrier with the byte count; warp 1 (one elected lane) issues
+//     tcgen05.mma.cta_group::1.kind::f16 (M = 128, N = BN, K = 16, four per stage) and releases
+//     the stage with tcgen05.commit on its "empty" mbarrier; after the last block a commit on the
+//     "accumulator full" mbarrier hands the tile to the epilogue;
+//   * warps 2..5 are the epilogue: each owns 32 TMEM lanes (= 32 rows of the tile), reads its row
+//     with tcgen05.ld 32 columns at a time and writes it out: store (float32 or bfloat16),
+//     accumulate into a float32 C (the residual stream), or SwiGLU (the B tile holds 128 gate rows
+//     and the 128 up rows of the same index; out = silu(gate) * up).
+//   Rows beyond M and columns beyond N come in as zeros from TMA and are dropped at the store.
+//
+// Every wait on an mbarrier is bounded: when the limit is hit the thread records a code in the
+// error word, raises the CTA's abort flag, every role leaves its loop, copies still in flight are
+// waited for (bounded again), TMEM is freed and the kernel returns; the host reads the error word.
+//
+// AxiomOperator/rllm hands these products to cuBLAS (crates/rllm-cuda/src/gpu.rs:238-268) and
+// follows gate/up with a separate silu_mul kernel (crates/rllm-cuda/kernels/kernels.cu:1212-1219).
+#include "common.cuh"
+#include <cuda.h>
+#include <math.h>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1u << 22)
+
+enum { TC_EPI_STORE = 0, TC_EPI_ACCUM = 1, TC_EPI_SWIGLU = 2 };
+enum { TC_ERR_FULL = 1, TC_ERR_EMPTY = 2, TC_ERR_ACC = 3 };
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(s_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit was hit or another thread raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(s_addr(dst)), "l"(map), "r"(s_addr(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(slot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (SBO), descriptor version 1 (sm_100), layout type 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    const uint32_t lo = ((saddr & 0x3FFFFu) >> 4) | (1u << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, shape M x N.
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ---------------------------------------------------------------- the kernel
+template <typename TC> __device__ __forceinline__ void store_row32(TC* dst, const float (&v)[32], int n_valid);
+template <> __device__ __forceinline__ void store_row32<float>(float* dst, const float (&v)[32], int n_valid) {
+    if (n_valid >= 32 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < n_valid) dst[j] = v[j];
+    }
+}
+template <> __device__ __forceinline__ void store_row32<bf16>(bf16* dst, const float (&v)[32], int n_valid) {
+    if (n_valid >= 32 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint4 u;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+            u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
+            u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
+            reinterpret_cast<uint4*>(dst)[j] = u;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < n_valid) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+}
+
+template <int BN, int EPI, typename TC, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TC* __restrict__ C,
+               int ldc, int M, int N, int K, int up_row_offset, int* __restrict__ err) {
+    constexpr int A_BYTES = TC_BM * TC_BK * 2;
+    constexpr int B_BYTES = BN * TC_BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int BN_OUT = (EPI == TC_EPI_SWIGLU) ? BN / 2 : BN;        // output columns per CTA
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[STAGES];
+    __shared__ __align__(8) uint64_t acc_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN_OUT;
+    const int nkb = (K + TC_BK - 1) / TC_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_slot, BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    pdl_wait();                                    // the A operand is written by the kernel before
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer
+        int issued = 0;
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag)) {
+                if (!abort_flag) { atomicExch(err, TC_ERR_EMPTY); abort_flag = 1; }
+                break;
+            }
+            unsigned char* a_s = smem + (size_t)s * STAGE_BYTES;
+            unsigned char* b_s = a_s + A_BYTES;
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            tma_load_2d(a_s, &tmA, kb * TC_BK, m0, &full_bar[s]);
+            if (EPI == TC_EPI_SWIGLU) {
+                tma_load_2d(b_s, &tmB, kb * TC_BK, n0, &full_bar[s]);
+                tma_load_2d(b_s + B_BYTES / 2, &tmB, kb * TC_BK, up_row_offset + n0, &full_bar[s]);
+            } else {
+                tma_load_2d(b_s, &tmB, kb * TC_BK, n0, &full_bar[s]);
+            }
+            issued = kb + 1;
+        }
+        if (abort_flag) {
+            // copies already issued must land before the CTA's shared memory goes away
+            for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                for (uint32_t i = 0; i < TC_SPIN_LIMIT && !mbar_try_wait(&full_bar[s], ph); ++i) {}
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        constexpr uint32_t idesc = idesc_bf16(TC_BM, BN);
+        bool ok = true;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            if (!mbar_wait(&full_bar[s], ph, &abort_flag)) {
+                if (!abort_flag) { atomicExch(err, TC_ERR_FULL); abort_flag = 1; }
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = s_addr(smem + (size_t)s * STAGE_BYTES);
+            const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < TC_BK / 16; ++kk)       // 16 elements = 32 bytes along K: +2 in 16-byte units
+                umma_bf16(tmem_base, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+            umma_commit(&empty_bar[s]);                  // arrives when these MMAs have read the stage
+        }
+        if (ok) umma_commit(&acc_bar);
+    } else if (warp >= 2) {
+        // ---- epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int gm = m0 + row;
+        bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
+        if (!ok && !abort_flag) { atomicExch(err, TC_ERR_ACC); abort_flag = 1; }
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+            pdl_launch_dependents();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
+                uint32_t r[32];
+                float v[32];
+                tmem_ld32(taddr + c0, r);
+                if (EPI == TC_EPI_SWIGLU) {
+                    uint32_t u[32];
+                    tmem_ld32(taddr + BN / 2 + c0, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float g = __uint_as_float(r[j]);
+                        v[j] = g / (1.0f + __expf(-g)) * __uint_as_float(u[j]);
+                    }
+                } else {
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                }
+                const int gn = n0 + c0;
+                if (gm < M && gn < N) {
+                    TC* dst = C + (size_t)gm * ldc + gn;
+                    const int n_valid = min(32, N - gn);
+                    if (EPI == TC_EPI_ACCUM) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (j < n_valid) v[j] += to_f<TC>(dst[j]);
+                    }
+                    store_row32<TC>(dst, v, n_valid);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, BN);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*TmapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static TmapEncodeFn tmap_encoder() {
+    static TmapEncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (TmapEncodeFn)p;
+    }
+    return fn;
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] with row stride ld (elements): boxes of
+// box_rows x 64 elements, 128-byte swizzle, zero fill outside.  Needs a 16-byte aligned base and
+// ld a multiple of 8.
+static int make_tmap(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+    TmapEncodeFn enc = tmap_encoder();
+    if (!enc) return 30001;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 30000 + (int)r;
+}
+
+template <int BN, int EPI, typename TC, int STAGES>
+static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int ldc, int M, int N, int K, int up,
+                     int* err, cudaStream_t stream) {
+    constexpr int BN_OUT = (EPI == TC_EPI_SWIGLU) ? BN / 2 : BN;
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    auto kern = gemm_tc_kernel<BN, EPI, TC, STAGES>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid((M + TC_BM - 1) / TC_BM, (N + BN_OUT - 1) / BN_OUT);
+    return rllm_launch(kern, grid, dim3(TC_THREADS), smem, stream, ta, tb, (TC*)C, ldc, M, N, K, up, err);
+}
+
+// C[M,N] (+)= A[M,K] . B[N,K]^T on the tcgen05 tensor cores.  epilogue 0 store, 1 accumulate into a
+// float32 C, 2 SwiGLU (B holds N gate rows and, from row up_row_offset, N up rows; C[M,N] =
+// silu(gate) * up).  A, B bfloat16 row-major with 16-byte aligned bases and lda, ldb multiples of 8;
+// K a multiple of 8.  `err` is a device int that receives a code if a bounded wait ran out.
+// Returns 0, a cudaError_t, 30000 + CUresult of the tensor-map encoder, or cudaErrorInvalidValue.
+RLLM_API int rllm_gemm_tc(const void* A, const void* B, void* C, int c_dtype, int M, int N, int K, int lda, int ldb,
+                          int ldc, int epilogue, int up_row_offset, int* err, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || !err)
+        return (int)cudaErrorInvalidValue;
+    if (epilogue == TC_EPI_ACCUM && c_dtype != RLLM_F32) return (int)cudaErrorInvalidValue;
+    CUtensorMap ta, tb;
+    int st = make_tmap(&ta, A, M, K, lda, TC_BM);
+    if (st) return st;
+    const int b_rows = epilogue == TC_EPI_SWIGLU ? up_row_offset + N : N;
+    const int b_box = epilogue == TC_EPI_SWIGLU ? 128 : 256;
+    st = make_tmap(&tb, B, b_rows, K, ldb, b_box);
+    if (st) return st;
+    if (epilogue == TC_EPI_STORE) {
+        return c_dtype == RLLM_F32 ? launch_tc<256, TC_EPI_STORE, float, 4>(ta, tb, C, ldc, M, N, K, 0, err, stream)
+                                   : launch_tc<256, TC_EPI_STORE, bf16, 4>(ta, tb, C, ldc, M, N, K, 0, err, stream);
+    } else if (epilogue == TC_EPI_ACCUM) {
+        return launch_tc<256, TC_EPI_ACCUM, float, 4>(ta, tb, C, ldc, M, N, K, 0, err, stream);
+    } else if (epilogue == TC_EPI_SWIGLU) {
+        return c_dtype == RLLM_F32
+                   ? launch_tc<256, TC_EPI_SWIGLU, float, 4>(ta, tb, C, ldc, M, N, K, up_row_offset, err, stream)
+                   : launch_tc<256, TC_EPI_SWIGLU, bf16, 4>(ta, tb, C, ldc, M, N, K, up_row_offset, err, stream);
+    }
+    return (int)cudaErrorInvalidValue;
+}

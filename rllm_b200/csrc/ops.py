@@ -140,8 +140,8 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_ou
     assert qkv.shape[1] == (H + 2 * K) * hd and q_out.shape == (n, H * hd)
     assert positions.dtype == torch.int32 and slots.dtype == torch.int32
     assert positions.numel() == n and slots.numel() == n
-    if hd % 2:
-        raise KernelError(f"head size {hd} must be even for the rotary embedding")
+    if hd % 4 or hd > 256:
+        raise KernelError(f"head size {hd} is not supported: the q/k norm + rotary kernel takes multiples of 4 up to 256")
     for w in (q_norm_w, k_norm_w):
         assert w is None or (w.dtype == torch.float32 and w.numel() == hd)
     assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == hd // 2)
@@ -266,6 +266,55 @@ def skinny_gemm(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
     return out
 
 
+_error_words: dict = {}
+
+
+def error_word(device) -> torch.Tensor:
+    """The device int into which kernels with bounded waits write a code when a wait runs out."""
+    key = torch.device(device).index or 0
+    if key not in _error_words:
+        _error_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_words[key]
+
+
+def check_device_errors(device="cuda:0") -> None:
+    """Raises if a kernel reported a wait that ran out (reads one int from the device)."""
+    code = int(error_word(device).item())
+    if code:
+        error_word(device).zero_()
+        raise KernelError(f"a kernel's bounded wait ran out (code {code}: 1 operand tiles never arrived, "
+                          f"2 a stage was never released, 3 the accumulator never completed)")
+
+
+def _tc_ok(a, w) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
+    """out (+)= a . w^T on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory).
+    epilogue as for skinny_gemm.  See gemm_tc.cu."""
+    _need_cuda(a, w, out)
+    if not _tc_ok(a, w):
+        raise KernelError("gemm_tc needs bfloat16 operands, k a multiple of 8 and 16-byte aligned rows")
+    m, k = a.shape
+    n = out.shape[1]
+    assert out.shape[0] == m and out.stride(1) == 1
+    if epilogue == EPI_SWIGLU:
+        assert w.shape[0] >= up_row_offset + n
+    else:
+        assert w.shape[0] == n
+    st = build.load("tc").rllm_gemm_tc(
+        _ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
+        c_int(w.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
+        _ptr(error_word(a.device)), _stream())
+    if st >= 30000:
+        raise KernelError(f"gemm_tc: tensor map encoding failed (CUresult {st - 30000}) for m={m} n={n} k={k}")
+    _check(st, "gemm_tc")
+    return out
+
+
 def linear(a, w, out=None, out_dtype=None, accumulate=False):
     """out (+)= a . w^T, choosing the kernel by element type and shape.
 
@@ -297,12 +346,15 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False):
 
 def gate_up_swiglu(h, w_gate_up, out):
     """out[m, F] = silu(h . Wg^T) * (h . Wu^T) with w_gate_up = [Wg; Wu] stacked ([2F, k]).
-    At most 64 rows in bfloat16: one kernel; otherwise a product followed by the activation."""
+    bfloat16: one kernel (the weight-streaming kernel up to 64 rows, the tcgen05 kernel above);
+    float32 and odd shapes: a product followed by the activation kernel."""
     m = h.shape[0]
     F = out.shape[1]
     if _skinny_ok(h, w_gate_up):
         return skinny_gemm(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
-    gu = linear(h, w_gate_up, out_dtype=torch.float32)     # same rounding points as the fused kernel
+    if _tc_ok(h, w_gate_up) and out.data_ptr() % 16 == 0:
+        return gemm_tc(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)     # tcgen05, activation in the epilogue
+    gu = linear(h, w_gate_up, out_dtype=torch.float32)     # same rounding points as the fused kernels
     return silu_mul(gu, out)
 
 

@@ -34,8 +34,8 @@ class Attention(Mixer):
         self.scale = float(p["scale"])
         if self.H % self.K:
             raise PartError(f"attention: {self.H} heads are not a multiple of {self.K} key/value heads")
-        if self.hd % 16:
-            raise PartError(f"attention: head_dim {self.hd} must be a multiple of 16")
+        if self.hd % 16 or self.hd > 256:
+            raise PartError(f"attention: head_dim {self.hd} must be a multiple of 16 and at most 256")
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
 
     def cache_need(self):

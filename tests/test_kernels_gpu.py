@@ -297,3 +297,43 @@ def test_paged_flash_attention(hd, H, K, bs, window, lens, q_lens):
     ops().paged_attention_generic(c["q"], c["kc"], c["vc"], plain, c["pos"], c["sid"], c["table"], H, K, hd,
                                   bs, 1.0 / math.sqrt(hd), window)
     assert rel_err(out.float().cpu(), plain.float().cpu()) < 1.5e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (65, 40, 8), (200, 300, 264), (1000, 1111, 1096), (2048, 512, 4096)])
+def test_gemm_tc(m, n, k):
+    """The tcgen05 / TMA product: tiles that are cut by every edge (m, n and k tails)."""
+    o = ops()
+    a, w = rnd(m, k, seed=24, dtype=torch.bfloat16), rnd(n, k, seed=25, scale=0.1, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    out = torch.full((m, n), float("nan"), device=DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), out)
+    torch.cuda.synchronize()
+    o.check_device_errors()
+    assert rel_err(out.cpu(), ref) < 1e-5
+    out16 = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), out16)
+    assert rel_err(out16.float().cpu(), ref) < 5e-3
+    base = rnd(m, n, seed=26)
+    acc = base.to(DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), acc, epilogue=o.EPI_ACCUM)
+    assert rel_err(acc.cpu(), ref + base) < 1e-5
+    plain = torch.empty(m, n, device=DEV)
+    o.gemm_plain(a.to(DEV), w.to(DEV), plain)
+    assert rel_err(out.cpu(), plain.cpu()) < 1e-5
+    o.check_device_errors()
+
+
+@pytest.mark.parametrize("m,F,k", [(65, 224, 96), (300, 1000, 264), (1024, 3072, 1024)])
+def test_gemm_tc_swiglu(m, F, k):
+    o = ops()
+    a = rnd(m, k, seed=27, dtype=torch.bfloat16)
+    w = rnd(2 * F, k, seed=28, scale=0.2, dtype=torch.bfloat16)
+    g, u = a.float() @ w[:F].float().t(), a.float() @ w[F:].float().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    out = torch.full((m, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.gate_up_swiglu(a.to(DEV), w.to(DEV), out)
+    assert rel_err(out.float().cpu(), ref) < 5e-3
+    out32 = torch.full((m, F), float("nan"), device=DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), out32, epilogue=o.EPI_SWIGLU, up_row_offset=F)
+    assert rel_err(out32.cpu(), ref) < 1e-5
+    o.check_device_errors()
