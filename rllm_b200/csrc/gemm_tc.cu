@@ -355,3 +355,250 @@ RLLM_API int rllm_gemm_tc(const void* A, const void* B, void* C, int c_dtype, in
     }
     return (int)cudaErrorInvalidValue;
 }
+
+// =====================================================================================================
+// Few rows (decode): the same machinery with the operands swapped.  The weight matrix W[n,k] is the
+// M side (128 weight rows per CTA, streamed once from HBM through a deep TMA ring), the m <= 64
+// batch rows X[m,k] are the N side, so the accumulator D[weight row, batch row] is C transposed.
+// The K range may be split over grid.y CTAs to fill the machine when n/128 is small; the CTAs of a
+// tile write float32 partials, and the one that finishes last (a counter per tile) adds them in
+// split order -- the order is fixed, whoever comes last -- applies the epilogue and resets the
+// counter.  SwiGLU: a CTA takes 64 gate rows and the 64 up rows of the same index.
+// =====================================================================================================
+template <int BN, int STAGES, int EPI, typename TC>
+__global__ void __launch_bounds__(TC_THREADS, 2)
+gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                    TC* __restrict__ C, int ldc, int m, int n, int K, int up_row_offset,
+                    float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ err) {
+    constexpr int A_BYTES = TC_BM * TC_BK * 2;          // 128 weight rows x 64 k
+    constexpr int B_BYTES = BN * TC_BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int ROWS_OUT = (EPI == TC_EPI_SWIGLU) ? TC_BM / 2 : TC_BM;     // output columns of C per CTA
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[STAGES];
+    __shared__ __align__(8) uint64_t acc_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+    __shared__ int is_last;
+    __shared__ float up_vals[(EPI == TC_EPI_SWIGLU) ? 64 * BN : 1];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
+    const int n0 = tile * ROWS_OUT;
+    const int nkb = (K + TC_BK - 1) / TC_BK;
+    const int kb_per = (nkb + n_splits - 1) / n_splits;
+    const int kb0 = split * kb_per, kb1 = min(nkb, kb0 + kb_per);
+    const int my_kb = max(0, kb1 - kb0);
+
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX) : "memory");
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_bar, 1);
+        abort_flag = 0;
+        is_last = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_slot, BN < 32 ? 32 : BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer.  The weights do not depend on the kernel before: their loads start at once;
+        // the activations are loaded only after the wait.
+        int issued = 0;
+        bool waited = false;
+        for (int i = 0; i < my_kb; ++i) {
+            const int kb = kb0 + i, s = i % STAGES;
+            const uint32_t ph = (i / STAGES) & 1;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag)) {
+                if (!abort_flag) { atomicExch(err, TC_ERR_EMPTY); abort_flag = 1; }
+                break;
+            }
+            unsigned char* a_s = smem + (size_t)s * STAGE_BYTES;
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            if (EPI == TC_EPI_SWIGLU) {
+                tma_load_2d(a_s, &tmW, kb * TC_BK, n0, &full_bar[s]);
+                tma_load_2d(a_s + A_BYTES / 2, &tmW, kb * TC_BK, up_row_offset + n0, &full_bar[s]);
+            } else {
+                tma_load_2d(a_s, &tmW, kb * TC_BK, n0, &full_bar[s]);
+            }
+            if (!waited) { pdl_wait(); waited = true; }
+            tma_load_2d(a_s + A_BYTES, &tmX, kb * TC_BK, 0, &full_bar[s]);
+            issued = i + 1;
+        }
+        if (abort_flag) {
+            for (int i = max(0, issued - STAGES); i < issued; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                for (uint32_t j = 0; j < TC_SPIN_LIMIT && !mbar_try_wait(&full_bar[s], ph); ++j) {}
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        constexpr uint32_t idesc = idesc_bf16(TC_BM, BN);
+        bool ok = true;
+        for (int i = 0; i < my_kb && ok; ++i) {
+            const int s = i % STAGES;
+            const uint32_t ph = (i / STAGES) & 1;
+            if (!mbar_wait(&full_bar[s], ph, &abort_flag)) {
+                if (!abort_flag) { atomicExch(err, TC_ERR_FULL); abort_flag = 1; }
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = s_addr(smem + (size_t)s * STAGE_BYTES);
+            const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < TC_BK / 16; ++kk)
+                umma_bf16(tmem_base, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (i | kk) != 0);
+            umma_commit(&empty_bar[s]);
+        }
+        if (ok) umma_commit(&acc_bar);
+    } else if (warp >= 2) {
+        // ---- epilogue: thread = weight row of the tile, registers = batch columns
+        pdl_wait();                                     // C (and the counters) may be touched from here on
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;            // 0..127 within the tile
+        bool ok = true;
+        if (my_kb > 0) {
+            ok = mbar_wait(&acc_bar, 0, &abort_flag);
+            if (!ok && !abort_flag) { atomicExch(err, TC_ERR_ACC); abort_flag = 1; }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        float v[BN];
+        if (ok && my_kb > 0) {
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[c0 + j] = __uint_as_float(r[j]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < BN; ++j) v[j] = 0.f;
+        }
+        pdl_launch_dependents();
+        // global weight row of this thread (SwiGLU: rows 0..63 gate j, rows 64..127 up j)
+        const int out_col = (EPI == TC_EPI_SWIGLU) ? n0 + (row & 63) : n0 + row;
+        const bool col_ok = out_col < n;
+        if (ok && n_splits > 1) {
+            // partial sums P[tile][split][b][row], then the last CTA of the tile reduces
+            float* P = partials + (((size_t)tile * n_splits + split) * BN) * TC_BM;
+#pragma unroll
+            for (int b = 0; b < BN; ++b) if (b < m) P[(size_t)b * TC_BM + row] = v[b];
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
+            if (warp == 2 && lane == 0) {
+                const int prev = atomicAdd(&counters[tile], 1);
+                is_last = (prev == n_splits - 1);
+                if (is_last) counters[tile] = 0;                     // ready for the next launch
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (is_last) {
+                __threadfence();
+#pragma unroll
+                for (int b = 0; b < BN; ++b) v[b] = 0.f;
+                for (int z = 0; z < n_splits; ++z) {
+                    const float* Pz = partials + (((size_t)tile * n_splits + z) * BN) * TC_BM;
+#pragma unroll
+                    for (int b = 0; b < BN; ++b) if (b < m) v[b] += __ldcg(Pz + (size_t)b * TC_BM + row);
+                }
+            } else {
+                ok = false;                                          // another CTA writes the result
+            }
+        }
+        if (EPI == TC_EPI_SWIGLU) {
+            if (ok && row >= 64) {
+#pragma unroll
+                for (int b = 0; b < BN; ++b) up_vals[(row - 64) * BN + b] = v[b];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ok && row < 64 && col_ok) {
+#pragma unroll
+                for (int b = 0; b < BN; ++b)
+                    if (b < m) {
+                        const float g = v[b];
+                        C[(size_t)b * ldc + out_col] = from_f<TC>(g / (1.0f + expf(-g)) * up_vals[row * BN + b]);
+                    }
+            }
+        } else if (ok && col_ok) {
+#pragma unroll
+            for (int b = 0; b < BN; ++b)
+                if (b < m) {
+                    TC* c = C + (size_t)b * ldc + out_col;
+                    if (EPI == TC_EPI_ACCUM) *c = from_f<TC>(to_f<TC>(*c) + v[b]);
+                    else *c = from_f<TC>(v[b]);
+                }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
+}
+
+template <int BN, int EPI, typename TC>
+static int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, void* C, int ldc, int m, int n, int K, int up,
+                       float* partials, int* counters, int n_splits, int* err, cudaStream_t stream) {
+    constexpr int STAGES = 4;             // 4 x 24 KB: two CTAs share an SM, one streams while the other starts or ends
+    constexpr int ROWS_OUT = (EPI == TC_EPI_SWIGLU) ? TC_BM / 2 : TC_BM;
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    auto kern = gemm_tc_swap_kernel<BN, STAGES, EPI, TC>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    dim3 grid((n + ROWS_OUT - 1) / ROWS_OUT, n_splits);
+    return rllm_launch(kern, grid, dim3(TC_THREADS), smem, stream, tw, tx, (TC*)C, ldc, m, n, K, up, partials,
+                       counters, err);
+}
+
+// C[m,n] (+)= X[m,k] . W[n,k]^T for m <= 64 with W as the streamed operand (see above).  `partials`
+// must hold tiles * n_splits * BN * 128 floats (BN = 32 for m <= 32, else 64) and `counters` one
+// zero-initialised int per tile when n_splits > 1; both may be null for n_splits == 1.
+RLLM_API int rllm_gemm_tc_swap(const void* W, const void* X, void* C, int c_dtype, int m, int n, int K, int ldw,
+                               int ldx, int ldc, int epilogue, int up_row_offset, int n_splits, float* partials,
+                               int* counters, int* err, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (m > 64 || K <= 0 || (K & 7) || (ldw & 7) || (ldx & 7) || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) || !err ||
+        n_splits < 1 || (n_splits > 1 && (!partials || !counters)))
+        return (int)cudaErrorInvalidValue;
+    if (epilogue == TC_EPI_ACCUM && c_dtype != RLLM_F32) return (int)cudaErrorInvalidValue;
+    CUtensorMap tw, tx;
+    const int w_rows = epilogue == TC_EPI_SWIGLU ? up_row_offset + n : n;
+    int st = make_tmap(&tw, W, w_rows, K, ldw, epilogue == TC_EPI_SWIGLU ? 64 : 128);
+    if (st) return st;
+    const int bn = m <= 32 ? 32 : 64;
+    st = make_tmap(&tx, X, m, K, ldx, bn);
+    if (st) return st;
+#define SWAP(BN_, EPI_, TC_) \
+    return launch_swap<BN_, EPI_, TC_>(tw, tx, C, ldc, m, n, K, up_row_offset, partials, counters, n_splits, err, stream)
+    if (epilogue == TC_EPI_STORE) {
+        if (c_dtype == RLLM_F32) { if (bn == 32) { SWAP(32, TC_EPI_STORE, float); } SWAP(64, TC_EPI_STORE, float); }
+        if (bn == 32) { SWAP(32, TC_EPI_STORE, bf16); }
+        SWAP(64, TC_EPI_STORE, bf16);
+    } else if (epilogue == TC_EPI_ACCUM) {
+        if (bn == 32) { SWAP(32, TC_EPI_ACCUM, float); }
+        SWAP(64, TC_EPI_ACCUM, float);
+    } else if (epilogue == TC_EPI_SWIGLU) {
+        if (c_dtype == RLLM_F32) { if (bn == 32) { SWAP(32, TC_EPI_SWIGLU, float); } SWAP(64, TC_EPI_SWIGLU, float); }
+        if (bn == 32) { SWAP(32, TC_EPI_SWIGLU, bf16); }
+        SWAP(64, TC_EPI_SWIGLU, bf16);
+    }
+#undef SWAP
+    return (int)cudaErrorInvalidValue;
+}

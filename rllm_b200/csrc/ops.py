@@ -315,6 +315,63 @@ def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
     return out
 
 
+_split_counters: dict = {}
+
+
+def _counters(device, n: int) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    t = _split_counters.get(key)
+    if t is None or t.numel() < n:
+        t = _split_counters[key] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+    return t
+
+
+def tc_swap_splits(n_tiles: int, k: int) -> int:
+    """Number of K splits for the swapped tcgen05 product: enough CTAs to fill the 148 SMs, at
+    least 8 blocks of 64 along K per CTA."""
+    nkb = -(-k // 64)
+    return max(1, min(296 // n_tiles, nkb // 8))
+
+
+def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None):
+    """out (+)= a . w^T for at most 64 rows of a on the tcgen05 tensor cores with the weights as
+    the streamed M operand (TMA ring of 8 stages), split over K where the weight matrix has few rows."""
+    _need_cuda(a, w, out)
+    if not _tc_ok(a, w) or a.shape[0] > 64:
+        raise KernelError("skinny_gemm_tc needs bfloat16 operands, at most 64 rows, k a multiple of 8 and "
+                          "16-byte aligned rows")
+    m, k = a.shape
+    n = out.shape[1]
+    assert out.shape[0] == m and out.stride(1) == 1
+    rows_out = 64 if epilogue == EPI_SWIGLU else 128
+    n_tiles = -(-n // rows_out)
+    if n_splits is None:
+        n_splits = tc_swap_splits(n_tiles, k)
+    partials = counters = None
+    if n_splits > 1:
+        bn = 32 if m <= 32 else 64
+        partials = torch.empty(n_tiles * n_splits * bn * 128, dtype=torch.float32, device=a.device)
+        counters = _counters(a.device, n_tiles)
+    st = build.load("tc").rllm_gemm_tc_swap(
+        _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
+        c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), c_int(n_splits),
+        _ptr(partials), _ptr(counters), _ptr(error_word(a.device)), _stream())
+    if st >= 30000:
+        raise KernelError(f"skinny_gemm_tc: tensor map encoding failed (CUresult {st - 30000})")
+    _check(st, "skinny_gemm_tc")
+    return out
+
+
+def _prefer_tc_swap(m: int, n: int) -> bool:
+    """Measured crossover between the two few-row kernels (B200, k = 4096): the tcgen05 kernel wins
+    once the batch columns no longer fit one MMA n-tile per warp cheaply (m > 16) and the weight
+    matrix has enough 128-row tiles to fill the SMs without splitting K much; for 9..16 rows only
+    very tall matrices (the LM head) gain."""
+    if m > 16:
+        return n >= 5120
+    return m > 8 and n >= 65536
+
+
 def linear(a, w, out=None, out_dtype=None, accumulate=False):
     """out (+)= a . w^T, choosing the kernel by element type and shape.
 
@@ -335,6 +392,8 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False):
             raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
         return gemm_plain(a, w, out, accumulate)
     if _skinny_ok(a, w):
+        if _prefer_tc_swap(m, n) and out.data_ptr() % 16 == 0:
+            return skinny_gemm_tc(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
         return skinny_gemm(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
     aligned = (a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
                and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
@@ -351,6 +410,8 @@ def gate_up_swiglu(h, w_gate_up, out):
     m = h.shape[0]
     F = out.shape[1]
     if _skinny_ok(h, w_gate_up):
+        if _prefer_tc_swap(m, 2 * F):
+            return skinny_gemm_tc(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
         return skinny_gemm(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
     if _tc_ok(h, w_gate_up) and out.data_ptr() % 16 == 0:
         return gemm_tc(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)     # tcgen05, activation in the epilogue

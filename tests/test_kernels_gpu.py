@@ -337,3 +337,46 @@ def test_gemm_tc_swiglu(m, F, k):
     o.gemm_tc(a.to(DEV), w.to(DEV), out32, epilogue=o.EPI_SWIGLU, up_row_offset=F)
     assert rel_err(out32.cpu(), ref) < 1e-5
     o.check_device_errors()
+
+
+@pytest.mark.parametrize("m", [1, 8, 17, 32, 33, 64])
+@pytest.mark.parametrize("n,k,splits", [(96, 512, None), (37, 264, 1), (4096, 4096, None), (1000, 1096, 3), (300, 8, 1),
+                                        (130, 2048, 4)])
+def test_skinny_gemm_tc(m, n, k, splits):
+    """The swapped tcgen05 product: weights as the streamed operand, with and without split K."""
+    o = ops()
+    a, w = rnd(m, k, seed=29, dtype=torch.bfloat16), rnd(n, k, seed=30, scale=0.1, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    for _ in range(2):                               # twice: the tile counters must have been reset
+        out = torch.full((m, n), float("nan"), device=DEV)
+        o.skinny_gemm_tc(a.to(DEV), w.to(DEV), out, n_splits=splits)
+        assert rel_err(out.cpu(), ref) < 1e-5
+    out16 = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.skinny_gemm_tc(a.to(DEV), w.to(DEV), out16, n_splits=splits)
+    assert rel_err(out16.float().cpu(), ref) < 5e-3
+    base = rnd(m, n, seed=31)
+    acc = base.to(DEV)
+    o.skinny_gemm_tc(a.to(DEV), w.to(DEV), acc, epilogue=o.EPI_ACCUM, n_splits=splits)
+    assert rel_err(acc.cpu(), ref + base) < 1e-5
+    # a request's column does not depend on its batch-mates
+    alone = torch.empty(1, n, device=DEV)
+    o.skinny_gemm_tc(a[m - 1:m].to(DEV), w.to(DEV), alone, n_splits=splits)
+    assert torch.equal(alone[0], out[m - 1])
+    o.check_device_errors()
+
+
+@pytest.mark.parametrize("m", [2, 20, 64])
+@pytest.mark.parametrize("F,k,splits", [(224, 96, 1), (1000, 264, 2), (12288, 4096, None), (37, 64, 1)])
+def test_skinny_gemm_tc_swiglu(m, F, k, splits):
+    o = ops()
+    a = rnd(m, k, seed=32, dtype=torch.bfloat16)
+    w = rnd(2 * F, k, seed=33, scale=0.2, dtype=torch.bfloat16)
+    g, u = a.float() @ w[:F].float().t(), a.float() @ w[F:].float().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    out = torch.full((m, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.skinny_gemm_tc(a.to(DEV), w.to(DEV), out, epilogue=o.EPI_SWIGLU, up_row_offset=F, n_splits=splits)
+    assert rel_err(out.float().cpu(), ref) < 5e-3
+    out32 = torch.full((m, F), float("nan"), device=DEV)
+    o.skinny_gemm_tc(a.to(DEV), w.to(DEV), out32, epilogue=o.EPI_SWIGLU, up_row_offset=F, n_splits=splits)
+    assert rel_err(out32.cpu(), ref) < 1e-5
+    o.check_device_errors()
