@@ -1,0 +1,379 @@
+// Causal flash attention over the paged cache for prompt portions on the Blackwell tensor cores:
+// S = Q K^T and O += P V are tcgen05.mma with the accumulators S (double-buffered) and O in tensor
+// memory; Q, K and V tiles arrive by TMA (128-byte swizzle), P goes from the softmax threads to
+// shared memory as the A operand of the second product.
+//
+//   tile        128 rows = (128 / g) tokens x g query heads of one key/value head (g = H / K),
+//               key tiles of 128 keys (whole pages), head size 128
+//   warp 0      TMA producer: Q once (one 3-D box per half of the head), then a ring of two K and
+//               two V stages, one 2-D box per page and half
+//   warp 1      MMA issuer: QK^T of tile j+1 is issued before PV of tile j, so the tensor cores
+//               work on the next scores while the softmax threads are busy with the current ones
+//   warps 2..5  softmax: one thread per row (= one TMEM lane): tcgen05.ld of the 128 scores, mask,
+//               maximum and sum without any shuffle, exp2 with the scale folded in, P as bfloat16
+//               into the swizzled shared-memory tile.  The reference maximum of a row is only
+//               raised when the new maximum exceeds it by more than 8 (factor 256): then the
+//               thread rescales its own O row in TMEM (tcgen05.ld / st); otherwise O is left alone.
+//   end         O / l -> bfloat16 -> out[token, head, :]
+// Every mbarrier wait is bounded (see tcgen05.cuh); a wait that runs out records a code in the
+// error word, raises the abort flag, and every role leaves.
+//
+// Limits: bfloat16, head size 128, page size a power of two from 8 to 128, g a divisor of 128.
+// Other shapes take the mma.sync kernel (attention_flash.cu).  Counterpart in AxiomOperator/rllm:
+// attn_fa (crates/rllm-cuda/kernels/kernels.cu:3022-3309), an mma.sync kernel.
+#include "tcgen05.cuh"
+#include <math.h>
+
+#define AT_HD 128
+#define AT_BM 128
+#define AT_BN 128
+#define AT_THREADS 192
+#define AT_HALF_BYTES (128 * 128)          // 128 rows x 64 elements x 2 bytes
+#define AT_TILE_BYTES (2 * AT_HALF_BYTES)
+#define AT_TABLE_SMEM 4096                 // block-table entries kept in shared memory (more are read from global)
+
+enum { AT_ERR_Q = 11, AT_ERR_KV = 12, AT_ERR_S = 13, AT_ERR_P = 14, AT_ERR_STAGE = 15 };
+
+struct AttnTcParams {
+    bf16* out;                  // [n, H, 128]
+    const int* positions;       // [n]
+    const int* cu_q;            // [R+1]
+    const int* block_table;     // [R, table_stride]
+    const int* tile_req;        // [tiles]
+    const int* tile_tok0;       // [tiles]
+    int table_stride, H, K, bs, window, TT, g, n_tiles;
+    float scale_log2;
+    int* err;
+};
+
+// K-major, 128-byte swizzle (Q, K, P): see smem_desc_sw128.  MN-major (V: dims contiguous):
+// leading byte offset = distance between the two 64-dim halves, stride byte offset = 8 keys.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t lbo_bytes) {
+    const uint32_t lo = ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = smem;                               // 32 KB
+    unsigned char* sP = smem + AT_TILE_BYTES;               // 32 KB
+    unsigned char* sK = smem + 2 * AT_TILE_BYTES;           // 2 x 32 KB
+    unsigned char* sV = smem + 4 * AT_TILE_BYTES;           // 2 x 32 KB
+    __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2],
+        p_full, p_empty;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+    __shared__ int s_table[AT_TABLE_SMEM];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = p.n_tiles - 1 - (int)blockIdx.x;       // long tiles first
+    const int kvh = blockIdx.y;
+    const int req = p.tile_req[tile], tok0 = p.tile_tok0[tile];
+    const int nt = min(p.TT, p.cu_q[req + 1] - tok0);
+    const int head0 = kvh * p.g;
+    const int pos_first = p.positions[tok0], pos_last = p.positions[tok0 + nt - 1];
+    int kb = p.window > 0 ? max(0, pos_first + 1 - p.window) : 0;
+    kb = kb / AT_BN * AT_BN;
+    const int n_kt = (pos_last + 1 - kb + AT_BN - 1) / AT_BN;      // >= 1
+
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmK) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmV) : "memory");
+        mbar_init(&q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128);
+        }
+        mbar_init(&p_full, 128);
+        mbar_init(&p_empty, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    const uint32_t tS0 = tmem_base, tO = tmem_base + 256;   // S buffers at columns 0 and 128, O at 256
+    pdl_wait();                                             // queries and this step's keys come from earlier kernels
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (the whole warp)
+        // The request's block table goes to shared memory once (the lookups would otherwise be a
+        // chain of dependent global loads in front of every tile); lane pg then issues the two boxes
+        // (one per 64-dim half) of page pg of a tile.
+        const int* table = p.block_table + (size_t)req * p.table_stride;
+        const int pages = AT_BN / p.bs;                      // pages per key tile (<= 16)
+        const int last_blk = pos_last / p.bs;                // last block that exists for this request
+        const int first_blk = kb / p.bs;
+        const int n_blk = last_blk - first_blk + 1;
+        for (int i = lane; i < min(n_blk, AT_TABLE_SMEM); i += 32) s_table[i] = table[first_blk + i];
+        __syncwarp();
+        if (lane == 0) {
+            mbar_expect_tx(&q_full, AT_TILE_BYTES);
+            tma_load_3d(sQ, &tmQ, 0, head0, tok0, &q_full);
+            tma_load_3d(sQ + AT_HALF_BYTES, &tmQ, 64, head0, tok0, &q_full);
+        }
+        int issued = 0;
+        bool ok = true;
+        for (int j = 0; j < n_kt && ok; ++j) {
+            const int s = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            const int rel = min(j * pages + lane, n_blk - 1);          // pages past the context: the last valid page, masked
+            int y = 0;
+            if (lane < pages) {
+                const int page = rel < AT_TABLE_SMEM ? s_table[rel] : table[first_blk + rel];
+                y = (page * p.K + kvh) * p.bs;
+            }
+            ok = mbar_wait(&k_empty[s], ph ^ 1, &abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(&k_full[s], AT_TILE_BYTES);
+            __syncwarp();
+            if (lane < pages) {
+                unsigned char* dst = sK + s * AT_TILE_BYTES + lane * p.bs * 128;
+                tma_load_2d(dst, &tmK, 0, y, &k_full[s]);
+                tma_load_2d(dst + AT_HALF_BYTES, &tmK, 64, y, &k_full[s]);
+            }
+            issued = 2 * j + 1;
+            ok = mbar_wait(&v_empty[s], ph ^ 1, &abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(&v_full[s], AT_TILE_BYTES);
+            __syncwarp();
+            if (lane < pages) {
+                unsigned char* dst = sV + s * AT_TILE_BYTES + lane * p.bs * 128;
+                tma_load_2d(dst, &tmV, 0, y, &v_full[s]);
+                tma_load_2d(dst + AT_HALF_BYTES, &tmV, 64, y, &v_full[s]);
+            }
+            issued = 2 * j + 2;
+        }
+        if (!ok && lane == 0 && !abort_flag) { atomicExch(p.err, AT_ERR_STAGE); abort_flag = 1; }
+        if (abort_flag && lane == 0) {
+            // copies that were issued must land before the CTA's shared memory goes away
+            volatile int no_abort = 0;
+            mbar_wait(&q_full, 0, &no_abort);
+            for (int i = max(0, issued - 4); i < issued; ++i) {
+                const int j = i >> 1, s = j & 1;
+                const uint32_t ph = (j >> 1) & 1;
+                mbar_wait((i & 1) ? &v_full[s] : &k_full[s], ph, &no_abort);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_s = idesc_bf16(AT_BM, AT_BN);                 // Q, K both K-major
+        constexpr uint32_t idesc_o = idesc_bf16(AT_BM, AT_HD) | (1u << 16);    // V is MN-major
+        bool ok = mbar_wait(&q_full, 0, &abort_flag);
+        if (!ok && !abort_flag) { atomicExch(p.err, AT_ERR_Q); abort_flag = 1; }
+        const uint32_t q_addr = s_addr(sQ), p_addr = s_addr(sP);
+        auto issue_qk = [&](int j) -> bool {
+            const int s = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            if (!mbar_wait(&k_full[s], ph, &abort_flag)) return false;
+            if (!mbar_wait(&s_empty[s], ph ^ 1, &abort_flag)) return false;   // softmax of tile j-2 has read S[s]
+            tc_fence_after();
+            const uint32_t k_addr = s_addr(sK + s * AT_TILE_BYTES);
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma_bf16(tS0 + s * AT_BN, smem_desc_sw128(q_addr + h * AT_HALF_BYTES) + 2 * kk,
+                              smem_desc_sw128(k_addr + h * AT_HALF_BYTES) + 2 * kk, idesc_s, (h | kk) != 0);
+            umma_commit(&k_empty[s]);
+            umma_commit(&s_full[s]);
+            return true;
+        };
+        auto issue_pv = [&](int j) -> bool {
+            const int s = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            if (!mbar_wait(&p_full, j & 1, &abort_flag)) return false;
+            if (!mbar_wait(&v_full[s], ph, &abort_flag)) return false;
+            tc_fence_after();
+            const uint32_t v_addr = s_addr(sV + s * AT_TILE_BYTES);
+#pragma unroll
+            for (int k8 = 0; k8 < 8; ++k8)        // 16 keys a step: P advances 32 bytes inside its half, V 16 rows
+                umma_bf16(tO, smem_desc_sw128(p_addr + (k8 >> 2) * AT_HALF_BYTES) + 2 * (k8 & 3),
+                          smem_desc_sw128_mn(v_addr + k8 * 16 * 128, AT_HALF_BYTES), idesc_o, (j | k8) != 0);
+            umma_commit(&v_empty[s]);
+            umma_commit(&p_empty);
+            return true;
+        };
+        if (ok) ok = issue_qk(0);
+        for (int j = 0; j < n_kt && ok; ++j) {
+            if (j + 1 < n_kt) ok = issue_qk(j + 1);
+            if (ok) ok = issue_pv(j);
+        }
+        if (!ok && !abort_flag) { atomicExch(p.err, AT_ERR_KV); abort_flag = 1; }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------ softmax and epilogue: one row per thread
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int tl = r / p.g, hl = r % p.g;
+        const bool valid = tl < nt;
+        const int pos_r = valid ? p.positions[tok0 + tl] : -1;
+        const int first_r = p.window > 0 ? max(0, pos_r + 1 - p.window) : 0;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kt && ok; ++j) {
+            const int b = j & 1;
+            const int kt = kb + j * AT_BN;
+            if (!mbar_wait(&s_full[b], (j >> 1) & 1, &abort_flag)) {
+                if (!abort_flag) { atomicExch(p.err, AT_ERR_S); abort_flag = 1; }
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            float sv[AT_BN];
+#pragma unroll
+            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
+                uint32_t rr[32];
+                tmem_ld32(tS0 + b * AT_BN + lane_base + c0, rr);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sv[c0 + i] = __uint_as_float(rr[i]);
+            }
+            tc_fence_before();
+            mbar_arrive(&s_empty[b]);
+            const bool need_mask = (kt + AT_BN > pos_r + 1) || (kt < first_r);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < AT_BN; ++c) {
+                float v = sv[c] * p.scale_log2;
+                if (need_mask && (kt + c > pos_r || kt + c < first_r)) v = -INFINITY;
+                sv[c] = v;
+                mx = fmaxf(mx, v);
+            }
+            float alpha = 1.f;
+            bool rescale = false;
+            if (m_ref == -INFINITY) m_ref = mx;                          // nothing accumulated yet for this row
+            else if (mx > m_ref + 8.f) { alpha = exp2f(m_ref - mx); m_ref = mx; rescale = true; }
+            // P of the tile before must have been read (and O updated) before P and O are touched
+            if (j > 0 && !mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
+                if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
+                ok = false;
+                break;
+            }
+            // tcgen05.ld / st are warp-wide: the whole warp goes through when any of its rows rescales
+            if (__any_sync(0xffffffffu, rescale)) {
+                tc_fence_after();
+                l *= alpha;
+#pragma unroll
+                for (int c0 = 0; c0 < AT_HD; c0 += 32) {
+                    uint32_t rr[32];
+                    tmem_ld32(tO + lane_base + c0, rr);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
+                    tmem_st32(tO + lane_base + c0, rr);
+                }
+                tmem_st_wait();
+            }
+            const float mref = m_ref == -INFINITY ? 0.f : m_ref;
+            float sum = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < 16; ++ch) {                             // 16 chunks of 8 keys = 16 bytes
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { e[i] = exp2f(sv[ch * 8 + i] - mref); sum += e[i]; }
+                uint4 u;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(e[0], e[1]), p1 = __floats2bfloat162_rn(e[2], e[3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(e[4], e[5]), p3 = __floats2bfloat162_rn(e[6], e[7]);
+                u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
+                u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
+                unsigned char* dst = sP + (ch >> 3) * AT_HALF_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = u;
+            }
+            l += sum;
+            fence_async_smem();                                            // P visible to the tensor core's reads
+            tc_fence_before();
+            mbar_arrive(&p_full);
+        }
+        if (ok) {
+            if (!mbar_wait(&p_empty, (n_kt - 1) & 1, &abort_flag)) {
+                if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
+                ok = false;
+            }
+        }
+        pdl_launch_dependents();
+        if (__all_sync(0xffffffffu, ok)) {                         // warp-uniform: the TMEM loads are warp-wide
+            tc_fence_after();
+            const bool store = valid && l > 0.f;
+            const float inv = store ? 1.0f / l : 0.f;
+            bf16* dst = p.out + ((size_t)(tok0 + (valid ? tl : 0)) * p.H + head0 + hl) * AT_HD;
+#pragma unroll
+            for (int c0 = 0; c0 < AT_HD; c0 += 32) {
+                uint32_t rr[32];
+                tmem_ld32(tO + lane_base + c0, rr);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 u;
+                    __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(rr[8 * q]) * inv, __uint_as_float(rr[8 * q + 1]) * inv);
+                    __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(rr[8 * q + 2]) * inv, __uint_as_float(rr[8 * q + 3]) * inv);
+                    __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(rr[8 * q + 4]) * inv, __uint_as_float(rr[8 * q + 5]) * inv);
+                    __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(rr[8 * q + 6]) * inv, __uint_as_float(rr[8 * q + 7]) * inv);
+                    u.x = *reinterpret_cast<uint32_t*>(&a0); u.y = *reinterpret_cast<uint32_t*>(&a1);
+                    u.z = *reinterpret_cast<uint32_t*>(&a2); u.w = *reinterpret_cast<uint32_t*>(&a3);
+                    if (store) reinterpret_cast<uint4*>(dst + c0)[q] = u;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// q, out [n, H, 128] bfloat16; caches [pages, K, bs, 128] bfloat16; tiles of TT = 128 / (H / K) tokens.
+// Returns cudaErrorInvalidValue for shapes outside the limits named at the top of this file.
+RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
+                               long long n_pages, const int* positions, const int* cu_q, const int* block_table,
+                               int table_stride, const int* tile_req, const int* tile_tok0, int n_tiles, int H, int K,
+                               int hd, int bs, float scale, int window, int* err, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (hd != AT_HD || K <= 0 || H % K || bs < 8 || bs > 128 || (bs & (bs - 1)) || !err) return (int)cudaErrorInvalidValue;
+    const int g = H / K;
+    if (g > 128 || 128 % g) return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
+        return (int)cudaErrorInvalidValue;
+    const int TT = 128 / g;
+    CUtensorMap tq, tk, tv;
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)H, (cuuint64_t)n_tokens};
+        cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)H * hd * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)g, (cuuint32_t)TT};
+        int st = tmap_encode_bf16(&tq, q, 3, dims, strides, box);
+        if (st) return st;
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)n_pages * K * bs};
+        cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)bs};
+        int st = tmap_encode_bf16(&tk, k_cache, 2, dims, strides, box);
+        if (st) return st;
+        st = tmap_encode_bf16(&tv, v_cache, 2, dims, strides, box);
+        if (st) return st;
+    }
+    AttnTcParams p;
+    p.out = (bf16*)out; p.positions = positions; p.cu_q = cu_q; p.block_table = block_table; p.tile_req = tile_req;
+    p.tile_tok0 = tile_tok0; p.table_stride = table_stride; p.H = H; p.K = K; p.bs = bs; p.window = window; p.TT = TT;
+    p.g = g; p.n_tiles = n_tiles; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
+    constexpr int smem = 6 * AT_TILE_BYTES + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    return rllm_launch(attention_tc_kernel, dim3(n_tiles, K), dim3(AT_THREADS), smem, stream, tq, tk, tv, p);
+}

@@ -36,6 +36,7 @@ LIBRARIES = {
     "fast": (["skinny_gemm.cu"], []),
     "attn": (["attention_flash.cu"], []),
     "tc": (["gemm_tc.cu"], []),
+    "attn_tc": (["attention_tc.cu"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

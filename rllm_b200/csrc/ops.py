@@ -420,6 +420,7 @@ def gate_up_swiglu(h, w_gate_up, out):
 
 
 FLASH_HEAD_DIMS = (64, 128)
+USE_ATTENTION_TC = True        # prompt portions with head size 128 take the tcgen05 kernel where it applies
 DECODE_SPLIT_KEYS = 128        # keys per split of the decode shape: a constant, so that a request's
                                # result never depends on the batch around it
 DECODE_MAX_Q = 8               # requests with at most this many tokens in the step take the decode shape
@@ -462,11 +463,21 @@ class AttentionPlan:
             for t0 in range(0, ctx.q_lens[r], self.TTp):
                 p_req.append(r)
                 p_tok.append(cu[r] + t0)
-        self.n_dec, self.n_pre, self.n_splits = len(d_req), len(p_req), n_splits
-        flat = torch.tensor(d_req + d_tok + p_req + p_tok + [0], dtype=torch.int32).to(device)
-        nd, np_ = self.n_dec, self.n_pre
+        # tiles of the tcgen05 kernel: 128 rows = (128 / g) tokens x g heads, when g divides 128
+        t_req, t_tok = [], []
+        self.TTt = 128 // g if g <= 128 and 128 % g == 0 else 0
+        if self.TTt:
+            for r in pre:
+                for t0 in range(0, ctx.q_lens[r], self.TTt):
+                    t_req.append(r)
+                    t_tok.append(cu[r] + t0)
+        self.n_dec, self.n_pre, self.n_tc, self.n_splits = len(d_req), len(p_req), len(t_req), n_splits
+        flat = torch.tensor(d_req + d_tok + p_req + p_tok + t_req + t_tok + [0], dtype=torch.int32).to(device)
+        nd, np_, nt = self.n_dec, self.n_pre, self.n_tc
         self.d_req, self.d_tok = flat[:nd], flat[nd:2 * nd]
         self.p_req, self.p_tok = flat[2 * nd:2 * nd + np_], flat[2 * nd + np_:2 * nd + 2 * np_]
+        o = 2 * nd + 2 * np_
+        self.t_req, self.t_tok = flat[o:o + nt], flat[o + nt:o + 2 * nt]
 
 
 def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0,
@@ -496,6 +507,31 @@ def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table
     return out
 
 
+def attention_tc_ok(q, hd, block_size, H, K) -> bool:
+    g = H // K
+    return (q.dtype == torch.bfloat16 and hd == 128 and 8 <= block_size <= 128
+            and block_size & (block_size - 1) == 0 and g <= 128 and 128 % g == 0)
+
+
+def attention_tc(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0, n_tiles, H, K, hd,
+                 block_size, scale, window):
+    """Prefill attention on the tcgen05 tensor cores (S and O in tensor memory); see attention_tc.cu."""
+    _need_cuda(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_req, tile_tok0)
+    _need_contig(q=q, k_cache=k_cache, v_cache=v_cache, out=out)
+    if not attention_tc_ok(q, hd, block_size, H, K):
+        raise KernelError("attention_tc takes bfloat16, head size 128, a power-of-two page size from 8 to 128 and "
+                          "a number of query heads per key/value head that divides 128")
+    st = build.load("attn_tc").rllm_attention_tc(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), c_int(q.shape[0]), c_longlong(k_cache.shape[0]),
+        _ptr(positions), _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req),
+        _ptr(tile_tok0), c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale),
+        c_int(window), _ptr(error_word(q.device)), _stream())
+    if st >= 30000:
+        raise KernelError(f"attention_tc: tensor map encoding failed (CUresult {st - 30000})")
+    _check(st, "attention_tc")
+    return out
+
+
 def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_size, scale, window=0):
     """Attention of the step's tokens over the paged cache; chooses the kernel by element type,
     head size and the shape of the step (`ctx`: the step's StepContext).  float32, and head sizes
@@ -507,7 +543,10 @@ def paged_attention(q, k_cache, v_cache, out, ctx, block_table, H, K, hd, block_
     plan = ctx.plans.get(key)
     if plan is None:
         plan = ctx.plans[key] = AttentionPlan(ctx, H, K, window, q.device)
-    if plan.n_pre:
+    if plan.n_pre and plan.n_tc and USE_ATTENTION_TC and attention_tc_ok(q, hd, block_size, H, K):
+        attention_tc(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.t_req, plan.t_tok,
+                     plan.n_tc, H, K, hd, block_size, scale, window)
+    elif plan.n_pre:
         paged_flash_attention(q, k_cache, v_cache, out, ctx.positions, ctx.cu_q, block_table, plan.p_req,
                               plan.p_tok, plan.n_pre, H, K, hd, block_size, scale, window, 0, plan.TTp,
                               plan.GHp, plan.chunks_p)
