@@ -37,6 +37,7 @@ LIBRARIES = {
     "attn": (["attention_flash.cu"], []),
     "tc": (["gemm_tc.cu"], []),
     "attn_tc": (["attention_tc.cu"], []),
+    "host": (["host_runtime.cpp"], []),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -122,6 +123,16 @@ def build(name: str, verbose: bool = True) -> Path:
     stamp = out_dir / f"librllm_{name}.stamp"
     want = _digest(srcs + headers, flags)
     if so.exists() and stamp.exists() and stamp.read_text().strip() == want:
+        return so
+    if all(p.suffix == ".cpp" for p in srcs):
+        # host-only library: the C++ compiler alone
+        cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+        if not cxx:
+            raise BuildError("no C++ compiler (g++) found for the host runtime")
+        tmp_so = out_dir / f".librllm_{name}.{os.getpid()}.so"
+        _run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-o", str(tmp_so), *map(str, srcs)], f"{name} (host C++)")
+        os.replace(tmp_so, so)
+        stamp.write_text(want)
         return so
     nvcc = _nvcc()
     if verbose:

@@ -1,0 +1,335 @@
+// Host runtime of the engine in C++: page allocator, cache manager (groups of layers with their
+// own page pools, block tables per request, windows that give pages back, state slots) and the
+// builder that turns a step's items into the flat int32 arrays the kernels read, written straight
+// into the pinned staging buffer.  No CUDA in this file; Python reaches it through the extern "C"
+// functions at the end (ctypes).
+//
+// Behaviour follows AxiomOperator/rllm's host crates: BlockAllocator and SeqKv
+// (crates/rllm-kv/src/lib.rs:17-133: free list popped lowest id first, all-or-nothing append,
+// slot = page * block_size + offset) and the batch flattening of KvPool::step_sampled
+// (crates/rllm-model/src/generate.rs:85-139: tokens, positions, token -> request, logit rows,
+// block tables; pre-checks before any mutation).
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+
+struct Allocator {
+    std::vector<int> free_list;      // back() is the lowest free id
+    std::vector<int> ref;
+    explicit Allocator(int n) : ref(n, 0) {
+        free_list.reserve(n);
+        for (int i = n - 1; i >= 0; --i) free_list.push_back(i);
+    }
+    int n_free() const { return (int)free_list.size(); }
+    int take() {
+        int b = free_list.back();
+        free_list.pop_back();
+        ref[b] = 1;
+        return b;
+    }
+    bool release(int b) {
+        if (b < 0 || b >= (int)ref.size() || ref[b] <= 0) return false;
+        if (--ref[b] == 0) free_list.push_back(b);
+        return true;
+    }
+};
+
+struct Request {
+    int length = 0;
+    int state_slot = -1;
+    std::vector<std::vector<int>> tables;   // per group: page per logical block, -1 = given back
+};
+
+struct Group {
+    int window;
+    Allocator alloc;
+    Group(int w, int n_blocks) : window(w), alloc(n_blocks) {}
+};
+
+enum : int { OK = 0, ERR_OUT_OF_PAGES = 1, ERR_OUT_OF_SLOTS = 2, ERR_UNKNOWN_REQUEST = 3, ERR_BAD_ARG = 4,
+             ERR_DOUBLE_FREE = 5, ERR_INVARIANT = 6, ERR_LIVE_TWICE = 7, ERR_BUFFER = 8 };
+
+struct Cache {
+    int block_size, n_blocks, max_requests;
+    std::vector<Group> groups;
+    std::vector<int> free_slots;
+    std::unordered_map<int64_t, Request> requests;
+    int last_need = 0, last_free = 0;        // of the most recent refusal
+
+    Cache(int n_groups, const int* windows, int bs, int nb, int mr) : block_size(bs), n_blocks(nb), max_requests(mr) {
+        for (int g = 0; g < n_groups; ++g) groups.emplace_back(windows[g], nb);
+        for (int s = mr - 1; s >= 0; --s) free_slots.push_back(s);
+    }
+    int blocks_for(int tokens) const { return (tokens + block_size - 1) / block_size; }
+
+    void pages_needed(int64_t rid, int n_new, int* out) const {
+        auto it = requests.find(rid);
+        const int length = it == requests.end() ? 0 : it->second.length;
+        for (size_t g = 0; g < groups.size(); ++g) {
+            const int have = it == requests.end() ? 0 : (int)it->second.tables[g].size();
+            out[g] = std::max(0, blocks_for(length + n_new) - have);
+        }
+    }
+    // 0 if all items can be appended together, else an error code (nothing is taken either way)
+    int check_append(int n_items, const int64_t* rids, const int* n_new) {
+        std::vector<int> need(groups.size(), 0), one(groups.size());
+        int new_requests = 0;
+        for (int i = 0; i < n_items; ++i) {
+            if (n_new[i] <= 0) return ERR_BAD_ARG;
+            if (!requests.count(rids[i])) ++new_requests;
+            pages_needed(rids[i], n_new[i], one.data());
+            for (size_t g = 0; g < groups.size(); ++g) need[g] += one[g];
+        }
+        if (new_requests > (int)free_slots.size()) {
+            last_need = new_requests; last_free = (int)free_slots.size();
+            return ERR_OUT_OF_SLOTS;
+        }
+        for (size_t g = 0; g < groups.size(); ++g)
+            if (need[g] > groups[g].alloc.n_free()) {
+                last_need = need[g]; last_free = groups[g].alloc.n_free();
+                return ERR_OUT_OF_PAGES;
+            }
+        return OK;
+    }
+    int add_request(int64_t rid) {
+        if (requests.count(rid)) return ERR_LIVE_TWICE;
+        if (free_slots.empty()) { last_need = 1; last_free = 0; return ERR_OUT_OF_SLOTS; }
+        Request r;
+        r.state_slot = free_slots.back();
+        free_slots.pop_back();
+        r.tables.resize(groups.size());
+        requests.emplace(rid, std::move(r));
+        return OK;
+    }
+    // slots_out: [group][n_new]
+    int append(int64_t rid, int n_new, int* slots_out, int* is_new) {
+        int st = check_append(1, &rid, &n_new);
+        if (st) return st;
+        if (is_new) *is_new = 0;
+        if (!requests.count(rid)) {
+            st = add_request(rid);
+            if (st) return st;
+            if (is_new) *is_new = 1;
+        }
+        Request& r = requests[rid];
+        for (size_t g = 0; g < groups.size(); ++g) {
+            auto& table = r.tables[g];
+            const int want = blocks_for(r.length + n_new);
+            while ((int)table.size() < want) table.push_back(groups[g].alloc.take());
+            if (slots_out)
+                for (int i = 0; i < n_new; ++i) {
+                    const int p = r.length + i;
+                    slots_out[g * n_new + i] = table[p / block_size] * block_size + p % block_size;
+                }
+        }
+        r.length += n_new;
+        return OK;
+    }
+    int release_passed(int64_t rid, int* released) {
+        auto it = requests.find(rid);
+        if (it == requests.end()) return ERR_UNKNOWN_REQUEST;
+        int count = 0;
+        for (size_t g = 0; g < groups.size(); ++g) {
+            if (groups[g].window <= 0) continue;
+            const int first = std::max(0, it->second.length + 1 - groups[g].window) / block_size;
+            auto& table = it->second.tables[g];
+            for (int b = 0; b < std::min(first, (int)table.size()); ++b)
+                if (table[b] >= 0) {
+                    if (!groups[g].alloc.release(table[b])) return ERR_DOUBLE_FREE;
+                    table[b] = -1;
+                    ++count;
+                }
+        }
+        if (released) *released = count;
+        return OK;
+    }
+    int free_request(int64_t rid) {
+        auto it = requests.find(rid);
+        if (it == requests.end()) return ERR_UNKNOWN_REQUEST;
+        for (size_t g = 0; g < groups.size(); ++g)
+            for (int b : it->second.tables[g])
+                if (b >= 0 && !groups[g].alloc.release(b)) return ERR_DOUBLE_FREE;
+        free_slots.push_back(it->second.state_slot);
+        requests.erase(it);
+        return OK;
+    }
+    int truncate(int64_t rid, int length) {
+        auto it = requests.find(rid);
+        if (it == requests.end()) return ERR_UNKNOWN_REQUEST;
+        if (length > it->second.length || length < 0) return ERR_BAD_ARG;
+        const int keep = blocks_for(length);
+        for (size_t g = 0; g < groups.size(); ++g) {
+            auto& table = it->second.tables[g];
+            while ((int)table.size() > keep) {
+                if (table.back() >= 0 && !groups[g].alloc.release(table.back())) return ERR_DOUBLE_FREE;
+                table.pop_back();
+            }
+        }
+        it->second.length = length;
+        return OK;
+    }
+    int check_invariants() const {
+        for (size_t g = 0; g < groups.size(); ++g) {
+            std::vector<int> seen(n_blocks, 0);
+            int held = 0;
+            for (auto& kv : requests)
+                for (int b : kv.second.tables[g])
+                    if (b >= 0) { if (b >= n_blocks || seen[b]++) return ERR_INVARIANT; ++held; }
+            for (int b : groups[g].alloc.free_list) { if (b < 0 || b >= n_blocks || seen[b]++) return ERR_INVARIANT; }
+            if (held + groups[g].alloc.n_free() != n_blocks) return ERR_INVARIANT;
+        }
+        std::vector<int> slot_seen(max_requests, 0);
+        for (auto& kv : requests) {
+            const int s = kv.second.state_slot;
+            if (s < 0 || s >= max_requests || slot_seen[s]++) return ERR_INVARIANT;
+        }
+        for (int s : free_slots) if (s < 0 || s >= max_requests || slot_seen[s]++) return ERR_INVARIANT;
+        if ((int)requests.size() + (int)free_slots.size() != max_requests) return ERR_INVARIANT;
+        return OK;
+    }
+};
+
+inline int round4(int n) { return (n + 3) / 4 * 4; }
+
+}  // namespace
+
+#define API extern "C" __attribute__((visibility("default")))
+
+API void* rllm_cache_create(int n_groups, const int* windows, int block_size, int n_blocks, int max_requests) {
+    if (n_groups < 0 || block_size <= 0 || n_blocks < 0 || max_requests < 0) return nullptr;
+    return new Cache(n_groups, windows, block_size, n_blocks, max_requests);
+}
+API void rllm_cache_destroy(void* c) { delete static_cast<Cache*>(c); }
+API int rllm_cache_has(void* c, int64_t rid) { return (int)static_cast<Cache*>(c)->requests.count(rid); }
+API int rllm_cache_length(void* c, int64_t rid) {
+    auto& r = static_cast<Cache*>(c)->requests;
+    auto it = r.find(rid);
+    return it == r.end() ? -1 : it->second.length;
+}
+API int rllm_cache_n_requests(void* c) { return (int)static_cast<Cache*>(c)->requests.size(); }
+API int rllm_cache_state_slot(void* c, int64_t rid) {
+    auto& r = static_cast<Cache*>(c)->requests;
+    auto it = r.find(rid);
+    return it == r.end() ? -1 : it->second.state_slot;
+}
+API int rllm_cache_n_free_pages(void* c, int group) { return static_cast<Cache*>(c)->groups[group].alloc.n_free(); }
+API int rllm_cache_n_free_slots(void* c) { return (int)static_cast<Cache*>(c)->free_slots.size(); }
+API void rllm_cache_pages_needed(void* c, int64_t rid, int n_new, int* out) { static_cast<Cache*>(c)->pages_needed(rid, n_new, out); }
+API int rllm_cache_check_append(void* c, int n_items, const int64_t* rids, const int* n_new) {
+    return static_cast<Cache*>(c)->check_append(n_items, rids, n_new);
+}
+API void rllm_cache_last_refusal(void* c, int* need, int* free_) {
+    *need = static_cast<Cache*>(c)->last_need;
+    *free_ = static_cast<Cache*>(c)->last_free;
+}
+API int rllm_cache_add_request(void* c, int64_t rid) { return static_cast<Cache*>(c)->add_request(rid); }
+API int rllm_cache_append(void* c, int64_t rid, int n_new, int* slots_out, int* is_new) {
+    return static_cast<Cache*>(c)->append(rid, n_new, slots_out, is_new);
+}
+API int rllm_cache_release_passed(void* c, int64_t rid, int* released) { return static_cast<Cache*>(c)->release_passed(rid, released); }
+API int rllm_cache_free(void* c, int64_t rid) { return static_cast<Cache*>(c)->free_request(rid); }
+API int rllm_cache_truncate(void* c, int64_t rid, int length) { return static_cast<Cache*>(c)->truncate(rid, length); }
+API int rllm_cache_check_invariants(void* c) { return static_cast<Cache*>(c)->check_invariants(); }
+// Copies the block table of (rid, group) into out (capacity cap); returns its length; pages given back read as 0.
+API int rllm_cache_block_table(void* c, int64_t rid, int group, int* out, int cap, int raw) {
+    auto& r = static_cast<Cache*>(c)->requests;
+    auto it = r.find(rid);
+    if (it == r.end()) return -1;
+    const auto& t = it->second.tables[group];
+    for (int i = 0; i < (int)t.size() && i < cap; ++i) out[i] = raw ? t[i] : std::max(t[i], 0);
+    return (int)t.size();
+}
+
+// Builds the flat arrays of a step in `out` (int32, every array starting at a multiple of 4
+// entries): tokens[n], positions[n], seq_ids[n], cu_q[R+1], ctx_lens[R], state_slots[R],
+// logit_rows[m], then per group slots[n], then per group block_table[R, width].
+// Appends every item's tokens to its request first (all-or-nothing: on an error nothing changed).
+// pad_requests > 0: the step holds one token per request and is padded to that many requests
+// (padding rows: token 0, position 0, slot -1) with all n rows as logit rows and tables of
+// pad_width columns.  `offsets` receives the start of each array, `meta` = {n, R, m, width, total}.
+// `new_flags[i]` tells whether item i created its request (its state slot must be zeroed).
+API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n_tok, const int* tokens_flat,
+                        const int* n_want, const int* want_flat, int vocab, int pad_requests, int pad_width,
+                        int32_t* out, int out_cap, int* offsets, int* meta, int* new_flags) {
+    Cache* c = static_cast<Cache*>(cv);
+    if (n_items <= 0) return ERR_BAD_ARG;
+    int n_real = 0, m = 0;
+    {
+        int t = 0, w = 0;
+        for (int i = 0; i < n_items; ++i) {
+            if (n_tok[i] <= 0) return ERR_BAD_ARG;
+            for (int j = 0; j < n_tok[i]; ++j) if (tokens_flat[t + j] < 0 || tokens_flat[t + j] >= vocab) return ERR_BAD_ARG;
+            for (int j = 0; j < n_want[i]; ++j) if (want_flat[w + j] < 0 || want_flat[w + j] >= n_tok[i]) return ERR_BAD_ARG;
+            for (int k = 0; k < i; ++k) if (rids[k] == rids[i]) return ERR_LIVE_TWICE;
+            t += n_tok[i]; w += n_want[i];
+            n_real += n_tok[i]; m += n_want[i];
+        }
+    }
+    int st = c->check_append(n_items, rids, n_tok);
+    if (st) return st;
+    const int G = (int)c->groups.size();
+    const int R = std::max(n_items, pad_requests);
+    const int n = n_real + (R - n_items);
+    if (pad_requests) m = n;
+    // table width after the append
+    int width = std::max(1, pad_width);
+    for (int i = 0; i < n_items; ++i) {
+        auto it = c->requests.find(rids[i]);
+        const int len = (it == c->requests.end() ? 0 : it->second.length) + n_tok[i];
+        width = std::max(width, c->blocks_for(len));
+    }
+    int off = 0, k = 0;
+    auto place = [&](int count) { offsets[k++] = off; off += round4(count); return offsets[k - 1]; };
+    const int o_tok = place(n), o_pos = place(n), o_seq = place(n), o_cu = place(R + 1), o_ctx = place(R),
+              o_state = place(R), o_rows = place(m);
+    std::vector<int> o_slots(G), o_tab(G);
+    for (int g = 0; g < G; ++g) o_slots[g] = place(n);
+    for (int g = 0; g < G; ++g) o_tab[g] = place(R * width);
+    const int total = std::max(off, 4);
+    meta[0] = n; meta[1] = R; meta[2] = m; meta[3] = width; meta[4] = total;
+    if (total > out_cap) return ERR_BUFFER;           // nothing appended yet: the caller grows the buffer and retries
+    std::memset(out, 0, sizeof(int32_t) * total);
+    std::vector<int> slots;
+    int base = 0, t = 0, w = 0, row = 0;
+    out[o_cu] = 0;
+    for (int i = 0; i < n_items; ++i) {
+        const int cnt = n_tok[i];
+        auto it = c->requests.find(rids[i]);
+        const int start = it == c->requests.end() ? 0 : it->second.length;
+        slots.assign((size_t)G * cnt, -1);
+        st = c->append(rids[i], cnt, slots.data(), &new_flags[i]);
+        if (st) return ERR_INVARIANT;                   // cannot happen after check_append
+        for (int j = 0; j < cnt; ++j) {
+            out[o_tok + base + j] = tokens_flat[t + j];
+            out[o_pos + base + j] = start + j;
+            out[o_seq + base + j] = i;
+            for (int g = 0; g < G; ++g) out[o_slots[g] + base + j] = slots[(size_t)g * cnt + j];
+        }
+        if (!pad_requests)
+            for (int j = 0; j < n_want[i]; ++j) out[o_rows + row++] = base + want_flat[w + j];
+        out[o_cu + i + 1] = base + cnt;
+        out[o_ctx + i] = start + cnt;
+        const Request& r = c->requests[rids[i]];
+        out[o_state + i] = r.state_slot;
+        for (int g = 0; g < G; ++g) {
+            const auto& tab = r.tables[g];
+            for (size_t b = 0; b < tab.size(); ++b) out[o_tab[g] + i * width + (int)b] = std::max(tab[b], 0);
+        }
+        base += cnt; t += cnt; w += n_want[i];
+    }
+    for (int i = n_items; i < R; ++i) {                 // padding rows
+        out[o_seq + base] = i;
+        for (int g = 0; g < G; ++g) out[o_slots[g] + base] = -1;
+        out[o_cu + i + 1] = base + 1;
+        out[o_ctx + i] = 1;
+        ++base;
+    }
+    if (pad_requests)
+        for (int j = 0; j < n; ++j) { out[o_rows + j] = j; out[o_seq + j] = j; }
+    return OK;
+}

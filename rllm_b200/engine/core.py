@@ -23,6 +23,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheManager, PagedKVView, StateView
+from ..cache.native import NativeCacheManager
 from ..csrc import ops
 from .batch import StepContext, StepItem
 
@@ -70,7 +71,9 @@ class _DecodeGraph:
 
 class Engine:
     def __init__(self, model, block_size: int = 16, max_tokens: int = 4096, max_requests: int = 64,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, native_host: bool = True):
+        """`native_host`: page accounting and the step's index arrays are built by the C++ host
+        runtime (default); False keeps them in Python (same results, slower)."""
         if not model.loaded:
             raise ValueError("the model has no weights loaded")
         self.model = model
@@ -80,7 +83,9 @@ class Engine:
                                f"(got device {self.runtime.device})")
         self.vocab_size = model.spec.vocab_size
         needs, cache_of = model.cache_needs()
-        self.cache = CacheManager(needs, cache_of, block_size, max_tokens, max_requests)
+        self.native_host = native_host
+        manager = NativeCacheManager if native_host else CacheManager
+        self.cache = manager(needs, cache_of, block_size, max_tokens, max_requests)
         self.cache.allocate_device(self.runtime.device, self.runtime.dtype)
         self.block_size = block_size
         self.use_graphs = use_graphs
@@ -92,10 +97,9 @@ class Engine:
         self.last_upload_bytes = 0
 
     # ------------------------------------------------------------------ staging
-    def _stage(self, arrays: Sequence[np.ndarray], layout: _Layout) -> torch.Tensor:
-        """Packs the arrays into a pinned buffer (a ring of four, each reused only after its last
-        copy has finished) and returns the pinned slice to copy from."""
-        total = layout.total
+    def _staging_buffer(self, total: int) -> torch.Tensor:
+        """The next pinned buffer of a ring of four (each reused only after its last copy has
+        finished), at least `total` int32 long."""
         if not self._staging or self._staging[0].numel() < total:
             cap = max(4096, 1 << (total - 1).bit_length())
             for ev in self._staging_events:
@@ -105,12 +109,49 @@ class Engine:
         i = self._staging_next
         self._staging_next = (i + 1) % len(self._staging)
         self._staging_events[i].synchronize()
-        hv = self._staging[i].numpy()
+        self._staged = i
+        return self._staging[i]
+
+    def _stage(self, arrays: Sequence[np.ndarray], layout: _Layout) -> torch.Tensor:
+        """Packs the arrays into a pinned buffer and returns the pinned slice to copy from."""
+        total = layout.total
+        buf = self._staging_buffer(total)
+        hv = buf.numpy()
         for a, o in zip(arrays, layout.offsets):
             hv[o:o + a.size] = a.reshape(-1)
-        self._staged = i
         self.last_upload_bytes = 4 * total
-        return self._staging[i][:total]
+        return buf[:total]
+
+    def _build(self, items: Sequence[StepItem], pad_requests: int = 0, pad_width: int = 0):
+        """Appends the items to the cache and stages the step's arrays in pinned memory.
+        Returns (pinned slice, layout, meta)."""
+        if not self.native_host:
+            arrays, meta = self._arrays(items, pad_requests, pad_width)
+            layout = _Layout([a.shape for a in arrays])
+            return self._stage(arrays, layout), layout, meta
+        guess = 4096
+        while True:
+            buf = self._staging_buffer(guess)
+            offsets, m, _ = self.cache.build_step(items, self.vocab_size, buf, pad_requests, pad_width)
+            if offsets is not None:
+                break
+            self._staging_next = self._staged            # the buffer was not used: hand it out again
+            guess = m[4]
+        n, R, n_rows, width, total = m
+        G = len(self.cache.paged)
+        shapes = [(n,), (n,), (n,), (R + 1,), (R,), (R,), (n_rows,)] + [(n,)] * G + [(R, width)] * G
+        layout = _Layout(shapes)
+        assert layout.offsets == offsets and layout.total == total
+        hv = buf.numpy()
+        cu = hv[offsets[3]:offsets[3] + R + 1]
+        q_lens = np.diff(cu).tolist()
+        start_pos = hv[offsets[1] + cu[:-1]].tolist()
+        ctx_lens = hv[offsets[4]:offsets[4] + R].tolist()
+        rows = hv[offsets[6]:offsets[6] + n_rows].tolist() if not pad_requests else \
+            [int(cu[i]) + int(w) for i, it in enumerate(items) for w in it.want]
+        meta = dict(n=n, R=R, q_lens=q_lens, start_pos=start_pos, rows=rows, ctx_lens=ctx_lens)
+        self.last_upload_bytes = 4 * total
+        return buf[:total], layout, meta
 
     def _copy_in(self, dev: torch.Tensor, host: torch.Tensor) -> None:
         dev.copy_(host, non_blocking=True)
@@ -128,10 +169,11 @@ class Engine:
             k = len(it.tokens)
             if k == 0:
                 raise StepError(f"request {it.request_id!r}: an item needs at least one token")
-            for t in it.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise StepError(f"request {it.request_id!r}: token id {t} is outside the "
-                                    f"vocabulary of {self.vocab_size}")
+            toks = np.asarray(it.tokens)
+            if toks.dtype.kind not in "iu" or toks.min() < 0 or toks.max() >= self.vocab_size:
+                bad = next((t for t in it.tokens if not (isinstance(t, (int, np.integer)) and 0 <= t < self.vocab_size)), None)
+                raise StepError(f"request {it.request_id!r}: token id {bad} is outside the "
+                                f"vocabulary of {self.vocab_size}")
             for w in it.want:
                 if not 0 <= int(w) < k:
                     raise StepError(f"request {it.request_id!r}: wanted place {w} is outside its "
@@ -224,9 +266,7 @@ class Engine:
                 and all(len(it.tokens) == 1 for it in items)):
             logits = self._graph_step(items)
         else:
-            arrays, meta = self._arrays(items)
-            layout = _Layout([a.shape for a in arrays])
-            host = self._stage(arrays, layout)
+            host, layout, meta = self._build(items)
             dev = torch.empty(layout.total, dtype=torch.int32, device=self.runtime.device)
             self._copy_in(dev, host)
             ctx, views = self._context(layout.views(dev), meta, bool(meta["rows"]))
@@ -243,16 +283,16 @@ class Engine:
         ctx_pad = -(-longest // GRAPH_CTX_QUANTUM) * GRAPH_CTX_QUANTUM
         width = -(-ctx_pad // self.block_size)
         key = (B, ctx_pad)
-        arrays, meta = self._arrays(items, pad_requests=B, pad_width=width)
+        host, layout, meta = self._build(items, pad_requests=B, pad_width=width)
         g = self._graphs.get(key)
         if g is None:
             g = self._graphs[key] = _DecodeGraph()
-            g.layout = _Layout([a.shape for a in arrays])
+            g.layout = layout
             g.static = torch.zeros(g.layout.total, dtype=torch.int32, device=self.runtime.device)
             # host-side shape of the step as the graph sees it: every request at the padded length
             meta_pad = dict(meta, start_pos=[ctx_pad - 1] * B, ctx_lens=[ctx_pad] * B, q_lens=[1] * B)
             g.ctx, g.views = self._context(g.layout.views(g.static), meta_pad, True)
-        host = self._stage(arrays, g.layout)
+        assert layout.offsets == g.layout.offsets
         self._copy_in(g.static, host)
         g.uses += 1
         if g.uses == 1:

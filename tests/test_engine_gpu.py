@@ -176,6 +176,25 @@ def test_sampling_is_reproducible_whatever_the_batch(dirs):
     assert h1 == host.generate(prompts[:2], **kw) and all(len(t) == 12 for t in h1)
 
 
+def test_python_and_native_host_agree(dirs):
+    """The C++ host runtime and the Python one drive the same kernels to the same logits."""
+    from rllm_b200.engine import Engine
+    from rllm_b200.models.model import load_model
+    import test_replay_gpu as T
+    _, model = load_model(dirs["W", "float32"], "float32", DEV)
+    reqs = T.requests_for(TINY["W"], 500)
+    steps = T.mixed_schedule(reqs)
+    outs = []
+    for native in (True, False):
+        eng = Engine(model, block_size=16, max_tokens=256, max_requests=8, native_host=native)
+        outs.append(helpers.run_steps(eng, steps))
+        eng.cache.check_invariants()
+        assert not eng.cache.requests
+    assert set(outs[0]) == set(outs[1])
+    for k in outs[0]:
+        assert torch.equal(outs[0][k], outs[1][k])
+
+
 def test_step_errors_change_nothing(dirs):
     from rllm_b200.cache import OutOfPages
     from rllm_b200.engine import StepError, StepItem

@@ -451,3 +451,110 @@ def test_plain_forward_is_causal_and_windows_matter(tmp_path):
     assert torch.allclose(other[:24], full[:24], atol=1e-5)            # within the window nothing changes
     assert not torch.allclose(other[30:], full[30:], atol=1e-3)
     assert plain_impl.greedy_generate(cfg, w, toks[:5], 3) == plain_impl.greedy_generate(cfg, w, toks[:5], 3)
+
+
+# ---------------------------------------------------------------- the C++ host runtime against the Python one
+
+def _needs():
+    return [PagedKVNeed(1, 16, 0), PagedKVNeed(1, 16, 9), PagedKVNeed(1, 16, 0), StateNeed((2,)), None], [None, None, 0, None, None]
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_native_cache_manager_matches_python(seed):
+    from rllm_b200.cache.native import NativeCacheManager
+    rng = random.Random(100 + seed)
+    needs, cache_of = _needs()
+    bs = rng.choice([1, 4, 16])
+    py = CacheManager(needs, cache_of, bs, 150, 4)
+    nat = NativeCacheManager(needs, cache_of, bs, 150, 4)
+    assert nat.entry_place == py.entry_place and len(nat.paged) == 2
+    live = []
+    for step in range(500):
+        op = rng.random()
+        if op < 0.6:
+            rid = rng.choice(live) if live and rng.random() < 0.7 else f"r{step}"
+            n = rng.choice([1, 1, 2, 7, 30, 64])
+            assert py.pages_needed(rid, n) == nat.pages_needed(rid, n)
+            assert py.can_append([(rid, n)]) == nat.can_append([(rid, n)])
+            try:
+                want = py.append(rid, n)
+            except OutOfPages as e:
+                with pytest.raises(OutOfPages) as e2:
+                    nat.append(rid, n)
+                assert (e.need, e.free, e.what) == (e2.value.need, e2.value.free, e2.value.what)
+                assert nat.has(rid) == py.has(rid)
+            else:
+                assert nat.append(rid, n) == want
+                if rid not in live:
+                    live.append(rid)
+                assert py.release_passed(rid) == nat.release_passed(rid)
+        elif op < 0.75 and live:
+            rid = rng.choice(live)
+            keep = rng.randrange(0, py.length(rid) + 1)
+            if all(None not in py.requests[rid].tables[g] for g in range(2)):
+                py.truncate(rid, keep); nat.truncate(rid, keep)
+        elif live:
+            rid = live.pop(rng.randrange(len(live)))
+            py.free(rid); nat.free(rid)
+            with pytest.raises(KeyError):
+                nat.free(rid)
+        for rid in live:
+            assert py.length(rid) == nat.length(rid) and py.state_slot(rid) == nat.state_slot(rid)
+            for g in range(2):
+                assert py.block_table(rid, g) == nat.block_table(rid, g)
+                assert py.requests[rid].tables[g] == nat.block_table(rid, g, raw=True)
+        assert [py.n_free_pages(g) for g in range(2)] == [nat.n_free_pages(g) for g in range(2)]
+        assert py.slots.n_free == nat.slots.n_free
+        nat.check_invariants()
+    for rid in live:
+        nat.free(rid)
+    nat.check_invariants()
+    assert nat.n_free_pages(0) == nat.n_blocks and not nat.requests
+
+
+def test_native_step_builder_arrays():
+    from rllm_b200.cache.native import NativeCacheManager
+    from rllm_b200.engine.batch import StepItem
+    needs, cache_of = _needs()
+    nat = NativeCacheManager(needs, cache_of, 4, 200, 8)
+    buf = torch.zeros(4096, dtype=torch.int32)
+    nat.append("a", 6)
+    items = [StepItem("a", [5, 6, 7], [0, 2]), StepItem("b", [9], []), StepItem("c", [1, 2, 3, 4, 5], [4])]
+    off, (n, R, m, width, total), flags = nat.build_step(items, 100, buf)
+    assert (n, R, m, width) == (9, 3, 3, 3) and flags == [0, 1, 1] and all(o % 4 == 0 for o in off)
+    a = buf.numpy()
+    assert a[off[0]:off[0] + n].tolist() == [5, 6, 7, 9, 1, 2, 3, 4, 5]
+    assert a[off[1]:off[1] + n].tolist() == [6, 7, 8, 0, 0, 1, 2, 3, 4]
+    assert a[off[2]:off[2] + n].tolist() == [0, 0, 0, 1, 2, 2, 2, 2, 2]
+    assert a[off[3]:off[3] + R + 1].tolist() == [0, 3, 4, 9] and a[off[4]:off[4] + R].tolist() == [9, 1, 5]
+    assert a[off[5]:off[5] + R].tolist() == [nat.state_slot(r) for r in "abc"]
+    assert a[off[6]:off[6] + m].tolist() == [0, 2, 8]
+    for g in range(2):
+        tab = a[off[9 + g]:off[9 + g] + R * width].reshape(R, width)
+        slots = a[off[7 + g]:off[7 + g] + n]
+        for i, r in enumerate("abc"):
+            t = nat.block_table(r, g)
+            assert tab[i, :len(t)].tolist() == t
+        pos = a[off[1]:off[1] + n]; seq = a[off[2]:off[2] + n]
+        assert all(slots[t] == tab[seq[t], pos[t] // 4] * 4 + pos[t] % 4 for t in range(n))
+    # errors change nothing
+    before = (nat.n_free_pages(0), nat.length("a"), len(nat.requests))
+    with pytest.raises(OutOfPages):
+        nat.build_step([StepItem("a", [1], [0]), StepItem("z", list(range(99)) * 9, [])], 100, buf)
+    with pytest.raises(ValueError):
+        nat.build_step([StepItem("a", [1], [3])], 100, buf)
+    with pytest.raises(ValueError):
+        nat.build_step([StepItem("q", [100], [0])], 100, buf)
+    assert before == (nat.n_free_pages(0), nat.length("a"), len(nat.requests))
+    # a buffer that is too small reports the size and appends nothing
+    small = torch.zeros(8, dtype=torch.int32)
+    off2, meta2, _ = nat.build_step([StepItem("a", [1, 2], [1])], 100, small)
+    assert off2 is None and meta2[4] > 8 and nat.length("a") == 9
+    # padded decode step
+    off, (n, R, m, width, total), _ = nat.build_step([StepItem("a", [3], [0]), StepItem("b", [4], [0])], 100, buf,
+                                                     pad_requests=4, pad_width=16)
+    a = buf.numpy()
+    assert (n, R, m, width) == (4, 4, 4, 16)
+    assert a[off[0]:off[0] + 4].tolist() == [3, 4, 0, 0] and a[off[1]:off[1] + 4].tolist() == [9, 1, 0, 0]
+    assert a[off[7]:off[7] + 4].tolist()[2:] == [-1, -1] and a[off[6]:off[6] + 4].tolist() == [0, 1, 2, 3]
+    nat.check_invariants()
