@@ -26,6 +26,12 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
                 max_position_embeddings=40960, use_sliding_window=False)
+# the other Qwen3 shapes the reference's numbers are quoted on (not the default run)
+QWEN3_06B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
+                 intermediate_size=3072, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
+                 intermediate_size=25600)
+SHAPES = {"8b": QWEN3_8B, "0.6b": QWEN3_06B, "32b": QWEN3_32B}
 FULL_LAYERS = 36
 CTX, PROMPT, PREFILL_TOKENS = 4096, 2048, 2048
 METRIC = "decode tok/s at batch 8 (Qwen3-8B bf16, 2,048-token prompts, ctx 4,096)"
@@ -76,8 +82,8 @@ def reference_arm():
     """AxiomOperator/rllm is a Rust workspace (Cargo.toml, no setup.py / pyproject.toml): pip has
     nothing to install, and neither cargo nor rustc exist in this image."""
     print(json.dumps({"impl": "reference",
-                      "unavailable": "AxiomOperator/rllm is a Rust workspace without a Python package; "
-                                     "pip cannot install it and cargo/rustc are not in this image"}))
+                      "unavailable": "AxiomOperator/rllm is a Rust workspace: pip answers 'not installable, neither "
+                                     "setup.py nor pyproject.toml found', and cargo/rustc are not in this image"}))
     return 0
 
 
@@ -99,7 +105,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: Qwen3-8B (default), 0.6B or 32B")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
@@ -123,7 +130,10 @@ def main():
     from rllm_b200.sampling.params import SamplingParams
 
     pk = peaks()
-    cfg_d = dict(QWEN3_8B, num_hidden_layers=a.layers)
+    full_layers = SHAPES[a.shape]["num_hidden_layers"]
+    if a.layers is None:
+        a.layers = full_layers
+    cfg_d = dict(SHAPES[a.shape], num_hidden_layers=a.layers)
     config = config_from_dict(cfg_d)
     torch.cuda.set_device(0)
     model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0", generate_on_device=True)
@@ -201,12 +211,14 @@ def main():
     e2e_run = decode_run(a.batch, a.steps, a.warmup, e2e=True)
 
     out = {
-        "metric": METRIC, "value": round(main_run["tok_s"], 2), "unit": "tok/s", "n_gpus": 1,
+        "metric": METRIC if a.shape == "8b" else METRIC.replace("Qwen3-8B", f"Qwen3-{a.shape.upper()}"), "value": round(main_run["tok_s"], 2), "unit": "tok/s", "n_gpus": 1,
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(main_run["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
-        "config": {"model": "Qwen3-8B-shaped", "layers": a.layers, "layers_full_model": FULL_LAYERS,
-                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 12288,
+        "config": {"model": f"Qwen3-{a.shape.upper()}-shaped", "layers": a.layers, "layers_full_model": full_layers,
+                   "hidden": config.hidden_size, "heads": config.num_attention_heads,
+                   "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
+                   "intermediate": config.intermediate_size,
                    "vocab": V, "global_batch": a.batch, "seq_len": CTX, "prompt_len": PROMPT,
                    "kv_block": 16, "parallelism": "single GPU",
                    "l2": "no flush: each step streams %.1f GB of weights (> 126 MB L2)" % (wbytes / 1e9),

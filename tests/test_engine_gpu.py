@@ -430,3 +430,39 @@ def test_toy_stateful_mixer_registers_and_steps(tmp_path):
     first = helpers.run_steps(eng, [{"entries": [{"id": "x", "tokens": a, "want": [20]}], "end": ["x"]}])
     again = helpers.run_steps(eng, [{"entries": [{"id": "y", "tokens": a, "want": [20]}], "end": ["y"]}])
     assert rel_err(again["y", 20], first["x", 20]) < 1e-6
+
+
+# ---------------------------------------------------------------- the command line
+
+def _cli(*args, timeout=600):
+    return subprocess.run([sys.executable, str(ROOT / "bin" / "rllm"), *map(str, args)], capture_output=True, text=True,
+                          timeout=timeout)
+
+
+def test_command_line(dirs, tmp_path):
+    cfg, w = plain_impl.load_model(dirs["A", "float32"])
+    prompt = helpers.random_tokens(9, cfg["vocab_size"], 8)
+    want = plain_impl.greedy_generate(cfg, w, prompt, 6)
+    r = _cli("run", dirs["A", "float32"], ",".join(map(str, prompt)), "-n", 6, "--kv-type", "f32", "--ctx", 64, "--show-ids")
+    assert r.returncode == 0, r.stderr[-1500:]
+    assert [int(t) for t in r.stdout.split()] == want and "tok/s" in r.stderr
+    ids = tmp_path / "ids.txt"
+    ids.write_text(" ".join(map(str, prompt)))
+    r = _cli("run", dirs["A", "float32"], f"@{ids}", "-n", 6, "--kv-type", "f32", "--ctx", 64, "-t", 0.7, "--top-p", 0.9,
+             "--top-k", 20, "--seed", 3)
+    assert r.returncode == 0 and len(r.stdout.split()) == 6
+    r = _cli("run", dirs["A", "float32"], "1,2,3", "-n", 100, "--ctx", 64)
+    assert r.returncode == 2 and "exceed --ctx" in r.stderr
+    r = _cli("bench", dirs["B", "bfloat16"], "-p", 40, "-n", 8, "-r", 1, "-b", 2, "--depth", 16)
+    assert r.returncode == 0, r.stderr[-1500:]
+    res = json.loads(r.stdout.strip().splitlines()[-1])
+    assert res["pp_tok_s"] > 0 and res["tg_tok_s"] > 0 and res["batch"] == 2
+    r = _cli("compare", dirs["B", "bfloat16"], ",".join(map(str, prompt)), "-n", 4)
+    assert r.returncode == 0 and "max relative logit diff" in r.stdout
+    assert float(r.stdout.split("diff")[1].split(";")[0]) < 3e-2
+    r = _cli("inspect", dirs["B", "bfloat16"])
+    assert r.returncode == 0 and "model.layers.2.mlp.down_proj.weight" in r.stdout and "Qwen3Config" in r.stdout
+    cfgfile = tmp_path / "c.json"
+    cfgfile.write_text(json.dumps(TINY["F"]))
+    r = _cli("random-model", tmp_path / "rm", "--config", cfgfile, "--seed", 5)
+    assert r.returncode == 0 and (tmp_path / "rm" / "model.safetensors").exists()
