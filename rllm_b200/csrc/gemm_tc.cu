@@ -1,9 +1,10 @@
 // Blackwell tensor-core product for many rows: D[M,N] = A[M,K] . B[N,K]^T, bfloat16 operands,
 // float32 accumulation in tensor memory (TMEM), operands staged in shared memory by TMA.
 //
-//   * one CTA computes a 128 x BN tile (BN = 128 or 256); K is walked in blocks of 64 elements
-//     through a ring of shared-memory stages, each holding a [128 x 64] A tile and a [BN x 64]
-//     B tile in the 128-byte-swizzled K-major layout that both TMA writes and tcgen05.mma reads;
+//   * persistent CTAs (one per SM) walk over 128 x 256 output tiles; K is walked in blocks of 64
+//     elements through a ring of shared-memory stages, each holding a [128 x 64] A tile and a
+//     [256 x 64] B tile in the 128-byte-swizzled K-major layout that both TMA writes and
+//     tcgen05.mma reads; two accumulators in TMEM let one tile's epilogue overlap the next tile's MMAs;
 //   * warp 0 (one elected lane) issues the TMA loads (cp.async.bulk.tensor.2d) and arms the
 //     stage's "full" mbarrier with the byte count; warp 1 (one elected lane) issues
 //     tcgen05.mma.cta_group::1.kind::f16 (M = 128, N = BN, K = 16, four per stage) and releases
@@ -60,6 +61,10 @@ template <> __device__ __forceinline__ void store_row32<bf16>(bf16* dst, const f
     }
 }
 
+// Persistent: the grid is one CTA per SM; CTA c takes tiles c, c + grid, c + 2 grid, ... (m fastest, so
+// the CTAs running together share few weight rows and the whole of A stays in L2).  Two accumulator
+// buffers in TMEM (2 x BN columns): the epilogue of one tile overlaps the MMAs of the next, and the
+// operand ring never drains between tiles.
 template <int BN, int EPI, typename TC, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TC* __restrict__ C,
@@ -67,28 +72,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int A_BYTES = TC_BM * TC_BK * 2;
     constexpr int B_BYTES = BN * TC_BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int BN_OUT = (EPI == TC_EPI_SWIGLU) ? BN / 2 : BN;        // output columns per CTA
+    constexpr int BN_OUT = (EPI == TC_EPI_SWIGLU) ? BN / 2 : BN;        // output columns per tile
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t full_bar[STAGES];
     __shared__ __align__(8) uint64_t empty_bar[STAGES];
-    __shared__ __align__(8) uint64_t acc_bar;
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN_OUT;
     const int nkb = (K + TC_BK - 1) / TC_BK;
+    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN_OUT - 1) / BN_OUT;
+    const int total_tiles = m_tiles * n_tiles;
 
     if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&acc_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc(&tmem_base_slot, BN);
+        tmem_alloc(&tmem_base_slot, 2 * BN);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -98,68 +107,87 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     pdl_wait();                                    // the A operand is written by the kernel before
 
     if (warp == 0 && lane == 0) {
-        // ---- TMA producer
-        int issued = 0;
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag)) {
-                if (!abort_flag) { atomicExch(err, TC_ERR_EMPTY); abort_flag = 1; }
-                break;
+        // ---- TMA producer: one continuous ring over all of this CTA's tiles
+        int it = 0, issued = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN_OUT;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag)) {
+                    if (!abort_flag) { atomicExch(err, TC_ERR_EMPTY); abort_flag = 1; }
+                    ok = false;
+                    break;
+                }
+                unsigned char* a_s = smem + (size_t)s * STAGE_BYTES;
+                unsigned char* b_s = a_s + A_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                tma_load_2d(a_s, &tmA, kb * TC_BK, m0, &full_bar[s]);
+                if (EPI == TC_EPI_SWIGLU) {
+                    tma_load_2d(b_s, &tmB, kb * TC_BK, n0, &full_bar[s]);
+                    tma_load_2d(b_s + B_BYTES / 2, &tmB, kb * TC_BK, up_row_offset + n0, &full_bar[s]);
+                } else {
+                    tma_load_2d(b_s, &tmB, kb * TC_BK, n0, &full_bar[s]);
+                }
+                issued = it + 1;
             }
-            unsigned char* a_s = smem + (size_t)s * STAGE_BYTES;
-            unsigned char* b_s = a_s + A_BYTES;
-            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-            tma_load_2d(a_s, &tmA, kb * TC_BK, m0, &full_bar[s]);
-            if (EPI == TC_EPI_SWIGLU) {
-                tma_load_2d(b_s, &tmB, kb * TC_BK, n0, &full_bar[s]);
-                tma_load_2d(b_s + B_BYTES / 2, &tmB, kb * TC_BK, up_row_offset + n0, &full_bar[s]);
-            } else {
-                tma_load_2d(b_s, &tmB, kb * TC_BK, n0, &full_bar[s]);
-            }
-            issued = kb + 1;
         }
         if (abort_flag) {
             // copies already issued must land before the CTA's shared memory goes away
-            for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                { volatile int no_abort = 0; mbar_wait(&full_bar[s], ph, &no_abort); }
-            }
+            volatile int no_abort = 0;
+            for (int i = max(0, issued - STAGES); i < issued; ++i)
+                mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1, &no_abort);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer
         constexpr uint32_t idesc = idesc_bf16(TC_BM, BN);
+        int it = 0, local = 0;
         bool ok = true;
-        for (int kb = 0; kb < nkb && ok; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait(&full_bar[s], ph, &abort_flag)) {
-                if (!abort_flag) { atomicExch(err, TC_ERR_FULL); abort_flag = 1; }
-                ok = false;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            // the epilogue of the tile that used this buffer two tiles ago must have read it
+            if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, &abort_flag)) {
+                if (!abort_flag) { atomicExch(err, TC_ERR_ACC); abort_flag = 1; }
                 break;
             }
             tc_fence_after();
-            const uint32_t a_addr = s_addr(smem + (size_t)s * STAGE_BYTES);
-            const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_BYTES);
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (!mbar_wait(&full_bar[s], ph, &abort_flag)) {
+                    if (!abort_flag) { atomicExch(err, TC_ERR_FULL); abort_flag = 1; }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = s_addr(smem + (size_t)s * STAGE_BYTES);
+                const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
-            for (int kk = 0; kk < TC_BK / 16; ++kk)       // 16 elements = 32 bytes along K: +2 in 16-byte units
-                umma_bf16(tmem_base, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
-            umma_commit(&empty_bar[s]);                  // arrives when these MMAs have read the stage
+                for (int kk = 0; kk < TC_BK / 16; ++kk)       // 16 elements = 32 bytes along K: +2 in 16-byte units
+                    umma_bf16(d_tmem, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kb | kk) != 0);
+                umma_commit(&empty_bar[s]);                  // arrives when these MMAs have read the stage
+            }
+            if (ok) umma_commit(&acc_full[buf]);
         }
-        if (ok) umma_commit(&acc_bar);
     } else if (warp >= 2) {
         // ---- epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
-        const int gm = m0 + row;
-        bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
-        if (!ok && !abort_flag) { atomicExch(err, TC_ERR_ACC); abort_flag = 1; }
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
+        int local = 0;
+        bool first = true;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN_OUT;
+            const int gm = m0 + row;
+            bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, &abort_flag);
+            if (!ok && !abort_flag) { atomicExch(err, TC_ERR_ACC); abort_flag = 1; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             tc_fence_after();
-            pdl_launch_dependents();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            if (first && tile + (int)gridDim.x >= total_tiles) { pdl_launch_dependents(); first = false; }
+            const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
                 uint32_t r[32];
@@ -179,13 +207,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
                 }
+                if (c0 + 32 >= BN_OUT) {                     // all of this thread's TMEM reads of the tile are done
+                    tc_fence_before();
+                    mbar_arrive(&acc_empty[buf]);
+                }
                 const int gn = n0 + c0;
                 if (gm < M && gn < N) {
                     TC* dst = C + (size_t)gm * ldc + gn;
                     const int n_valid = min(32, N - gn);
                     if (EPI == TC_EPI_ACCUM) {
+                        if (sizeof(TC) == 4 && n_valid >= 32 && ((uintptr_t)dst & 15) == 0) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) if (j < n_valid) v[j] += to_f<TC>(dst[j]);
+                            for (int j = 0; j < 8; ++j) {
+                                const float4 c4 = reinterpret_cast<const float4*>(dst)[j];
+                                v[4 * j] += c4.x; v[4 * j + 1] += c4.y; v[4 * j + 2] += c4.z; v[4 * j + 3] += c4.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (j < n_valid) v[j] += to_f<TC>(dst[j]);
+                        }
                     }
                     store_row32<TC>(dst, v, n_valid);
                 }
@@ -194,7 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, BN);
+    if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
 // ---------------------------------------------------------------- host side
@@ -226,7 +266,15 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int 
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    dim3 grid((M + TC_BM - 1) / TC_BM, (N + BN_OUT - 1) / BN_OUT);
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        if (n_sm <= 0) n_sm = 148;
+    }
+    const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN_OUT - 1) / BN_OUT);
+    dim3 grid(tiles < n_sm ? tiles : n_sm);
     return rllm_launch(kern, grid, dim3(TC_THREADS), smem, stream, ta, tb, (TC*)C, ldc, M, N, K, up, err);
 }
 
