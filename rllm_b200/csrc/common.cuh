@@ -101,4 +101,32 @@ static inline int rllm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     return (int)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// The same with the CTAs of grid dimension y grouped into thread-block clusters of `cluster_y`.
+template <typename... KArgs, typename... Args>
+static inline int rllm_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      int cluster_y, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (rllm_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_y > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = (unsigned)cluster_y;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return (int)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 #define RLLM_LAUNCH_STATUS() ((int)cudaGetLastError())

@@ -313,16 +313,16 @@ RLLM_API int rllm_gemm_tc(const void* A, const void* B, void* C, int c_dtype, in
 // Few rows (decode): the same machinery with the operands swapped.  The weight matrix W[n,k] is the
 // M side (128 weight rows per CTA, streamed once from HBM through a deep TMA ring), the m <= 64
 // batch rows X[m,k] are the N side, so the accumulator D[weight row, batch row] is C transposed.
-// The K range may be split over grid.y CTAs to fill the machine when n/128 is small; the CTAs of a
-// tile write float32 partials, and the one that finishes last (a counter per tile) adds them in
-// split order -- the order is fixed, whoever comes last -- applies the epilogue and resets the
-// counter.  SwiGLU: a CTA takes 64 gate rows and the 64 up rows of the same index.
+// The K range may be split over the grid.y CTAs of a thread-block cluster to fill the machine when
+// n/128 is small: each CTA accumulates its K slice, the followers park their sums in their own
+// shared memory, and the cluster's leader adds them in rank order through distributed shared
+// memory (mapa / ld.shared::cluster) and applies the epilogue -- no global scratch, no atomics, a
+// fixed order of addition.  SwiGLU: a CTA takes 64 gate rows and the 64 up rows of the same index.
 // =====================================================================================================
 template <int BN, int STAGES, int EPI, typename TC>
-__global__ void __launch_bounds__(TC_THREADS, 2)
+__global__ void __launch_bounds__(TC_THREADS, STAGES > 4 ? 1 : 2)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                    TC* __restrict__ C, int ldc, int m, int n, int K, int up_row_offset,
-                    float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ err) {
+                    TC* __restrict__ C, int ldc, int m, int n, int K, int up_row_offset, int* __restrict__ err) {
     constexpr int A_BYTES = TC_BM * TC_BK * 2;          // 128 weight rows x 64 k
     constexpr int B_BYTES = BN * TC_BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -334,8 +334,11 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     __shared__ __align__(8) uint64_t acc_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
-    __shared__ int is_last;
-    __shared__ float up_vals[(EPI == TC_EPI_SWIGLU) ? 64 * BN : 1];
+    float* red = reinterpret_cast<float*>(smem);            // exchange buffer: the stages are free once the MMAs are done
+    float v[BN];                                            // this thread's accumulator row (epilogue warps)
+#pragma unroll
+    for (int j = 0; j < BN; ++j) v[j] = 0.f;
+    bool ep_ok = true;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
@@ -351,7 +354,6 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
         abort_flag = 0;
-        is_last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -417,18 +419,15 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         if (ok) umma_commit(&acc_bar);
     } else if (warp >= 2) {
-        // ---- epilogue: thread = weight row of the tile, registers = batch columns
-        pdl_wait();                                     // C (and the counters) may be touched from here on
+        // ---- epilogue, first half: accumulator -> registers (thread = weight row, registers = batch columns)
+        pdl_wait();                                     // C may be touched from here on
         const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;            // 0..127 within the tile
-        bool ok = true;
         if (my_kb > 0) {
-            ok = mbar_wait(&acc_bar, 0, &abort_flag);
-            if (!ok && !abort_flag) { atomicExch(err, TC_ERR_ACC); abort_flag = 1; }
+            ep_ok = mbar_wait(&acc_bar, 0, &abort_flag);
+            if (!ep_ok && !abort_flag) { atomicExch(err, TC_ERR_ACC); abort_flag = 1; }
         }
-        ok = __all_sync(0xffffffffu, ok);
-        float v[BN];
-        if (ok && my_kb > 0) {
+        ep_ok = __all_sync(0xffffffffu, ep_ok);
+        if (ep_ok && my_kb > 0) {
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
@@ -439,73 +438,76 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[c0 + j] = __uint_as_float(r[j]);
             }
-        } else {
-#pragma unroll
-            for (int j = 0; j < BN; ++j) v[j] = 0.f;
         }
         pdl_launch_dependents();
-        // global weight row of this thread (SwiGLU: rows 0..63 gate j, rows 64..127 up j)
-        const int out_col = (EPI == TC_EPI_SWIGLU) ? n0 + (row & 63) : n0 + row;
-        const bool col_ok = out_col < n;
-        if (ok && n_splits > 1) {
-            // partial sums P[tile][split][b][row], then the last CTA of the tile reduces
-            float* P = partials + (((size_t)tile * n_splits + split) * BN) * TC_BM;
+        if (n_splits > 1 && split > 0) {
+            // a follower of the cluster: park the partial sums in this CTA's own shared memory
+            // (the stages are free: all MMAs that read them have completed)
+            const int row = quarter * 32 + lane;
 #pragma unroll
-            for (int b = 0; b < BN; ++b) if (b < m) P[(size_t)b * TC_BM + row] = v[b];
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
-            if (warp == 2 && lane == 0) {
-                const int prev = atomicAdd(&counters[tile], 1);
-                is_last = (prev == n_splits - 1);
-                if (is_last) counters[tile] = 0;                     // ready for the next launch
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (is_last) {
-                __threadfence();
-#pragma unroll
-                for (int b = 0; b < BN; ++b) v[b] = 0.f;
-                for (int z = 0; z < n_splits; ++z) {
-                    const float* Pz = partials + (((size_t)tile * n_splits + z) * BN) * TC_BM;
-#pragma unroll
-                    for (int b = 0; b < BN; ++b) if (b < m) v[b] += __ldcg(Pz + (size_t)b * TC_BM + row);
-                }
-            } else {
-                ok = false;                                          // another CTA writes the result
-            }
-        }
-        if (EPI == TC_EPI_SWIGLU) {
-            if (ok && row >= 64) {
-#pragma unroll
-                for (int b = 0; b < BN; ++b) up_vals[(row - 64) * BN + b] = v[b];
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (ok && row < 64 && col_ok) {
-#pragma unroll
-                for (int b = 0; b < BN; ++b)
-                    if (b < m) {
-                        const float g = v[b];
-                        C[(size_t)b * ldc + out_col] = from_f<TC>(g / (1.0f + expf(-g)) * up_vals[row * BN + b]);
-                    }
-            }
-        } else if (ok && col_ok) {
-#pragma unroll
-            for (int b = 0; b < BN; ++b)
-                if (b < m) {
-                    TC* c = C + (size_t)b * ldc + out_col;
-                    if (EPI == TC_EPI_ACCUM) *c = from_f<TC>(to_f<TC>(*c) + v[b]);
-                    else *c = from_f<TC>(v[b]);
-                }
+            for (int b = 0; b < BN; ++b) red[b * TC_BM + row] = v[b];
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (n_splits > 1) {
+        // Every thread of every CTA of the cluster comes here, whatever happened before: the
+        // cluster barrier has no time-out.  #1: the followers' partial sums are in place.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    if (warp >= 2 && split == 0) {
+        // ---- epilogue, second half (the cluster's leader): add the followers' sums in rank order, write out
+        const int row = (warp & 3) * 32 + lane;
+        for (int z = 1; z < n_splits; ++z) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(s_addr(red)), "r"(z));
+#pragma unroll
+            for (int b = 0; b < BN; ++b) {
+                float f;
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f) : "r"(remote + (uint32_t)(b * TC_BM + row) * 4) : "memory");
+                v[b] += f;
+            }
+        }
+        // global weight row of this thread (SwiGLU: rows 0..63 gate j, rows 64..127 up j)
+        const int out_col = (EPI == TC_EPI_SWIGLU) ? n0 + (row & 63) : n0 + row;
+        const bool col_ok = out_col < n;
+        if (EPI == TC_EPI_SWIGLU) {
+            if (ep_ok && row >= 64) {
+#pragma unroll
+                for (int b = 0; b < BN; ++b) red[(row - 64) * BN + b] = v[b];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
+            if (ep_ok && row < 64 && col_ok) {
+#pragma unroll
+                for (int b = 0; b < BN; ++b)
+                    if (b < m) {
+                        const float g = v[b];
+                        C[(size_t)b * ldc + out_col] = from_f<TC>(g / (1.0f + expf(-g)) * red[row * BN + b]);
+                    }
+            }
+        } else if (ep_ok && col_ok) {
+            if (EPI == TC_EPI_ACCUM) {                   // all loads first, then the stores: independent round trips
+#pragma unroll
+                for (int b = 0; b < BN; ++b)
+                    if (b < m) v[b] += to_f<TC>(C[(size_t)b * ldc + out_col]);
+            }
+#pragma unroll
+            for (int b = 0; b < BN; ++b)
+                if (b < m) C[(size_t)b * ldc + out_col] = from_f<TC>(v[b]);
+        }
+    }
+    if (n_splits > 1) {
+        // #2: the leader has read the followers' shared memory; they may exit
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
     if (warp == 1) tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
 }
 
-template <int BN, int EPI, typename TC>
-static int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, void* C, int ldc, int m, int n, int K, int up,
-                       float* partials, int* counters, int n_splits, int* err, cudaStream_t stream) {
-    constexpr int STAGES = 4;             // 4 x 24 KB: two CTAs share an SM, one streams while the other starts or ends
+template <int BN, int EPI, typename TC, int STAGES>
+static int launch_swap_stages(const CUtensorMap& tw, const CUtensorMap& tx, void* C, int ldc, int m, int n, int K, int up,
+                              int n_splits, int* err, cudaStream_t stream) {
     constexpr int ROWS_OUT = (EPI == TC_EPI_SWIGLU) ? TC_BM / 2 : TC_BM;
     constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
     auto kern = gemm_tc_swap_kernel<BN, STAGES, EPI, TC>;
@@ -516,19 +518,31 @@ static int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, void* C, in
         attr_set = true;
     }
     dim3 grid((n + ROWS_OUT - 1) / ROWS_OUT, n_splits);
-    return rllm_launch(kern, grid, dim3(TC_THREADS), smem, stream, tw, tx, (TC*)C, ldc, m, n, K, up, partials,
-                       counters, err);
+    return rllm_launch_cluster(kern, grid, dim3(TC_THREADS), smem, stream, n_splits, tw, tx, (TC*)C, ldc, m, n, K, up,
+                               err);
 }
 
-// C[m,n] (+)= X[m,k] . W[n,k]^T for m <= 64 with W as the streamed operand (see above).  `partials`
-// must hold tiles * n_splits * BN * 128 floats (BN = 32 for m <= 32, else 64) and `counters` one
-// zero-initialised int per tile when n_splits > 1; both may be null for n_splits == 1.
+// Few CTAs (at most one per SM): one CTA per SM with a ring of 8 stages, so that a single CTA keeps
+// 190 KB in flight.  Many CTAs: 4 stages, two CTAs share an SM and one streams while the other
+// starts or ends.
+template <int BN, int EPI, typename TC>
+static int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, void* C, int ldc, int m, int n, int K, int up,
+                       int n_splits, int* err, cudaStream_t stream) {
+    constexpr int ROWS_OUT = (EPI == TC_EPI_SWIGLU) ? TC_BM / 2 : TC_BM;
+    const int ctas = ((n + ROWS_OUT - 1) / ROWS_OUT) * n_splits;
+    if (ctas <= 160)
+        return launch_swap_stages<BN, EPI, TC, 8>(tw, tx, C, ldc, m, n, K, up, n_splits, err, stream);
+    return launch_swap_stages<BN, EPI, TC, 4>(tw, tx, C, ldc, m, n, K, up, n_splits, err, stream);
+}
+
+// C[m,n] (+)= X[m,k] . W[n,k]^T for m <= 64 with W as the streamed operand (see above).
+// n_splits (1..8) CTAs of a cluster share each tile's K range.
 RLLM_API int rllm_gemm_tc_swap(const void* W, const void* X, void* C, int c_dtype, int m, int n, int K, int ldw,
-                               int ldx, int ldc, int epilogue, int up_row_offset, int n_splits, float* partials,
-                               int* counters, int* err, cudaStream_t stream) {
+                               int ldx, int ldc, int epilogue, int up_row_offset, int n_splits, int* err,
+                               cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 64 || K <= 0 || (K & 7) || (ldw & 7) || (ldx & 7) || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) || !err ||
-        n_splits < 1 || (n_splits > 1 && (!partials || !counters)))
+        n_splits < 1 || n_splits > 8)
         return (int)cudaErrorInvalidValue;
     if (epilogue == TC_EPI_ACCUM && c_dtype != RLLM_F32) return (int)cudaErrorInvalidValue;
     CUtensorMap tw, tx;
@@ -539,7 +553,7 @@ RLLM_API int rllm_gemm_tc_swap(const void* W, const void* X, void* C, int c_dtyp
     st = make_tmap(&tx, X, m, K, ldx, bn);
     if (st) return st;
 #define SWAP(BN_, EPI_, TC_) \
-    return launch_swap<BN_, EPI_, TC_>(tw, tx, C, ldc, m, n, K, up_row_offset, partials, counters, n_splits, err, stream)
+    return launch_swap<BN_, EPI_, TC_>(tw, tx, C, ldc, m, n, K, up_row_offset, n_splits, err, stream)
     if (epilogue == TC_EPI_STORE) {
         if (c_dtype == RLLM_F32) { if (bn == 32) { SWAP(32, TC_EPI_STORE, float); } SWAP(64, TC_EPI_STORE, float); }
         if (bn == 32) { SWAP(32, TC_EPI_STORE, bf16); }

@@ -315,27 +315,21 @@ def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
     return out
 
 
-_split_counters: dict = {}
-
-
-def _counters(device, n: int) -> torch.Tensor:
-    key = torch.device(device).index or 0
-    t = _split_counters.get(key)
-    if t is None or t.numel() < n:
-        t = _split_counters[key] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
-    return t
-
-
 def tc_swap_splits(n_tiles: int, k: int) -> int:
-    """Number of K splits for the swapped tcgen05 product: enough CTAs to fill the 148 SMs, at
-    least 8 blocks of 64 along K per CTA."""
+    """Number of K splits (CTAs of a cluster) for the swapped tcgen05 product: enough CTAs to put
+    about one on every SM, at least 8 blocks of 64 along K each, at most 8."""
     nkb = -(-k // 64)
-    return max(1, min(296 // n_tiles, nkb // 8))
+    limit = max(1, min(148 // n_tiles, nkb // 8, 8))
+    splits = 1
+    while splits * 2 <= limit:           # powers of two: clusters of 3, 5, 6, 7 CTAs schedule badly
+        splits *= 2
+    return splits
 
 
 def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None):
     """out (+)= a . w^T for at most 64 rows of a on the tcgen05 tensor cores with the weights as
-    the streamed M operand (TMA ring of 8 stages), split over K where the weight matrix has few rows."""
+    the streamed M operand (TMA ring), the K range split over the CTAs of a cluster where the weight
+    matrix has few rows."""
     _need_cuda(a, w, out)
     if not _tc_ok(a, w) or a.shape[0] > 64:
         raise KernelError("skinny_gemm_tc needs bfloat16 operands, at most 64 rows, k a multiple of 8 and "
@@ -347,29 +341,29 @@ def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None
     n_tiles = -(-n // rows_out)
     if n_splits is None:
         n_splits = tc_swap_splits(n_tiles, k)
-    partials = counters = None
-    if n_splits > 1:
-        bn = 32 if m <= 32 else 64
-        partials = torch.empty(n_tiles * n_splits * bn * 128, dtype=torch.float32, device=a.device)
-        counters = _counters(a.device, n_tiles)
+    n_splits = max(1, min(int(n_splits), 8))
     st = build.load("tc").rllm_gemm_tc_swap(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
         c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), c_int(n_splits),
-        _ptr(partials), _ptr(counters), _ptr(error_word(a.device)), _stream())
+        _ptr(error_word(a.device)), _stream())
     if st >= 30000:
         raise KernelError(f"skinny_gemm_tc: tensor map encoding failed (CUresult {st - 30000})")
     _check(st, "skinny_gemm_tc")
     return out
 
 
-def _prefer_tc_swap(m: int, n: int) -> bool:
-    """Measured crossover between the two few-row kernels (B200, k = 4096): the tcgen05 kernel wins
-    once the batch columns no longer fit one MMA n-tile per warp cheaply (m > 16) and the weight
-    matrix has enough 128-row tiles to fill the SMs without splitting K much; for 9..16 rows only
-    very tall matrices (the LM head) gain."""
-    if m > 16:
-        return n >= 5120
-    return m > 8 and n >= 65536
+def _prefer_tc_swap(m: int, n: int, k: int, swiglu: bool = False) -> bool:
+    """Measured crossover between the two few-row kernels (B200, Qwen3-8B shapes).  The mma.sync
+    kernel wins on the small per-layer matrices up to 8 rows (1.5-3 us less fixed cost); the
+    tcgen05 kernel wins wherever there are more rows to multiply: everything above 16 rows, and all
+    but the smallest matrix between 9 and 16 rows."""
+    if k < 512 or n < 512:
+        return False                      # tiny models: the fixed cost of TMEM and TMA set-up dominates
+    if m <= 8:
+        return False                      # (gate/up alone is 2.5 us faster on tcgen05, but not inside a decode step)
+    if m <= 16:
+        return n * k > 4096 * 4096
+    return True
 
 
 def linear(a, w, out=None, out_dtype=None, accumulate=False):
@@ -392,7 +386,7 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False):
             raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
         return gemm_plain(a, w, out, accumulate)
     if _skinny_ok(a, w):
-        if _prefer_tc_swap(m, n) and out.data_ptr() % 16 == 0:
+        if _prefer_tc_swap(m, n, k) and out.data_ptr() % 16 == 0:
             return skinny_gemm_tc(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
         return skinny_gemm(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
     aligned = (a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
@@ -410,7 +404,7 @@ def gate_up_swiglu(h, w_gate_up, out):
     m = h.shape[0]
     F = out.shape[1]
     if _skinny_ok(h, w_gate_up):
-        if _prefer_tc_swap(m, 2 * F):
+        if _prefer_tc_swap(m, 2 * F, h.shape[1], swiglu=True):
             return skinny_gemm_tc(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
         return skinny_gemm(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
     if _tc_ok(h, w_gate_up) and out.data_ptr() % 16 == 0:
