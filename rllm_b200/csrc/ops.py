@@ -12,7 +12,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-from . import build
+from . import build, profiler
 
 F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
@@ -72,8 +72,22 @@ def _check(status: int, what: str, own: bool = True):
         _launches += 1
 
 
+_timed: dict = {}
+
+
+def _lib(name: str):
+    """The loaded library `name`; with RLLM_B200_PROFILE=1 its launchers are timed with CUDA events."""
+    lib = build.load(name)
+    if profiler.enabled():
+        t = _timed.get(name)
+        if t is None:
+            t = _timed[name] = profiler.TimedLibrary(lib)
+        return t
+    return lib
+
+
 def core():
-    return build.load("core")
+    return _lib("core")
 
 
 # ------------------------------------------------------------------ elementwise
@@ -225,7 +239,7 @@ def gemm_lib(a, w, out, accumulate=False):
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert w.shape[1] == k and out.shape == (m, n)
     assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-    st = build.load("blas").rllm_gemm_lib(_ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(m), c_int(n),
+    st = _lib("blas").rllm_gemm_lib(_ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(m), c_int(n),
                                           c_int(k), c_int(a.stride(0)), c_int(w.stride(0)),
                                           c_int(out.stride(0)), c_int(1 if accumulate else 0), _stream())
     if st >= 10000:
@@ -259,7 +273,7 @@ def skinny_gemm(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
         assert w.shape[0] >= up_row_offset + n
     else:
         assert w.shape[0] == n
-    _check(build.load("fast").rllm_skinny_gemm(
+    _check(_lib("fast").rllm_skinny_gemm(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
         c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), _stream()),
         "skinny_gemm")
@@ -305,7 +319,7 @@ def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
         assert w.shape[0] >= up_row_offset + n
     else:
         assert w.shape[0] == n
-    st = build.load("tc").rllm_gemm_tc(
+    st = _lib("tc").rllm_gemm_tc(
         _ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
         c_int(w.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
         _ptr(error_word(a.device)), _stream())
@@ -342,7 +356,7 @@ def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None
     if n_splits is None:
         n_splits = tc_swap_splits(n_tiles, k)
     n_splits = max(1, min(int(n_splits), 8))
-    st = build.load("tc").rllm_gemm_tc_swap(
+    st = _lib("tc").rllm_gemm_tc_swap(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
         c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), c_int(n_splits),
         _ptr(error_word(a.device)), _stream())
@@ -490,7 +504,7 @@ def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table
         rows = n_tiles * K * head_chunks * n_splits * TT * GH
         part_o = torch.empty(rows * hd, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(rows * 2, dtype=torch.float32, device=q.device)
-    _check(build.load("attn").rllm_paged_flash_attention(
+    _check(_lib("attn").rllm_paged_flash_attention(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(positions),
         _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req), _ptr(tile_tok0),
         c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
@@ -516,7 +530,7 @@ def attention_tc(q, k_cache, v_cache, out, positions, cu_q, block_table, tile_re
     if not attention_tc_ok(q, hd, block_size, H, K):
         raise KernelError("attention_tc takes bfloat16, head size 128, a power-of-two page size from 8 to 128 and "
                           "a number of query heads per key/value head that divides 128")
-    st = build.load("attn_tc").rllm_attention_tc(
+    st = _lib("attn_tc").rllm_attention_tc(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), c_int(q.shape[0]), c_longlong(k_cache.shape[0]),
         _ptr(positions), _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req),
         _ptr(tile_tok0), c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale),

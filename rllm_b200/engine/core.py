@@ -24,7 +24,7 @@ import torch
 
 from ..cache import CacheManager, PagedKVView, StateView
 from ..cache.native import NativeCacheManager
-from ..csrc import ops
+from ..csrc import ops, profiler
 from .batch import StepContext, StepItem
 
 
@@ -88,7 +88,7 @@ class Engine:
         self.cache = manager(needs, cache_of, block_size, max_tokens, max_requests)
         self.cache.allocate_device(self.runtime.device, self.runtime.dtype)
         self.block_size = block_size
-        self.use_graphs = use_graphs
+        self.use_graphs = use_graphs and not profiler.enabled()    # events cannot be recorded into a capture
         self._graphs: dict = {}
         self._staging = []
         self._staging_events = []

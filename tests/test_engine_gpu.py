@@ -466,3 +466,17 @@ def test_command_line(dirs, tmp_path):
     cfgfile.write_text(json.dumps(TINY["F"]))
     r = _cli("random-model", tmp_path / "rm", "--config", cfgfile, "--seed", 5)
     assert r.returncode == 0 and (tmp_path / "rm" / "model.safetensors").exists()
+
+
+def test_profile_switch_times_every_launcher(dirs):
+    """RLLM_B200_PROFILE=1: event pairs around the launchers, a table at exit, graphs off."""
+    env = dict(os.environ, RLLM_B200_PROFILE="1")
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "rllm"), "run", str(dirs["B", "bfloat16"]), "1,2,3,4,5", "-n", "6",
+                        "--ctx", "64", "--show-ids"], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stderr[-1500:]
+    lines = [l for l in r.stderr.splitlines() if l.startswith("[rllm_b200 profile]")]
+    names = {l.split()[2] for l in lines[1:-1]}
+    assert {"rllm_embed", "rllm_add_rms_norm", "rllm_qk_norm_rope_store", "rllm_sample_rows"} <= names, r.stderr[-1500:]
+    assert "graphs off" in lines[-1]
+    plain = _cli("run", dirs["B", "bfloat16"], "1,2,3,4,5", "-n", 6, "--ctx", 64, "--show-ids")
+    assert plain.stdout.split() == r.stdout.split()          # the switch changes no token

@@ -193,3 +193,71 @@ def test_mixed_with_page_reuse(model_dirs, name, dtype):
     eng.cache.check_invariants()
     assert eng.cache.n_free_pages(0) == eng.cache.n_blocks
     assert not eng.cache.requests
+
+
+# ---------------------------------------------------------------- layer sizes of a real model
+# The tiny configurations are too narrow for the kernels that serve real models: the tcgen05
+# products want a reduction of 512 and more, the swapped product 17 to 64 rows, the tcgen05
+# attention a head size of 128 and portions of more than 8 tokens.  This configuration has the
+# layer sizes of the smallest model of the family (two layers of it, a small vocabulary that is no
+# power of two), and the steps below have the row counts that reach each of those kernels.
+REAL = dict(TINY["A"], hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+            intermediate_size=3072, num_hidden_layers=2, vocab_size=1999, rope_theta=1e6,
+            max_position_embeddings=1024, tie_word_embeddings=True)
+
+
+@pytest.fixture(scope="module")
+def real_dirs(tmp_path_factory):
+    out = {}
+    for dtype in ("float32", "bfloat16"):
+        d = tmp_path_factory.mktemp(f"real_{dtype}")
+        helpers.make_model_dir(d, REAL, seed=77, dtype=getattr(torch, dtype), std=0.03)
+        out[dtype] = d
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_sizes_of_a_real_model(real_dirs, dtype):
+    lens = {"a": 333, "b": 190, "c": 75}
+    reqs = {rid: helpers.random_tokens(n, REAL["vocab_size"], 500 + i) for i, (rid, n) in enumerate(lens.items())}
+    refs = {rid: reference(real_dirs[dtype], dtype, t) for rid, t in reqs.items()}
+    eng = make_engine(real_dirs[dtype], dtype, max_tokens=1024)
+
+    # each request whole (more than 64 rows: the large-tile products and the tcgen05 attention)
+    for rid, toks in reqs.items():
+        want = sorted({0, 1, 15, 16, 63, 64, 127, 128, len(toks) - 2, len(toks) - 1} & set(range(len(toks))))
+        out = helpers.run_steps(eng, [{"entries": [{"id": rid, "tokens": toks, "want": want}], "end": [rid]}])
+        check(out, refs, dtype, f"real sizes, whole {rid}")
+
+    # portions of 17 to 64 rows (the swapped product), of 9 to 16, and single tokens, three requests
+    # beside one another so that decoded tokens share steps with portions
+    sizes = {"a": [40, 130, 2, 17, 111, 1, 1, 30, 1], "b": [64, 1, 1, 100, 12, 1, 11], "c": [9, 33, 1, 1, 31]}
+    cut = {rid: 0 for rid in reqs}
+    steps = []
+    for i in range(max(len(v) for v in sizes.values())):
+        entries, end = [], []
+        for rid, toks in reqs.items():
+            if i >= len(sizes[rid]):
+                continue
+            k = sizes[rid][i]
+            assert cut[rid] + k <= len(toks)
+            entries.append({"id": rid, "tokens": toks[cut[rid]:cut[rid] + k], "want": sorted({0, k - 1})})
+            cut[rid] += k
+            if i == len(sizes[rid]) - 1:
+                end.append(rid)
+        steps.append({"entries": entries, "end": end})
+    out = helpers.run_steps(eng, steps)
+    check(out, refs, dtype, "real sizes, portions beside decoded tokens")
+
+    # 40 single-token steps of all three at once after a whole prompt (CUDA graphs of the decode step)
+    steps = [{"entries": [{"id": rid, "tokens": toks[:len(toks) - 40], "want": []} for rid, toks in reqs.items()]}]
+    for j in range(40):
+        steps.append({"entries": [{"id": rid, "tokens": [toks[len(toks) - 40 + j]], "want": [0]}
+                                  for rid, toks in reqs.items()]})
+    steps[-1]["end"] = list(reqs)
+    out = helpers.run_steps(eng, steps)
+    check(out, refs, dtype, "real sizes, decoding")
+    eng.cache.check_invariants()
+    assert eng.cache.n_free_pages(0) == eng.cache.n_blocks
+    from rllm_b200.csrc import ops
+    ops.check_device_errors()
