@@ -366,6 +366,51 @@ def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None
     return out
 
 
+STREAM_MAX_ROWS = 16
+N_SM = 148
+
+
+def stream_plan(n: int, k: int, swiglu: bool = False):
+    """(CTAs, ring stages) of gemv_stream for n output rows on 148 SMs: three CTAs of three stages
+    per SM when each still gets three and more boxes of 8 rows, else two."""
+    boxes = -(-n // 8) * (2 if swiglu else 1)
+    per_sm = 3 if boxes >= 3 * 3 * N_SM else 2
+    return per_sm * N_SM, 3
+
+
+def gemv_stream(a, w, out, epilogue=EPI_STORE, up_row_offset=0, grid=None, stages=None):
+    """out (+)= a . w^T for at most 16 rows of `a`: persistent CTAs stream their shares of w's rows
+    through TMA rings (mma.sync consumers).  Epilogues as skinny_gemm.  grid, stages: number of CTAs
+    and ring depth (3, 5 or 10); by default from stream_plan."""
+    _need_cuda(a, w, out)
+    m, k = a.shape
+    n = out.shape[1]
+    if m > STREAM_MAX_ROWS or k % 64 or not _tc_ok(a, w):
+        raise KernelError("gemv_stream: needs at most 16 rows, k % 64 == 0, bfloat16 operands with 16-byte aligned rows")
+    if epilogue == EPI_SWIGLU:
+        assert w.shape[0] >= up_row_offset + n
+    else:
+        assert w.shape[0] == n
+    assert out.stride(1) == 1 and w.shape[1] == k
+    plan = stream_plan(n, k, epilogue == EPI_SWIGLU)
+    st = _lib("stream").rllm_gemv_stream(
+        _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
+        c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
+        c_int(plan[0] if grid is None else grid), c_int(plan[1] if stages is None else stages),
+        _ptr(error_word(a.device)), _stream())
+    _check(st, "gemv_stream")
+    return out
+
+
+USE_STREAM = True
+STREAM_MIN_WEIGHTS = 1 << 23      # below 16 MB of weights the short-lived CTAs of skinny_gemm start faster
+
+
+def _prefer_stream(a, w, n: int) -> bool:
+    m, k = a.shape
+    return (USE_STREAM and m <= 8 and k % 64 == 0 and n * k >= STREAM_MIN_WEIGHTS and _tc_ok(a, w))
+
+
 def _prefer_tc_swap(m: int, n: int, k: int, swiglu: bool = False) -> bool:
     """Measured crossover between the two few-row kernels (B200, Qwen3-8B shapes).  The mma.sync
     kernel wins on the small per-layer matrices up to 8 rows (1.5-3 us less fixed cost); the
@@ -400,6 +445,8 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False):
             raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
         return gemm_plain(a, w, out, accumulate)
     if _skinny_ok(a, w):
+        if _prefer_stream(a, w, n):
+            return gemv_stream(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
         if _prefer_tc_swap(m, n, k) and out.data_ptr() % 16 == 0:
             return skinny_gemm_tc(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
         return skinny_gemm(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
@@ -418,6 +465,8 @@ def gate_up_swiglu(h, w_gate_up, out):
     m = h.shape[0]
     F = out.shape[1]
     if _skinny_ok(h, w_gate_up):
+        if _prefer_stream(h, w_gate_up, 2 * F):
+            return gemv_stream(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
         if _prefer_tc_swap(m, 2 * F, h.shape[1], swiglu=True):
             return skinny_gemm_tc(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
         return skinny_gemm(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)

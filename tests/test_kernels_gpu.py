@@ -382,3 +382,53 @@ def test_skinny_gemm_tc_swiglu(m, F, k, splits):
     o.skinny_gemm_tc(a.to(DEV), w.to(DEV), out32, epilogue=o.EPI_SWIGLU, up_row_offset=F, n_splits=splits)
     assert rel_err(out32.cpu(), ref) < 1e-5
     o.check_device_errors()
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k,grid,stages", [(96, 512, None, None), (37, 64, 3, 3), (4096, 4096, None, None),
+                                             (1000, 1216, 148, 5), (6144, 1024, 444, 3), (520, 12288, 148, 10),
+                                             (8, 192, None, None), (2500, 320, 7, 5)])
+def test_gemv_stream(m, n, k, grid, stages):
+    """The persistent TMA-fed product for decode steps: every stage shape (shares of 1, 2 and more
+    granules), shares that end inside a stage, rows that are no multiple of 8, k that is no multiple
+    of a stage, one and two batch tiles."""
+    o = ops()
+    a, w = rnd(m, k, seed=41, dtype=torch.bfloat16), rnd(n, k, seed=42, scale=0.1, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    for _ in range(2):
+        out = torch.full((m, n), float("nan"), device=DEV)
+        o.gemv_stream(a.to(DEV), w.to(DEV), out, grid=grid, stages=stages)
+        assert rel_err(out.cpu(), ref) < 1e-5
+    out16 = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.gemv_stream(a.to(DEV), w.to(DEV), out16, grid=grid, stages=stages)
+    assert rel_err(out16.float().cpu(), ref) < 5e-3
+    base = rnd(m, n, seed=43)
+    acc = base.to(DEV)
+    o.gemv_stream(a.to(DEV), w.to(DEV), acc, epilogue=o.EPI_ACCUM, grid=grid, stages=stages)
+    assert rel_err(acc.cpu(), ref + base) < 1e-5
+    # a request's column does not depend on its batch-mates, nor on the grid
+    alone = torch.empty(1, n, device=DEV)
+    o.gemv_stream(a[m - 1:m].to(DEV), w.to(DEV), alone, grid=grid, stages=stages)
+    assert torch.equal(alone[0], out[m - 1])
+    other = torch.empty(m, n, device=DEV)
+    o.gemv_stream(a.to(DEV), w.to(DEV), other, grid=5, stages=3)
+    assert torch.equal(other, out)
+    o.check_device_errors()
+
+
+@pytest.mark.parametrize("m", [2, 8, 13])
+@pytest.mark.parametrize("F,k,grid,stages", [(224, 128, None, None), (1000, 320, 148, 5), (12288, 4096, None, None),
+                                             (37, 64, 2, 3), (3072, 1024, 444, 3)])
+def test_gemv_stream_swiglu(m, F, k, grid, stages):
+    o = ops()
+    a = rnd(m, k, seed=44, dtype=torch.bfloat16)
+    w = rnd(2 * F, k, seed=45, scale=0.2, dtype=torch.bfloat16)
+    g, u = a.float() @ w[:F].float().t(), a.float() @ w[F:].float().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    out = torch.full((m, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.gemv_stream(a.to(DEV), w.to(DEV), out, epilogue=o.EPI_SWIGLU, up_row_offset=F, grid=grid, stages=stages)
+    assert rel_err(out.float().cpu(), ref) < 5e-3
+    out32 = torch.full((m, F), float("nan"), device=DEV)
+    o.gemv_stream(a.to(DEV), w.to(DEV), out32, epilogue=o.EPI_SWIGLU, up_row_offset=F, grid=grid, stages=stages)
+    assert rel_err(out32.cpu(), ref) < 1e-5
+    o.check_device_errors()
