@@ -141,23 +141,31 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     static_assert((NW * 32) % CH == 0, "threads must cover whole rows of chunks");
     constexpr int ROWS_PER_PASS = NW * 32 / CH;
     const int my_chunk = tid % CH, my_row0 = tid / CH;
-    const int bs_shift = (p.bs & (p.bs - 1)) == 0 ? __ffs(p.bs) - 1 : -1;
+    const int last_blk = (ke - 1) / p.bs;
     auto load_tile = [&](int stage, int kt) {
         unsigned char* sk = smem + (size_t)stage * 2 * TILE_BYTES;
         unsigned char* sv = sk + TILE_BYTES;
+        // page by page: one table look-up and one base address per page, then a stride per row
+        int row0 = 0;                                    // first tile row of the current page
+        while (row0 < BN) {
+            const int key0 = kt + row0;
+            const int blk = key0 / p.bs, off0 = key0 - blk * p.bs;
+            const int rows_here = min(p.bs - off0, BN - row0);
+            const int page = table[min(blk, last_blk)];  // beyond the range: any valid address, zero fill
+            const size_t base = (((size_t)page * p.K + kvh) * p.bs + off0) * HD + my_chunk * 8;
+            const bf16* ksrc = p.k_cache + base;
+            const bf16* vsrc = p.v_cache + base;
+            // this thread's rows are those congruent to my_row0 modulo ROWS_PER_PASS
+            int r = (my_row0 - row0 % ROWS_PER_PASS + ROWS_PER_PASS) % ROWS_PER_PASS;
 #pragma unroll 4
-        for (int row = my_row0; row < BN; row += ROWS_PER_PASS) {
-            const int key = kt + row;
-            const bool ok = key < ke;              // beyond the range: zero fill
-            const int kk = ok ? key : kb;
-            int blk, off;
-            if (bs_shift >= 0) { blk = kk >> bs_shift; off = kk & (p.bs - 1); }
-            else { blk = kk / p.bs; off = kk - blk * p.bs; }
-            const int page = table[blk];
-            const size_t src = (((size_t)page * p.K + kvh) * p.bs + off) * HD + my_chunk * 8;
-            const uint32_t dst = row * (HD * 2) + ((my_chunk ^ (row & 7)) << 4);
-            cp_async16(smem_u32(sk + dst), p.k_cache + src, ok ? 16 : 0);
-            cp_async16(smem_u32(sv + dst), p.v_cache + src, ok ? 16 : 0);
+            for (; r < rows_here; r += ROWS_PER_PASS) {
+                const int row = row0 + r;
+                const bool ok = blk <= last_blk && kt + row < ke;
+                const uint32_t dst = row * (HD * 2) + ((my_chunk ^ (row & 7)) << 4);
+                cp_async16(smem_u32(sk + dst), ksrc + (ok ? r * HD : 0), ok ? 16 : 0);
+                cp_async16(smem_u32(sv + dst), vsrc + (ok ? r * HD : 0), ok ? 16 : 0);
+            }
+            row0 += rows_here;
         }
     };
 
@@ -332,9 +340,254 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
 
 // Merges the partials of the decode shape in split order (fixed order: the result is reproducible)
 // and writes the normalized output.  grid (tiles, K * head_chunks, rows), one thread per output dim.
+
+// ---------------------------------------------------------------------------------------------------
+// Decode with at most 8 query rows per tile: the product is turned round.  In the kernel above the
+// query rows are the M side of the MMA (16 rows, of which a decode step with a GQA group of 4 uses 4).
+// Here the KEYS are the M side (16 keys per MMA, all of them real) and the query rows the N side
+// (8 columns):
+//
+//   S^T[key, row] = K . Q^T  : A = K rows via ldmatrix, B = Q fragments kept in registers
+//   softmax over the keys    : across the 8 lanes that share a column pair, float32
+//   O^T[d, row] += V^T . P^T : A = V via ldmatrix.trans, B = P^T from the S^T accumulators through
+//                              movmatrix (an 8x8 transpose inside the warp)
+//
+// Half the MMAs, ldmatrix and exponentials of the 16-row form for the same keys, and half the
+// accumulators; the kernel is bound by the latency of its own instruction stream (one warp per
+// CTA, few warps per SM), so that is what counts.  Same splits, partials and combine kernel.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+
+template <int HD, int BN, int NS>
+__global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashParams p) {
+    constexpr int CH = HD / 8;
+    constexpr int TILE_BYTES = BN * HD * 2;
+    constexpr int KB = BN / 16;                   // blocks of 16 keys per tile
+    constexpr int DT = HD / 16;                   // blocks of 16 head dims
+    extern __shared__ __align__(128) unsigned char smem[];   // [NS stages][K tile, V tile]
+    const int lane = threadIdx.x, g = lane >> 2, t = lane & 3;
+    pdl_wait();
+
+    const int tile = blockIdx.x;
+    const int req = p.tile_req[tile], tok0 = p.tile_tok0[tile];
+    const int nt = min(p.TT, p.cu_q[req + 1] - tok0);
+    const int grp = p.H / p.K;
+    const int kvh = blockIdx.y / p.head_chunks, hc = blockIdx.y % p.head_chunks;
+    const int head0 = kvh * grp + hc * p.GH;
+    const int nh = min(p.GH, grp - hc * p.GH);
+    const int pos_first = p.positions[tok0], pos_last = p.positions[tok0 + nt - 1];
+    int lo = p.window > 0 ? max(0, pos_first + 1 - p.window) : 0;
+    lo = lo / BN * BN;
+    int kb = lo, ke = pos_last + 1;
+    if (p.split_keys > 0) {
+        kb = lo + blockIdx.z * p.split_keys;
+        ke = min(ke, kb + p.split_keys);
+    }
+    const size_t part_base = (((size_t)tile * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z) * p.part_rows;
+
+    // the two columns (query rows) of this lane's accumulators: 2t and 2t + 1
+    int rowc[2], tlc[2], hlc[2], firstc[2], hic[2];
+    bool validc[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        rowc[x] = 2 * t + x;
+        tlc[x] = rowc[x] / p.GH;
+        hlc[x] = rowc[x] % p.GH;
+        validc[x] = tlc[x] < nt && hlc[x] < nh;
+        const int pos = validc[x] ? p.positions[tok0 + tlc[x]] : -1;
+        firstc[x] = p.window > 0 ? max(0, pos + 1 - p.window) : 0;
+        hic[x] = min(pos + 1, ke);
+    }
+    if (kb >= ke) {                                // an empty split: mark it so
+        if (p.split_keys > 0 && g == 0) {
+#pragma unroll
+            for (int x = 0; x < 2; ++x)
+                if (rowc[x] < p.part_rows) {
+                    p.part_ml[(part_base + rowc[x]) * 2] = -INFINITY;
+                    p.part_ml[(part_base + rowc[x]) * 2 + 1] = 0.f;
+                }
+        }
+        return;
+    }
+
+    // Q as the B operand: column g is query row g
+    uint32_t qf[DT][2];
+    {
+        const int tlq = g / p.GH, hlq = g % p.GH;
+        const bool validq = tlq < nt && hlq < nh;
+        const bf16* qr = p.q + ((size_t)(tok0 + (validq ? tlq : 0)) * p.H + head0 + (validq ? hlq : 0)) * HD;
+#pragma unroll
+        for (int ks = 0; ks < DT; ++ks) {
+            qf[ks][0] = validq ? *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 2 * t) : 0u;
+            qf[ks][1] = validq ? *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+
+    const int* table = p.block_table + (size_t)req * p.table_stride;
+    constexpr int ROWS_PER_PASS = 32 / CH;
+    static_assert(32 % CH == 0, "a warp must cover whole rows of chunks");
+    const int my_chunk = lane % CH, my_row0 = lane / CH;
+    const int last_blk = (ke - 1) / p.bs;
+    auto load_tile = [&](int stage, int kt) {
+        unsigned char* sk = smem + (size_t)stage * 2 * TILE_BYTES;
+        unsigned char* sv = sk + TILE_BYTES;
+        int row0 = 0;
+        while (row0 < BN) {
+            const int key0 = kt + row0;
+            const int blk = key0 / p.bs, off0 = key0 - blk * p.bs;
+            const int rows_here = min(p.bs - off0, BN - row0);
+            const int page = table[min(blk, last_blk)];
+            const size_t base = (((size_t)page * p.K + kvh) * p.bs + off0) * HD + my_chunk * 8;
+            const bf16* ksrc = p.k_cache + base;
+            const bf16* vsrc = p.v_cache + base;
+            int r = (my_row0 - row0 % ROWS_PER_PASS + ROWS_PER_PASS) % ROWS_PER_PASS;
+#pragma unroll 4
+            for (; r < rows_here; r += ROWS_PER_PASS) {
+                const int row = row0 + r;
+                const bool ok = blk <= last_blk && kt + row < ke;
+                const uint32_t dst = row * (HD * 2) + ((my_chunk ^ (row & 7)) << 4);
+                cp_async16(smem_u32(sk + dst), ksrc + (ok ? r * HD : 0), ok ? 16 : 0);
+                cp_async16(smem_u32(sv + dst), vsrc + (ok ? r * HD : 0), ok ? 16 : 0);
+            }
+            row0 += rows_here;
+        }
+    };
+
+    float o[DT][4];                                // O^T: (d = 16 dp + g, + 8) x (rows 2t, 2t + 1)
+#pragma unroll
+    for (int j = 0; j < DT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float mx[2] = {-INFINITY, -INFINITY}, lsum[2] = {0.f, 0.f};
+
+    const int n_tiles = (ke - kb + BN - 1) / BN;
+#pragma unroll
+    for (int i = 0; i < NS - 1; ++i) {             // NS - 1 tiles ahead; empty groups keep the count uniform
+        if (i < n_tiles) load_tile(i, kb + i * BN);
+        cp_async_commit();
+    }
+    // ldmatrix lane roles.  K (A of S^T, no transpose): matrices (keys 0-7 | 8-15) x (d 0-7 | 8-15).
+    // V (A of O^T, transposed): matrices (d 0-7 | 8-15) x (keys 0-7 | 8-15).
+    const int mat = lane >> 3, ri = lane & 7;
+    const int k_row = (mat & 1) * 8 + ri, k_ch = mat >> 1;
+    const int v_row = (mat >> 1) * 8 + ri, v_ch = mat & 1;
+    for (int it = 0; it < n_tiles; ++it) {
+        const int kt = kb + it * BN;
+        if (it + NS - 1 < n_tiles) load_tile((it + NS - 1) % NS, kt + (NS - 1) * BN);
+        cp_async_commit();
+        cp_async_wait<NS - 1>();
+        __syncwarp();
+        const unsigned char* sk = smem + (size_t)(it % NS) * 2 * TILE_BYTES;
+        const unsigned char* sv = sk + TILE_BYTES;
+
+        // ---- S^T = K Q^T
+        float s[KB][4];
+#pragma unroll
+        for (int j = 0; j < KB; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < DT; ++ks) {
+#pragma unroll
+            for (int j = 0; j < KB; ++j) {
+                const int row = j * 16 + k_row;
+                uint32_t a0, a1, a2, a3;
+                ldsm_x4(smem_u32(sk + row * (HD * 2) + (((ks * 2 + k_ch) ^ (row & 7)) << 4)), a0, a1, a2, a3);
+                mma_bf16(s[j], a0, a1, a2, a3, qf[ks][0], qf[ks][1]);
+            }
+        }
+        // ---- scale, mask, online softmax over the keys (lanes of equal t hold one column pair)
+        const bool need_mask = (kt + BN > min(hic[0], hic[1])) || (kt < max(firstc[0], firstc[1]));
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = s[j][e] * p.scale_log2;
+                if (need_mask) {
+                    const int key = kt + 16 * j + g + (e >> 1) * 8;
+                    const int x = e & 1;
+                    if (!(key >= firstc[x] && key < hic[x])) v = -INFINITY;
+                }
+                s[j][e] = v;
+            }
+            tmax[0] = fmaxf(tmax[0], fmaxf(s[j][0], s[j][2]));
+            tmax[1] = fmaxf(tmax[1], fmaxf(s[j][1], s[j][3]));
+        }
+        float al[2], ms[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            tmax[x] = fmaxf(tmax[x], __shfl_xor_sync(0xffffffffu, tmax[x], 4));
+            tmax[x] = fmaxf(tmax[x], __shfl_xor_sync(0xffffffffu, tmax[x], 8));
+            tmax[x] = fmaxf(tmax[x], __shfl_xor_sync(0xffffffffu, tmax[x], 16));
+            const float mn = fmaxf(mx[x], tmax[x]);
+            ms[x] = mn == -INFINITY ? 0.f : mn;
+            al[x] = exp2f(mx[x] - ms[x]);                          // exp2(-inf) = 0
+            mx[x] = mn;
+        }
+        float rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+            s[j][0] = exp2f(s[j][0] - ms[0]); s[j][1] = exp2f(s[j][1] - ms[1]);
+            s[j][2] = exp2f(s[j][2] - ms[0]); s[j][3] = exp2f(s[j][3] - ms[1]);
+            rs[0] += s[j][0] + s[j][2];
+            rs[1] += s[j][1] + s[j][3];
+        }
+        lsum[0] = lsum[0] * al[0] + rs[0];          // this lane's share of the keys; summed over lanes at the end
+        lsum[1] = lsum[1] * al[1] + rs[1];
+#pragma unroll
+        for (int j = 0; j < DT; ++j) { o[j][0] *= al[0]; o[j][1] *= al[1]; o[j][2] *= al[0]; o[j][3] *= al[1]; }
+        // ---- O^T += V^T P^T
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+            const uint32_t b0 = movmatrix_trans(pack_bf16(s[j][0], s[j][1]));     // keys 0-7 of the block
+            const uint32_t b1 = movmatrix_trans(pack_bf16(s[j][2], s[j][3]));     // keys 8-15
+#pragma unroll
+            for (int dp = 0; dp < DT; ++dp) {
+                const int row = j * 16 + v_row;
+                uint32_t a0, a1, a2, a3;
+                ldsm_x4_t(smem_u32(sv + row * (HD * 2) + (((dp * 2 + v_ch) ^ (row & 7)) << 4)), a0, a1, a2, a3);
+                mma_bf16(o[dp], a0, a1, a2, a3, b0, b1);
+            }
+        }
+        __syncwarp();                              // the stage may be overwritten from here on
+    }
+    pdl_launch_dependents();
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        lsum[x] += __shfl_xor_sync(0xffffffffu, lsum[x], 4);
+        lsum[x] += __shfl_xor_sync(0xffffffffu, lsum[x], 8);
+        lsum[x] += __shfl_xor_sync(0xffffffffu, lsum[x], 16);
+    }
+    if (p.split_keys > 0) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            if (rowc[x] >= p.part_rows) continue;
+            float* po = p.part_o + (part_base + rowc[x]) * HD;
+#pragma unroll
+            for (int dp = 0; dp < DT; ++dp) { po[16 * dp + g] = o[dp][x]; po[16 * dp + 8 + g] = o[dp][2 + x]; }
+            if (g == 0) {
+                p.part_ml[(part_base + rowc[x]) * 2] = mx[x];
+                p.part_ml[(part_base + rowc[x]) * 2 + 1] = validc[x] ? lsum[x] : 0.f;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            if (!validc[x]) continue;
+            const float inv = lsum[x] > 0.f ? 1.0f / lsum[x] : 0.f;
+            bf16* po = p.out + ((size_t)(tok0 + tlc[x]) * p.H + head0 + hlc[x]) * HD;
+#pragma unroll
+            for (int dp = 0; dp < DT; ++dp) {
+                po[16 * dp + g] = from_f<bf16>(o[dp][x] * inv);
+                po[16 * dp + 8 + g] = from_f<bf16>(o[dp][2 + x] * inv);
+            }
+        }
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(HD) paged_flash_combine_kernel(const FlashParams p, int n_splits) {
-    extern __shared__ float wgt[];               // [n_splits] weight of each split, then the sum
+    extern __shared__ float wgt[];               // [n_splits] m, then the weight, of each split; [n_splits] l
     pdl_wait();
     pdl_launch_dependents();
     const int tile = blockIdx.x, R = blockIdx.z;
@@ -348,25 +601,46 @@ __global__ void __launch_bounds__(HD) paged_flash_combine_kernel(const FlashPara
     if (tl >= nt || hl >= nh) return;
     const int d = threadIdx.x;
     const size_t base = ((size_t)tile * gridDim.y + blockIdx.y) * n_splits;
-    // weights exp2(m_z - M) * [l_z > 0], computed once per block
-    float M = -INFINITY;
-    for (int z = 0; z < n_splits; ++z) {
-        const float* ml = p.part_ml + ((base + z) * p.part_rows + R) * 2;
-        if (ml[1] > 0.f) M = fmaxf(M, ml[0]);
-    }
+    // The splits' (m, l) are read side by side, one per thread, not one after the other: the kernel is
+    // a chain of memory round trips, so their number is what it costs.  Then the weights
+    // exp2(m_z - M) * [l_z > 0] and their sum go to shared memory, and every thread adds its column
+    // of the partial outputs in split order with all loads in flight at once.
+    __shared__ float red[HD / 32];
+    float m_loc = -INFINITY;
     for (int z = d; z < n_splits; z += HD) {
-        const float* ml = p.part_ml + ((base + z) * p.part_rows + R) * 2;
-        wgt[z] = ml[1] > 0.f ? exp2f(ml[0] - M) : 0.f;
+        const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + ((base + z) * p.part_rows + R) * 2);
+        wgt[z] = ml.x;
+        wgt[n_splits + z] = ml.y;
+        if (ml.y > 0.f) m_loc = fmaxf(m_loc, ml.x);
+    }
+    m_loc = warp_max(m_loc);
+    if ((d & 31) == 0) red[d >> 5] = m_loc;
+    __syncthreads();
+    float M = red[0];
+#pragma unroll
+    for (int w = 1; w < HD / 32; ++w) M = fmaxf(M, red[w]);
+    for (int z = d; z < n_splits; z += HD) {
+        const float l = wgt[n_splits + z];
+        wgt[z] = l > 0.f ? exp2f(wgt[z] - M) : 0.f;
     }
     __syncthreads();
     float num = 0.f, den = 0.f;
-    for (int z = 0; z < n_splits; ++z) {
-        const float w = wgt[z];
-        if (w > 0.f) {
-            const size_t row = (base + z) * p.part_rows + R;
-            num += p.part_o[row * HD + d] * w;
-            den += p.part_ml[row * 2 + 1] * w;
+    const float* po = p.part_o + (base * p.part_rows + R) * HD + d;
+    const size_t zstride = (size_t)p.part_rows * HD;
+    int z = 0;
+    for (; z + 4 <= n_splits; z += 4) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = po[(z + u) * zstride];      // a split without keys wrote nothing: the value is dropped below
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float w = wgt[z + u];
+            if (w > 0.f) { num += v[u] * w; den += wgt[n_splits + z + u] * w; }
         }
+    }
+    for (; z < n_splits; ++z) {
+        const float w = wgt[z];
+        if (w > 0.f) { num += po[z * zstride] * w; den += wgt[n_splits + z] * w; }
     }
     p.out[((size_t)(tok0 + tl) * p.H + head0 + hl) * HD + d] = from_f<bf16>(den > 0.f ? num / den : 0.f);
 }
@@ -404,13 +678,20 @@ static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_split
             attr_set = true;
         }
         st = rllm_launch(kern, grid, dim3(NW * 32), smem, stream, p);
+    } else if (p.part_rows <= 8) {
+        // tiles of at most 8 query rows: the keys as the M side of the MMA.  Tiles of 16 keys in a ring
+        // of three (24 KB): nine CTAs share an SM, which counts for more here than a deeper ring
+        // (measured at batch 8 and 64, context 2,048: 32-key tiles x 2 stages 24.8 / 109 us,
+        // 16 x 3: 21.0 / 104, 16 x 4: 25.6 / 112, 32 x 4: 30.8 / 166).
+        constexpr int BN = 16, NS = 3;
+        st = rllm_launch(paged_decode_attention_kernel<HD, BN, NS>, grid, dim3(32), NS * 2 * BN * HD * 2, stream, p);
     } else {
         constexpr int BN = 32;
         st = rllm_launch(paged_flash_attention_kernel<HD, 1, BN, false>, grid, dim3(32), 2 * 2 * BN * HD * 2, stream, p);
     }
     if (st) return st;
     return rllm_launch(paged_flash_combine_kernel<HD>, dim3(n_tiles, p.K * p.head_chunks, p.part_rows), dim3(HD),
-                       n_splits * sizeof(float), stream, p, n_splits);
+                       2 * n_splits * sizeof(float), stream, p, n_splits);
 }
 
 // mode 0: prefill shape (64-row tiles, no split; part_* unused).  mode 1: decode shape (16-row tiles,

@@ -481,6 +481,7 @@ USE_ATTENTION_TC = True        # prompt portions with head size 128 take the tcg
 DECODE_SPLIT_KEYS = 128        # keys per split of the decode shape: a constant, so that a request's
                                # result never depends on the batch around it
 DECODE_MAX_Q = 8               # requests with at most this many tokens in the step take the decode shape
+DECODE_ROWS = 8                # (token, head) rows of a decode tile: 8 takes the kernel with the keys as the M side
 DECODE_VARIANT = 0             # 0: chosen by the number of CTAs; 1: one warp and a ring of tiles; 2: four warps split the keys
 
 
@@ -491,14 +492,14 @@ class AttentionPlan:
 
     def __init__(self, ctx, H, K, window, device):
         g = H // K
-        self.GHd = min(g, 16)
+        self.GHd = min(g, DECODE_ROWS)
         self.chunks_d = -(-g // self.GHd)
         self.GHp = min(g, 64)
         self.chunks_p = -(-g // self.GHp)
         self.TTp = 64 // self.GHp
         dec = [r for r in range(ctx.n_requests) if ctx.q_lens[r] <= DECODE_MAX_Q]
         pre = [r for r in range(ctx.n_requests) if ctx.q_lens[r] > DECODE_MAX_Q]
-        self.TTd = 1 if all(ctx.q_lens[r] == 1 for r in dec) else max(1, 16 // self.GHd)
+        self.TTd = 1 if all(ctx.q_lens[r] == 1 for r in dec) else max(1, DECODE_ROWS // self.GHd)
         cu = [0]
         for ql in ctx.q_lens:
             cu.append(cu[-1] + ql)
