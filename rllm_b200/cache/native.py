@@ -49,7 +49,7 @@ def host_lib():
         lib.rllm_cache_check_invariants.argtypes = [c_void_p]
         lib.rllm_cache_block_table.argtypes = [c_void_p, c_int64, c_int, POINTER(c_int), c_int, c_int]
         lib.rllm_step_build.argtypes = [c_void_p, c_int, POINTER(c_int64), POINTER(c_int), POINTER(c_int),
-                                        POINTER(c_int), POINTER(c_int), c_int, c_int, c_int, c_void_p, c_int,
+                                        POINTER(c_int), POINTER(c_int), c_int, c_int, c_int, c_int, c_void_p, c_int,
                                         POINTER(c_int), POINTER(c_int), POINTER(c_int)]
         _lib = lib
     return _lib
@@ -217,43 +217,54 @@ class NativeCacheManager(CacheManager):
             raise AssertionError("request handles out of step with the native cache")
 
     # ---- the step builder
-    def build_step(self, items, vocab: int, out: torch.Tensor, pad_requests: int = 0, pad_width: int = 0):
+    def build_step(self, items, vocab: int, out: torch.Tensor, pad_requests: int = 0, pad_width: int = 0,
+                   pad_quantum: int = 0):
         """Appends the items and writes the step's arrays into the pinned int32 tensor `out`.
-        Returns (offsets, meta = (n, R, m, width, total), new_request_flags) or raises; returns
-        None when `out` is too small (nothing appended; meta total tells the size needed)."""
+        Returns (offsets, meta = (n, R, m, width, total, longest), new_request_flags) or raises;
+        returns (None, meta, None) when `out` is too small (nothing appended; meta's total tells the
+        size needed).  pad_quantum: block tables as wide as the longest request rounded up to that
+        many tokens (the padded shape of a captured decode step)."""
         n_items = len(items)
+        ids = self._ids
         created = []
         rids = np.empty(n_items, np.int64)
         for i, it in enumerate(items):
-            if it.request_id not in self._ids:
+            h = ids.get(it.request_id)
+            if h is None:
                 created.append(it.request_id)
-            rids[i] = self._id(it.request_id, create=True)
-        n_tok = np.fromiter((len(it.tokens) for it in items), np.int32, n_items)
-        n_want = np.fromiter((len(it.want) for it in items), np.int32, n_items)
+                h = self._id(it.request_id, create=True)
+            rids[i] = h
         try:
-            toks = np.concatenate([np.asarray(it.tokens, np.int64) for it in items]) if n_items else np.empty(0, np.int64)
+            if all(len(it.tokens) == 1 for it in items):          # decode steps: no per-item arrays
+                n_tok = np.ones(n_items, np.int32)
+                toks = np.fromiter((it.tokens[0] for it in items), np.int64, n_items)
+            else:
+                n_tok = np.fromiter((len(it.tokens) for it in items), np.int32, n_items)
+                toks = np.concatenate([np.asarray(it.tokens, np.int64) for it in items]) if n_items else np.empty(0, np.int64)
             if toks.size and (toks.min() < 0 or toks.max() >= vocab):
                 raise ValueError
             toks = toks.astype(np.int32)
-            want = np.concatenate([np.asarray(it.want, np.int32).reshape(-1) for it in items]) if n_items else np.empty(0, np.int32)
+            n_want = np.fromiter((len(it.want) for it in items), np.int32, n_items)
+            want = np.fromiter((w for it in items for w in it.want), np.int32, int(n_want.sum()))
         except (ValueError, TypeError):
             for r in created:
                 del self._ids[r]
             raise ValueError("bad token ids or wanted places")
         G = len(self.paged)
         offsets = (c_int * (7 + 2 * G))()
-        meta = (c_int * 5)()
+        meta = (c_int * 6)()
         flags = (c_int * max(1, n_items))()
         st = host_lib().rllm_step_build(self._h, n_items, rids.ctypes.data_as(POINTER(c_int64)), _ip(n_tok), _ip(toks),
-                                        _ip(n_want), _ip(np.ascontiguousarray(want, np.int32)), vocab, pad_requests,
-                                        pad_width, c_void_p(out.data_ptr()), out.numel(), offsets, meta, flags)
+                                        _ip(n_want), _ip(want), vocab, pad_requests, pad_width, pad_quantum,
+                                        c_void_p(out.data_ptr()), out.numel(), offsets, meta, flags)
         if st:
             for r in created:
                 del self._ids[r]
             if st == ERR_BUFFER:
                 return None, tuple(meta), None
             self._raise(st, "step")
-        for i, it in enumerate(items):
-            if flags[i] and self.stateful:
-                self._zero_state(it.request_id)
+        if self.stateful:
+            for i, it in enumerate(items):
+                if flags[i]:
+                    self._zero_state(it.request_id)
         return list(offsets), tuple(meta), list(flags)[:n_items]

@@ -255,7 +255,7 @@ API int rllm_cache_block_table(void* c, int64_t rid, int group, int* out, int ca
 // `new_flags[i]` tells whether item i created its request (its state slot must be zeroed).
 API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n_tok, const int* tokens_flat,
                         const int* n_want, const int* want_flat, int vocab, int pad_requests, int pad_width,
-                        int32_t* out, int out_cap, int* offsets, int* meta, int* new_flags) {
+                        int pad_quantum, int32_t* out, int out_cap, int* offsets, int* meta, int* new_flags) {
     Cache* c = static_cast<Cache*>(cv);
     if (n_items <= 0) return ERR_BAD_ARG;
     int n_real = 0, m = 0;
@@ -277,12 +277,16 @@ API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n
     const int n = n_real + (R - n_items);
     if (pad_requests) m = n;
     // table width after the append
-    int width = std::max(1, pad_width);
+    int width = std::max(1, pad_width), longest = 0;
     for (int i = 0; i < n_items; ++i) {
         auto it = c->requests.find(rids[i]);
         const int len = (it == c->requests.end() ? 0 : it->second.length) + n_tok[i];
+        longest = std::max(longest, len);
         width = std::max(width, c->blocks_for(len));
     }
+    // pad_quantum: the tables are as wide as the longest request rounded up to that many tokens
+    if (pad_quantum > 0) width = std::max(width, c->blocks_for((longest + pad_quantum - 1) / pad_quantum * pad_quantum));
+    meta[5] = longest;
     int off = 0, k = 0;
     auto place = [&](int count) { offsets[k++] = off; off += round4(count); return offsets[k - 1]; };
     const int o_tok = place(n), o_pos = place(n), o_seq = place(n), o_cu = place(R + 1), o_ctx = place(R),

@@ -17,6 +17,7 @@ the same pre-checks before any mutation (86-100); graph replay keyed by the step
 """
 from __future__ import annotations
 
+import math
 from typing import Optional, Sequence
 
 import numpy as np
@@ -50,11 +51,11 @@ class _Layout:
         self.shapes, self.offsets, total = list(shapes), [], 0
         for shp in self.shapes:
             self.offsets.append(total)
-            total += (int(np.prod(shp)) + 3) // 4 * 4
+            total += (math.prod(shp) + 3) // 4 * 4
         self.total = max(total, 4)
 
     def views(self, flat: torch.Tensor):
-        return [flat[o:o + int(np.prod(s))].view(s) for s, o in zip(self.shapes, self.offsets)]
+        return [flat[o:o + math.prod(s)].view(s) for s, o in zip(self.shapes, self.offsets)]
 
 
 class _DecodeGraph:
@@ -88,6 +89,7 @@ class Engine:
         self.cache = manager(needs, cache_of, block_size, max_tokens, max_requests)
         self.cache.allocate_device(self.runtime.device, self.runtime.dtype)
         self.block_size = block_size
+        self._windowed = any(g.need.window > 0 for g in self.cache.paged)     # only then do pages fall out of reach
         self.use_graphs = use_graphs and not profiler.enabled()    # events cannot be recorded into a capture
         self._graphs: dict = {}
         self._staging = []
@@ -129,15 +131,11 @@ class Engine:
             arrays, meta = self._arrays(items, pad_requests, pad_width)
             layout = _Layout([a.shape for a in arrays])
             return self._stage(arrays, layout), layout, meta
-        guess = 4096
-        while True:
-            buf = self._staging_buffer(guess)
-            offsets, m, _ = self.cache.build_step(items, self.vocab_size, buf, pad_requests, pad_width)
-            if offsets is not None:
-                break
-            self._staging_next = self._staged            # the buffer was not used: hand it out again
-            guess = m[4]
-        n, R, n_rows, width, total = m
+        return self._finish_build(items, pad_requests, *self._build_native(items, pad_requests, pad_width))
+
+    def _finish_build(self, items, pad_requests: int, buf, offsets, m):
+        """Layout and host-side shape of a step that the C++ builder has written into `buf`."""
+        n, R, n_rows, width, total = m[:5]
         G = len(self.cache.paged)
         shapes = [(n,), (n,), (n,), (R + 1,), (R,), (R,), (n_rows,)] + [(n,)] * G + [(R, width)] * G
         layout = _Layout(shapes)
@@ -152,6 +150,18 @@ class Engine:
         meta = dict(n=n, R=R, q_lens=q_lens, start_pos=start_pos, rows=rows, ctx_lens=ctx_lens)
         self.last_upload_bytes = 4 * total
         return buf[:total], layout, meta
+
+    def _build_native(self, items, pad_requests: int, pad_width: int, pad_quantum: int = 0):
+        """The C++ step builder on the next pinned buffer: (buffer, offsets, (n, R, rows, width, total, longest))."""
+        guess = 4096
+        while True:
+            buf = self._staging_buffer(guess)
+            offsets, m, _ = self.cache.build_step(items, self.vocab_size, buf, pad_requests, pad_width, pad_quantum)
+            if offsets is not None:
+                self.last_upload_bytes = 4 * m[4]
+                return buf, offsets, m
+            self._staging_next = self._staged            # the buffer was not used: hand it out again
+            guess = m[4]
 
     def _copy_in(self, dev: torch.Tensor, host: torch.Tensor) -> None:
         dev.copy_(host, non_blocking=True)
@@ -259,32 +269,54 @@ class Engine:
 
     # ------------------------------------------------------------------ the step
     def step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
-        self._check_items(items)
+        decode_only = bool(items) and all(len(it.tokens) == 1 for it in items)
+        # A decode-only step on the C++ host is checked there (token range, wanted places, a request
+        # named twice, pages: all before anything changes); the Python check runs only to word the
+        # error.  Anything that is not a plain int goes through the Python check first.
+        light = self.native_host and decode_only and all(type(it.tokens[0]) is int for it in items)
+        if not light:
+            self._check_items(items)
         self.stats["steps"] += 1
         self.stats["step_tokens"] += sum(len(it.tokens) for it in items)
-        if (self.use_graphs and len(items) <= GRAPH_MAX_REQUESTS and not self.cache.stateful
-                and all(len(it.tokens) == 1 for it in items)):
-            logits = self._graph_step(items)
+        if self.use_graphs and decode_only and len(items) <= GRAPH_MAX_REQUESTS and not self.cache.stateful:
+            try:
+                logits = self._graph_step(items)
+            except (ValueError, KeyError):
+                if light:
+                    self._check_items(items)         # raises the StepError that names the fault
+                raise
         else:
             host, layout, meta = self._build(items)
             dev = torch.empty(layout.total, dtype=torch.int32, device=self.runtime.device)
             self._copy_in(dev, host)
             ctx, views = self._context(layout.views(dev), meta, bool(meta["rows"]))
             logits = self.model.forward(ctx, views)
-        for it in items:
-            self.cache.release_passed(it.request_id)
+        if self._windowed:
+            for it in items:
+                self.cache.release_passed(it.request_id)
         return logits
 
     def _graph_step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
         R = len(items)
         B = _bucket(R)
-        longest = max((self.cache.length(it.request_id) if self.cache.has(it.request_id) else 0) + 1
-                      for it in items)
-        ctx_pad = -(-longest // GRAPH_CTX_QUANTUM) * GRAPH_CTX_QUANTUM
-        width = -(-ctx_pad // self.block_size)
-        key = (B, ctx_pad)
-        host, layout, meta = self._build(items, pad_requests=B, pad_width=width)
-        g = self._graphs.get(key)
+        if self.native_host:
+            # the C++ builder finds the longest request and pads the tables itself: one call per step
+            buf, offsets, m = self._build_native(items, B, 0, GRAPH_CTX_QUANTUM)
+            ctx_pad = -(-m[5] // GRAPH_CTX_QUANTUM) * GRAPH_CTX_QUANTUM
+            key = (B, ctx_pad)
+            g = self._graphs.get(key)
+            if g is None:
+                host, layout, meta = self._finish_build(items, B, buf, offsets, m)
+            else:
+                host, layout, meta = buf[:m[4]], None, None
+                assert offsets == g.layout.offsets
+        else:
+            longest = max((self.cache.length(it.request_id) if self.cache.has(it.request_id) else 0) + 1
+                          for it in items)
+            ctx_pad = -(-longest // GRAPH_CTX_QUANTUM) * GRAPH_CTX_QUANTUM
+            key = (B, ctx_pad)
+            host, layout, meta = self._build(items, pad_requests=B, pad_width=-(-ctx_pad // self.block_size))
+            g = self._graphs.get(key)
         if g is None:
             g = self._graphs[key] = _DecodeGraph()
             g.layout = layout
@@ -292,7 +324,8 @@ class Engine:
             # host-side shape of the step as the graph sees it: every request at the padded length
             meta_pad = dict(meta, start_pos=[ctx_pad - 1] * B, ctx_lens=[ctx_pad] * B, q_lens=[1] * B)
             g.ctx, g.views = self._context(g.layout.views(g.static), meta_pad, True)
-        assert layout.offsets == g.layout.offsets
+        elif layout is not None:
+            assert layout.offsets == g.layout.offsets
         self._copy_in(g.static, host)
         g.uses += 1
         if g.uses == 1:
@@ -310,7 +343,7 @@ class Engine:
                 ops.add_launches(g.launches)
             g.graph.replay()
             self.stats["graph_replays"] += 1
-        rows = meta["rows"]
+        rows = [i for i, it in enumerate(items) for _ in it.want]      # one token each: its row is the item's index
         if not rows:
             return None
         if rows == list(range(R)):

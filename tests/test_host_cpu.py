@@ -520,8 +520,8 @@ def test_native_step_builder_arrays():
     buf = torch.zeros(4096, dtype=torch.int32)
     nat.append("a", 6)
     items = [StepItem("a", [5, 6, 7], [0, 2]), StepItem("b", [9], []), StepItem("c", [1, 2, 3, 4, 5], [4])]
-    off, (n, R, m, width, total), flags = nat.build_step(items, 100, buf)
-    assert (n, R, m, width) == (9, 3, 3, 3) and flags == [0, 1, 1] and all(o % 4 == 0 for o in off)
+    off, (n, R, m, width, total, longest), flags = nat.build_step(items, 100, buf)
+    assert (n, R, m, width, longest) == (9, 3, 3, 3, 9) and flags == [0, 1, 1] and all(o % 4 == 0 for o in off)
     a = buf.numpy()
     assert a[off[0]:off[0] + n].tolist() == [5, 6, 7, 9, 1, 2, 3, 4, 5]
     assert a[off[1]:off[1] + n].tolist() == [6, 7, 8, 0, 0, 1, 2, 3, 4]
@@ -551,10 +551,14 @@ def test_native_step_builder_arrays():
     off2, meta2, _ = nat.build_step([StepItem("a", [1, 2], [1])], 100, small)
     assert off2 is None and meta2[4] > 8 and nat.length("a") == 9
     # padded decode step
-    off, (n, R, m, width, total), _ = nat.build_step([StepItem("a", [3], [0]), StepItem("b", [4], [0])], 100, buf,
-                                                     pad_requests=4, pad_width=16)
+    off, (n, R, m, width, total, longest), _ = nat.build_step([StepItem("a", [3], [0]), StepItem("b", [4], [0])],
+                                                              100, buf, pad_requests=4, pad_width=16)
     a = buf.numpy()
-    assert (n, R, m, width) == (4, 4, 4, 16)
+    assert (n, R, m, width, longest) == (4, 4, 4, 16, 10)
     assert a[off[0]:off[0] + 4].tolist() == [3, 4, 0, 0] and a[off[1]:off[1] + 4].tolist() == [9, 1, 0, 0]
     assert a[off[7]:off[7] + 4].tolist()[2:] == [-1, -1] and a[off[6]:off[6] + 4].tolist() == [0, 1, 2, 3]
+    # the builder pads the tables itself to the longest request rounded up to a quantum of tokens
+    off, meta3, _ = nat.build_step([StepItem("a", [3], [0]), StepItem("b", [4], [])], 100, buf, pad_requests=2,
+                                   pad_quantum=32)
+    assert meta3[5] == 11 and meta3[3] == 32 // 4
     nat.check_invariants()
