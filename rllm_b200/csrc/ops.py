@@ -406,9 +406,14 @@ USE_STREAM = True
 STREAM_MIN_WEIGHTS = 1 << 23      # below 16 MB of weights the short-lived CTAs of skinny_gemm start faster
 
 
-def _prefer_stream(a, w, n: int) -> bool:
+def _prefer_stream(a, w, n: int, swiglu: bool = False) -> bool:
+    """gemv_stream takes up to 8 rows always, and 9 to 16 rows for the layer's plain products; with
+    9 to 16 rows the gate/up product and the LM head are faster on the tcgen05 kernel (measured
+    inside the decode step at batch 9, 12 and 16: 3 to 7 % of the step)."""
     m, k = a.shape
-    return (USE_STREAM and m <= 8 and k % 64 == 0 and n * k >= STREAM_MIN_WEIGHTS and _tc_ok(a, w))
+    if not USE_STREAM or k % 64 or n * k < STREAM_MIN_WEIGHTS or not _tc_ok(a, w):
+        return False
+    return m <= 8 or (m <= STREAM_MAX_ROWS and not swiglu and n * k < (1 << 27))
 
 
 def _prefer_tc_swap(m: int, n: int, k: int, swiglu: bool = False) -> bool:
@@ -465,7 +470,7 @@ def gate_up_swiglu(h, w_gate_up, out):
     m = h.shape[0]
     F = out.shape[1]
     if _skinny_ok(h, w_gate_up):
-        if _prefer_stream(h, w_gate_up, 2 * F):
+        if _prefer_stream(h, w_gate_up, 2 * F, swiglu=True):
             return gemv_stream(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
         if _prefer_tc_swap(m, 2 * F, h.shape[1], swiglu=True):
             return skinny_gemm_tc(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
