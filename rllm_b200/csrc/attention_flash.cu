@@ -369,8 +369,9 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
     constexpr int DT = HD / 16;                   // blocks of 16 head dims
     extern __shared__ __align__(128) unsigned char smem[];   // [NS stages][K tile, V tile]
     const int lane = threadIdx.x, g = lane >> 2, t = lane & 3;
-    pdl_wait();
-
+    // No griddepcontrol.wait yet: the tiles, positions and block tables were uploaded before the
+    // step's first kernel, and the keys of earlier steps are in the cache; only the queries and
+    // this step's own keys come from the kernels before (see below).
     const int tile = blockIdx.x;
     const int req = p.tile_req[tile], tok0 = p.tile_tok0[tile];
     const int nt = min(p.TT, p.cu_q[req + 1] - tok0);
@@ -402,6 +403,7 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
         hic[x] = min(pos + 1, ke);
     }
     if (kb >= ke) {                                // an empty split: mark it so
+        pdl_wait();                                // the partials of the layer before may still be read
         if (p.split_keys > 0 && g == 0) {
 #pragma unroll
             for (int x = 0; x < 2; ++x)
@@ -413,25 +415,42 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
         return;
     }
 
-    // Q as the B operand: column g is query row g
-    uint32_t qf[DT][2];
-    {
-        const int tlq = g / p.GH, hlq = g % p.GH;
-        const bool validq = tlq < nt && hlq < nh;
-        const bf16* qr = p.q + ((size_t)(tok0 + (validq ? tlq : 0)) * p.H + head0 + (validq ? hlq : 0)) * HD;
-#pragma unroll
-        for (int ks = 0; ks < DT; ++ks) {
-            qf[ks][0] = validq ? *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 2 * t) : 0u;
-            qf[ks][1] = validq ? *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 8 + 2 * t) : 0u;
-        }
-    }
-
     const int* table = p.block_table + (size_t)req * p.table_stride;
     constexpr int ROWS_PER_PASS = 32 / CH;
     static_assert(32 % CH == 0, "a warp must cover whole rows of chunks");
     const int my_chunk = lane % CH, my_row0 = lane / CH;
     const int last_blk = (ke - 1) / p.bs;
+    // Fast path (page size a power of two and at least a tile): a tile lies in one page, so one
+    // table look-up and one base address per tile; this lane's rows are my_row0 + i * ROWS_PER_PASS,
+    // their swizzled positions are fixed and kept in registers.
+    constexpr int MY_ROWS = BN / ROWS_PER_PASS;
+    const bool one_page = (p.bs & (p.bs - 1)) == 0 && p.bs >= BN;
+    const int bs_shift = __ffs(p.bs) - 1;
+    uint32_t dst_off[MY_ROWS];
+#pragma unroll
+    for (int i = 0; i < MY_ROWS; ++i) {
+        const int row = my_row0 + i * ROWS_PER_PASS;
+        dst_off[i] = row * (HD * 2) + ((my_chunk ^ (row & 7)) << 4);
+    }
+    const uint32_t smem_base = smem_u32(smem);
     auto load_tile = [&](int stage, int kt) {
+        if (one_page) {
+            const int blk = kt >> bs_shift, off0 = kt & (p.bs - 1);
+            const int page = table[min(blk, last_blk)];
+            const size_t base = (((size_t)page * p.K + kvh) * p.bs + off0 + my_row0) * HD + my_chunk * 8;
+            const bf16* ksrc = p.k_cache + base;
+            const bf16* vsrc = p.v_cache + base;
+            const uint32_t sk = smem_base + stage * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
+            const int left = ke - kt - my_row0;             // rows i with i * ROWS_PER_PASS < left exist
+#pragma unroll
+            for (int i = 0; i < MY_ROWS; ++i) {
+                const bool ok = i * ROWS_PER_PASS < left;   // beyond the range: zero fill, any valid address
+                const int src = ok ? i * ROWS_PER_PASS * HD : 0;
+                cp_async16(sk + dst_off[i], ksrc + src, ok ? 16 : 0);
+                cp_async16(sv + dst_off[i], vsrc + src, ok ? 16 : 0);
+            }
+            return;
+        }
         unsigned char* sk = smem + (size_t)stage * 2 * TILE_BYTES;
         unsigned char* sv = sk + TILE_BYTES;
         int row0 = 0;
@@ -462,11 +481,39 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
     float mx[2] = {-INFINITY, -INFINITY}, lsum[2] = {0.f, 0.f};
 
     const int n_tiles = (ke - kb + BN - 1) / BN;
+    // The first NS - 1 tiles are requested before the wait when they hold keys of earlier steps
+    // only (all splits of a request but its last one or two): the kernel starts while the one
+    // before it still runs, and its first memory round trip is over when that one ends.
+    const int written_from = p.positions[p.cu_q[req]];          // first position this step writes for the request
+    const bool ahead = kb + min(n_tiles, NS - 1) * BN <= written_from;
+    if (ahead) {
 #pragma unroll
-    for (int i = 0; i < NS - 1; ++i) {             // NS - 1 tiles ahead; empty groups keep the count uniform
-        if (i < n_tiles) load_tile(i, kb + i * BN);
-        cp_async_commit();
+        for (int i = 0; i < NS - 1; ++i) {         // NS - 1 tiles ahead; empty groups keep the count uniform
+            if (i < n_tiles) load_tile(i, kb + i * BN);
+            cp_async_commit();
+        }
     }
+    pdl_wait();
+    if (!ahead) {
+#pragma unroll
+        for (int i = 0; i < NS - 1; ++i) {
+            if (i < n_tiles) load_tile(i, kb + i * BN);
+            cp_async_commit();
+        }
+    }
+    // Q as the B operand: column g is query row g
+    uint32_t qf[DT][2];
+    {
+        const int tlq = g / p.GH, hlq = g % p.GH;
+        const bool validq = tlq < nt && hlq < nh;
+        const bf16* qr = p.q + ((size_t)(tok0 + (validq ? tlq : 0)) * p.H + head0 + (validq ? hlq : 0)) * HD;
+#pragma unroll
+        for (int ks = 0; ks < DT; ++ks) {
+            qf[ks][0] = validq ? *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 2 * t) : 0u;
+            qf[ks][1] = validq ? *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+
     // ldmatrix lane roles.  K (A of S^T, no transpose): matrices (keys 0-7 | 8-15) x (d 0-7 | 8-15).
     // V (A of O^T, transposed): matrices (d 0-7 | 8-15) x (keys 0-7 | 8-15).
     const int mat = lane >> 3, ri = lane & 7;
@@ -534,8 +581,10 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
         }
         lsum[0] = lsum[0] * al[0] + rs[0];          // this lane's share of the keys; summed over lanes at the end
         lsum[1] = lsum[1] * al[1] + rs[1];
+        if (__any_sync(0xffffffffu, al[0] != 1.f || al[1] != 1.f)) {       // the maxima seldom move after the first tiles
 #pragma unroll
-        for (int j = 0; j < DT; ++j) { o[j][0] *= al[0]; o[j][1] *= al[1]; o[j][2] *= al[0]; o[j][3] *= al[1]; }
+            for (int j = 0; j < DT; ++j) { o[j][0] *= al[0]; o[j][1] *= al[1]; o[j][2] *= al[0]; o[j][3] *= al[1]; }
+        }
         // ---- O^T += V^T P^T
 #pragma unroll
         for (int j = 0; j < KB; ++j) {
