@@ -367,15 +367,25 @@ def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None
 
 
 STREAM_MAX_ROWS = 16
-N_SM = 148
+_n_sm: dict = {}
 
 
-def stream_plan(n: int, k: int, swiglu: bool = False):
-    """(CTAs, ring stages) of gemv_stream for n output rows on 148 SMs: three CTAs of three stages
-    per SM when each still gets three and more boxes of 8 rows, else two."""
+def sm_count(device=None) -> int:
+    """Number of SMs of the device (148 on a B200), looked up once."""
+    key = torch.device(device).index if device is not None else torch.cuda.current_device()
+    key = key or 0
+    if key not in _n_sm:
+        _n_sm[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _n_sm[key]
+
+
+def stream_plan(n: int, k: int, swiglu: bool = False, n_sm: int = 148):
+    """(CTAs, ring stages) of gemv_stream for n output rows: three CTAs of three stages per SM when
+    each still gets three and more boxes of 8 rows, else two (measured inside the decode step of
+    the 8B layer sizes: 444 x 3 for gate/up and the LM head, 296 x 3 for QKV, O and down)."""
     boxes = -(-n // 8) * (2 if swiglu else 1)
-    per_sm = 3 if boxes >= 3 * 3 * N_SM else 2
-    return per_sm * N_SM, 3
+    per_sm = 3 if boxes >= 3 * 3 * n_sm else 2
+    return per_sm * n_sm, 3
 
 
 def gemv_stream(a, w, out, epilogue=EPI_STORE, up_row_offset=0, grid=None, stages=None):
@@ -392,7 +402,7 @@ def gemv_stream(a, w, out, epilogue=EPI_STORE, up_row_offset=0, grid=None, stage
     else:
         assert w.shape[0] == n
     assert out.stride(1) == 1 and w.shape[1] == k
-    plan = stream_plan(n, k, epilogue == EPI_SWIGLU)
+    plan = stream_plan(n, k, epilogue == EPI_SWIGLU, sm_count(a.device))
     st = _lib("stream").rllm_gemv_stream(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
         c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
