@@ -432,6 +432,135 @@ def test_toy_stateful_mixer_registers_and_steps(tmp_path):
     assert rel_err(again["y", 20], first["x", 20]) < 1e-6
 
 
+def test_toy_routed_ffn_and_other_position_encoding(tmp_path):
+    """A feed-forward that routes every token to one of several experts, and a position encoding
+    other than the model family's (rotary with interpolated positions), both defined here:
+    registered, chosen by a configuration layer by layer beside the framework's own parts, built,
+    loaded from a model folder and stepped, with no change to the framework's files.  Never a
+    model of anyone's: two layers of toys."""
+    from rllm_b200.config import (LayerSpec, ModelConfig, ModelSpec, PartSpec, RunEntry, load_config,
+                                  register_architecture)
+    from rllm_b200.engine import Engine
+    from rllm_b200.models.model import expected_tensors, load_model
+    from rllm_b200.parts import FeedForward, Part, register_part
+    from rllm_b200.weights import write_safetensors
+
+    chosen = []
+
+    @register_part("ffn", "toy_top1_experts")
+    class ToyTop1Experts(FeedForward):
+        """out_t = W2[e_t] relu(W1[e_t] x_t) with e_t = argmax(router x_t); router logits in float32."""
+
+        def __init__(self, params, prefix, runtime):
+            super().__init__(params, prefix, runtime)
+            self.d, self.f, self.e = params["hidden_size"], params["expert_size"], params["num_experts"]
+
+        def expected_tensors(self):
+            return {self.prefix + "router.weight": ((self.e, self.d), "matrix"),
+                    self.prefix + "w1": ((self.e, self.f, self.d), "matrix"),
+                    self.prefix + "w2": ((self.e, self.d, self.f), "matrix")}
+
+        def load(self, tensors):
+            self.router = self._to_device(tensors[self.prefix + "router.weight"], torch.float32)
+            self.w1 = self._to_device(tensors[self.prefix + "w1"], torch.float32)
+            self.w2 = self._to_device(tensors[self.prefix + "w2"], torch.float32)
+
+        def forward(self, h, ctx=None, residual=None):
+            x = h.float()
+            e = (x @ self.router.t()).argmax(-1)
+            chosen.extend(e.tolist())
+            hid = torch.relu(torch.einsum("tfd,td->tf", self.w1[e], x))
+            out = torch.einsum("tdf,tf->td", self.w2[e], hid)
+            if residual is not None:
+                residual += out
+                return None
+            return out
+
+    @register_part("position", "toy_rotary_interpolated")
+    class ToyRotaryInterpolated(Part):
+        """Rotate-half rotary with positions divided by `factor`: the same table interface as the
+        family's own rotary part (a float32 inv_freq vector), so the attention kernel takes it as is."""
+
+        def __init__(self, params, prefix, runtime):
+            super().__init__(params, prefix, runtime)
+            hd, theta, factor = params["head_dim"], params["theta"], params["factor"]
+            i = torch.arange(0, hd, 2, dtype=torch.float32)
+            self.inv_freq = (1.0 / torch.pow(torch.tensor(float(theta)), i / hd) / factor).to(runtime.device)
+
+        def table(self):
+            return self.inv_freq
+
+    @dataclass(frozen=True)
+    class Toy2Config(ModelConfig):
+        hidden: int
+        vocab: int
+        experts: int
+        factor: float
+        architecture: str = "Toy2ForCausalLM"
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["hidden"], d["vocab"], d["experts"], d["factor"])
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], hidden=self.hidden, vocab=self.vocab,
+                        experts=self.experts, factor=self.factor)
+
+        def model_spec(self):
+            norm = lambda p: PartSpec("rms_norm", {"size": self.hidden, "eps": 1e-5}, p)
+            attn = lambda p: PartSpec("attention", {"hidden_size": self.hidden, "num_heads": 3, "num_kv_heads": 3,
+                                                    "head_dim": 16, "qk_norm": True, "qk_norm_eps": 1e-5, "window": 0,
+                                                    "scale": 0.25}, p)
+            routed = lambda p: PartSpec("toy_top1_experts", {"hidden_size": self.hidden, "expert_size": 24,
+                                                             "num_experts": self.experts}, p)
+            dense = lambda p: PartSpec("swiglu", {"hidden_size": self.hidden, "intermediate_size": 40}, p)
+            pos = [PartSpec("toy_rotary_interpolated", {"head_dim": 16, "theta": 1e4, "factor": self.factor}),
+                   PartSpec("rotary_neox", {"head_dim": 16, "theta": 1e4})]
+            layers = tuple(LayerSpec("pre_norm", attn(f"l.{i}.mix."), (routed if i == 0 else dense)(f"l.{i}.mlp."),
+                                     {"mixer": norm(f"l.{i}.n1."), "ffn": norm(f"l.{i}.n2.")}, pos[i]) for i in range(2))
+            return ModelSpec(self.vocab, self.hidden,
+                             PartSpec("embedding", {"vocab_size": self.vocab, "hidden_size": self.hidden}, "emb."),
+                             layers, (RunEntry(0), RunEntry(1)), norm("fn."),
+                             PartSpec("lm_head", {"vocab_size": self.vocab, "hidden_size": self.hidden, "tied_to": None}, "head."),
+                             256)
+
+    register_architecture("Toy2ForCausalLM", Toy2Config)
+
+    def build(factor, sub):
+        cfg = Toy2Config(hidden=48, vocab=61, experts=4, factor=factor)
+        d = tmp_path / sub
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps(cfg.to_dict()))
+        g = torch.Generator().manual_seed(5)
+        tensors = {n: (1 + 0.1 * torch.randn(s, generator=g)) if r == "norm" else 0.3 * torch.randn(s, generator=g)
+                   for n, (s, r) in expected_tensors(cfg.model_spec()).items()}
+        write_safetensors(d / "model.safetensors", tensors)
+        assert isinstance(load_config(d), Toy2Config)
+        return load_model(d, "float32", DEV)[1]
+
+    model = build(4.0, "toy2")
+    a, b = helpers.random_tokens(37, 61, 3), helpers.random_tokens(12, 61, 4)
+    whole = helpers.run_steps(Engine(model, block_size=8, max_tokens=64, max_requests=2),
+                              [{"entries": [{"id": r, "tokens": t, "want": list(range(len(t)))}], "end": [r]}
+                               for r, t in (("a", a), ("b", b))])
+    assert len(set(chosen)) > 1                     # the router sends tokens to different experts
+    cut = helpers.run_steps(Engine(model, block_size=8, max_tokens=64, max_requests=2), [
+        {"entries": [{"id": "a", "tokens": a[:9], "want": list(range(9))}]},
+        {"entries": [{"id": "a", "tokens": a[9:11], "want": [0, 1]}, {"id": "b", "tokens": b[:5], "want": list(range(5))}]},
+        {"entries": [{"id": "a", "tokens": [a[11]], "want": [0]}, {"id": "b", "tokens": b[5:], "want": list(range(7))}], "end": ["b"]},
+        {"entries": [{"id": "a", "tokens": a[12:], "want": list(range(25))}], "end": ["a"]},
+    ])
+    assert set(whole) == set(cut)
+    for key in whole:
+        assert rel_err(cut[key], whole[key]) < 1e-5
+    # the position encoding is really the toy's: factor 1 gives other logits from the second token on
+    # (at position 0 every rotation is the identity), the same weights otherwise
+    plain_pos = helpers.run_steps(Engine(build(1.0, "toy2_f1"), block_size=8, max_tokens=64, max_requests=1),
+                                  [{"entries": [{"id": "a", "tokens": a, "want": [0, 20, 36]}], "end": ["a"]}])
+    assert rel_err(plain_pos["a", 0], whole["a", 0]) < 1e-6
+    assert rel_err(plain_pos["a", 20], whole["a", 20]) > 1e-3 and rel_err(plain_pos["a", 36], whole["a", 36]) > 1e-3
+
+
 # ---------------------------------------------------------------- the command line
 
 def _cli(*args, timeout=600):
