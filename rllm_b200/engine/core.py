@@ -17,6 +17,7 @@ the same pre-checks before any mutation (86-100); graph replay keyed by the step
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Optional, Sequence
 
@@ -92,6 +93,7 @@ class Engine:
         self._windowed = any(g.need.window > 0 for g in self.cache.paged)     # only then do pages fall out of reach
         self.use_graphs = use_graphs and not profiler.enabled()    # events cannot be recorded into a capture
         self._graphs: dict = {}
+        self._graph_pool = None
         self._staging = []
         self._staging_events = []
         self._staging_next = 0
@@ -296,6 +298,26 @@ class Engine:
                 self.cache.release_passed(it.request_id)
         return logits
 
+    @contextlib.contextmanager
+    def _capture(self, graph):
+        """Stream capture into `graph` on a side stream, from the pool that all of this engine's
+        graphs share (only one of them runs at a time, and a step's logits are valid until the next
+        step).  Unlike torch.cuda.graph() it does not empty the caching allocator first: that
+        costs most of a second each time a request grows into a new context bucket, and
+        cudaMalloc calls for a while after."""
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph.capture_begin(pool=self._graph_pool)
+            try:
+                yield
+            finally:
+                graph.capture_end()
+        torch.cuda.current_stream().wait_stream(side)
+
     def _graph_step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
         R = len(items)
         B = _bucket(R)
@@ -335,7 +357,7 @@ class Engine:
             if g.graph is None:
                 before = ops.launch_count()
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
+                with self._capture(graph):
                     g.logits = self.model.forward(g.ctx, g.views)
                 g.graph, g.launches = graph, ops.launch_count() - before
                 self.stats["graphs_captured"] += 1
