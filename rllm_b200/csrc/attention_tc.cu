@@ -54,6 +54,14 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t 
     return ((uint64_t)hi << 32) | lo;
 }
 
+// 2^x by the special-function unit alone (two units in the last place of float32, far below the
+// bfloat16 rounding of P that follows); exp2f() costs several instructions more for denormal results.
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
@@ -233,26 +241,34 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 break;
             }
             tc_fence_after();
+            // the whole row of scores with one wait: four loads of 32 columns in flight together
+            uint32_t rr[AT_BN / 32][32];
+#pragma unroll
+            for (int c0 = 0; c0 < AT_BN / 32; ++c0) tmem_ld32(tS0 + b * AT_BN + lane_base + c0 * 32, rr[c0]);
+            tmem_ld_wait();
             float sv[AT_BN];
 #pragma unroll
-            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
-                uint32_t rr[32];
-                tmem_ld32(tS0 + b * AT_BN + lane_base + c0, rr);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sv[c0 + i] = __uint_as_float(rr[i]);
-            }
+            for (int c = 0; c < AT_BN; ++c) sv[c] = __uint_as_float(rr[c >> 5][c & 31]);
             tc_fence_before();
             mbar_arrive(&s_empty[b]);
+            // The maximum is taken over the raw scores (the scale is positive) and the scale goes into
+            // the exponent's multiply-add: one FFMA and one MUFU per score.  The softmax warps have one
+            // warp per scheduler to themselves, so their instruction stream is what a key tile costs
+            // until the tiles come in from L2 no faster (two warps per scheduler, each thread half a
+            // row, was tried and gave nothing more).
             const bool need_mask = (kt + AT_BN > pos_r + 1) || (kt < first_r);
             float mx = -INFINITY;
+            if (need_mask) {
 #pragma unroll
-            for (int c = 0; c < AT_BN; ++c) {
-                float v = sv[c] * p.scale_log2;
-                if (need_mask && (kt + c > pos_r || kt + c < first_r)) v = -INFINITY;
-                sv[c] = v;
-                mx = fmaxf(mx, v);
+                for (int c = 0; c < AT_BN; ++c) {
+                    if (kt + c > pos_r || kt + c < first_r) sv[c] = -INFINITY;
+                    mx = fmaxf(mx, sv[c]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < AT_BN; ++c) mx = fmaxf(mx, sv[c]);
             }
+            mx *= p.scale_log2;
             float alpha = 1.f;
             bool rescale = false;
             if (m_ref == -INFINITY) m_ref = mx;                          // nothing accumulated yet for this row
@@ -284,7 +300,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int ch = 0; ch < 16; ++ch) {                             // 16 chunks of 8 keys = 16 bytes
                 float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { e[i] = exp2f(sv[ch * 8 + i] - mref); sum += e[i]; }
+                for (int i = 0; i < 8; ++i) { e[i] = ex2_approx(fmaf(sv[ch * 8 + i], p.scale_log2, -mref)); sum += e[i]; }
                 uint4 u;
                 __nv_bfloat162 p0 = __floats2bfloat162_rn(e[0], e[1]), p1 = __floats2bfloat162_rn(e[2], e[3]);
                 __nv_bfloat162 p2 = __floats2bfloat162_rn(e[4], e[5]), p3 = __floats2bfloat162_rn(e[6], e[7]);
