@@ -110,6 +110,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: Qwen3-8B (default), 0.6B or 32B")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--block-size", type=int, default=32, help="tokens per page of the KV cache")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
     ap.add_argument("--profile", choices=["decode", "prefill"],
@@ -146,7 +147,7 @@ def main():
 
     def decode_run(batch, steps, warmup):
         """Prefills `batch` prompts of PROMPT tokens, then times `steps` decode steps."""
-        eng = Engine(model, block_size=16, max_tokens=batch * CTX, max_requests=batch)
+        eng = Engine(model, block_size=a.block_size, max_tokens=batch * CTX, max_requests=batch)
         prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(batch)]
         for b in range(batch):                       # prefill in portions of 512, one request at a time
             for c in range(0, PROMPT, 512):
@@ -187,7 +188,7 @@ def main():
         decode step is the difference between a run that generates warmup + steps tokens and one
         that generates warmup tokens, over `steps` (wall clock, synchronized on both sides)."""
         from rllm_b200 import LLM
-        llm = LLM(model, ctx=CTX, block_size=16, prefill_chunk=batch * PROMPT, parallel=batch, kv_tokens=batch * CTX)
+        llm = LLM(model, ctx=CTX, block_size=a.block_size, prefill_chunk=batch * PROMPT, parallel=batch, kv_tokens=batch * CTX)
         prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(batch)]
 
         def timed(n_tokens):
@@ -208,7 +209,7 @@ def main():
         return {"ms": ms, "tok_s": batch * 1000.0 / ms, "h2d": staging, "d2h": 4 * batch}
 
     if a.profile:
-        eng = Engine(model, block_size=16, max_tokens=a.batch * CTX, max_requests=a.batch)
+        eng = Engine(model, block_size=a.block_size, max_tokens=a.batch * CTX, max_requests=a.batch)
         prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(a.batch)]
         if a.profile == "prefill":
             eng.step([StepItem(0, prompts[0], [PROMPT - 1])])          # warm-up
@@ -247,7 +248,7 @@ def main():
                    "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
                    "intermediate": config.intermediate_size,
                    "vocab": V, "global_batch": a.batch, "seq_len": CTX, "prompt_len": PROMPT,
-                   "kv_block": 16, "parallelism": "single GPU",
+                   "kv_block": a.block_size, "parallelism": "single GPU",
                    "l2": "no flush: each step streams %.1f GB of weights (> 126 MB L2)" % (wbytes / 1e9),
                    "peaks": pk["source"]},
         "clocks": clk,
@@ -260,7 +261,7 @@ def main():
     }
     if not a.skip_points:
         # prefill of 2,048 tokens in one step
-        eng = Engine(model, block_size=16, max_tokens=CTX, max_requests=1)
+        eng = Engine(model, block_size=a.block_size, max_tokens=CTX, max_requests=1)
         toks = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
         times = []
         for rep in range(4):

@@ -1,7 +1,7 @@
 """Command line in the manner of AxiomOperator/rllm's ``rllm`` (crates/rllm-cli/src/main.rs:24-237):
 
   rllm run MODEL PROMPT [-n/--max-tokens 256] [-t/--temperature 0] [--top-k 0] [--top-p 1.0]
-                        [--seed 0] [--ctx 4096] [--block-size 16] [--prefill-chunk 512]
+                        [--seed 0] [--ctx 4096] [--block-size 32] [--prefill-chunk 512]
                         [--kv-type bf16|f32] [--show-ids]
   rllm bench MODEL [-p/--n-prompt 512] [-n/--n-gen 128] [-r/--reps 3] [--depth 0] [-b/--batch 1]
   rllm compare MODEL PROMPT [-n/--steps 32]      engine float32 against engine bfloat16, same tokens
@@ -148,7 +148,7 @@ def main(argv=None) -> int:
     def common(p):
         p.add_argument("model")
         p.add_argument("-d", "--device", default="cuda:0")
-        p.add_argument("--block-size", type=int, default=16)
+        p.add_argument("--block-size", type=int, default=32)
         p.add_argument("--kv-type", default="bf16", choices=["bf16", "f32", "bfloat16", "float32"])
 
     p = sub.add_parser("run"); common(p)

@@ -54,6 +54,17 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t 
     return ((uint64_t)hi << 32) | lo;
 }
 
+// tcgen05.mma with the A operand in tensor memory (rows = lanes, two bfloat16 per 32-bit column) and B
+// from shared memory: the P.V product reads P where the softmax threads left it.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // 2^x by the special-function unit alone (two units in the last place of float32, far below the
 // bfloat16 rounding of P that follows); exp2f() costs several instructions more for denormal results.
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -68,9 +79,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = smem;                               // 32 KB
-    unsigned char* sP = smem + AT_TILE_BYTES;               // 32 KB
-    unsigned char* sK = smem + 2 * AT_TILE_BYTES;           // 2 x 32 KB
-    unsigned char* sV = smem + 4 * AT_TILE_BYTES;           // 2 x 32 KB
+    unsigned char* sK = smem + AT_TILE_BYTES;               // 2 x 32 KB
+    unsigned char* sV = smem + 3 * AT_TILE_BYTES;           // 2 x 32 KB
     __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2],
         p_full, p_empty;
     __shared__ uint32_t tmem_base_slot;
@@ -182,7 +192,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         constexpr uint32_t idesc_o = idesc_bf16(AT_BM, AT_HD) | (1u << 16);    // V is MN-major
         bool ok = mbar_wait(&q_full, 0, &abort_flag);
         if (!ok && !abort_flag) { atomicExch(p.err, AT_ERR_Q); abort_flag = 1; }
-        const uint32_t q_addr = s_addr(sQ), p_addr = s_addr(sP);
+        const uint32_t q_addr = s_addr(sQ);
         auto issue_qk = [&](int j) -> bool {
             const int s = j & 1;
             const uint32_t ph = (j >> 1) & 1;
@@ -208,9 +218,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tc_fence_after();
             const uint32_t v_addr = s_addr(sV + s * AT_TILE_BYTES);
 #pragma unroll
-            for (int k8 = 0; k8 < 8; ++k8)        // 16 keys a step: P advances 32 bytes inside its half, V 16 rows
-                umma_bf16(tO, smem_desc_sw128(p_addr + (k8 >> 2) * AT_HALF_BYTES) + 2 * (k8 & 3),
-                          smem_desc_sw128_mn(v_addr + k8 * 16 * 128, AT_HALF_BYTES), idesc_o, (j | k8) != 0);
+            for (int k8 = 0; k8 < 8; ++k8)        // 16 keys a step: P advances 8 columns (two keys a column), V 16 rows
+                umma_bf16_ts(tO, tS0 + s * AT_BN + k8 * 8, smem_desc_sw128_mn(v_addr + k8 * 16 * 128, AT_HALF_BYTES),
+                             idesc_o, (j | k8) != 0);
             umma_commit(&v_empty[s]);
             umma_commit(&p_empty);
             return true;
@@ -273,44 +283,46 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             bool rescale = false;
             if (m_ref == -INFINITY) m_ref = mx;                          // nothing accumulated yet for this row
             else if (mx > m_ref + 8.f) { alpha = exp2f(m_ref - mx); m_ref = mx; rescale = true; }
-            // P of the tile before must have been read (and O updated) before P and O are touched
-            if (j > 0 && !mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
-                if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
-                ok = false;
-                break;
-            }
+            // P goes to tensor memory over this tile's own scores (columns 0-63 of S[b], read above),
+            // where nothing else is pending: S[b] was written by Q.K^T of this tile, which the tensor
+            // pipe ran after P.V of tile j-2.  Only O is shared with the products in flight: it is
+            // rescaled after P.V of the tile before has completed.
             // tcgen05.ld / st are warp-wide: the whole warp goes through when any of its rows rescales
             if (__any_sync(0xffffffffu, rescale)) {
+                if (j > 0 && !mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
+                    if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
+                    ok = false;
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
                 tc_fence_after();
                 l *= alpha;
 #pragma unroll
                 for (int c0 = 0; c0 < AT_HD; c0 += 32) {
-                    uint32_t rr[32];
-                    tmem_ld32(tO + lane_base + c0, rr);
+                    uint32_t rr2[32];
+                    tmem_ld32(tO + lane_base + c0, rr2);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
-                    tmem_st32(tO + lane_base + c0, rr);
+                    for (int i = 0; i < 32; ++i) rr2[i] = __float_as_uint(__uint_as_float(rr2[i]) * alpha);
+                    tmem_st32(tO + lane_base + c0, rr2);
                 }
                 tmem_st_wait();
             }
             const float mref = m_ref == -INFINITY ? 0.f : m_ref;
             float sum = 0.f;
+            uint32_t pk[AT_BN / 64][32];                                   // the row's P, two keys per word
 #pragma unroll
-            for (int ch = 0; ch < 16; ++ch) {                             // 16 chunks of 8 keys = 16 bytes
-                float e[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { e[i] = ex2_approx(fmaf(sv[ch * 8 + i], p.scale_log2, -mref)); sum += e[i]; }
-                uint4 u;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(e[0], e[1]), p1 = __floats2bfloat162_rn(e[2], e[3]);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(e[4], e[5]), p3 = __floats2bfloat162_rn(e[6], e[7]);
-                u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
-                u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
-                unsigned char* dst = sP + (ch >> 3) * AT_HALF_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) = u;
+            for (int c = 0; c < AT_BN; c += 2) {
+                const float e0 = ex2_approx(fmaf(sv[c], p.scale_log2, -mref));
+                const float e1 = ex2_approx(fmaf(sv[c + 1], p.scale_log2, -mref));
+                sum += e0 + e1;
+                __nv_bfloat162 pp = __floats2bfloat162_rn(e0, e1);
+                pk[c >> 6][(c >> 1) & 31] = *reinterpret_cast<uint32_t*>(&pp);
             }
             l += sum;
-            fence_async_smem();                                            // P visible to the tensor core's reads
+#pragma unroll
+            for (int c0 = 0; c0 < AT_BN / 64; ++c0) tmem_st32(tS0 + b * AT_BN + lane_base + c0 * 32, pk[c0]);
+            tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&p_full);
         }
@@ -384,7 +396,7 @@ RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v
     p.out = (bf16*)out; p.positions = positions; p.cu_q = cu_q; p.block_table = block_table; p.tile_req = tile_req;
     p.tile_tok0 = tile_tok0; p.table_stride = table_stride; p.H = H; p.K = K; p.bs = bs; p.window = window; p.TT = TT;
     p.g = g; p.n_tiles = n_tiles; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
-    constexpr int smem = 6 * AT_TILE_BYTES + 1024;
+    constexpr int smem = 5 * AT_TILE_BYTES + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -72,7 +72,7 @@ class _DecodeGraph:
 
 
 class Engine:
-    def __init__(self, model, block_size: int = 16, max_tokens: int = 4096, max_requests: int = 64,
+    def __init__(self, model, block_size: int = 32, max_tokens: int = 4096, max_requests: int = 64,
                  use_graphs: bool = True, native_host: bool = True):
         """`native_host`: page accounting and the step's index arrays are built by the C++ host
         runtime (default); False keeps them in Python (same results, slower)."""

@@ -2,7 +2,7 @@
 
 Token ids in, token ids out (the engine has no tokenizer).  Options carry AxiomOperator/rllm's
 names and meanings where it has them (crates/rllm-cli/src/main.rs:39-110, 195-237):
-``ctx`` (context per request, default 4096), ``block_size`` (16), ``prefill_chunk`` (512),
+``ctx`` (context per request, default 4096), ``block_size`` (32 tokens per page; the reference defaults to 16, here a page is a TMA box and 32 halves the copies per key tile), ``prefill_chunk`` (512),
 ``parallel`` (requests running at once, 4), ``kv_tokens`` (tokens the cache holds, default
 ctx * parallel), ``max_tokens`` (256), ``temperature`` (0 = greedy), ``top_k`` (0 = off),
 ``top_p`` (1.0 = off), ``seed`` (0), ``host_sampling`` (sample on the host from copied logits
@@ -24,7 +24,7 @@ from .sampling.params import SamplingParams
 
 
 class LLM:
-    def __init__(self, model, dtype="bfloat16", device="cuda:0", ctx: int = 4096, block_size: int = 16,
+    def __init__(self, model, dtype="bfloat16", device="cuda:0", ctx: int = 4096, block_size: int = 32,
                  prefill_chunk: int = 512, parallel: int = 4, kv_tokens: Optional[int] = None,
                  host_sampling: bool = False):
         """`model`: a folder with config.json and model.safetensors, or a loaded DecoderModel."""
@@ -91,7 +91,7 @@ class LLM:
 
 def generate(model, prompts, max_tokens: int = 256, temperature: float = 0.0, top_k: int = 0,
              top_p: float = 1.0, seed: int = 0, dtype="bfloat16", device="cuda:0", ctx: int = 4096,
-             block_size: int = 16, prefill_chunk: int = 512, parallel: int = 4,
+             block_size: int = 32, prefill_chunk: int = 512, parallel: int = 4,
              kv_tokens: Optional[int] = None, stop_ids=(), host_sampling: bool = False):
     """One call: load `model` (a folder), generate for `prompts` (lists of token ids)."""
     llm = LLM(model, dtype=dtype, device=device, ctx=ctx, block_size=block_size,

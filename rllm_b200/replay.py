@@ -12,7 +12,7 @@ import json
 import sys
 from pathlib import Path
 
-PAGE_TOKENS = 16      # the engine's page size; 64 is a multiple, so --max-tokens needs no rounding
+PAGE_TOKENS = 32      # the engine's page size; 64 is a multiple, so --max-tokens needs no rounding
 
 
 def main(argv=None) -> int:
