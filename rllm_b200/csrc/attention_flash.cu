@@ -10,12 +10,17 @@
 //   softmax    : online, float32, exp2 with the scale folded in, masks for causality and window
 //   O += P V   : P re-used from the S accumulators as A fragments, B = V via ldmatrix.trans
 //
-// One template, two shapes:
+// Shapes:
 //   prefill: NW = 4 warps x 16 rows, key tiles of 64, whole key range, writes normalized output
-//   decode : 16 rows, the key range cut into splits of `split_keys` keys (a function of the
-//            position only, never of the batch); the 4 warps of a CTA take 32 keys each of the
-//            CTA's split, all requested at once; unnormalized partials (o, m, l) per split that
-//            paged_flash_combine merges in split order.
+//            (head size 128 with a suitable group size takes the tcgen05 kernel in attention_tc.cu)
+//   decode : the key range cut into splits of `split_keys` keys (a function of the position only,
+//            never of the batch); unnormalized partials (o, m, l) per split that
+//            paged_flash_combine merges in split order.  Three kernels write those partials:
+//            - paged_decode_attention_kernel, tiles of at most 8 (token, head) rows, the product
+//              turned round (keys as the M side of the MMA); one warp per CTA; the default;
+//            - the 4-warp variant of the template below (KEYSPLIT), whose warps take 32 keys each
+//              of the CTA's split, all requested at once: chosen when all CTAs fit the SMs at once;
+//            - the 1-warp, 16-row variant of the template for callers with tiles of 9 to 16 rows.
 // K/V tiles come in through cp.async (16-byte chunks, zero-filled beyond the context) into a
 // double buffer with an XOR swizzle on the chunk index, so ldmatrix is free of bank conflicts.
 // Any page size; head size 64 or 128 (other sizes take the plain kernel).
@@ -706,9 +711,10 @@ static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_split
         if (e != cudaSuccess) return (int)e;
         return rllm_launch(kern, grid, dim3(NW * 32), smem, stream, p);
     }
-    // decode shape, two variants of the same kernel.  Few CTAs (they all fit the SMs at once): 4 warps
-    // split the CTA's keys and request them all at once (64 KB of tiles per CTA, one memory round
-    // trip).  Many CTAs: one warp per CTA with a ring of two tiles (32 KB), so that 7 CTAs share an SM.
+    // decode shape.  Few CTAs (they all fit the SMs at once): 4 warps split the CTA's keys and request
+    // them all at once (64 KB of tiles per CTA, one memory round trip).  Many CTAs: one warp per CTA,
+    // the keys-as-M kernel for tiles of at most 8 rows (24 KB: nine CTAs share an SM), else the
+    // 16-row variant with a ring of two 32-key tiles.
     int dev = 0, n_sm = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
