@@ -211,6 +211,17 @@ def gemm_plain(a, w, out, accumulate=False):
 
 # ------------------------------------------------------------------ sampling
 
+def logit_adjust(logits, index, delta):
+    """logits.view(-1)[index[i]] += delta[i] in place (float32 logits, int64 index, float32 delta on
+    the device; the positions must be distinct)."""
+    _need_cuda(logits, index, delta)
+    assert logits.dtype == torch.float32 and index.dtype == torch.int64 and delta.dtype == torch.float32
+    assert index.numel() == delta.numel() and index.is_contiguous() and delta.is_contiguous()
+    _check(core().rllm_logit_adjust(_ptr(logits), _ptr(index), _ptr(delta), c_int(index.numel()), _stream()),
+           "logit_adjust")
+    return logits
+
+
 def sample_rows(logits, out_ids, temperature=None, top_k=None, top_p=None, seed=None, counter=None):
     """One token id per row of float32 logits [rows, vocab]; all parameter arrays are per row
     (float32, int32, float32, int64, int64) or None (greedy)."""

@@ -133,6 +133,22 @@ sample_rows_kernel(const float* __restrict__ logits, long long row_stride, int v
     if (tid == 0) out[r] = b.idx < 0 ? 0 : b.idx;
 }
 
+// logits[index[i]] += delta[i] (logit bias, frequency and presence penalties): index is the flat
+// position row * row_stride + token; the caller has summed the deltas of equal positions, so no
+// two threads touch one value (crates/rllm-cuda/kernels/kernels.cu:875-880).
+__global__ void logit_adjust_kernel(float* __restrict__ logits, const long long* __restrict__ index,
+                                    const float* __restrict__ delta, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) logits[index[i]] += delta[i];
+}
+
+RLLM_API int rllm_logit_adjust(float* logits, const long long* index, const float* delta, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    return rllm_launch(logit_adjust_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, logits, index, delta, n);
+}
+
 RLLM_API int rllm_sample_rows(const float* logits, long long row_stride, int rows, int vocab,
                               const float* temperature, const int* top_k, const float* top_p,
                               const unsigned long long* seed, const unsigned long long* counter,

@@ -53,6 +53,7 @@ class _Seq:
         self.cached = 0                      # tokens whose keys/values are in the cache
         self.budget = budget
         self.order = order                   # admission order (set when admitted)
+        self.counts: dict = {}               # token -> times generated (for the penalties; survives preemption)
 
     @property
     def rid(self):
@@ -200,6 +201,8 @@ class Scheduler:
                 continue
             tok = int(next(it))
             s.tokens.append(tok)
+            if s.req.params.adjusts:
+                s.counts[tok] = s.counts.get(tok, 0) + 1
             self.stats["generated_tokens"] += 1
             reason = None
             if tok in s.req.stop_ids:

@@ -5,7 +5,8 @@ names and meanings where it has them (crates/rllm-cli/src/main.rs:39-110, 195-23
 ``ctx`` (context per request, default 4096), ``block_size`` (32 tokens per page; the reference defaults to 16, here a page is a TMA box and 32 halves the copies per key tile), ``prefill_chunk`` (512),
 ``parallel`` (requests running at once, 4), ``kv_tokens`` (tokens the cache holds, default
 ctx * parallel), ``max_tokens`` (256), ``temperature`` (0 = greedy), ``top_k`` (0 = off),
-``top_p`` (1.0 = off), ``seed`` (0), ``host_sampling`` (sample on the host from copied logits
+``top_p`` (1.0 = off), ``seed`` (0), ``frequency_penalty`` / ``presence_penalty`` / ``logit_bias``
+(the request parameters of the reference's server), ``host_sampling`` (sample on the host from copied logits
 instead of on the device).
 """
 from __future__ import annotations
@@ -41,14 +42,20 @@ class LLM:
 
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, seed: int = 0, stop_ids: Sequence[int] = (),
-                 return_reasons: bool = False):
+                 return_reasons: bool = False, frequency_penalty: float = 0.0, presence_penalty: float = 0.0,
+                 logit_bias=()):
         """Generates for every prompt (continuous batching); returns the generated ids per prompt,
-        in order.  Request i samples with seed `seed + i`."""
+        in order.  Request i samples with seed `seed + i`.  logit_bias: (token, delta) pairs or a
+        {token: delta} mapping, added to the logits with the frequency and presence penalties over
+        the tokens generated so far before the token is chosen."""
+        if isinstance(logit_bias, dict):
+            logit_bias = tuple(logit_bias.items())
         sched = Scheduler(self.engine.cache, ctx=self.ctx, max_num_seqs=self.parallel,
                           prefill_chunk=self.prefill_chunk)
         for i, p in enumerate(prompts):
             sched.add(Request(i, list(p), max_tokens,
-                              SamplingParams(temperature, top_k, top_p, seed + i), frozenset(stop_ids)))
+                              SamplingParams(temperature, top_k, top_p, seed + i, frequency_penalty,
+                                             presence_penalty, tuple(logit_bias)), frozenset(stop_ids)))
         results = {}
         host_samplers = {}
         while sched.has_work():
@@ -72,10 +79,11 @@ class LLM:
                     rows = logits.float().cpu().numpy()
                     for r, p in enumerate(wanted):
                         hs = host_samplers.setdefault(p.seq.rid, HostSampler(p.seq.req.params))
-                        ids.append(hs.sample(rows[r]))
+                        ids.append(hs.sample(rows[r], p.seq.counts))
                 else:
                     counters = [p.seq.cached + p.take for p in wanted]
-                    ids = sample_rows(logits, [p.seq.req.params for p in wanted], counters).tolist()
+                    ids = sample_rows(logits, [p.seq.req.params for p in wanted], counters,
+                                      [p.seq.counts for p in wanted]).tolist()
             sched.commit(plan, ids)
             for f in sched.collect():
                 results[f.request_id] = f
@@ -92,10 +100,12 @@ class LLM:
 def generate(model, prompts, max_tokens: int = 256, temperature: float = 0.0, top_k: int = 0,
              top_p: float = 1.0, seed: int = 0, dtype="bfloat16", device="cuda:0", ctx: int = 4096,
              block_size: int = 32, prefill_chunk: int = 512, parallel: int = 4,
-             kv_tokens: Optional[int] = None, stop_ids=(), host_sampling: bool = False):
+             kv_tokens: Optional[int] = None, stop_ids=(), host_sampling: bool = False,
+             frequency_penalty: float = 0.0, presence_penalty: float = 0.0, logit_bias=()):
     """One call: load `model` (a folder), generate for `prompts` (lists of token ids)."""
     llm = LLM(model, dtype=dtype, device=device, ctx=ctx, block_size=block_size,
               prefill_chunk=prefill_chunk, parallel=parallel, kv_tokens=kv_tokens,
               host_sampling=host_sampling)
     return llm.generate(prompts, max_tokens=max_tokens, temperature=temperature, top_k=top_k,
-                        top_p=top_p, seed=seed, stop_ids=stop_ids)
+                        top_p=top_p, seed=seed, stop_ids=stop_ids, frequency_penalty=frequency_penalty,
+                        presence_penalty=presence_penalty, logit_bias=logit_bias)

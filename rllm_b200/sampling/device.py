@@ -15,11 +15,26 @@ from ..csrc import ops
 from .params import SamplingParams
 
 
-def sample_rows(logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]) -> torch.Tensor:
-    """logits float32 [rows, vocab] on the device -> int32 ids [rows] on the device."""
+def sample_rows(logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
+                counts: Sequence = None) -> torch.Tensor:
+    """logits float32 [rows, vocab] on the device -> int32 ids [rows] on the device.
+    counts: per row, {token: times generated so far} (or None) for the penalties; rows whose
+    parameters ask for a bias or a penalty have it added to their logits in place first."""
     rows = logits.shape[0]
     assert len(params) == rows and len(counters) == rows
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if any(p.adjusts for p in params):
+        index, delta = [], []
+        stride, vocab = logits.stride(0), logits.shape[1]
+        for r, p in enumerate(params):
+            if p.adjusts:
+                for t, d in p.adjustments(counts[r] if counts is not None else None).items():
+                    if 0 <= t < vocab and d != 0.0:
+                        index.append(r * stride + t)
+                        delta.append(d)
+        if index:
+            ops.logit_adjust(logits, torch.tensor(index, dtype=torch.int64).to(logits.device),
+                             torch.tensor(delta, dtype=torch.float32).to(logits.device))
     if all(p.greedy for p in params):
         return ops.sample_rows(logits, out)
     dev = logits.device

@@ -54,9 +54,15 @@ class HostSampler:
             order, probs = order[:keep], probs[:keep]
         return order, probs
 
-    def sample(self, logits) -> int:
+    def sample(self, logits, counts=None) -> int:
+        """counts: {token: times generated so far} for the penalties (applied to a copy of the row)."""
         logits = np.asarray(logits, dtype=np.float32)
         p = self.params
+        if p.adjusts:
+            logits = logits.copy()
+            for t, d in p.adjustments(counts).items():
+                if 0 <= t < logits.size:
+                    logits[t] += np.float32(d)
         if p.greedy:
             return argmax(logits)
         clean = np.where(np.isnan(logits), -np.inf, logits)

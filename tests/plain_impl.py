@@ -254,10 +254,14 @@ def threshold(x, top_k, top_p, steps=40):
     return thr
 
 
-def sample_row(logits, temperature, top_k, top_p, seed, counter):
-    """Greedy for temperature <= 0, else Gumbel-max over the thresholded candidates.
+def sample_row(logits, temperature, top_k, top_p, seed, counter, adjust=()):
+    """Greedy for temperature <= 0, else Gumbel-max over the thresholded candidates; `adjust`
+    ((token, delta) pairs: logit bias, penalties) is added to a copy of the row first.
     crates/rllm-core/src/sample.rs:53-83"""
     x = np.asarray(logits, dtype=np.float32).copy()
+    for t, d in adjust:
+        if 0 <= t < x.size:
+            x[t] += np.float32(d)
     if temperature <= 0:
         return int(np.argmax(x))
     x = x * np.float32(1.0 / temperature)

@@ -176,6 +176,34 @@ def test_sampling_is_reproducible_whatever_the_batch(dirs):
     assert h1 == host.generate(prompts[:2], **kw) and all(len(t) == 12 for t in h1)
 
 
+def test_penalties_and_bias_through_generate(dirs):
+    """frequency / presence penalties and logit bias reach the sampler through LLM.generate, on the
+    device and on the host alike."""
+    from rllm_b200 import LLM
+    cfg, w = plain_impl.load_model(dirs["A", "float32"])
+    prompt = helpers.random_tokens(12, cfg["vocab_size"], 77)
+    llm = LLM(dirs["A", "float32"], dtype="float32", device=DEV, ctx=128, parallel=2)
+    plain = llm.generate([prompt], max_tokens=24)[0]
+    assert plain == plain_impl.greedy_generate(cfg, w, prompt, 24)
+    assert len(set(plain)) < len(plain)                      # the tiny model repeats itself
+    no_repeat = llm.generate([prompt], max_tokens=24, presence_penalty=1000.0)[0]
+    assert len(set(no_repeat)) == len(no_repeat) and no_repeat[0] == plain[0]
+    banned = llm.generate([prompt], max_tokens=6, logit_bias={plain[0]: -1000.0})[0]
+    assert plain[0] not in banned
+    # the plain implementation with the same rule, token by token
+    seq, counts = list(prompt), {}
+    for _ in range(10):
+        row = plain_impl.forward(cfg, w, seq)[-1].numpy()
+        adj = [(t, -(c * 0.7 + 0.3)) for t, c in counts.items()]
+        tok = plain_impl.sample_row(row, 0, 0, 1.0, 0, 0, adjust=adj)
+        counts[tok] = counts.get(tok, 0) + 1
+        seq.append(tok)
+    kw = dict(max_tokens=10, frequency_penalty=0.7, presence_penalty=0.3)
+    assert llm.generate([prompt], **kw)[0] == seq[len(prompt):]
+    host = LLM(dirs["A", "float32"], dtype="float32", device=DEV, ctx=128, parallel=2, host_sampling=True)
+    assert host.generate([prompt], **kw)[0] == seq[len(prompt):]
+
+
 def test_python_and_native_host_agree(dirs):
     """The C++ host runtime and the Python one drive the same kernels to the same logits."""
     from rllm_b200.engine import Engine

@@ -403,6 +403,32 @@ def test_host_sampler():
     assert np.abs(freq - p).max() < 0.012
 
 
+def test_logit_bias_and_penalties():
+    """The adjustments of crates/rllm-server/src/engine.rs:1113-1129: bias pairs, and for every
+    token generated c times so far -(c * frequency_penalty + presence_penalty); equal tokens summed."""
+    p = SamplingParams(frequency_penalty=0.5, presence_penalty=1.0, logit_bias=((3, 2.0), (7, -100.0), (3, 0.25)))
+    assert p.adjusts and not SamplingParams().adjusts
+    assert p.adjustments(None) == {3: 2.25, 7: -100.0}
+    assert p.adjustments({3: 2, 5: 1}) == {3: 2.25 - 2.0, 7: -100.0, 5: -1.5}
+    logits = np.array([0.0, 1.0, 0.5, 0.9, 0.2, 0.95, 0.1, 5.0], dtype=np.float32)
+    assert HostSampler(SamplingParams()).sample(logits) == 7
+    assert HostSampler(p).sample(logits) == 3                          # 7 is biased away, 3 biased up
+    assert HostSampler(p).sample(logits, {3: 4}) == 1                  # 3 generated four times: 3.15 - 3.0 < 1.0
+    assert logits[7] == 5.0                                            # the row itself is left alone
+    assert plain_impl.sample_row(logits, 0, 0, 1.0, 0, 0, adjust=p.adjustments({3: 4}).items()) == 1
+    # the scheduler counts what a request generated
+    from rllm_b200.cache import CacheManager
+    from rllm_b200.parts import PagedKVNeed
+    cache = CacheManager([PagedKVNeed(1, 16, 0)], [None], 4, 64, 2)
+    sched = Scheduler(cache, ctx=64, max_num_seqs=2, prefill_chunk=16)
+    sched.add(Request("a", [1, 2, 3], 4, p, frozenset()))
+    for tok in (5, 5, 9):
+        plan = sched.plan()
+        cache.append("a", plan[0].take)
+        sched.commit(plan, [tok])
+    assert sched.running[0].counts == {5: 2, 9: 1}
+
+
 def test_plain_sampler_reference():
     x = np.array([2.0, 1.0, 0.0, -1.0, 1.5, -3.0], dtype=np.float32)
     assert plain_impl.sample_row(x, 0, 0, 1.0, 0, 0) == 0

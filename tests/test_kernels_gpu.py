@@ -245,6 +245,31 @@ def test_sample_rows_matches_plain():
     assert same >= rows - 1, (ids.tolist(), want)     # float rounding of log/exp may flip a near tie
 
 
+def test_logit_adjust_then_sample():
+    """Bias and penalties on the device: logits[row, token] += delta before the draw, as the plain sampler."""
+    from rllm_b200.sampling.device import sample_rows
+    from rllm_b200.sampling.params import SamplingParams
+    rows, V = 5, 777
+    logits = rnd(rows, V, seed=51, scale=2.0)
+    top = logits.argmax(1).tolist()
+    params = [SamplingParams(),                                                      # untouched
+              SamplingParams(logit_bias=((top[1], -50.0),)),                         # greedy, its best token banned
+              SamplingParams(presence_penalty=60.0),                                 # greedy, penalised by counts
+              SamplingParams(temperature=0.9, top_k=30, seed=5, frequency_penalty=1.5, logit_bias=((11, 3.0), (11, 1.0))),
+              SamplingParams(temperature=1.1, top_p=0.8, seed=6)]
+    counts = [None, None, {top[2]: 1}, {7: 3, 11: 2}, None]
+    dev = logits.to(DEV)
+    ids = sample_rows(dev, params, [0, 1, 2, 3, 4], counts).tolist()
+    want = [plain_impl.sample_row(logits[r].numpy(), p.temperature, p.top_k, p.top_p, p.seed, r,
+                                  adjust=p.adjustments(counts[r]).items()) for r, p in enumerate(params)]
+    assert ids == want
+    assert ids[0] == top[0] and ids[1] != top[1] and ids[2] != top[2]
+    # the adjusted rows were changed in place, the others not
+    after = dev.cpu()
+    assert torch.equal(after[0], logits[0]) and torch.equal(after[4], logits[4])
+    assert abs(float(after[3, 11] - logits[3, 11]) - (4.0 - 3.0)) < 1e-5 and abs(float(after[3, 7] - logits[3, 7]) + 4.5) < 1e-5
+
+
 def test_sample_rows_frequencies():
     """Draws follow softmax(logits / T) (crates/rllm-core/src/sample.rs:133-161)."""
     V, N = 6, 20000
