@@ -5,6 +5,8 @@
                         [--kv-type bf16|f32] [--show-ids]
   rllm bench MODEL [-p/--n-prompt 512] [-n/--n-gen 128] [-r/--reps 3] [--depth 0] [-b/--batch 1]
   rllm compare MODEL PROMPT [-n/--steps 32]      engine float32 against engine bfloat16, same tokens
+  rllm compare-ref MODEL DUMP [--prefill-chunk 512]
+                                                  engine against a reference's logits on the same tokens
   rllm inspect MODEL                              configuration and tensor list
   rllm random-model OUT --config FILE [--seed 0] [--dtype bfloat16]
   rllm replay ...                                 same as bin/trace_run
@@ -118,6 +120,73 @@ def cmd_compare(a) -> int:
     return 0
 
 
+def read_ref_dump(path):
+    """A reference dump: "RLLMREF1" | u32 n_vocab | u32 n_prompt | u32 n_total | u32 tokens[n_total] |
+    f32 logits[n_total][n_vocab], little-endian; row i holds the logits after tokens[0..=i]
+    (tools/llama-ref/llama_ref.cpp:6-9, crates/rllm-cli/src/main.rs:525-536)."""
+    import numpy as np
+    raw = Path(path).read_bytes()
+    if len(raw) < 20 or raw[:8] != b"RLLMREF1":
+        raise ValueError(f"{path} is not a reference dump (no RLLMREF1 header)")
+    n_vocab, n_prompt, n_total = (int(x) for x in np.frombuffer(raw, "<u4", 3, 8))
+    tok_end = 20 + 4 * n_total
+    if len(raw) != tok_end + 4 * n_total * n_vocab:
+        raise ValueError(f"{path}: truncated reference dump")
+    tokens = np.frombuffer(raw, "<u4", n_total, 20).astype(np.int64).tolist()
+    logits = np.frombuffer(raw, "<f4", n_total * n_vocab, tok_end).reshape(n_total, n_vocab)
+    return n_vocab, n_prompt, tokens, logits
+
+
+def write_ref_dump(path, n_prompt: int, tokens, logits) -> None:
+    """Writes a dump in the format read_ref_dump reads (logits: [len(tokens), vocab] float32)."""
+    import numpy as np
+    logits = np.ascontiguousarray(logits, dtype="<f4")
+    head = np.array([logits.shape[1], n_prompt, len(tokens)], dtype="<u4").tobytes()
+    Path(path).write_bytes(b"RLLMREF1" + head + np.asarray(tokens, dtype="<u4").tobytes() + logits.tobytes())
+
+
+def cmd_compare_ref(a) -> int:
+    """Feeds the dump's token ids through the engine (prompt in portions of --prefill-chunk) and
+    reports, per position, the largest logit difference, the relative difference, KL(reference ||
+    ours) and the two top-1 tokens, then a summary (crates/rllm-cli/src/main.rs:538-606)."""
+    import numpy as np
+    from .engine import Engine, StepItem
+    from .models.model import load_model
+    n_vocab, n_prompt, tokens, ref = read_ref_dump(a.reference)
+    _, model = load_model(a.model, _dtype(a.kv_type), a.device)
+    if model.spec.vocab_size != n_vocab:
+        print(f"vocab mismatch: model {model.spec.vocab_size} vs reference {n_vocab}", file=sys.stderr)
+        return 2
+    eng = Engine(model, block_size=a.block_size, max_tokens=len(tokens) + 64, max_requests=1)
+    rows = []
+    for c in range(0, len(tokens), a.prefill_chunk):
+        part = tokens[c:c + a.prefill_chunk]
+        rows.append(eng.step([StepItem(0, part, list(range(len(part))))]).float().cpu().numpy())
+    ours = np.concatenate(rows)
+
+    def log_softmax(x):
+        x = x.astype(np.float64)
+        m = x.max()
+        return x - (m + np.log(np.exp(x - m).sum()))
+
+    kl_sum = kl_max = worst_rel = 0.0
+    agree = 0
+    print(f"{'pos':>6} {'max|diff|':>10} {'rel':>10} {'KL':>10}  {'ref':>8} {'rllm':>8}  next token")
+    for i in range(len(tokens)):
+        diff = float(np.abs(ref[i] - ours[i]).max())
+        rel = diff / max(float(np.abs(ref[i]).max()), 1e-30)
+        lp, lq = log_softmax(ref[i]), log_softmax(ours[i])
+        kl = max(float((np.exp(lp) * (lp - lq)).sum()), 0.0)
+        ta, tb = int(np.nan_to_num(ref[i], nan=-np.inf).argmax()), int(np.nan_to_num(ours[i], nan=-np.inf).argmax())
+        kl_sum, kl_max, worst_rel, agree = kl_sum + kl, max(kl_max, kl), max(worst_rel, rel), agree + (ta == tb)
+        if i + 3 >= n_prompt or ta != tb:           # the last prompt rows and every generated row
+            print(f"{i:>6} {diff:>10.4f} {rel:>10.2e} {kl:>10.2e}  {ta:>8} {tb:>8}" + ("  <-- top-1 differs" if ta != tb else ""))
+    n = len(tokens)
+    print(f"summary: {n} positions | top-1 agreement {agree}/{n} | KL mean {kl_sum / n:.2e} max {kl_max:.2e} | "
+          f"worst relative logit diff {worst_rel:.2e}")
+    return 0
+
+
 def cmd_inspect(a) -> int:
     from .config import load_config
     from .weights import SafetensorsFile
@@ -178,6 +247,11 @@ def main(argv=None) -> int:
     p.add_argument("-n", "--steps", type=int, default=32)
     p.add_argument("--prefill-chunk", type=int, default=512)
     p.set_defaults(fn=cmd_compare)
+
+    p = sub.add_parser("compare-ref"); common(p)
+    p.add_argument("reference")
+    p.add_argument("--prefill-chunk", type=int, default=512)
+    p.set_defaults(fn=cmd_compare_ref)
 
     p = sub.add_parser("inspect"); p.add_argument("model"); p.set_defaults(fn=cmd_inspect)
 

@@ -617,6 +617,17 @@ def test_command_line(dirs, tmp_path):
     r = _cli("compare", dirs["B", "bfloat16"], ",".join(map(str, prompt)), "-n", 4)
     assert r.returncode == 0 and "max relative logit diff" in r.stdout
     assert float(r.stdout.split("diff")[1].split(";")[0]) < 3e-2
+    # compare-ref: a dump of the plain implementation's logits in the reference's format
+    from rllm_b200.cli import write_ref_dump
+    cfgB, wB = plain_impl.load_model(dirs["B", "float32"])
+    toks = helpers.random_tokens(23, cfgB["vocab_size"], 12)
+    dump = tmp_path / "ref.bin"
+    write_ref_dump(dump, 15, toks, plain_impl.forward(cfgB, wB, toks).numpy())
+    r = _cli("compare-ref", dirs["B", "float32"], dump, "--kv-type", "f32", "--prefill-chunk", 7)
+    assert r.returncode == 0, r.stderr[-1500:]
+    assert "top-1 agreement 23/23" in r.stdout and float(r.stdout.split("worst relative logit diff")[1]) < 5e-6
+    (tmp_path / "bad.bin").write_bytes(b"RLLMREF1" + b"\0" * 11)
+    assert _cli("compare-ref", dirs["B", "float32"], tmp_path / "bad.bin").returncode != 0
     r = _cli("inspect", dirs["B", "bfloat16"])
     assert r.returncode == 0 and "model.layers.2.mlp.down_proj.weight" in r.stdout and "Qwen3Config" in r.stdout
     cfgfile = tmp_path / "c.json"
