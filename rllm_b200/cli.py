@@ -7,6 +7,8 @@
   rllm compare MODEL PROMPT [-n/--steps 32]      engine float32 against engine bfloat16, same tokens
   rllm compare-ref MODEL DUMP [--prefill-chunk 512]
                                                   engine against a reference's logits on the same tokens
+  rllm perplexity MODEL TOKENS [--ctx 512] [--chunks N]
+                                                  perplexity over a file of token ids, chunk by chunk
   rllm inspect MODEL                              configuration and tensor list
   rllm random-model OUT --config FILE [--seed 0] [--dtype bfloat16]
   rllm replay ...                                 same as bin/trace_run
@@ -187,6 +189,47 @@ def cmd_compare_ref(a) -> int:
     return 0
 
 
+def cmd_perplexity(a) -> int:
+    """Perplexity over a file of token ids (the engine has no tokenizer: the reference scores a text
+    file): chunks of --ctx tokens, each in a fresh cache, the positions ctx/2 .. ctx-2 of a chunk
+    scored on the token that follows; log-sum-exp on the device in float64
+    (crates/rllm-cli/src/main.rs:608-679)."""
+    import math
+    import torch
+    from .engine import Engine, StepItem
+    from .models.model import load_model
+    tokens = _ids(a.tokens if a.tokens.startswith("@") else "@" + a.tokens)
+    n_ctx = a.ctx
+    if n_ctx < 4 or len(tokens) < 2 * n_ctx:
+        print(f"need at least {2 * n_ctx} tokens for --ctx {n_ctx}", file=sys.stderr)
+        return 2
+    n_chunk = min(len(tokens) // n_ctx, a.chunks or 1 << 60)
+    _, model = load_model(a.model, _dtype(a.kv_type), a.device)
+    eng = Engine(model, block_size=a.block_size, max_tokens=n_ctx + 64, max_requests=1)
+    first = n_ctx // 2
+    rows = list(range(first, n_ctx - 1))
+    nll = nll2 = 0.0
+    count = 0
+    t0 = time.time()
+    for c in range(n_chunk):
+        chunk = tokens[c * n_ctx:(c + 1) * n_ctx]
+        logits = eng.step([StepItem(c, chunk, rows)]).double()
+        eng.finish(c)
+        target = torch.tensor(chunk[first + 1:], dtype=torch.long, device=logits.device)
+        v = (torch.logsumexp(logits, dim=1) - logits.gather(1, target[:, None])[:, 0]).cpu()
+        nll += float(v.sum())
+        nll2 += float((v * v).sum())
+        count += v.numel()
+        print(f"[{c + 1}]{math.exp(nll / count):.4f} ", end="", file=sys.stderr, flush=True)
+    print(file=sys.stderr)
+    mean = nll / count
+    ppl = math.exp(mean)
+    err = ppl * math.sqrt(max(nll2 / count - mean * mean, 0.0) / max(count - 1, 1))
+    print(f"Final estimate: PPL = {ppl:.4f} +/- {err:.5f}  ({n_chunk} chunks, {count} scored tokens, "
+          f"{time.time() - t0:.1f} s)")
+    return 0
+
+
 def cmd_inspect(a) -> int:
     from .config import load_config
     from .weights import SafetensorsFile
@@ -252,6 +295,12 @@ def main(argv=None) -> int:
     p.add_argument("reference")
     p.add_argument("--prefill-chunk", type=int, default=512)
     p.set_defaults(fn=cmd_compare_ref)
+
+    p = sub.add_parser("perplexity"); common(p)
+    p.add_argument("tokens", help="file of token ids")
+    p.add_argument("--ctx", type=int, default=512)
+    p.add_argument("--chunks", type=int, default=None)
+    p.set_defaults(fn=cmd_perplexity)
 
     p = sub.add_parser("inspect"); p.add_argument("model"); p.set_defaults(fn=cmd_inspect)
 

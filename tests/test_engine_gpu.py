@@ -628,6 +628,19 @@ def test_command_line(dirs, tmp_path):
     assert "top-1 agreement 23/23" in r.stdout and float(r.stdout.split("worst relative logit diff")[1]) < 5e-6
     (tmp_path / "bad.bin").write_bytes(b"RLLMREF1" + b"\0" * 11)
     assert _cli("compare-ref", dirs["B", "float32"], tmp_path / "bad.bin").returncode != 0
+    # perplexity over token ids, against the plain implementation's own log-likelihoods
+    stream = helpers.random_tokens(100, cfgB["vocab_size"], 13)
+    (tmp_path / "stream.txt").write_text(" ".join(map(str, stream)))
+    r = _cli("perplexity", dirs["B", "float32"], tmp_path / "stream.txt", "--ctx", 32, "--kv-type", "f32")
+    assert r.returncode == 0, r.stderr[-1500:]
+    nll = []
+    for c in range(3):
+        chunk = stream[32 * c:32 * c + 32]
+        lp = torch.log_softmax(plain_impl.forward(cfgB, wB, chunk).double(), dim=1)
+        nll += [-float(lp[i, chunk[i + 1]]) for i in range(16, 31)]
+    want_ppl = math.exp(sum(nll) / len(nll))
+    got_ppl = float(r.stdout.split("PPL =")[1].split("+/-")[0])
+    assert abs(got_ppl - want_ppl) / want_ppl < 1e-4 and "45 scored tokens" in r.stdout
     r = _cli("inspect", dirs["B", "bfloat16"])
     assert r.returncode == 0 and "model.layers.2.mlp.down_proj.weight" in r.stdout and "Qwen3Config" in r.stdout
     cfgfile = tmp_path / "c.json"
