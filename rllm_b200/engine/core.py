@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import contextlib
 import math
+import os
 from typing import Optional, Sequence
 
 import numpy as np
@@ -91,7 +92,10 @@ class Engine:
         self.cache.allocate_device(self.runtime.device, self.runtime.dtype)
         self.block_size = block_size
         self._windowed = any(g.need.window > 0 for g in self.cache.paged)     # only then do pages fall out of reach
-        self.use_graphs = use_graphs and not profiler.enabled()    # events cannot be recorded into a capture
+        # RLLM_B200_NO_GRAPHS=1 turns graph replay off (the reference's RLLM_NO_GRAPHS); the profiling
+        # switch does too: events cannot be recorded into a capture
+        self.use_graphs = (use_graphs and not profiler.enabled()
+                           and os.environ.get("RLLM_B200_NO_GRAPHS", "0") in ("", "0"))
         self._graphs: dict = {}
         self._graph_pool = None
         self._staging = []
