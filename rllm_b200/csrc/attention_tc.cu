@@ -82,7 +82,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     unsigned char* sK = smem + AT_TILE_BYTES;               // 2 x 32 KB
     unsigned char* sV = smem + 3 * AT_TILE_BYTES;           // 2 x 32 KB
     __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2],
-        p_full, p_empty;
+        p_full[2], p_empty;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ int s_table[AT_TABLE_SMEM];
@@ -107,7 +107,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128);
         }
-        mbar_init(&p_full, 128);
+        // p_full has one barrier per S buffer: a softmax warp may be one tile ahead of the others (the
+        // scores of tile j + 1 are ready early) and must not add its arrival to the phase of tile j
+        mbar_init(&p_full[0], 128);
+        mbar_init(&p_full[1], 128);
         mbar_init(&p_empty, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -213,7 +216,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         auto issue_pv = [&](int j) -> bool {
             const int s = j & 1;
             const uint32_t ph = (j >> 1) & 1;
-            if (!mbar_wait(&p_full, j & 1, &abort_flag)) return false;
+            if (!mbar_wait(&p_full[s], (j >> 1) & 1, &abort_flag)) return false;
             if (!mbar_wait(&v_full[s], ph, &abort_flag)) return false;
             tc_fence_after();
             const uint32_t v_addr = s_addr(sV + s * AT_TILE_BYTES);
@@ -227,7 +230,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         };
         if (ok) ok = issue_qk(0);
         for (int j = 0; j < n_kt && ok; ++j) {
-            if (j + 1 < n_kt) ok = issue_qk(j + 1);
+            if (j + 1 < n_kt) ok = issue_qk(j + 1);      // over P of tile j - 1, behind the product that reads it
             if (ok) ok = issue_pv(j);
         }
         if (!ok && !abort_flag) { atomicExch(p.err, AT_ERR_KV); abort_flag = 1; }
@@ -285,16 +288,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             else if (mx > m_ref + 8.f) { alpha = exp2f(m_ref - mx); m_ref = mx; rescale = true; }
             // P goes to tensor memory over this tile's own scores (columns 0-63 of S[b], read above),
             // where nothing else is pending: S[b] was written by Q.K^T of this tile, which the tensor
-            // pipe ran after P.V of tile j-2.  Only O is shared with the products in flight: it is
-            // rescaled after P.V of the tile before has completed.
+            // pipe ran after P.V of tile j-2.  O is shared with the products in flight: it is rescaled
+            // only after P.V of the tile before has completed.  Every thread waits for every phase of
+            // p_empty, one after the other, whether it rescales or not: a parity wait is only right
+            // for the phase after the last one seen (skipping a phase once let the epilogue read O two
+            // products early).
+            if (j > 0 && !mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
+                if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
+                ok = false;
+                break;
+            }
             // tcgen05.ld / st are warp-wide: the whole warp goes through when any of its rows rescales
             if (__any_sync(0xffffffffu, rescale)) {
-                if (j > 0 && !mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
-                    if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
-                    ok = false;
-                }
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
                 tc_fence_after();
                 l *= alpha;
 #pragma unroll
@@ -324,7 +329,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int c0 = 0; c0 < AT_BN / 64; ++c0) tmem_st32(tS0 + b * AT_BN + lane_base + c0 * 32, pk[c0]);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&p_full);
+            mbar_arrive(&p_full[b]);
         }
         if (ok) {
             if (!mbar_wait(&p_empty, (n_kt - 1) & 1, &abort_flag)) {
