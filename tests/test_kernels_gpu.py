@@ -458,3 +458,18 @@ def test_gemv_stream_swiglu(m, F, k, grid, stages):
     o.gemv_stream(a.to(DEV), w.to(DEV), out32, epilogue=o.EPI_SWIGLU, up_row_offset=F, grid=grid, stages=stages)
     assert rel_err(out32.cpu(), ref) < 1e-5
     o.check_device_errors()
+
+
+def test_gemv_stream_lm_head_size():
+    """The largest matrix of the decode step (vocabulary 151,936 x 4,096): 444 CTAs, dozens of chunks each."""
+    o = ops()
+    m, n, k = 8, 151936, 4096
+    a, w = rnd(m, k, seed=46, dtype=torch.bfloat16), rnd(n, k, seed=47, scale=0.05, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    out = torch.full((m, n), float("nan"), device=DEV)
+    o.gemv_stream(a.to(DEV), w.to(DEV), out)
+    assert rel_err(out.cpu(), ref) < 1e-5
+    again = torch.full((m, n), float("nan"), device=DEV)
+    o.gemv_stream(a.to(DEV), w.to(DEV), again)
+    assert torch.equal(again, out)
+    o.check_device_errors()
