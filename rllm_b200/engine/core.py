@@ -37,6 +37,7 @@ class StepError(ValueError):
 
 GRAPH_MAX_REQUESTS = 64
 GRAPH_CTX_QUANTUM = 256          # context lengths are padded to a multiple of this many tokens
+GRAPH_CACHE_MAX = 48             # captured decode shapes kept per engine
 
 
 def _bucket(n: int) -> int:
@@ -70,6 +71,7 @@ class _DecodeGraph:
         self.graph = None
         self.logits = None
         self.launches = 0
+        self.last_used = 0
 
 
 class Engine:
@@ -344,6 +346,9 @@ class Engine:
             host, layout, meta = self._build(items, pad_requests=B, pad_width=-(-ctx_pad // self.block_size))
             g = self._graphs.get(key)
         if g is None:
+            if len(self._graphs) >= GRAPH_CACHE_MAX:
+                # the least recently used shape goes (requests grow through context buckets and do not come back)
+                del self._graphs[min(self._graphs, key=lambda k: self._graphs[k].last_used)]
             g = self._graphs[key] = _DecodeGraph()
             g.layout = layout
             g.static = torch.zeros(g.layout.total, dtype=torch.int32, device=self.runtime.device)
@@ -354,6 +359,7 @@ class Engine:
             assert layout.offsets == g.layout.offsets
         self._copy_in(g.static, host)
         g.uses += 1
+        g.last_used = self.stats["steps"]
         if g.uses == 1:
             # first time: run the padded step eagerly (loads kernels, builds the dispatch plans)
             g.logits = self.model.forward(g.ctx, g.views)

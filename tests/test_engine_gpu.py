@@ -661,3 +661,22 @@ def test_profile_switch_times_every_launcher(dirs):
     assert "graphs off" in lines[-1]
     plain = _cli("run", dirs["B", "bfloat16"], "1,2,3,4,5", "-n", 6, "--ctx", 64, "--show-ids")
     assert plain.stdout.split() == r.stdout.split()          # the switch changes no token
+
+
+def test_graph_cache_is_bounded(dirs, monkeypatch):
+    """Captured decode shapes are kept up to a bound; the least recently used one goes, and a shape
+    that comes back is captured again with the same results."""
+    from rllm_b200.engine import StepItem
+    from rllm_b200.engine import core
+    monkeypatch.setattr(core, "GRAPH_CACHE_MAX", 2)
+    monkeypatch.setattr(core, "GRAPH_CTX_QUANTUM", 16)
+    cfg, w = plain_impl.load_model(dirs["A", "float32"])
+    toks = helpers.random_tokens(70, cfg["vocab_size"], 21)
+    ref = plain_impl.forward(cfg, w, toks)
+    eng = engine(dirs["A", "float32"], "float32", max_tokens=128, max_requests=2)
+    for i, t in enumerate(toks):                      # context buckets of 16: five shapes in turn
+        row = eng.step([StepItem("r", [t], [0])])[0].float().cpu()
+        assert rel_err(row, ref[i]) <= 5e-6
+        assert len(eng._graphs) <= 2
+    assert eng.stats["graphs_captured"] >= 4
+    eng.finish("r")
