@@ -15,12 +15,10 @@
 //            (head size 128 with a suitable group size takes the tcgen05 kernel in attention_tc.cu)
 //   decode : the key range cut into splits of `split_keys` keys (a function of the position only,
 //            never of the batch); unnormalized partials (o, m, l) per split that
-//            paged_flash_combine merges in split order.  Three kernels write those partials:
+//            paged_flash_combine merges in split order.  Two kernels write those partials:
 //            - paged_decode_attention_kernel, tiles of at most 8 (token, head) rows, the product
 //              turned round (keys as the M side of the MMA); one warp per CTA; the default;
-//            - the 4-warp variant of the template below (KEYSPLIT), whose warps take 32 keys each
-//              of the CTA's split, all requested at once: chosen when all CTAs fit the SMs at once;
-//            - the 1-warp, 16-row variant of the template for callers with tiles of 9 to 16 rows.
+//            - the 1-warp, 16-row instance of the template for callers with tiles of 9 to 16 rows.
 // K/V tiles come in through cp.async (16-byte chunks, zero-filled beyond the context) into a
 // double buffer with an XOR swizzle on the chunk index, so ldmatrix is free of bank conflicts.
 // Any page size; head size 64 or 128 (other sizes take the plain kernel).
@@ -78,11 +76,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// KEYSPLIT false (prefill): the NW warps take 16 rows each and share every key tile (ring of two).
-// KEYSPLIT true  (decode) : the NW warps share the tile's 16 rows and split the CTA's keys: all of
-//   the CTA's (at most NW) key tiles are requested at once by all threads -- one memory round
-//   trip --, warp w computes on tile w, and the warps' (o, m, l) are merged through shared memory.
-template <int HD, int NW, int BN, bool KEYSPLIT>
+// The NW warps take 16 rows each and share every key tile (ring of two).
+template <int HD, int NW, int BN>
 __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const FlashParams p) {
     constexpr int CH = HD / 8;                    // 16-byte chunks per key row
     constexpr int TILE_BYTES = BN * HD * 2;
@@ -110,7 +105,7 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     const size_t part_base = (((size_t)tile * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z) * p.part_rows;
 
     // this thread's two rows: (token, head) pairs
-    const int R0 = (KEYSPLIT ? 0 : warp * 16) + g, R1 = R0 + 8;
+    const int R0 = warp * 16 + g, R1 = R0 + 8;
     const int tl0 = R0 / p.GH, hl0 = R0 % p.GH, tl1 = R1 / p.GH, hl1 = R1 % p.GH;
     const bool valid0 = tl0 < nt && hl0 < nh, valid1 = tl1 < nt && hl1 < nh;
     const int pos0 = valid0 ? p.positions[tok0 + tl0] : -1, pos1 = valid1 ? p.positions[tok0 + tl1] : -1;
@@ -179,26 +174,17 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
     for (int j = 0; j < NT_O; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    const int n_tiles = (ke - kb + BN - 1) / BN;        // KEYSPLIT: at most NW (the launcher's choice of split)
-    if (KEYSPLIT) {
-        for (int it = 0; it < n_tiles; ++it) load_tile(it, kb + it * BN);
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
-    } else {
-        load_tile(0, kb);
-        cp_async_commit();
-    }
+    const int n_tiles = (ke - kb + BN - 1) / BN;
+    load_tile(0, kb);
+    cp_async_commit();
     const int mi = lane >> 3, ri = lane & 7;
-    for (int it = KEYSPLIT ? warp : 0; it < n_tiles; it += KEYSPLIT ? NW : 1) {
+    for (int it = 0; it < n_tiles; ++it) {
         const int kt = kb + it * BN;
-        if (!KEYSPLIT) {
-            if (it + 1 < n_tiles) load_tile((it + 1) & 1, kt + BN);
-            cp_async_commit();
-            cp_async_wait<1>();
-            __syncthreads();
-        }
-        const unsigned char* sk = smem + (size_t)(KEYSPLIT ? it : (it & 1)) * 2 * TILE_BYTES;
+        if (it + 1 < n_tiles) load_tile((it + 1) & 1, kt + BN);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const unsigned char* sk = smem + (size_t)(it & 1) * 2 * TILE_BYTES;
         const unsigned char* sv = sk + TILE_BYTES;
 
         // ---- S = Q K^T
@@ -270,47 +256,11 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
                 mma_bf16(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
             }
         }
-        if (!KEYSPLIT) __syncthreads();            // the stage may be overwritten from here on
+        __syncthreads();                           // the stage may be overwritten from here on
     }
     pdl_launch_dependents();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-
-    if (KEYSPLIT) {
-        // merge the warps' partial results: [warp][row][HD] and [warp][row][2] in the (now free) tile memory
-        __syncthreads();
-        float* mo = reinterpret_cast<float*>(smem);
-        float* mml = mo + NW * 16 * HD;
-#pragma unroll
-        for (int j = 0; j < NT_O; ++j) {
-            *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + g) * HD + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
-            *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + g + 8) * HD + 8 * j + 2 * t) = make_float2(o[j][2], o[j][3]);
-        }
-        if (t == 0) {
-            mml[(warp * 16 + g) * 2] = m0; mml[(warp * 16 + g) * 2 + 1] = valid0 ? l0 : 0.f;
-            mml[(warp * 16 + g + 8) * 2] = m1; mml[(warp * 16 + g + 8) * 2 + 1] = valid1 ? l1 : 0.f;
-        }
-        __syncthreads();
-        for (int idx = tid; idx < p.part_rows * HD; idx += NW * 32) {
-            const int row = idx / HD, d = idx - row * HD;
-            float M = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) if (mml[(w * 16 + row) * 2 + 1] > 0.f) M = fmaxf(M, mml[(w * 16 + row) * 2]);
-            float num = 0.f, den = 0.f;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) {
-                const float lw = mml[(w * 16 + row) * 2 + 1];
-                if (lw > 0.f) {
-                    const float e = exp2f(mml[(w * 16 + row) * 2] - M);
-                    num += mo[((size_t)w * 16 + row) * HD + d] * e;
-                    den += lw * e;
-                }
-            }
-            p.part_o[(part_base + row) * HD + d] = num;
-            if (d == 0) { p.part_ml[(part_base + row) * 2] = M; p.part_ml[(part_base + row) * 2 + 1] = den; }
-        }
-        return;
-    }
 
     if (p.split_keys > 0) {
         if (R0 < p.part_rows) {
@@ -700,40 +650,22 @@ __global__ void __launch_bounds__(HD) paged_flash_combine_kernel(const FlashPara
 }
 
 template <int HD>
-static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_splits, int decode_variant,
-                        cudaStream_t stream) {
+static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_splits, cudaStream_t stream) {
     dim3 grid(n_tiles, p.K * p.head_chunks, mode == 0 ? 1 : n_splits);
     if (mode == 0) {
         constexpr int NW = 4, BN = 64;
         const int smem = 2 * 2 * BN * HD * 2;
-        auto kern = paged_flash_attention_kernel<HD, NW, BN, false>;
+        auto kern = paged_flash_attention_kernel<HD, NW, BN>;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         return rllm_launch(kern, grid, dim3(NW * 32), smem, stream, p);
     }
-    // decode shape.  Few CTAs (they all fit the SMs at once): 4 warps split the CTA's keys and request
-    // them all at once (64 KB of tiles per CTA, one memory round trip).  Many CTAs: one warp per CTA,
-    // the keys-as-M kernel for tiles of at most 8 rows (24 KB: nine CTAs share an SM), else the
-    // 16-row variant with a ring of two 32-key tiles.
-    int dev = 0, n_sm = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-    const long long ctas = (long long)grid.x * grid.y * grid.z;
-    const bool keysplit = decode_variant == 2 || (decode_variant == 0 && ctas <= 3ll * n_sm);
+    // decode shape: one warp per CTA, the keys-as-M kernel for tiles of at most 8 rows, else the 16-row
+    // instance of the template with a ring of two 32-key tiles.  (A 4-warp variant that split a CTA's
+    // keys and requested them all at once was faster at batch 1 until the 8-row kernel asked for its
+    // first tiles before the dependency wait: 11.3 against 10.6 us; it is gone.)
     int st;
-    if (keysplit) {
-        constexpr int NW = 4, BN = 32;
-        if (p.split_keys > NW * BN) return (int)cudaErrorInvalidValue;
-        constexpr int smem = NW * 2 * BN * HD * 2;
-        auto kern = paged_flash_attention_kernel<HD, NW, BN, true>;
-        static bool attr_set = false;
-        if (!attr_set && smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-            if (e != cudaSuccess) return (int)e;
-            attr_set = true;
-        }
-        st = rllm_launch(kern, grid, dim3(NW * 32), smem, stream, p);
-    } else if (p.part_rows <= 8) {
+    if (p.part_rows <= 8) {
         // tiles of at most 8 query rows: the keys as the M side of the MMA.  Tiles of 16 keys in a ring
         // of three (24 KB): nine CTAs share an SM, which counts for more here than a deeper ring
         // (measured at batch 8 and 64, context 2,048: 32-key tiles x 2 stages 24.8 / 109 us,
@@ -742,7 +674,7 @@ static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_split
         st = rllm_launch(paged_decode_attention_kernel<HD, BN, NS>, grid, dim3(32), NS * 2 * BN * HD * 2, stream, p);
     } else {
         constexpr int BN = 32;
-        st = rllm_launch(paged_flash_attention_kernel<HD, 1, BN, false>, grid, dim3(32), 2 * 2 * BN * HD * 2, stream, p);
+        st = rllm_launch(paged_flash_attention_kernel<HD, 1, BN>, grid, dim3(32), 2 * 2 * BN * HD * 2, stream, p);
     }
     if (st) return st;
     return rllm_launch(paged_flash_combine_kernel<HD>, dim3(n_tiles, p.K * p.head_chunks, p.part_rows), dim3(HD),
@@ -752,15 +684,14 @@ static int launch_flash(const FlashParams& p, int mode, int n_tiles, int n_split
 // mode 0: prefill shape (64-row tiles, no split; part_* unused).  mode 1: decode shape (16-row tiles,
 // n_splits splits of split_keys keys; part_o needs tiles*K*head_chunks*n_splits*part_rows*hd floats,
 // part_ml the same with 2 in place of hd).  TT * GH must not exceed the tile's rows; split_keys must be
-// a multiple of 32 and at most 128.  decode_variant: 0 chosen by the number of CTAs, 1 one warp per
-// CTA with a ring of tiles, 2 four warps that split the keys.  Returns cudaErrorInvalidValue for a
+// a multiple of 32.  Returns cudaErrorInvalidValue for a
 // head size other than 64 or 128.
 RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, const void* v_cache, void* out,
                                         float* part_o, float* part_ml, const int* positions, const int* cu_q,
                                         const int* block_table, int table_stride, const int* tile_req,
                                         const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
                                         float scale, int window, int mode, int TT, int GH, int head_chunks,
-                                        int split_keys, int n_splits, int decode_variant, cudaStream_t stream) {
+                                        int split_keys, int n_splits, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     const int rows = mode == 0 ? 64 : 16;
     if (K <= 0 || H % K || TT <= 0 || GH <= 0 || TT * GH > rows || head_chunks * GH < H / K || bs <= 0)
@@ -774,8 +705,8 @@ RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, cons
     p.H = H; p.K = K; p.bs = bs; p.window = window; p.TT = TT; p.GH = GH; p.head_chunks = head_chunks;
     p.split_keys = mode == 0 ? 0 : split_keys; p.part_rows = TT * GH;
     p.scale_log2 = scale * 1.4426950408889634f;
-    if (hd == 128) return launch_flash<128>(p, mode, n_tiles, n_splits, decode_variant, stream);
-    if (hd == 64) return launch_flash<64>(p, mode, n_tiles, n_splits, decode_variant, stream);
+    if (hd == 128) return launch_flash<128>(p, mode, n_tiles, n_splits, stream);
+    if (hd == 64) return launch_flash<64>(p, mode, n_tiles, n_splits, stream);
     return (int)cudaErrorInvalidValue;
 }
 
@@ -830,5 +761,5 @@ RLLM_API int rllm_paged_flash_decode_static(const void* q, const void* k_cache, 
     float* part_ml = part_o + (size_t)RLLM_FLASH_STATIC_SCRATCH_ROWS * 128;
     return rllm_paged_flash_attention(q, k_cache, v_cache, out, part_o, part_ml, positions, cu_q, block_table,
                                       table_stride, tile_req, tile_tok0, n_tiles, H, K, hd, bs, scale, window,
-                                      /*mode=*/1, TT, GH, head_chunks, split_keys, n_splits, /*decode_variant=*/0, stream);
+                                      /*mode=*/1, TT, GH, head_chunks, split_keys, n_splits, stream);
 }

@@ -508,7 +508,6 @@ DECODE_SPLIT_KEYS = 128        # keys per split of the decode shape: a constant,
                                # result never depends on the batch around it
 DECODE_MAX_Q = 8               # requests with at most this many tokens in the step take the decode shape
 DECODE_ROWS = 8                # (token, head) rows of a decode tile: 8 takes the kernel with the keys as the M side
-DECODE_VARIANT = 0             # 0: chosen by the number of CTAs; 1: one warp and a ring of tiles; 2: four warps split the keys
 
 
 class AttentionPlan:
@@ -585,7 +584,7 @@ def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table
         _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req), _ptr(tile_tok0),
         c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
         c_int(mode), c_int(TT), c_int(GH), c_int(head_chunks), c_int(split_keys), c_int(n_splits),
-        c_int(DECODE_VARIANT), _stream()), "paged_flash_attention")
+        _stream()), "paged_flash_attention")
     global _launches
     if mode == 1:
         _launches += 1                         # the combine kernel

@@ -308,14 +308,13 @@ class FakeCtx:
     ([300, 64, 77, 200], [300, 9, 77, 65]),        # prefill shape, whole prompts and portions
     ([520, 5, 90, 130], [130, 1, 17, 2]),          # mixed: both shapes in one step
 ])
-@pytest.mark.parametrize("decode_variant,decode_rows", [(1, 8), (2, 8), (1, 16)])
-def test_paged_flash_attention(hd, H, K, bs, window, lens, q_lens, decode_variant, decode_rows, monkeypatch):
+@pytest.mark.parametrize("decode_rows", [8, 16])
+def test_paged_flash_attention(hd, H, K, bs, window, lens, q_lens, decode_rows, monkeypatch):
     c = paged_case(hd, H, K, bs, lens=lens, q_lens=q_lens, seed=23, dtype=torch.bfloat16, window=window,
                    spike=True)
     out = torch.full_like(c["q"], float("nan"))
     ctx = FakeCtx(c)
-    monkeypatch.setattr(ops(), "DECODE_VARIANT", decode_variant)     # every decode kernel, whatever the size:
-    monkeypatch.setattr(ops(), "DECODE_ROWS", decode_rows)           # keys as the M side (8 rows), 4 warps, 16 rows
+    monkeypatch.setattr(ops(), "DECODE_ROWS", decode_rows)           # both decode kernels: keys as the M side (8 rows), 16 rows
     ops().paged_attention(c["q"], c["kc"], c["vc"], out, ctx, c["table"], H, K, hd, bs, 1.0 / math.sqrt(hd), window)
     assert ctx.plans, "the tensor-core path was not taken"
     assert torch.isfinite(out.float()).all()
