@@ -427,6 +427,10 @@ USE_STREAM = True
 STREAM_MIN_WEIGHTS = 1 << 23      # below 16 MB of weights the short-lived CTAs of skinny_gemm start faster
 
 
+def _stream_ok(a, w) -> bool:
+    return USE_STREAM and a.shape[0] <= 8 and a.shape[1] % 64 == 0 and _tc_ok(a, w)
+
+
 def _prefer_stream(a, w, n: int, swiglu: bool = False) -> bool:
     """gemv_stream takes up to 8 rows always, and 9 to 16 rows for the layer's plain products; with
     9 to 16 rows the gate/up product and the LM head are faster on the tcgen05 kernel (measured
@@ -451,7 +455,7 @@ def _prefer_tc_swap(m: int, n: int, k: int, swiglu: bool = False) -> bool:
     return True
 
 
-def linear(a, w, out=None, out_dtype=None, accumulate=False):
+def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None):
     """out (+)= a . w^T, choosing the kernel by element type and shape.
 
     float32 operands always take the plain CUDA-core product (the true 32-bit path).
@@ -471,7 +475,10 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False):
             raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
         return gemm_plain(a, w, out, accumulate)
     if _skinny_ok(a, w):
-        if _prefer_stream(a, w, n):
+        # stream: the caller's wish for the kernel family (a product that follows a gemv_stream launch
+        # directly should be one too, whatever its size: see _prefer_stream), where the shape allows it
+        want_stream = _prefer_stream(a, w, n) if stream is None else (stream and _stream_ok(a, w))
+        if want_stream:
             return gemv_stream(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
         if _prefer_tc_swap(m, n, k) and out.data_ptr() % 16 == 0:
             return skinny_gemm_tc(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)

@@ -356,3 +356,33 @@ def test_long_context(long_dirs, dtype):
     assert eng.cache.n_free_pages(0) == eng.cache.n_blocks
     from rllm_b200.csrc import ops
     ops.check_device_errors()
+
+
+def test_down_product_follows_the_gate_up_kernel(tmp_path):
+    """A feed-forward whose gate/up matrix is large enough for the streaming product and whose down
+    matrix alone would not be: both take gemv_stream in a decode step (the down product directly
+    behind persistent CTAs must not be a launch of short-lived ones), and the logits are right."""
+    from rllm_b200.csrc import ops
+    cfg = dict(REAL, intermediate_size=4608, num_hidden_layers=1)
+    helpers.make_model_dir(tmp_path, cfg, seed=5, dtype=torch.bfloat16, std=0.03)
+    toks = helpers.random_tokens(40, cfg["vocab_size"], 6)
+    refs = {"a": reference(tmp_path, "bfloat16", toks)}
+    eng = make_engine(tmp_path, "bfloat16", max_tokens=128)
+    seen = []
+    real = ops.gemv_stream
+
+    def spy(a, w, out, epilogue=0, up_row_offset=0, grid=None, stages=None):
+        seen.append((tuple(w.shape), epilogue))
+        return real(a, w, out, epilogue, up_row_offset, grid, stages)
+
+    ops.gemv_stream = spy
+    try:
+        steps = [{"entries": [{"id": "a", "tokens": toks[:30], "want": [29]}]}]
+        steps += [{"entries": [{"id": "a", "tokens": [t], "want": [0]}]} for t in toks[30:]]
+        steps[-1]["end"] = ["a"]
+        out = helpers.run_steps(eng, steps)
+    finally:
+        ops.gemv_stream = real
+    check(out, refs, "bfloat16", "down follows gate/up")
+    assert ((2 * 4608, 1024), ops.EPI_SWIGLU) in seen and ((1024, 4608), ops.EPI_ACCUM) in seen
+    assert 2 * 4608 * 1024 >= ops.STREAM_MIN_WEIGHTS > 1024 * 4608
