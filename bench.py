@@ -113,6 +113,12 @@ def main():
     ap.add_argument("--block-size", type=int, default=32, help="tokens per page of the KV cache")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="decode: the default line.  serving: --requests prompts of 16..2,048 tokens with 128..512 "
+                         "generated tokens each through LLM.generate (continuous batching), one line of its own")
+    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--parallel", type=int, default=32, help="serving: requests running at once")
+    ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: prompt tokens per step")
     ap.add_argument("--profile", choices=["decode", "prefill"],
                     help="run only that step between cudaProfilerStart/Stop (for ncu --profile-from-start off) "
                          "and print no benchmark line")
@@ -207,6 +213,45 @@ def main():
         del llm
         torch.cuda.empty_cache()
         return {"ms": ms, "tok_s": batch * 1000.0 / ms, "h2d": staging, "d2h": 4 * batch}
+
+    def serving_run():
+        """Continuous batching through the entry point: requests of mixed lengths wait, are admitted
+        as others finish, prompts go in portions beside decoded tokens.  Wall clock around the
+        second of two identical generations (the first loads kernels and captures graphs)."""
+        from rllm_b200 import LLM
+        lens = torch.randint(16, PROMPT + 1, (a.requests,), generator=g).tolist()
+        outs = torch.randint(128, 513, (a.requests,), generator=g).tolist()
+        prompts = [torch.randint(0, V, (n,), generator=g).tolist() for n in lens]
+        llm = LLM(model, ctx=CTX, block_size=a.block_size, prefill_chunk=a.prefill_chunk, parallel=a.parallel,
+                  kv_tokens=a.parallel * (PROMPT + 512))
+        llm.generate(prompts, max_tokens=outs)
+        clocks = ClockSampler()
+        clocks.start()
+        launches0 = ops.launch_count()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = llm.generate(prompts, max_tokens=outs)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        clk = clocks.stop()
+        st = llm.last_stats
+        assert [len(r) for r in res] == outs
+        gen = sum(outs)
+        print(json.dumps({
+            "metric": f"generated tok/s, continuous batching (Qwen3-{a.shape.upper()} bf16, {a.requests} requests, "
+                      "prompts 16..2,048, 128..512 generated)",
+            "value": round(gen / dt, 1), "unit": "tok/s", "n_gpus": 1, "steps": st["steps"], "warmup": 1,
+            "ms_per_step": round(dt * 1000.0 / st["steps"], 4), "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
+            "config": {"model": f"Qwen3-{a.shape.upper()}-shaped", "layers": a.layers, "layers_full_model": full_layers,
+                       "requests": a.requests, "parallel": a.parallel, "prefill_chunk": a.prefill_chunk,
+                       "kv_block": a.block_size, "prompt_tokens": sum(lens), "generated_tokens": gen},
+            "prompt_tok_s": round(sum(lens) / dt, 1), "seconds": round(dt, 3), "preemptions": st["preemptions"],
+            "clocks": clk, "gpu_launches": ops.launch_count() - launches0}))
+        return 0
+
+    if a.workload == "serving":
+        return serving_run()
 
     if a.profile:
         eng = Engine(model, block_size=a.block_size, max_tokens=a.batch * CTX, max_requests=a.batch)

@@ -1,22 +1,24 @@
-// Weight-streaming product for decode steps, C[m,n] (+)= X[m,k] . W[n,k]^T with m <= 16, as one
-// persistent CTA per SM fed by TMA.
+// Weight-streaming product for decode steps, C[m,n] (+)= X[m,k] . W[n,k]^T with m <= 16, as a few
+// persistent CTAs per SM fed by TMA.
 //
 // The product is bound by reading W once from HBM, and the matrices of one layer are small (34 to
 // 200 MB): a grid of short-lived CTAs spends a good part of its time filling and draining the
-// machine.  Here the grid is the number of SMs.  The weight rows are cut into granules of 8 rows
-// and every CTA takes an equal share of consecutive granules (the shares differ by at most one).
-// A producer thread streams the CTA's share through a ring of shared-memory stages with TMA: a stage
-// is 64 k-columns of up to 64 weight rows (one 1 KB box of 8 rows x 128 bytes per granule, 128-byte
-// swizzle) and the same 64 k-columns of the batch rows.  Four consumer warps take 16 rows each,
-// read their fragments with ldmatrix and multiply with mma.sync m16n8k16 (float32 accumulators in
-// registers), release the stage, and write their rows when the K range is done, while the producer
-// is already filling the ring with the next rows.  Nothing waits on another CTA; the sum over k
-// runs in one fixed order, so a row's result does not depend on the batch or on the grid.
+// machine.  Here the grid is two or three CTAs per SM, all resident from the start.  The weight
+// rows are cut into granules of 8 rows and every CTA takes an equal share of consecutive granules
+// (the shares differ by at most one).  A producer thread streams the CTA's share through a ring of
+// shared-memory stages with TMA: a stage is 16 KB of weights, 128 / ATOMS rows of ATOMS * 64
+// k-columns (128-byte swizzle), and the same k-columns of the batch rows; the shape is chosen by
+// the launcher so that a share of a few rows still fills whole stages.  Four consumer warps split
+// the k16 steps of a stage, read their fragments with ldmatrix and multiply with mma.sync m16n8k16
+// (float32 accumulators in registers), release the stage, and add their partial sums in warp order
+// through shared memory when the K range of a chunk of rows is done, while the producer is already
+// filling the ring with the next rows.  Nothing waits on another CTA; the sum over k runs in one
+// fixed order, so a row's result does not depend on the batch or on the grid.
 //
 // With a programmatic dependent launch the kernel starts while the one before it is still running:
 // the weights do not depend on that kernel, so the ring is filled with weights at once, and only
-// the batch rows are loaded after griddepcontrol.wait.  The ring is sized so that two such kernels
-// fit one SM (the running one and the next, already holding its first weights).
+// the batch rows are loaded after griddepcontrol.wait.  The ring is sized so that the CTAs of two
+// such kernels fit one SM (the running one and the next, already holding its first weights).
 //
 // Epilogues as in the other products: store, accumulate into a float32 C, and SwiGLU (W holds n
 // gate rows and, from row up_row_offset on, n up rows; a granule is then 8 gate rows and the 8 up
@@ -108,8 +110,8 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
 
     // Every thread signals at once that the next kernel of the stream may be scheduled: all CTAs of
     // this grid are resident from the start, so the next kernel takes nothing from this one; it
-    // comes to rest beside it (shared memory allows two such CTAs per SM, not three) with its first
-    // weights in flight, and waits in its own griddepcontrol.wait for this grid to complete.
+    // comes to rest beside it (a ring of three stages is about 60 KB, so the CTAs of two grids fit
+    // the SM's shared memory) with its first weights in flight, and waits in its own griddepcontrol.wait for this grid to complete.
     pdl_launch_dependents();
     if (tid == 0) {
         for (int i = 0; i < 4; ++i) asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.w[i]) : "memory");

@@ -33,8 +33,14 @@ def _ptr(t):
     return c_void_p(0) if t is None else c_void_p(t.data_ptr())
 
 
+_raw_stream = torch._C._cuda_getCurrentRawStream
+_current_device = torch._C._cuda_getDevice
+
+
 def _stream():
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream of the current device, as the launchers take it (the raw handle: building a
+    torch.cuda.Stream object for every launch costs more than the launch)."""
+    return c_void_p(_raw_stream(_current_device()))
 
 
 def _need_cuda(*ts):
@@ -77,12 +83,12 @@ _timed: dict = {}
 
 def _lib(name: str):
     """The loaded library `name`; with RLLM_B200_PROFILE=1 its launchers are timed with CUDA events."""
-    lib = build.load(name)
-    if profiler.enabled():
-        t = _timed.get(name)
-        if t is None:
-            t = _timed[name] = profiler.TimedLibrary(lib)
-        return t
+    lib = _timed.get(name)
+    if lib is None:
+        lib = build.load(name)
+        if profiler.enabled():
+            lib = profiler.TimedLibrary(lib)
+        _timed[name] = lib
     return lib
 
 

@@ -40,20 +40,24 @@ class LLM:
         self.host_sampling = host_sampling
         self.last_stats = {}
 
-    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.0,
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens=256, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, seed: int = 0, stop_ids: Sequence[int] = (),
                  return_reasons: bool = False, frequency_penalty: float = 0.0, presence_penalty: float = 0.0,
                  logit_bias=()):
         """Generates for every prompt (continuous batching); returns the generated ids per prompt,
-        in order.  Request i samples with seed `seed + i`.  logit_bias: (token, delta) pairs or a
+        in order.  max_tokens: one number, or one per prompt.  Request i samples with seed
+        `seed + i`.  logit_bias: (token, delta) pairs or a
         {token: delta} mapping, added to the logits with the frequency and presence penalties over
         the tokens generated so far before the token is chosen."""
         if isinstance(logit_bias, dict):
             logit_bias = tuple(logit_bias.items())
+        limits = [max_tokens] * len(prompts) if isinstance(max_tokens, int) else list(max_tokens)
+        if len(limits) != len(prompts):
+            raise ValueError(f"max_tokens: {len(limits)} numbers for {len(prompts)} prompts")
         sched = Scheduler(self.engine.cache, ctx=self.ctx, max_num_seqs=self.parallel,
                           prefill_chunk=self.prefill_chunk)
         for i, p in enumerate(prompts):
-            sched.add(Request(i, list(p), max_tokens,
+            sched.add(Request(i, list(p), int(limits[i]),
                               SamplingParams(temperature, top_k, top_p, seed + i, frequency_penalty,
                                              presence_penalty, tuple(logit_bias)), frozenset(stop_ids)))
         results = {}

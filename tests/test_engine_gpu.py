@@ -152,6 +152,11 @@ def test_preemption_gives_the_same_tokens(dirs):
     got = tight.generate(prompts, max_tokens=100)
     assert tight.last_stats["preemptions"] >= 1
     assert got == want
+    # one limit per prompt: each request stops at its own, with the tokens it had under the common one
+    limits = [3, 100, 1, 40]
+    assert tight.generate(prompts, max_tokens=limits) == [w[:n] for w, n in zip(want, limits)]
+    with pytest.raises(ValueError, match="max_tokens"):
+        tight.generate(prompts, max_tokens=[3, 4])
 
 
 def test_sampling_is_reproducible_whatever_the_batch(dirs):
