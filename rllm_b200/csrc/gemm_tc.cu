@@ -319,6 +319,31 @@ RLLM_API int rllm_gemm_tc(const void* A, const void* B, void* C, int c_dtype, in
 // memory (mapa / ld.shared::cluster) and applies the epilogue -- no global scratch, no atomics, a
 // fixed order of addition.  SwiGLU: a CTA takes 64 gate rows and the 64 up rows of the same index.
 // =====================================================================================================
+// The sums of one weight row for BN / S batch columns, parked by the S CTAs of a cluster in their
+// shared memory as [batch column][weight row]: all loads are issued before the first addition (a
+// round trip through distributed shared memory takes about 200 ns), the additions run in rank order.
+template <int BN, int S>
+__device__ __forceinline__ void cluster_row_sums(uint32_t red_addr, uint32_t elem_offset, float (&acc)[BN / 2]) {
+    constexpr int COLS = BN / S;
+    float f[S][COLS];
+#pragma unroll
+    for (int z = 0; z < S; ++z) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr), "r"(z));
+        remote += elem_offset * 4;
+#pragma unroll
+        for (int i = 0; i < COLS; ++i)
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f[z][i]) : "r"(remote + (uint32_t)(i * TC_BM) * 4) : "memory");
+    }
+#pragma unroll
+    for (int i = 0; i < COLS; ++i) {
+        float a = f[0][i];
+#pragma unroll
+        for (int z = 1; z < S; ++z) a += f[z][i];
+        acc[i] = a;
+    }
+}
+
 template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(TC_THREADS, STAGES > 4 ? 1 : 2)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -336,8 +361,11 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     __shared__ volatile int abort_flag;
     float* red = reinterpret_cast<float*>(smem);            // exchange buffer: the stages are free once the MMAs are done
     float v[BN];                                            // this thread's accumulator row (epilogue warps)
+    float c_old[EPI == TC_EPI_ACCUM ? BN : 1];              // and the values of C it adds to
 #pragma unroll
     for (int j = 0; j < BN; ++j) v[j] = 0.f;
+#pragma unroll
+    for (int j = 0; j < (EPI == TC_EPI_ACCUM ? BN : 1); ++j) c_old[j] = 0.f;
     bool ep_ok = true;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -347,6 +375,14 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     const int kb_per = (nkb + n_splits - 1) / n_splits;
     const int kb0 = split * kb_per, kb1 = min(nkb, kb0 + kb_per);
     const int my_kb = max(0, kb1 - kb0);
+    // With 2, 4 or 8 CTAs on a tile the sums are added and written by all of them, each taking its
+    // share of the tile's weight rows (`scatter`): thread t of the 128 epilogue threads takes row
+    // split * R + t % R (R = 128 / n_splits rows per CTA) and the batch columns of group t / R.
+    const bool scatter = EPI != TC_EPI_SWIGLU && (n_splits == 2 || n_splits == 4 || n_splits == 8);
+    const int sc_rows = TC_BM / n_splits, sc_cols = BN / n_splits;
+    const int sc_t = (warp & 3) * 32 + lane;
+    const int sc_row = scatter ? split * sc_rows + (sc_t & (sc_rows - 1)) : 0;
+    const int sc_b0 = scatter ? (sc_t / sc_rows) * sc_cols : 0;
 
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW) : "memory");
@@ -422,6 +458,21 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         // ---- epilogue, first half: accumulator -> registers (thread = weight row, registers = batch columns)
         pdl_wait();                                     // C may be touched from here on
         const int quarter = warp & 3;
+        if (EPI == TC_EPI_ACCUM && scatter) {
+            // the old values of C: fetched while the MMAs run, so that the end of the kernel does not wait for them
+            if (n0 + sc_row < n) {
+#pragma unroll
+                for (int i = 0; i < BN / 2; ++i)
+                    if (i < sc_cols && sc_b0 + i < m) c_old[i] = to_f<TC>(C[(size_t)(sc_b0 + i) * ldc + n0 + sc_row]);
+            }
+        } else if (EPI == TC_EPI_ACCUM && split == 0) {
+            const int out_col = n0 + quarter * 32 + lane;
+            if (out_col < n) {
+#pragma unroll
+                for (int b = 0; b < BN; ++b)
+                    if (b < m) c_old[b] = to_f<TC>(C[(size_t)b * ldc + out_col]);
+            }
+        }
         if (my_kb > 0) {
             ep_ok = mbar_wait(&acc_bar, 0, &abort_flag);
             if (!ep_ok && !abort_flag) { atomicExch(err, TC_ERR_ACC); abort_flag = 1; }
@@ -440,8 +491,8 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             }
         }
         pdl_launch_dependents();
-        if (n_splits > 1 && split > 0) {
-            // a follower of the cluster: park the partial sums in this CTA's own shared memory
+        if (n_splits > 1 && (split > 0 || scatter)) {
+            // park the partial sums in this CTA's own shared memory for the CTAs that add them
             // (the stages are free: all MMAs that read them have completed)
             const int row = quarter * 32 + lane;
 #pragma unroll
@@ -456,17 +507,41 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
-    if (warp >= 2 && split == 0) {
+    if (warp >= 2 && scatter) {
+        // ---- epilogue, second half, shared by the cluster: this thread's row and columns from every
+        // CTA's parked sums (its own among them), in rank order, which is ascending k
+        float acc[BN / 2];
+#pragma unroll
+        for (int i = 0; i < BN / 2; ++i) acc[i] = 0.f;
+        const uint32_t off = (uint32_t)(sc_b0 * TC_BM + sc_row);
+        if (n_splits == 2) cluster_row_sums<BN, 2>(s_addr(red), off, acc);
+        else if (n_splits == 4) cluster_row_sums<BN, 4>(s_addr(red), off, acc);
+        else cluster_row_sums<BN, 8>(s_addr(red), off, acc);
+        const int out_col = n0 + sc_row;
+        if (ep_ok && out_col < n) {
+#pragma unroll
+            for (int i = 0; i < BN / 2; ++i)
+                if (i < sc_cols && sc_b0 + i < m) {
+                    const float o = (EPI == TC_EPI_ACCUM) ? acc[i] + c_old[i] : acc[i];
+                    C[(size_t)(sc_b0 + i) * ldc + out_col] = from_f<TC>(o);
+                }
+        }
+    } else if (warp >= 2 && split == 0) {
         // ---- epilogue, second half (the cluster's leader): add the followers' sums in rank order, write out
         const int row = (warp & 3) * 32 + lane;
         for (int z = 1; z < n_splits; ++z) {
             uint32_t remote;
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(s_addr(red)), "r"(z));
+            // 16 loads in flight at a time: issued one by one with the addition between them, each
+            // would wait for the round trip of the one before
 #pragma unroll
-            for (int b = 0; b < BN; ++b) {
-                float f;
-                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f) : "r"(remote + (uint32_t)(b * TC_BM + row) * 4) : "memory");
-                v[b] += f;
+            for (int b0 = 0; b0 < BN; b0 += 16) {
+                float f[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(f[i]) : "r"(remote + (uint32_t)((b0 + i) * TC_BM + row) * 4) : "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[b0 + i] += f[i];
             }
         }
         // global weight row of this thread (SwiGLU: rows 0..63 gate j, rows 64..127 up j)
@@ -475,7 +550,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (EPI == TC_EPI_SWIGLU) {
             if (ep_ok && row >= 64) {
 #pragma unroll
-                for (int b = 0; b < BN; ++b) red[(row - 64) * BN + b] = v[b];
+                for (int b = 0; b < BN; ++b) red[b * 64 + (row - 64)] = v[b];      // consecutive rows, consecutive banks
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
             if (ep_ok && row < 64 && col_ok) {
@@ -483,14 +558,13 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 for (int b = 0; b < BN; ++b)
                     if (b < m) {
                         const float g = v[b];
-                        C[(size_t)b * ldc + out_col] = from_f<TC>(g / (1.0f + expf(-g)) * red[row * BN + b]);
+                        C[(size_t)b * ldc + out_col] = from_f<TC>(__fdividef(g, 1.0f + __expf(-g)) * red[b * 64 + row]);
                     }
             }
         } else if (ep_ok && col_ok) {
-            if (EPI == TC_EPI_ACCUM) {                   // all loads first, then the stores: independent round trips
+            if (EPI == TC_EPI_ACCUM) {
 #pragma unroll
-                for (int b = 0; b < BN; ++b)
-                    if (b < m) v[b] += to_f<TC>(C[(size_t)b * ldc + out_col]);
+                for (int b = 0; b < BN; ++b) v[b] += c_old[b];
             }
 #pragma unroll
             for (int b = 0; b < BN; ++b)
