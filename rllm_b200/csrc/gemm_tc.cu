@@ -314,10 +314,16 @@ RLLM_API int rllm_gemm_tc(const void* A, const void* B, void* C, int c_dtype, in
 // M side (128 weight rows per CTA, streamed once from HBM through a deep TMA ring), the m <= 64
 // batch rows X[m,k] are the N side, so the accumulator D[weight row, batch row] is C transposed.
 // The K range may be split over the grid.y CTAs of a thread-block cluster to fill the machine when
-// n/128 is small: each CTA accumulates its K slice, the followers park their sums in their own
-// shared memory, and the cluster's leader adds them in rank order through distributed shared
-// memory (mapa / ld.shared::cluster) and applies the epilogue -- no global scratch, no atomics, a
-// fixed order of addition.  SwiGLU: a CTA takes 64 gate rows and the 64 up rows of the same index.
+// n/128 is small: each CTA accumulates its K slice and parks its sums in its own shared memory.
+// With 2, 4 or 8 CTAs every CTA of the cluster then takes its share of the tile's weight rows,
+// reads those rows' sums from all CTAs through distributed shared memory (mapa / ld.shared::cluster)
+// in rank order, which is ascending k, and writes its share of C; the old values of an
+// accumulating C are fetched while the MMAs still run.  (With the leader alone adding and writing,
+// the kernel's last 6 us were a chain of round trips: 192 loads through distributed shared memory
+// per thread, then 64 loads of C, then 64 stores; spread over four CTAs they take 2.)  Other split
+// counts, and SwiGLU, leave the additions to the cluster's leader.  No global scratch, no atomics,
+// a fixed order of addition.  SwiGLU: a CTA takes 64 gate rows and the 64 up rows of the same
+// index; the up rows' sums reach the gate rows' threads through shared memory.
 // =====================================================================================================
 // The sums of one weight row for BN / S batch columns, parked by the S CTAs of a cluster in their
 // shared memory as [batch column][weight row]: all loads are issued before the first addition (a
@@ -596,15 +602,20 @@ static int launch_swap_stages(const CUtensorMap& tw, const CUtensorMap& tx, void
                                err);
 }
 
-// Few CTAs (at most one per SM): one CTA per SM with a ring of 8 stages, so that a single CTA keeps
-// 190 KB in flight.  Many CTAs: 4 stages, two CTAs share an SM and one streams while the other
-// starts or ends.
+// At most one CTA per SM: a ring of 8 stages, so that a single CTA keeps 190 KB in flight.  More
+// CTAs than SMs: 4 stages, two CTAs share an SM and one streams while the other starts or ends.
 template <int BN, int EPI, typename TC>
 static int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, void* C, int ldc, int m, int n, int K, int up,
                        int n_splits, int* err, cudaStream_t stream) {
     constexpr int ROWS_OUT = (EPI == TC_EPI_SWIGLU) ? TC_BM / 2 : TC_BM;
     const int ctas = ((n + ROWS_OUT - 1) / ROWS_OUT) * n_splits;
-    if (ctas <= 160)
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            n_sm = 148;
+    }
+    if (ctas <= n_sm)
         return launch_swap_stages<BN, EPI, TC, 8>(tw, tx, C, ldc, m, n, K, up, n_splits, err, stream);
     return launch_swap_stages<BN, EPI, TC, 4>(tw, tx, C, ldc, m, n, K, up, n_splits, err, stream);
 }

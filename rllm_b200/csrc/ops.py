@@ -346,13 +346,22 @@ def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
     return out
 
 
-def tc_swap_splits(n_tiles: int, k: int) -> int:
-    """Number of K splits (CTAs of a cluster) for the swapped tcgen05 product: enough CTAs to put
-    about one on every SM, at least 8 blocks of 64 along K each, at most 8."""
+def tc_swap_splits(n_tiles: int, k: int, swiglu: bool = False, n_sm: int = 148) -> int:
+    """Number of K splits (CTAs of a cluster) for the swapped tcgen05 product, a power of two up to
+    8 (clusters of 3, 5, 6, 7 CTAs schedule badly) that leaves every CTA at least 4 blocks of 64
+    along K.  Plain products: as many as keep the CTAs under 1.6 per SM: above one per SM two CTAs
+    share an SM, one streaming while the other starts or ends, and the cluster's CTAs share the
+    additions and the writes.  (Measured at 24 and 64 rows on the layer sizes of Qwen3-0.6B, 8B and
+    32B: 48 tiles take 4 splits, 32 take 4, 40 take 4, 8 take 8.)  SwiGLU, where the cluster's
+    leader adds and writes alone: at most one CTA per SM."""
     nkb = -(-k // 64)
-    limit = max(1, min(148 // n_tiles, nkb // 8, 8))
+    if swiglu:
+        limit = min(n_sm // n_tiles, nkb // 8)
+    else:
+        limit = min(int(1.6 * n_sm) // n_tiles, nkb // 4)
+    limit = max(1, min(limit, 8))
     splits = 1
-    while splits * 2 <= limit:           # powers of two: clusters of 3, 5, 6, 7 CTAs schedule badly
+    while splits * 2 <= limit:
         splits *= 2
     return splits
 
@@ -371,7 +380,7 @@ def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None
     rows_out = 64 if epilogue == EPI_SWIGLU else 128
     n_tiles = -(-n // rows_out)
     if n_splits is None:
-        n_splits = tc_swap_splits(n_tiles, k)
+        n_splits = tc_swap_splits(n_tiles, k, epilogue == EPI_SWIGLU, sm_count(a.device))
     n_splits = max(1, min(int(n_splits), 8))
     st = _lib("tc").rllm_gemm_tc_swap(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),

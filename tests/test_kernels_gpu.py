@@ -368,9 +368,10 @@ def test_gemm_tc_swiglu(m, F, k):
 
 @pytest.mark.parametrize("m", [1, 8, 17, 32, 33, 64])
 @pytest.mark.parametrize("n,k,splits", [(96, 512, None), (37, 264, 1), (4096, 4096, None), (1000, 1096, 3), (300, 8, 1),
-                                        (130, 2048, 4)])
+                                        (130, 2048, 4), (640, 4096, 8), (200, 1024, 2)])
 def test_skinny_gemm_tc(m, n, k, splits):
-    """The swapped tcgen05 product: weights as the streamed operand, with and without split K."""
+    """The swapped tcgen05 product: weights as the streamed operand, with and without split K (2, 4
+    and 8 CTAs of a cluster share the additions and the writes; 3 leaves them to the leader)."""
     o = ops()
     a, w = rnd(m, k, seed=29, dtype=torch.bfloat16), rnd(n, k, seed=30, scale=0.1, dtype=torch.bfloat16)
     ref = a.float() @ w.float().t()
@@ -472,3 +473,12 @@ def test_gemv_stream_lm_head_size():
     o.gemv_stream(a.to(DEV), w.to(DEV), again)
     assert torch.equal(again, out)
     o.check_device_errors()
+
+
+def test_opbench_times_a_product():
+    """The single-kernel timer runs its graph of back-to-back launches and reports a positive time."""
+    from rllm_b200.csrc import opbench
+    us, gbs = opbench.time_product("skinny_gemm_tc", 24, 1024, 2048, "accum", launches=8)
+    assert us > 0 and gbs > 0
+    us, gbs = opbench.time_product("gemv_stream", 8, 4096, 2048, "swiglu", launches=8)
+    assert us > 0 and gbs > 0
