@@ -226,6 +226,26 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
             for (int j = 0; j < NT; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[sl][j][e] = 0.f;
+        // Accumulating: the old values of the rows this thread will write are fetched now and arrive
+        // while the chunk streams (read at the chunk's end they cost a round trip to L2 each, one
+        // after the other, at the end of the kernel).
+        float c_old[NT][4];
+        if (EPI == SV_EPI_ACCUM) {
+            if (!waited) { pdl_wait(); waited = true; }      // C belongs to the kernels before until here
+            if (warp < n_slots) {
+                const int row_end = min(n, g_last * SV_GRAN);
+                const int r_lo = (g0 + 2 * warp) * SV_GRAN + g;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int j = 0; j < NT; ++j)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int b = 8 * j + 2 * t + e, row = r_lo + 8 * h;
+                            c_old[j][2 * h + e] = (row < row_end && b < m) ? to_f<TC>(C[(size_t)b * ldc + row]) : 0.f;
+                        }
+            }
+        }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
@@ -306,7 +326,7 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
                         if (b < m) {
                             TC* c = C + (size_t)b * ldc + row;
                             const float val = v[j][2 * h + e];
-                            if (EPI == SV_EPI_ACCUM) *c = from_f<TC>(to_f<TC>(*c) + val);
+                            if (EPI == SV_EPI_ACCUM) *c = from_f<TC>(c_old[j][2 * h + e] + val);
                             else *c = from_f<TC>(val);
                         }
                     }
