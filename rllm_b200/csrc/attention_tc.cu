@@ -362,6 +362,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
         }
     }
+    __syncwarp();          // the lanes of the MMA warp that had no role meet the elected one: the barrier wants whole warps
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 512);

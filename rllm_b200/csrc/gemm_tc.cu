@@ -232,6 +232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         }
     }
+    __syncwarp();          // the lanes that had no role meet the elected one: the barrier below wants whole warps
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
@@ -505,6 +506,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             for (int b = 0; b < BN; ++b) red[b * TC_BM + row] = v[b];
         }
     }
+    __syncwarp();          // the lanes that had no role meet the elected one: the barriers below want whole warps
     tc_fence_before();
     __syncthreads();
     if (n_splits > 1) {
