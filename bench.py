@@ -284,7 +284,7 @@ def main():
     e2e_run = generate_run(a.batch, a.steps, a.warmup)
 
     out = {
-        "metric": METRIC if a.shape == "8b" else METRIC.replace("Qwen3-8B", f"Qwen3-{a.shape.upper()}"), "value": round(main_run["tok_s"], 2), "unit": "tok/s", "n_gpus": 1,
+        "metric": METRIC.replace("Qwen3-8B", f"Qwen3-{a.shape.upper()}").replace("batch 8", f"batch {a.batch}"), "value": round(main_run["tok_s"], 2), "unit": "tok/s", "n_gpus": 1,
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(main_run["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
