@@ -592,8 +592,8 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
 template <int HD>
 __global__ void __launch_bounds__(HD) paged_flash_combine_kernel(const FlashParams p, int n_splits) {
     extern __shared__ float wgt[];               // [n_splits] m, then the weight, of each split; [n_splits] l
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int tile = blockIdx.x, R = blockIdx.z;
     const int req = p.tile_req[tile], tok0 = p.tile_tok0[tile];
     const int nt = min(p.TT, p.cu_q[req + 1] - tok0);

@@ -45,8 +45,8 @@ __global__ void add_rms_norm_kernel(float* __restrict__ x, const TD* __restrict_
                                     const int* __restrict__ rows, const float* __restrict__ w,
                                     TO* __restrict__ out, int d, float eps, int write_x) {
     __shared__ float red[33];
+    pdl_launch_dependents();          // the product that follows fetches its first weights beside this kernel
     pdl_wait();
-    pdl_launch_dependents();
 
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -86,8 +86,8 @@ __global__ void __launch_bounds__(256)
 add_rms_norm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, const int* __restrict__ rows,
                         const float* __restrict__ w, TO* __restrict__ out, int d, float eps, int write_x) {
     __shared__ float red[33];
+    pdl_launch_dependents();          // as above
     pdl_wait();
-    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* xr = x + (size_t)src * d;
@@ -241,8 +241,11 @@ qk_norm_rope_store_token_kernel(const TI* __restrict__ qkv, const float* __restr
                                 TO* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache, int H,
                                 int K, int hd, int bs, float eps, int write_kv) {
     __shared__ float2 cs[128];                    // (cos, sin) of pair j at this token's position
-    pdl_wait();
+    // The attention kernel that follows may start at once: before its own wait (which ends when this
+    // grid has completed, and so the product before it) it reads only the step's index arrays and
+    // keys of earlier steps, and that part of it then runs beside this kernel and the end of the one before.
     pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
