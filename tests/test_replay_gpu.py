@@ -267,6 +267,76 @@ def test_layer_sizes_of_a_real_model(real_dirs, dtype):
     ops.check_device_errors()
 
 
+# The layer sizes of Qwen3-8B (one layer of it, a small vocabulary that is no power of two): matrices
+# of 16 MB and more, which the decode steps hand to the weight-streaming kernel (all four products
+# of the layer, and the down product with k = 12,288), portions of 17 to 64 rows to the swapped tcgen05
+# kernel with 4 CTAs of a cluster on a tile (QKV, O, down) and with one (gate/up), whole prompts to
+# the large-tile tcgen05 product with 24,576 weight rows.
+BIG = dict(REAL, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+           intermediate_size=12288, num_hidden_layers=1, vocab_size=4099, tie_word_embeddings=False)
+
+
+def test_layer_sizes_of_the_8b_model(tmp_path):
+    from rllm_b200.csrc import ops
+    helpers.make_model_dir(tmp_path, BIG, seed=78, dtype=torch.bfloat16, std=0.02)
+    lens = {"a": 210, "b": 97, "c": 64}
+    reqs = {rid: helpers.random_tokens(n, BIG["vocab_size"], 600 + i) for i, (rid, n) in enumerate(lens.items())}
+    refs = {rid: reference(tmp_path, "bfloat16", t) for rid, t in reqs.items()}
+    eng = make_engine(tmp_path, "bfloat16", max_tokens=1024, block_size=32)
+    seen = set()
+    real_stream, real_swap = ops.gemv_stream, ops.skinny_gemm_tc
+
+    def spy_stream(a, w, out, *args, **kw):
+        seen.add(("stream", tuple(w.shape)))
+        return real_stream(a, w, out, *args, **kw)
+
+    def spy_swap(a, w, out, *args, **kw):
+        seen.add(("swap", tuple(w.shape)))
+        return real_swap(a, w, out, *args, **kw)
+
+    ops.gemv_stream, ops.skinny_gemm_tc = spy_stream, spy_swap
+    try:
+        # whole prompts
+        for rid, toks in reqs.items():
+            want = sorted({0, 1, 63, len(toks) - 2, len(toks) - 1})
+            out = helpers.run_steps(eng, [{"entries": [{"id": rid, "tokens": toks, "want": want}], "end": [rid]}])
+            check(out, refs, "bfloat16", f"8B sizes, whole {rid}")
+        # portions of 17 to 64 rows, of 9 to 16 rows, and single tokens beside them
+        sizes = {"a": [64, 40, 17, 1, 1, 33, 12, 1, 1, 40], "b": [20, 1, 1, 50, 9, 1, 15], "c": [33, 16, 1, 1, 13]}
+        cut = {rid: 0 for rid in reqs}
+        steps = []
+        for i in range(max(len(v) for v in sizes.values())):
+            entries, end = [], []
+            for rid, toks in reqs.items():
+                if i >= len(sizes[rid]):
+                    continue
+                k = sizes[rid][i]
+                assert cut[rid] + k <= len(toks)
+                entries.append({"id": rid, "tokens": toks[cut[rid]:cut[rid] + k], "want": sorted({0, k - 1})})
+                cut[rid] += k
+                if i == len(sizes[rid]) - 1:
+                    end.append(rid)
+            steps.append({"entries": entries, "end": end})
+        out = helpers.run_steps(eng, steps)
+        check(out, refs, "bfloat16", "8B sizes, portions beside decoded tokens")
+        # 24 single-token steps of all three at once after a whole prompt (graphs of the decode step), twice
+        steps = [{"entries": [{"id": rid, "tokens": toks[:len(toks) - 24], "want": []} for rid, toks in reqs.items()]}]
+        for j in range(24):
+            steps.append({"entries": [{"id": rid, "tokens": [toks[len(toks) - 24 + j]], "want": [0]}
+                                      for rid, toks in reqs.items()]})
+        steps[-1]["end"] = list(reqs)
+        out = helpers.run_steps(eng, steps)
+        check(out, refs, "bfloat16", "8B sizes, decoding")
+        again = helpers.run_steps(eng, steps)
+        assert all(torch.equal(again[key], out[key]) for key in out)
+    finally:
+        ops.gemv_stream, ops.skinny_gemm_tc = real_stream, real_swap
+    for shape in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)):
+        assert ("stream", shape) in seen and ("swap", shape) in seen, (shape, sorted(seen))
+    eng.cache.check_invariants()
+    ops.check_device_errors()
+
+
 # ---------------------------------------------------------------- a long context
 # 3,001 tokens: dozens of key tiles per query tile in the prefill kernels, 24 splits in the decode
 # kernel, a block table of 94 pages, the graph's context paddings.  The q/k norm weights are scaled
