@@ -588,3 +588,26 @@ def test_native_step_builder_arrays():
                                    pad_quantum=32)
     assert meta3[5] == 11 and meta3[3] == 32 // 4
     nat.check_invariants()
+
+
+def test_launch_plans_of_the_few_row_products():
+    """The rules that pick CTAs and K splits are plain functions of the shape (no device needed)."""
+    from rllm_b200.csrc import ops
+    # swapped tcgen05 product: a power of two, CTAs up to 1.6 per SM, at least 4 blocks of 64 along K each
+    assert ops.tc_swap_splits(48, 4096) == 4            # QKV of the 8B sizes: 192 CTAs
+    assert ops.tc_swap_splits(32, 4096) == 4 and ops.tc_swap_splits(32, 12288) == 4      # O, down
+    assert ops.tc_swap_splits(40, 8192) == 4            # 160 CTAs
+    assert ops.tc_swap_splits(8, 2048) == 8
+    assert ops.tc_swap_splits(8, 512) == 2              # 8 blocks along K: 4 each
+    assert ops.tc_swap_splits(400, 4096) == 1
+    assert ops.tc_swap_splits(192, 4096, swiglu=True) == 1
+    assert ops.tc_swap_splits(48, 1024, swiglu=True) == 2 and ops.tc_swap_splits(48, 4096, swiglu=True) == 2
+    for tiles in range(1, 300, 7):
+        for k in (64, 512, 4096, 12288):
+            for sw in (False, True):
+                s = ops.tc_swap_splits(tiles, k, sw)
+                assert s in (1, 2, 4, 8) and (s == 1 or -(-k // 64) // s >= 4)
+    # weight-streaming product: two or three CTAs per SM, three stages
+    assert ops.stream_plan(4096, 4096) == (296, 3)
+    assert ops.stream_plan(12288, 4096, swiglu=True) == (444, 3)
+    assert ops.stream_plan(151936, 4096) == (444, 3)
