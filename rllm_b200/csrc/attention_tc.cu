@@ -1,20 +1,28 @@
 // Causal flash attention over the paged cache for prompt portions on the Blackwell tensor cores:
 // S = Q K^T and O += P V are tcgen05.mma with the accumulators S (double-buffered) and O in tensor
-// memory; Q, K and V tiles arrive by TMA (128-byte swizzle), P goes from the softmax threads to
-// shared memory as the A operand of the second product.
+// memory; Q, K and V tiles arrive by TMA (128-byte swizzle); P goes from the softmax threads to
+// tensor memory (two buffers of its own) and is the A operand of the second product from there.
 //
 //   tile        128 rows = (128 / g) tokens x g query heads of one key/value head (g = H / K),
 //               key tiles of 128 keys (whole pages), head size 128
-//   warp 0      TMA producer: Q once (one 3-D box per half of the head), then a ring of two K and
-//               two V stages, one 2-D box per page and half
-//   warp 1      MMA issuer: QK^T of tile j+1 is issued before PV of tile j, so the tensor cores
-//               work on the next scores while the softmax threads are busy with the current ones
+//   warp 0      TMA producer: Q once (one 3-D box per half of the head), then rings of three K and
+//               two V stages, one 2-D box per page and half; keys run one tile ahead of values
+//   warp 1      issuer of S = Q K^T (one thread): a tile's scores as soon as its keys are there and
+//               the softmax threads have read the buffer's scores of two tiles before
+//   warp 6      issuer of O += P V (one thread): a tile's product when its P is complete
 //   warps 2..5  softmax: one thread per row (= one TMEM lane): tcgen05.ld of the 128 scores, mask,
-//               maximum and sum without any shuffle, exp2 with the scale folded in, P as bfloat16
-//               into the swizzled shared-memory tile.  The reference maximum of a row is only
-//               raised when the new maximum exceeds it by more than 8 (factor 256): then the
-//               thread rescales its own O row in TMEM (tcgen05.ld / st); otherwise O is left alone.
+//               maximum (four chains) and sum without any shuffle, exp2 with the scale folded in,
+//               P as bfloat16 into its buffer.  The reference maximum of a row is only raised when
+//               the new maximum exceeds it by more than 8 (factor 256): then the thread rescales its
+//               own O row in TMEM (tcgen05.ld / st); otherwise O is left alone.
 //   end         O / l -> bfloat16 -> out[token, head, :]
+// What a key tile costs is the softmax threads' own instruction stream (about 2,100 cycles, of which
+// 1,024 are the special-function unit's 16,384 exponentials).  Three things that had been in front
+// of it, found with cycle stamps of one CTA: one thread issuing both products (2,000 cycles of
+// issue a tile: 70 per tcgen05.mma, 75 per commit, 110 per barrier looked at); P laid over its own
+// scores, which made Q K^T of tile j+2 wait for P V of tile j (softmax -> P V -> Q K^T -> softmax of
+// the tile after next, 4,700 cycles for two tiles); and the softmax threads waiting for P V of the
+// tile before in the middle of their tile, which they need only when they rescale O.
 // Every mbarrier wait is bounded (see tcgen05.cuh); a wait that runs out records a code in the
 // error word, raises the abort flag, and every role leaves.
 //
@@ -27,9 +35,12 @@
 #define AT_HD 128
 #define AT_BM 128
 #define AT_BN 128
-#define AT_THREADS 192
+#define AT_THREADS 224                     // TMA warp, Q.K^T issuer, four softmax warps, P.V issuer
 #define AT_HALF_BYTES (128 * 128)          // 128 rows x 64 elements x 2 bytes
 #define AT_TILE_BYTES (2 * AT_HALF_BYTES)
+#define AT_KS 3                            // key tiles in flight: Q.K^T of tile j+1 is issued a tile ahead, and a tile
+                                           // takes 2,000 to 3,000 cycles to come in, about what a tile costs
+#define AT_VS 2                            // value tiles in flight
 #define AT_TABLE_SMEM 4096                 // block-table entries kept in shared memory (more are read from global)
 
 enum { AT_ERR_Q = 11, AT_ERR_KV = 12, AT_ERR_S = 13, AT_ERR_P = 14, AT_ERR_STAGE = 15 };
@@ -79,10 +90,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = smem;                               // 32 KB
-    unsigned char* sK = smem + AT_TILE_BYTES;               // 2 x 32 KB
-    unsigned char* sV = smem + 3 * AT_TILE_BYTES;           // 2 x 32 KB
-    __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2],
-        p_full[2], p_empty;
+    unsigned char* sK = smem + AT_TILE_BYTES;               // AT_KS x 32 KB
+    unsigned char* sV = smem + (1 + AT_KS) * AT_TILE_BYTES; // AT_VS x 32 KB
+    __shared__ __align__(8) uint64_t q_full, k_full[AT_KS], v_full[AT_VS], k_empty[AT_KS], v_empty[AT_VS], s_full[2],
+        s_empty[2], p_full[2], p_empty;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ int s_table[AT_TABLE_SMEM];
@@ -103,10 +114,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmK) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmV) : "memory");
         mbar_init(&q_full, 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128);
-        }
+        for (int s = 0; s < AT_KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < AT_VS; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128); }
         // p_full has one barrier per S buffer: a softmax warp may be one tile ahead of the others (the
         // scores of tile j + 1 are ready early) and must not add its arrival to the phase of tile j
         mbar_init(&p_full[0], 128);
@@ -124,7 +134,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    const uint32_t tS0 = tmem_base, tO = tmem_base + 256;   // S buffers at columns 0 and 128, O at 256
+    // S buffers at columns 0 and 128, O at 256, P buffers (two keys per column) at 384 and 448.  P has
+    // columns of its own: laid over its scores it made Q.K^T of tile j + 2 wait for P.V of tile j, and
+    // the chain softmax -> P.V -> Q.K^T -> softmax of the tile after next was what a tile cost.
+    const uint32_t tS0 = tmem_base, tO = tmem_base + 256, tP0 = tmem_base + 384;
     pdl_wait();                                             // queries and this step's keys come from earlier kernels
 
     if (warp == 0) {
@@ -144,20 +157,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tma_load_3d(sQ, &tmQ, 0, head0, tok0, &q_full);
             tma_load_3d(sQ + AT_HALF_BYTES, &tmQ, 64, head0, tok0, &q_full);
         }
-        int issued = 0;
+        // Keys run one tile ahead of values: Q.K^T of tile j+1 is issued before P.V of tile j, so the
+        // key tile is wanted a tile earlier than the value tile of the same keys.
+        int k_issued = 0, v_issued = 0;
         bool ok = true;
-        for (int j = 0; j < n_kt && ok; ++j) {
-            const int s = j & 1;
-            const uint32_t ph = (j >> 1) & 1;
-            const int rel = min(j * pages + lane, n_blk - 1);          // pages past the context: the last valid page, masked
-            int y = 0;
-            if (lane < pages) {
-                const int page = rel < AT_TABLE_SMEM ? s_table[rel] : table[first_blk + rel];
-                y = (page * p.K + kvh) * p.bs;
-            }
-            ok = mbar_wait(&k_empty[s], ph ^ 1, &abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+        auto page_row = [&](int j) {                                // first cache row of this lane's page of tile j
+            const int rel = min(j * pages + lane, n_blk - 1);      // pages past the context: the last valid page, masked
+            if (lane >= pages) return 0;
+            const int page = rel < AT_TABLE_SMEM ? s_table[rel] : table[first_blk + rel];
+            return (page * p.K + kvh) * p.bs;
+        };
+        auto load_k = [&](int j) -> bool {
+            const int s = j % AT_KS;
+            const uint32_t ph = (j / AT_KS) & 1;
+            const int y = page_row(j);
+            bool got = mbar_wait(&k_empty[s], ph ^ 1, &abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) return false;
             if (lane == 0) mbar_expect_tx(&k_full[s], AT_TILE_BYTES);
             __syncwarp();
             if (lane < pages) {
@@ -165,10 +181,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tma_load_2d(dst, &tmK, 0, y, &k_full[s]);
                 tma_load_2d(dst + AT_HALF_BYTES, &tmK, 64, y, &k_full[s]);
             }
-            issued = 2 * j + 1;
-            ok = mbar_wait(&v_empty[s], ph ^ 1, &abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            k_issued = j + 1;
+            return true;
+        };
+        auto load_v = [&](int j) -> bool {
+            const int s = j % AT_VS;
+            const uint32_t ph = (j / AT_VS) & 1;
+            const int y = page_row(j);
+            bool got = mbar_wait(&v_empty[s], ph ^ 1, &abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) return false;
             if (lane == 0) mbar_expect_tx(&v_full[s], AT_TILE_BYTES);
             __syncwarp();
             if (lane < pages) {
@@ -176,65 +198,68 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tma_load_2d(dst, &tmV, 0, y, &v_full[s]);
                 tma_load_2d(dst + AT_HALF_BYTES, &tmV, 64, y, &v_full[s]);
             }
-            issued = 2 * j + 2;
+            v_issued = j + 1;
+            return true;
+        };
+        for (int j = 0; j < n_kt && ok; ++j) {
+            ok = load_k(j);
+            if (ok && j > 0) ok = load_v(j - 1);
         }
+        if (ok) ok = load_v(n_kt - 1);
         if (!ok && lane == 0 && !abort_flag) { atomicExch(p.err, AT_ERR_STAGE); abort_flag = 1; }
         if (abort_flag && lane == 0) {
             // copies that were issued must land before the CTA's shared memory goes away
             volatile int no_abort = 0;
             mbar_wait(&q_full, 0, &no_abort);
-            for (int i = max(0, issued - 4); i < issued; ++i) {
-                const int j = i >> 1, s = j & 1;
-                const uint32_t ph = (j >> 1) & 1;
-                mbar_wait((i & 1) ? &v_full[s] : &k_full[s], ph, &no_abort);
-            }
+            for (int j = max(0, k_issued - AT_KS); j < k_issued; ++j) mbar_wait(&k_full[j % AT_KS], (j / AT_KS) & 1, &no_abort);
+            for (int j = max(0, v_issued - AT_VS); j < v_issued; ++j) mbar_wait(&v_full[j % AT_VS], (j / AT_VS) & 1, &no_abort);
         }
     } else if (warp == 1 && lane == 0) {
-        // ------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------ issuer of S = Q.K^T
+        // Two threads issue the products, this one the scores, one of warp 6 the P.V products: a single
+        // thread spent 2,000 of the 2,400 cycles of a key tile issuing (about 70 cycles per
+        // tcgen05.mma, 75 per commit, 110 per barrier it looks at) and was what a tile cost.
         constexpr uint32_t idesc_s = idesc_bf16(AT_BM, AT_BN);                 // Q, K both K-major
-        constexpr uint32_t idesc_o = idesc_bf16(AT_BM, AT_HD) | (1u << 16);    // V is MN-major
         bool ok = mbar_wait(&q_full, 0, &abort_flag);
         if (!ok && !abort_flag) { atomicExch(p.err, AT_ERR_Q); abort_flag = 1; }
         const uint32_t q_addr = s_addr(sQ);
-        auto issue_qk = [&](int j) -> bool {
-            const int s = j & 1;
+        for (int j = 0; j < n_kt && ok; ++j) {
+            const int s = j & 1, ks = j % AT_KS;
             const uint32_t ph = (j >> 1) & 1;
-            if (!mbar_wait(&k_full[s], ph, &abort_flag)) return false;
-            if (!mbar_wait(&s_empty[s], ph ^ 1, &abort_flag)) return false;   // softmax of tile j-2 has read S[s]
+            ok = mbar_wait(&k_full[ks], (j / AT_KS) & 1, &abort_flag) &&
+                 mbar_wait(&s_empty[s], ph ^ 1, &abort_flag);                  // softmax of tile j-2 has read S[s]
+            if (!ok) break;
             tc_fence_after();
-            const uint32_t k_addr = s_addr(sK + s * AT_TILE_BYTES);
+            const uint32_t k_addr = s_addr(sK + ks * AT_TILE_BYTES);
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     umma_bf16(tS0 + s * AT_BN, smem_desc_sw128(q_addr + h * AT_HALF_BYTES) + 2 * kk,
                               smem_desc_sw128(k_addr + h * AT_HALF_BYTES) + 2 * kk, idesc_s, (h | kk) != 0);
-            umma_commit(&k_empty[s]);
+            umma_commit(&k_empty[ks]);
             umma_commit(&s_full[s]);
-            return true;
-        };
-        auto issue_pv = [&](int j) -> bool {
-            const int s = j & 1;
-            const uint32_t ph = (j >> 1) & 1;
-            if (!mbar_wait(&p_full[s], (j >> 1) & 1, &abort_flag)) return false;
-            if (!mbar_wait(&v_full[s], ph, &abort_flag)) return false;
-            tc_fence_after();
-            const uint32_t v_addr = s_addr(sV + s * AT_TILE_BYTES);
-#pragma unroll
-            for (int k8 = 0; k8 < 8; ++k8)        // 16 keys a step: P advances 8 columns (two keys a column), V 16 rows
-                umma_bf16_ts(tO, tS0 + s * AT_BN + k8 * 8, smem_desc_sw128_mn(v_addr + k8 * 16 * 128, AT_HALF_BYTES),
-                             idesc_o, (j | k8) != 0);
-            umma_commit(&v_empty[s]);
-            umma_commit(&p_empty);
-            return true;
-        };
-        if (ok) ok = issue_qk(0);
-        for (int j = 0; j < n_kt && ok; ++j) {
-            if (j + 1 < n_kt) ok = issue_qk(j + 1);      // over P of tile j - 1, behind the product that reads it
-            if (ok) ok = issue_pv(j);
         }
         if (!ok && !abort_flag) { atomicExch(p.err, AT_ERR_KV); abort_flag = 1; }
-    } else if (warp >= 2) {
+    } else if (warp == 6 && lane == 0) {
+        // ------------------------------------------------------------ issuer of O += P.V
+        constexpr uint32_t idesc_o = idesc_bf16(AT_BM, AT_HD) | (1u << 16);    // V is MN-major
+        bool ok = true;
+        for (int j = 0; j < n_kt && ok; ++j) {
+            const int s = j & 1, vs = j % AT_VS;
+            ok = mbar_wait(&p_full[s], (j >> 1) & 1, &abort_flag) && mbar_wait(&v_full[vs], (j / AT_VS) & 1, &abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t v_addr = s_addr(sV + vs * AT_TILE_BYTES);
+#pragma unroll
+            for (int k8 = 0; k8 < 8; ++k8)        // 16 keys a step: P advances 8 columns (two keys a column), V 16 rows
+                umma_bf16_ts(tO, tP0 + s * (AT_BN / 2) + k8 * 8, smem_desc_sw128_mn(v_addr + k8 * 16 * 128, AT_HALF_BYTES),
+                             idesc_o, (j | k8) != 0);
+            umma_commit(&v_empty[vs]);
+            umma_commit(&p_empty);
+        }
+        if (!ok && !abort_flag) { atomicExch(p.err, AT_ERR_KV); abort_flag = 1; }
+    } else if (warp >= 2 && warp < 6) {
         // ------------------------------------------------------------ softmax and epilogue: one row per thread
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
@@ -270,36 +295,41 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // until the tiles come in from L2 no faster (two warps per scheduler, each thread half a
             // row, was tried and gave nothing more).
             const bool need_mask = (kt + AT_BN > pos_r + 1) || (kt < first_r);
-            float mx = -INFINITY;
             if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < AT_BN; ++c) {
+                for (int c = 0; c < AT_BN; ++c)
                     if (kt + c > pos_r || kt + c < first_r) sv[c] = -INFINITY;
-                    mx = fmaxf(mx, sv[c]);
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < AT_BN; ++c) mx = fmaxf(mx, sv[c]);
             }
+            // four chains of 32: one chain of 128 maxima is 128 dependent instructions (500 cycles a tile)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < AT_BN; c += 4) {
+                mx4[0] = fmaxf(mx4[0], sv[c]); mx4[1] = fmaxf(mx4[1], sv[c + 1]);
+                mx4[2] = fmaxf(mx4[2], sv[c + 2]); mx4[3] = fmaxf(mx4[3], sv[c + 3]);
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             mx *= p.scale_log2;
             float alpha = 1.f;
             bool rescale = false;
             if (m_ref == -INFINITY) m_ref = mx;                          // nothing accumulated yet for this row
             else if (mx > m_ref + 8.f) { alpha = exp2f(m_ref - mx); m_ref = mx; rescale = true; }
-            // P goes to tensor memory over this tile's own scores (columns 0-63 of S[b], read above),
-            // where nothing else is pending: S[b] was written by Q.K^T of this tile, which the tensor
-            // pipe ran after P.V of tile j-2.  O is shared with the products in flight: it is rescaled
-            // only after P.V of the tile before has completed.  Every thread waits for every phase of
-            // p_empty, one after the other, whether it rescales or not: a parity wait is only right
-            // for the phase after the last one seen (skipping a phase once let the epilogue read O two
-            // products early).
-            if (j > 0 && !mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
-                if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
-                ok = false;
-                break;
-            }
+            // P goes to its buffer P[b] in tensor memory, which P.V of tile j-2 has read: the thread saw
+            // that product complete during tile j-1.  O is shared with the products in flight: it is
+            // rescaled only after P.V of the tile before has completed.  Every thread waits for every phase of p_empty, one
+            // after the other, whether it rescales or not: a parity wait is only right for the phase
+            // after the last one seen (skipping a phase once let the epilogue read O two products
+            // early).  A warp that rescales waits here; the others wait at the end of the tile, when
+            // that product has long completed, so that its latency is not part of what a tile costs.
             // tcgen05.ld / st are warp-wide: the whole warp goes through when any of its rows rescales
-            if (__any_sync(0xffffffffu, rescale)) {
+            const bool warp_rescales = __any_sync(0xffffffffu, rescale);
+            bool seen_pv = j == 0;
+            if (warp_rescales && j > 0) {
+                if (!mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
+                    if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
+                    ok = false;
+                    break;
+                }
+                seen_pv = true;
                 tc_fence_after();
                 l *= alpha;
 #pragma unroll
@@ -326,8 +356,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
             l += sum;
 #pragma unroll
-            for (int c0 = 0; c0 < AT_BN / 64; ++c0) tmem_st32(tS0 + b * AT_BN + lane_base + c0 * 32, pk[c0]);
+            for (int c0 = 0; c0 < AT_BN / 64; ++c0) tmem_st32(tP0 + b * (AT_BN / 2) + lane_base + c0 * 32, pk[c0]);
             tmem_st_wait();
+            // before this thread's arrival lets P.V of this tile start: p_empty cannot then be more
+            // than one phase ahead of what the thread has seen
+            if (!seen_pv && !mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
+                if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
+                ok = false;
+                break;
+            }
             tc_fence_before();
             mbar_arrive(&p_full[b]);
         }
@@ -402,7 +439,7 @@ RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v
     p.out = (bf16*)out; p.positions = positions; p.cu_q = cu_q; p.block_table = block_table; p.tile_req = tile_req;
     p.tile_tok0 = tile_tok0; p.table_stride = table_stride; p.H = H; p.K = K; p.bs = bs; p.window = window; p.TT = TT;
     p.g = g; p.n_tiles = n_tiles; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
-    constexpr int smem = 5 * AT_TILE_BYTES + 1024;
+    constexpr int smem = (1 + AT_KS + AT_VS) * AT_TILE_BYTES + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
