@@ -5,24 +5,36 @@
 //
 //   tile        128 rows = (128 / g) tokens x g query heads of one key/value head (g = H / K),
 //               key tiles of 128 keys (whole pages), head size 128
-//   warp 0      TMA producer: Q once (one 3-D box per half of the head), then rings of three K and
-//               two V stages, one 2-D box per page and half; keys run one tile ahead of values
+//   warp 0      TMA producer of Q (once, one 3-D box per half of the head) and of the key tiles: a ring
+//               of three stages, one 2-D box per page and half
+//   warp 11     TMA producer of the value tiles: a ring of two stages
 //   warp 1      issuer of S = Q K^T (one thread): a tile's scores as soon as its keys are there and
 //               the softmax threads have read the buffer's scores of two tiles before
-//   warp 6      issuer of O += P V (one thread): a tile's product when its P is complete
-//   warps 2..5  softmax: one thread per row (= one TMEM lane): tcgen05.ld of the 128 scores, mask,
-//               maximum (four chains) and sum without any shuffle, exp2 with the scale folded in,
-//               P as bfloat16 into its buffer.  The reference maximum of a row is only raised when
-//               the new maximum exceeds it by more than 8 (factor 256): then the thread rescales its
-//               own O row in TMEM (tcgen05.ld / st); otherwise O is left alone.
-//   end         O / l -> bfloat16 -> out[token, head, :]
-// What a key tile costs is the softmax threads' own instruction stream (about 2,100 cycles, of which
-// 1,024 are the special-function unit's 16,384 exponentials).  Three things that had been in front
-// of it, found with cycle stamps of one CTA: one thread issuing both products (2,000 cycles of
-// issue a tile: 70 per tcgen05.mma, 75 per commit, 110 per barrier looked at); P laid over its own
-// scores, which made Q K^T of tile j+2 wait for P V of tile j (softmax -> P V -> Q K^T -> softmax of
-// the tile after next, 4,700 cycles for two tiles); and the softmax threads waiting for P V of the
-// tile before in the middle of their tile, which they need only when they rescale O.
+//   warp 10     issuer of O += P V (one thread): a tile's product when its P is complete
+//   warps 2..9  softmax, two groups of four warps; group 0 takes the key tiles 0, 2, 4, ..., group 1 the
+//               others, each with the S and P buffer of its number.  One thread per row (= one TMEM
+//               lane) in each group: tcgen05.ld of the 128 scores, mask, maximum (four chains) and
+//               sum without any shuffle, exp2 with the scale folded in, P as bfloat16 into its buffer.
+//               The reference maximum of a row goes from the thread that treats tile j to the thread
+//               of the other group that treats tile j+1 (shared memory, a named barrier per warp
+//               pair); it is only raised when the new maximum exceeds it by more than 8 (factor 256):
+//               then the thread rescales the row of O in TMEM (tcgen05.ld / st).
+//   end         group 0 adds the two groups' row sums, O / l -> bfloat16 -> out[token, head, :]
+// What a key tile costs, from cycle stamps of one CTA (4,096 tokens): 2,400 cycles with one issuing
+// thread, one softmax group and P laid over its scores; then in turn
+//   - one thread issued both products: 2,000 cycles of issue a tile (70 per tcgen05.mma, 75 per
+//     commit, 110 per barrier looked at)                                    -> two issuing threads
+//   - P over its own scores made Q K^T of tile j+2 wait for P V of tile j: softmax -> P V -> Q K^T ->
+//     softmax of the tile after next, 4,700 cycles for two tiles            -> P buffers of its own
+//   - the softmax threads waited for P V of the tile before in the middle of their tile, which they
+//     need only when they rescale O                                         -> at the tile's end
+//   - 128 dependent maxima, 500 cycles                                      -> four chains
+//   - one softmax group: 2,100 cycles a tile of which the special-function unit works 1,024
+//                                                                           -> two groups, 1,800
+//   - one TMA warp: a key tile waited behind the value tile before it, which waits for a product
+//     two tiles back; keys came 900 cycles late                             -> a warp for each
+// What is left is latency inside each group's stream (barrier looks of 130 cycles, the hand-over of
+// the maximum, two warps per scheduler) with the special-function unit 57 % busy.
 // Every mbarrier wait is bounded (see tcgen05.cuh); a wait that runs out records a code in the
 // error word, raises the abort flag, and every role leaves.
 //
@@ -35,7 +47,7 @@
 #define AT_HD 128
 #define AT_BM 128
 #define AT_BN 128
-#define AT_THREADS 224                     // TMA warp, Q.K^T issuer, four softmax warps, P.V issuer
+#define AT_THREADS 384                     // key TMA warp, Q.K^T issuer, two groups of four softmax warps, P.V issuer, value TMA warp
 #define AT_HALF_BYTES (128 * 128)          // 128 rows x 64 elements x 2 bytes
 #define AT_TILE_BYTES (2 * AT_HALF_BYTES)
 #define AT_KS 3                            // key tiles in flight: Q.K^T of tile j+1 is issued a tile ahead, and a tile
@@ -93,7 +105,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     unsigned char* sK = smem + AT_TILE_BYTES;               // AT_KS x 32 KB
     unsigned char* sV = smem + (1 + AT_KS) * AT_TILE_BYTES; // AT_VS x 32 KB
     __shared__ __align__(8) uint64_t q_full, k_full[AT_KS], v_full[AT_VS], k_empty[AT_KS], v_empty[AT_VS], s_full[2],
-        s_empty[2], p_full[2], p_empty;
+        s_empty[2], p_full[2], p_empty[2];
+    __shared__ float m_sh[AT_BM], mg_sh[AT_BM], l_sh[AT_BM];      // per row: reference maximum; group 1's own, and its sum
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
     __shared__ int s_table[AT_TABLE_SMEM];
@@ -121,7 +134,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // scores of tile j + 1 are ready early) and must not add its arrival to the phase of tile j
         mbar_init(&p_full[0], 128);
         mbar_init(&p_full[1], 128);
-        mbar_init(&p_empty, 1);
+        mbar_init(&p_empty[0], 1);
+        mbar_init(&p_empty[1], 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
@@ -140,8 +154,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t tS0 = tmem_base, tO = tmem_base + 256, tP0 = tmem_base + 384;
     pdl_wait();                                             // queries and this step's keys come from earlier kernels
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer (the whole warp)
+    if (warp == 0 || warp == 11) {
+        // ------------------------------------------------------------ TMA producers (a whole warp each):
+        // warp 0 brings Q and the key tiles, warp 11 the value tiles.  One warp for both made a key
+        // tile wait in line behind the value tile before it, which itself waits for a product two
+        // tiles back to release its stage.
+        const bool keys = warp == 0;
         // The request's block table goes to shared memory once (the lookups would otherwise be a
         // chain of dependent global loads in front of every tile); lane pg then issues the two boxes
         // (one per 64-dim half) of page pg of a tile.
@@ -150,15 +168,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int last_blk = pos_last / p.bs;                // last block that exists for this request
         const int first_blk = kb / p.bs;
         const int n_blk = last_blk - first_blk + 1;
-        for (int i = lane; i < min(n_blk, AT_TABLE_SMEM); i += 32) s_table[i] = table[first_blk + i];
-        __syncwarp();
-        if (lane == 0) {
+        if (keys)
+            for (int i = lane; i < min(n_blk, AT_TABLE_SMEM); i += 32) s_table[i] = table[first_blk + i];
+        asm volatile("bar.sync 10, 64;" ::: "memory");              // the two producer warps: the table is in place
+        if (keys && lane == 0) {
             mbar_expect_tx(&q_full, AT_TILE_BYTES);
             tma_load_3d(sQ, &tmQ, 0, head0, tok0, &q_full);
             tma_load_3d(sQ + AT_HALF_BYTES, &tmQ, 64, head0, tok0, &q_full);
         }
-        // Keys run one tile ahead of values: Q.K^T of tile j+1 is issued before P.V of tile j, so the
-        // key tile is wanted a tile earlier than the value tile of the same keys.
         int k_issued = 0, v_issued = 0;
         bool ok = true;
         auto page_row = [&](int j) {                                // first cache row of this lane's page of tile j
@@ -201,16 +218,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             v_issued = j + 1;
             return true;
         };
-        for (int j = 0; j < n_kt && ok; ++j) {
-            ok = load_k(j);
-            if (ok && j > 0) ok = load_v(j - 1);
-        }
-        if (ok) ok = load_v(n_kt - 1);
+        for (int j = 0; j < n_kt && ok; ++j) ok = keys ? load_k(j) : load_v(j);
         if (!ok && lane == 0 && !abort_flag) { atomicExch(p.err, AT_ERR_STAGE); abort_flag = 1; }
         if (abort_flag && lane == 0) {
             // copies that were issued must land before the CTA's shared memory goes away
             volatile int no_abort = 0;
-            mbar_wait(&q_full, 0, &no_abort);
+            if (keys) mbar_wait(&q_full, 0, &no_abort);
             for (int j = max(0, k_issued - AT_KS); j < k_issued; ++j) mbar_wait(&k_full[j % AT_KS], (j / AT_KS) & 1, &no_abort);
             for (int j = max(0, v_issued - AT_VS); j < v_issued; ++j) mbar_wait(&v_full[j % AT_VS], (j / AT_VS) & 1, &no_abort);
         }
@@ -241,7 +254,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             umma_commit(&s_full[s]);
         }
         if (!ok && !abort_flag) { atomicExch(p.err, AT_ERR_KV); abort_flag = 1; }
-    } else if (warp == 6 && lane == 0) {
+    } else if (warp == 10 && lane == 0) {
         // ------------------------------------------------------------ issuer of O += P.V
         constexpr uint32_t idesc_o = idesc_bf16(AT_BM, AT_HD) | (1u << 16);    // V is MN-major
         bool ok = true;
@@ -256,11 +269,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 umma_bf16_ts(tO, tP0 + s * (AT_BN / 2) + k8 * 8, smem_desc_sw128_mn(v_addr + k8 * 16 * 128, AT_HALF_BYTES),
                              idesc_o, (j | k8) != 0);
             umma_commit(&v_empty[vs]);
-            umma_commit(&p_empty);
+            umma_commit(&p_empty[s]);
         }
         if (!ok && !abort_flag) { atomicExch(p.err, AT_ERR_KV); abort_flag = 1; }
-    } else if (warp >= 2 && warp < 6) {
+    } else if (warp >= 2 && warp < 10) {
         // ------------------------------------------------------------ softmax and epilogue: one row per thread
+        // Two groups of four warps: group 0 takes the key tiles 0, 2, 4, ..., group 1 the tiles 1, 3, 5, ...,
+        // each with the S and P buffers of its number, so that the exponentials of one tile (the
+        // special-function unit's 1,024 cycles) run beside the loads, maxima and barrier round trips
+        // of the next.  Row r belongs to thread r of both groups.  What the two share per row is the
+        // reference maximum: it is handed from the thread that treats tile j to the one that treats
+        // tile j+1 through shared memory and a named barrier of the two warps, right after the
+        // maximum of tile j is known.  Each group keeps its own part of the row sum, relative to the
+        // reference it last saw; O is one accumulator, rescaled by whichever thread raises the reference.
+        const int wg = (warp - 2) >> 2;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
@@ -268,114 +290,151 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const bool valid = tl < nt;
         const int pos_r = valid ? p.positions[tok0 + tl] : -1;
         const int first_r = p.window > 0 ? max(0, pos_r + 1 - p.window) : 0;
-        float m_ref = -INFINITY, l = 0.f;
+        const int bar_mine = 1 + wg * 4 + quarter;           // arrived at by this warp, waited for by its partner
+        const int bar_partner = 1 + (1 - wg) * 4 + quarter;
+        const int b = wg;
+        float m_mine = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_kt && ok; ++j) {
-            const int b = j & 1;
+        // Every iteration passes the named barriers, whatever happened: they have no time-out.  A wait
+        // that fails makes the rest of the thread's work empty (ok == false, uniform over the warp).
+        for (int j = wg; j < n_kt; j += 2) {
+            const uint32_t ph = (j >> 1) & 1;
             const int kt = kb + j * AT_BN;
-            if (!mbar_wait(&s_full[b], (j >> 1) & 1, &abort_flag)) {
+            if (ok && !mbar_wait(&s_full[b], ph, &abort_flag)) {
                 if (!abort_flag) { atomicExch(p.err, AT_ERR_S); abort_flag = 1; }
                 ok = false;
-                break;
             }
-            tc_fence_after();
-            // the whole row of scores with one wait: four loads of 32 columns in flight together
-            uint32_t rr[AT_BN / 32][32];
-#pragma unroll
-            for (int c0 = 0; c0 < AT_BN / 32; ++c0) tmem_ld32(tS0 + b * AT_BN + lane_base + c0 * 32, rr[c0]);
-            tmem_ld_wait();
+            ok = __all_sync(0xffffffffu, ok);
             float sv[AT_BN];
+            float mx = -INFINITY;
+            if (ok) {
+                tc_fence_after();
+                // the whole row of scores with one wait: four loads of 32 columns in flight together
+                uint32_t rr[AT_BN / 32][32];
 #pragma unroll
-            for (int c = 0; c < AT_BN; ++c) sv[c] = __uint_as_float(rr[c >> 5][c & 31]);
-            tc_fence_before();
-            mbar_arrive(&s_empty[b]);
-            // The maximum is taken over the raw scores (the scale is positive) and the scale goes into
-            // the exponent's multiply-add: one FFMA and one MUFU per score.  The softmax warps have one
-            // warp per scheduler to themselves, so their instruction stream is what a key tile costs
-            // until the tiles come in from L2 no faster (two warps per scheduler, each thread half a
-            // row, was tried and gave nothing more).
-            const bool need_mask = (kt + AT_BN > pos_r + 1) || (kt < first_r);
-            if (need_mask) {
+                for (int c0 = 0; c0 < AT_BN / 32; ++c0) tmem_ld32(tS0 + b * AT_BN + lane_base + c0 * 32, rr[c0]);
+                tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < AT_BN; ++c)
-                    if (kt + c > pos_r || kt + c < first_r) sv[c] = -INFINITY;
+                for (int c = 0; c < AT_BN; ++c) sv[c] = __uint_as_float(rr[c >> 5][c & 31]);
+                tc_fence_before();
+                mbar_arrive(&s_empty[b]);
+                // The maximum is taken over the raw scores (the scale is positive) and the scale goes
+                // into the exponent's multiply-add: one FFMA and one MUFU per score.
+                const bool need_mask = (kt + AT_BN > pos_r + 1) || (kt < first_r);
+                if (need_mask) {
+#pragma unroll
+                    for (int c = 0; c < AT_BN; ++c)
+                        if (kt + c > pos_r || kt + c < first_r) sv[c] = -INFINITY;
+                }
+                // four chains of 32: one chain of 128 maxima is 128 dependent instructions (500 cycles a tile)
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < AT_BN; c += 4) {
+                    mx4[0] = fmaxf(mx4[0], sv[c]); mx4[1] = fmaxf(mx4[1], sv[c + 1]);
+                    mx4[2] = fmaxf(mx4[2], sv[c + 2]); mx4[3] = fmaxf(mx4[3], sv[c + 3]);
+                }
+                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             }
-            // four chains of 32: one chain of 128 maxima is 128 dependent instructions (500 cycles a tile)
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int c = 0; c < AT_BN; c += 4) {
-                mx4[0] = fmaxf(mx4[0], sv[c]); mx4[1] = fmaxf(mx4[1], sv[c + 1]);
-                mx4[2] = fmaxf(mx4[2], sv[c + 2]); mx4[3] = fmaxf(mx4[3], sv[c + 3]);
-            }
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            mx *= p.scale_log2;
+            // the row's reference after tile j-1, from the partner; then this tile's decision, for the partner
+            if (j > 0) asm volatile("bar.sync %0, 64;" ::"r"(bar_partner) : "memory");
+            float m_ref = j > 0 ? m_sh[r] : -INFINITY;
             float alpha = 1.f;
             bool rescale = false;
-            if (m_ref == -INFINITY) m_ref = mx;                          // nothing accumulated yet for this row
-            else if (mx > m_ref + 8.f) { alpha = exp2f(m_ref - mx); m_ref = mx; rescale = true; }
-            // P goes to its buffer P[b] in tensor memory, which P.V of tile j-2 has read: the thread saw
-            // that product complete during tile j-1.  O is shared with the products in flight: it is
-            // rescaled only after P.V of the tile before has completed.  Every thread waits for every phase of p_empty, one
-            // after the other, whether it rescales or not: a parity wait is only right for the phase
-            // after the last one seen (skipping a phase once let the epilogue read O two products
-            // early).  A warp that rescales waits here; the others wait at the end of the tile, when
-            // that product has long completed, so that its latency is not part of what a tile costs.
+            if (ok) {
+                if (m_ref == -INFINITY) m_ref = mx;                          // nothing accumulated yet for this row
+                else if (mx > m_ref + 8.f) { alpha = exp2f(m_ref - mx); m_ref = mx; rescale = true; }
+            }
+            m_sh[r] = m_ref;
+            if (j + 1 < n_kt) asm volatile("bar.arrive %0, 64;" ::"r"(bar_mine) : "memory");
+            if (m_mine != m_ref) {                                           // this group's sum follows the reference
+                l = m_mine == -INFINITY ? 0.f : l * exp2f(m_mine - m_ref);
+                m_mine = m_ref;
+            }
+            // O is shared with the products in flight: it is rescaled only after P.V of the tile
+            // before (the partner's) has completed; P[b] is written only after P.V of this group's
+            // tile before (j-2) has read it.  p_empty[x] counts the products of the tiles of group x:
+            // a thread looks at every phase of both, in order and each once (a parity wait is only
+            // right for the phase after the last one seen), and at the partner's before its own
+            // arrival lets the next product start, so that no barrier is ever two phases ahead of it.
+            // A warp that rescales looks at the partner's here; the others at the end of the tile,
+            // when that product has long completed.
             // tcgen05.ld / st are warp-wide: the whole warp goes through when any of its rows rescales
             const bool warp_rescales = __any_sync(0xffffffffu, rescale);
-            bool seen_pv = j == 0;
-            if (warp_rescales && j > 0) {
-                if (!mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
+            bool seen_partner = j == 0;
+            if (ok && warp_rescales && j > 0) {
+                if (!mbar_wait(&p_empty[1 - b], ((j - 1) >> 1) & 1, &abort_flag)) {
                     if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
                     ok = false;
-                    break;
                 }
-                seen_pv = true;
-                tc_fence_after();
-                l *= alpha;
+                ok = __all_sync(0xffffffffu, ok);
+                seen_partner = true;
+                if (ok) {
+                    tc_fence_after();
 #pragma unroll
-                for (int c0 = 0; c0 < AT_HD; c0 += 32) {
-                    uint32_t rr2[32];
-                    tmem_ld32(tO + lane_base + c0, rr2);
-                    tmem_ld_wait();
+                    for (int c0 = 0; c0 < AT_HD; c0 += 32) {
+                        uint32_t rr2[32];
+                        tmem_ld32(tO + lane_base + c0, rr2);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) rr2[i] = __float_as_uint(__uint_as_float(rr2[i]) * alpha);
-                    tmem_st32(tO + lane_base + c0, rr2);
+                        for (int i = 0; i < 32; ++i) rr2[i] = __float_as_uint(__uint_as_float(rr2[i]) * alpha);
+                        tmem_st32(tO + lane_base + c0, rr2);
+                    }
+                    tmem_st_wait();
                 }
+            }
+            if (ok && j >= 2 && !mbar_wait(&p_empty[b], ph ^ 1, &abort_flag)) {   // P.V of tile j-2 has read P[b]
+                if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                const float mref = m_ref == -INFINITY ? 0.f : m_ref;
+                float sum = 0.f;
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    uint32_t pk[32];                                       // half the row's P, two keys per word
+#pragma unroll
+                    for (int c = 0; c < 64; c += 2) {
+                        const float e0 = ex2_approx(fmaf(sv[hh * 64 + c], p.scale_log2, -mref));
+                        const float e1 = ex2_approx(fmaf(sv[hh * 64 + c + 1], p.scale_log2, -mref));
+                        sum += e0 + e1;
+                        __nv_bfloat162 pp = __floats2bfloat162_rn(e0, e1);
+                        pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
+                    }
+                    tmem_st32(tP0 + b * (AT_BN / 2) + lane_base + hh * 32, pk);
+                }
+                l += sum;
                 tmem_st_wait();
+                if (!seen_partner && !mbar_wait(&p_empty[1 - b], ((j - 1) >> 1) & 1, &abort_flag)) {
+                    if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
+                    ok = false;
+                }
+                if (ok) {
+                    tc_fence_before();
+                    mbar_arrive(&p_full[b]);
+                }
             }
-            const float mref = m_ref == -INFINITY ? 0.f : m_ref;
-            float sum = 0.f;
-            uint32_t pk[AT_BN / 64][32];                                   // the row's P, two keys per word
-#pragma unroll
-            for (int c = 0; c < AT_BN; c += 2) {
-                const float e0 = ex2_approx(fmaf(sv[c], p.scale_log2, -mref));
-                const float e1 = ex2_approx(fmaf(sv[c + 1], p.scale_log2, -mref));
-                sum += e0 + e1;
-                __nv_bfloat162 pp = __floats2bfloat162_rn(e0, e1);
-                pk[c >> 6][(c >> 1) & 31] = *reinterpret_cast<uint32_t*>(&pp);
-            }
-            l += sum;
-#pragma unroll
-            for (int c0 = 0; c0 < AT_BN / 64; ++c0) tmem_st32(tP0 + b * (AT_BN / 2) + lane_base + c0 * 32, pk[c0]);
-            tmem_st_wait();
-            // before this thread's arrival lets P.V of this tile start: p_empty cannot then be more
-            // than one phase ahead of what the thread has seen
-            if (!seen_pv && !mbar_wait(&p_empty, (j - 1) & 1, &abort_flag)) {
-                if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
-                ok = false;
-                break;
-            }
-            tc_fence_before();
-            mbar_arrive(&p_full[b]);
+            ok = __all_sync(0xffffffffu, ok);
         }
-        if (ok) {
-            if (!mbar_wait(&p_empty, (n_kt - 1) & 1, &abort_flag)) {
+        // group 1 hands its part of the row sum to group 0, which writes the rows out
+        if (wg == 1) {
+            l_sh[r] = l;
+            mg_sh[r] = m_mine;
+            asm volatile("bar.arrive 9, 256;" ::: "memory");
+        } else {
+            asm volatile("bar.sync 9, 256;" ::: "memory");
+            const int jl = n_kt - 1;                                   // the last product: all before it have completed too
+            if (ok && !mbar_wait(&p_empty[jl & 1], (jl >> 1) & 1, &abort_flag)) {
                 if (!abort_flag) { atomicExch(p.err, AT_ERR_P); abort_flag = 1; }
                 ok = false;
             }
+            const float m_fin = m_sh[r];
+            const float m_other = mg_sh[r];
+            if (n_kt > 1 && m_other != -INFINITY) l = (m_mine == -INFINITY ? 0.f : l * exp2f(m_mine - m_fin)) + l_sh[r] * exp2f(m_other - m_fin);
+            else if (m_mine != -INFINITY && m_mine != m_fin) l *= exp2f(m_mine - m_fin);
         }
         pdl_launch_dependents();
-        if (__all_sync(0xffffffffu, ok)) {                         // warp-uniform: the TMEM loads are warp-wide
+        if (wg == 0 && __all_sync(0xffffffffu, ok)) {              // warp-uniform: the TMEM loads are warp-wide
             tc_fence_after();
             const bool store = valid && l > 0.f;
             const float inv = store ? 1.0f / l : 0.f;

@@ -24,10 +24,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(s_addr(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same question without waiting: test_wait answers at once, try_wait may suspend the thread for
+// a while before it answers (about 110 cycles on a barrier whose phase has long completed).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(s_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait: false when about a second has passed (TC_WAIT_CYCLES) or another thread raised the
 // abort flag.
 #define TC_WAIT_CYCLES (2000000000ll)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+    if (mbar_test_wait(bar, parity)) return true;
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 0;; ++i) {
