@@ -267,22 +267,45 @@ def test_layer_sizes_of_a_real_model(real_dirs, dtype):
     ops.check_device_errors()
 
 
-# The layer sizes of Qwen3-8B (one layer of it, a small vocabulary that is no power of two): matrices
-# of 16 MB and more, which the decode steps hand to the weight-streaming kernel (all four products
-# of the layer, and the down product with k = 12,288), portions of 17 to 64 rows to the swapped tcgen05
-# kernel with 4 CTAs of a cluster on a tile (QKV, O, down) and with one (gate/up), whole prompts to
-# the large-tile tcgen05 product with 24,576 weight rows.
-BIG = dict(REAL, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-           intermediate_size=12288, num_hidden_layers=1, vocab_size=4099, tie_word_embeddings=False)
+# The layer sizes of Qwen3-8B and Qwen3-32B (one layer each, a small vocabulary that is no power of
+# two): matrices of 16 MB and more, which the decode steps hand to the weight-streaming kernel (all
+# four products of the layer), portions of 17 to 64 rows to the swapped tcgen05 kernel with 4 CTAs of
+# a cluster on a tile (QKV, O, down) and with one (gate/up), whole prompts to the large-tile tcgen05
+# product.  In float32 the same steps run on the plain products and must agree to float32 rounding.
+BIG = {"8b": dict(REAL, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                  intermediate_size=12288, num_hidden_layers=1, vocab_size=4099, tie_word_embeddings=False),
+       "32b": dict(REAL, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                   intermediate_size=25600, num_hidden_layers=1, vocab_size=2053, tie_word_embeddings=False)}
+BIG_PRODUCTS = {"8b": ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)),
+                "32b": ((10240, 5120), (5120, 8192), (51200, 5120), (5120, 25600))}
 
 
-def test_layer_sizes_of_the_8b_model(tmp_path):
+@pytest.mark.parametrize("size,dtype", [("8b", "bfloat16"), ("8b", "float32"), ("32b", "bfloat16"), ("32b", "float32")])
+def test_layer_sizes_of_the_large_models(tmp_path, size, dtype):
     from rllm_b200.csrc import ops
-    helpers.make_model_dir(tmp_path, BIG, seed=78, dtype=torch.bfloat16, std=0.02)
+    cfg = BIG[size]
+    helpers.make_model_dir(tmp_path, cfg, seed=78, dtype=getattr(torch, dtype), std=0.02)
     lens = {"a": 210, "b": 97, "c": 64}
-    reqs = {rid: helpers.random_tokens(n, BIG["vocab_size"], 600 + i) for i, (rid, n) in enumerate(lens.items())}
-    refs = {rid: reference(tmp_path, "bfloat16", t) for rid, t in reqs.items()}
-    eng = make_engine(tmp_path, "bfloat16", max_tokens=1024, block_size=32)
+    reqs = {rid: helpers.random_tokens(n, cfg["vocab_size"], 600 + i) for i, (rid, n) in enumerate(lens.items())}
+    refs = {rid: reference(tmp_path, dtype, t) for rid, t in reqs.items()}
+    eng = make_engine(tmp_path, dtype, max_tokens=1024, block_size=32)
+    if dtype == "float32":
+        # sums over 12,288 and 25,600 terms: the plain implementation in float32 is itself some 1e-6 from
+        # its float64 twin, so the engine is held against the twin, within the short tests' tolerance
+        # plus twice the distance between the two plain runs (measured here, over the places checked)
+        import plain_impl
+        cfg64, w64 = plain_impl.load_model(tmp_path, torch.float64)
+        refs64 = {rid: plain_impl.forward(cfg64, w64, t) for rid, t in reqs.items()}
+
+        def check(out, refs, dtype, what):
+            floor = max(rel_err(refs[rid][0][pos].double(), refs64[rid][pos]) for (rid, pos) in out)
+            assert floor < 2e-5, f"{what}: the plain implementation itself is {floor:.2e} from its float64 twin"
+            for (rid, pos), row in out.items():
+                e = rel_err(row.double(), refs64[rid][pos])
+                assert e <= TOL["float32"] + 2 * floor, f"{what}: request {rid} position {pos}: rel err {e:.3e} (floor {floor:.1e})"
+                assert int(row.argmax()) == int(refs64[rid][pos].argmax()), f"{what}: request {rid} position {pos}: argmax differs"
+    else:
+        check = globals()["check"]
     seen = set()
     real_stream, real_swap = ops.gemv_stream, ops.skinny_gemm_tc
 
@@ -300,7 +323,7 @@ def test_layer_sizes_of_the_8b_model(tmp_path):
         for rid, toks in reqs.items():
             want = sorted({0, 1, 63, len(toks) - 2, len(toks) - 1})
             out = helpers.run_steps(eng, [{"entries": [{"id": rid, "tokens": toks, "want": want}], "end": [rid]}])
-            check(out, refs, "bfloat16", f"8B sizes, whole {rid}")
+            check(out, refs, dtype, f"{size} sizes, whole {rid}")
         # portions of 17 to 64 rows, of 9 to 16 rows, and single tokens beside them
         sizes = {"a": [64, 40, 17, 1, 1, 33, 12, 1, 1, 40], "b": [20, 1, 1, 50, 9, 1, 15], "c": [33, 16, 1, 1, 13]}
         cut = {rid: 0 for rid in reqs}
@@ -318,7 +341,7 @@ def test_layer_sizes_of_the_8b_model(tmp_path):
                     end.append(rid)
             steps.append({"entries": entries, "end": end})
         out = helpers.run_steps(eng, steps)
-        check(out, refs, "bfloat16", "8B sizes, portions beside decoded tokens")
+        check(out, refs, dtype, f"{size} sizes, portions beside decoded tokens")
         # 24 single-token steps of all three at once after a whole prompt (graphs of the decode step), twice
         steps = [{"entries": [{"id": rid, "tokens": toks[:len(toks) - 24], "want": []} for rid, toks in reqs.items()]}]
         for j in range(24):
@@ -326,13 +349,16 @@ def test_layer_sizes_of_the_8b_model(tmp_path):
                                       for rid, toks in reqs.items()]})
         steps[-1]["end"] = list(reqs)
         out = helpers.run_steps(eng, steps)
-        check(out, refs, "bfloat16", "8B sizes, decoding")
+        check(out, refs, dtype, f"{size} sizes, decoding")
         again = helpers.run_steps(eng, steps)
         assert all(torch.equal(again[key], out[key]) for key in out)
     finally:
         ops.gemv_stream, ops.skinny_gemm_tc = real_stream, real_swap
-    for shape in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)):
-        assert ("stream", shape) in seen and ("swap", shape) in seen, (shape, sorted(seen))
+    if dtype == "bfloat16":
+        for shape in BIG_PRODUCTS[size]:
+            assert ("stream", shape) in seen and ("swap", shape) in seen, (shape, sorted(seen))
+    else:
+        assert not seen
     eng.cache.check_invariants()
     ops.check_device_errors()
 
