@@ -334,6 +334,7 @@ def main():
         steps = max(8, a.steps // 2)
         out["points"] = {"decode_b1": round(decode_run(1, steps, a.warmup)["tok_s"], 2),
                          "decode_b64": round(decode_run(64, steps, a.warmup)["tok_s"], 2)}
+    ops.check_device_errors("cuda:0")          # a kernel that gave up a bounded wait: no number
     print(json.dumps(out))
     return 0
 

@@ -382,6 +382,12 @@ class Engine:
             return g.logits[:R]
         return g.logits[torch.tensor(rows, dtype=torch.long, device=self.runtime.device)]
 
+    def check_device_errors(self) -> None:
+        """Raises if a kernel of an earlier step gave up a bounded wait (operand tiles that never
+        arrived, a stage or accumulator that was never released): its results are then not to be
+        used.  Reads one int from the device, so callers do it where they synchronize anyway."""
+        ops.check_device_errors(self.runtime.device)
+
     def finish(self, request_id) -> None:
         """Gives back what a finished request holds.  Freed pages may be handed out again at once:
         kernels of earlier steps that read them are ordered before later writes by the stream."""

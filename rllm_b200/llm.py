@@ -62,6 +62,7 @@ class LLM:
                                              presence_penalty, tuple(logit_bias)), frozenset(stop_ids)))
         results = {}
         host_samplers = {}
+        steps = 0
         while sched.has_work():
             plan = sched.plan()
             for f in sched.collect():
@@ -91,6 +92,10 @@ class LLM:
             sched.commit(plan, ids)
             for f in sched.collect():
                 results[f.request_id] = f
+            steps += 1
+            if steps % 64 == 0:
+                self.engine.check_device_errors()     # the ids were just read: the device is idle
+        self.engine.check_device_errors()
         self.last_stats = dict(sched.stats)
         out = [results[i] for i in range(len(prompts))]
         for f in out:

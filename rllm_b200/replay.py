@@ -49,8 +49,9 @@ def main(argv=None) -> int:
         if items:
             logits = engine.step(items)
             if logits is not None:
-                logits.detach().to("cpu", torch.float32).contiguous().numpy().astype("<f4").tofile(
-                    out_dir / f"{step}.f32")
+                rows = logits.detach().to("cpu", torch.float32).contiguous().numpy().astype("<f4")
+                engine.check_device_errors()          # a kernel that gave up a wait: no logits are written
+                rows.tofile(out_dir / f"{step}.f32")
         for rid in rec.get("end", []):
             engine.finish(rid)
         print(f"done {step}", flush=True)

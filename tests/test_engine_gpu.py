@@ -685,3 +685,16 @@ def test_graph_cache_is_bounded(dirs, monkeypatch):
         assert len(eng._graphs) <= 2
     assert eng.stats["graphs_captured"] >= 4
     eng.finish("r")
+
+
+def test_a_kernel_that_gave_up_a_wait_fails_the_generation(dirs):
+    """The error word that kernels with bounded waits write is read by the entry point: a code in
+    it (set here by hand; no kernel is made to wait) raises, and the word is cleared."""
+    from rllm_b200 import LLM
+    from rllm_b200.csrc import ops
+    llm = LLM(dirs["A", "bfloat16"], dtype="bfloat16", device=DEV, ctx=64, parallel=1)
+    assert len(llm.generate([[1, 2, 3]], max_tokens=3)[0]) == 3
+    ops.error_word(DEV).fill_(2)
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        llm.generate([[1, 2, 3]], max_tokens=3)
+    assert len(llm.generate([[1, 2, 3]], max_tokens=3)[0]) == 3          # cleared: the next call is clean
