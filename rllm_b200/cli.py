@@ -317,7 +317,11 @@ def main(argv=None) -> int:
         from .replay import main as replay_main
         return replay_main(argv[1:])
     a = ap.parse_args(argv)
-    return a.fn(a)
+    rc = a.fn(a)
+    if getattr(a, "device", "").startswith("cuda"):
+        from .csrc import ops
+        ops.check_device_errors(a.device)       # a kernel that gave up a bounded wait: the command fails
+    return rc
 
 
 if __name__ == "__main__":
