@@ -1,4 +1,4 @@
 from .allocator import BlockAllocator, OutOfPages, SlotAllocator
-from .manager import CacheManager, PagedKVView, StateView
+from .manager import CacheManager, PagedKVView, RequestTooLong, StateView
 
-__all__ = ["BlockAllocator", "OutOfPages", "SlotAllocator", "CacheManager", "PagedKVView", "StateView"]
+__all__ = ["BlockAllocator", "OutOfPages", "SlotAllocator", "CacheManager", "RequestTooLong", "PagedKVView", "StateView"]

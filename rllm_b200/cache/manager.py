@@ -61,7 +61,22 @@ class PagedGroup:
         """Logical index of the first block that tokens at positions >= length can still read."""
         if self.need.window <= 0:
             return 0
-        return max(0, length + 1 - self.need.window) // self.block_size
+        return max(0, length + 1 - self.need.window) // RELEASE_ALIGN * RELEASE_ALIGN // self.block_size
+
+
+# Pages of a windowed group are given back in runs of this many keys: the attention kernels round
+# the start of a window down to their key tile (at most 128 keys) and load whole tiles, so a page
+# goes to another request only when no tile that is still read touches it.
+RELEASE_ALIGN = 128
+
+
+class RequestTooLong(ValueError):
+    """A request would hold more tokens than the model's positions reach; nothing was taken."""
+
+    def __init__(self, length, limit):
+        self.length, self.limit = length, limit
+        super().__init__(f"a request would hold {length} tokens, more than the {limit} positions the model "
+                         f"has (max_position_embeddings)")
 
 
 class StateGroup:
@@ -115,6 +130,11 @@ class CacheManager:
         self.cache_of = list(cache_of)
         self.slots = SlotAllocator(max_requests)
         self.requests: dict = {}
+        self.max_length = 0          # most tokens a request may hold (0: no limit); see set_max_length
+
+    def set_max_length(self, n: int) -> None:
+        """Appends that would take a request beyond `n` tokens raise RequestTooLong (0: no limit)."""
+        self.max_length = int(n)
 
     # ------------------------------------------------------------------ device side
     def allocate_device(self, device, dtype) -> None:
@@ -179,6 +199,9 @@ class CacheManager:
 
     def can_append(self, items: Sequence) -> bool:
         """`items`: (rid, n_new) pairs, each request at most once."""
+        if self.max_length > 0 and any((self.requests[rid].length if rid in self.requests else 0) + n_new
+                                       > self.max_length for rid, n_new in items):
+            return False
         need = [0] * len(self.paged)
         new_requests = 0
         for rid, n_new in items:
@@ -191,7 +214,12 @@ class CacheManager:
         return all(n <= grp.allocator.n_free for n, grp in zip(need, self.paged))
 
     def check_append(self, items: Sequence) -> None:
-        """Raises OutOfPages if `items` cannot all be appended; takes nothing."""
+        """Raises OutOfPages (or RequestTooLong) if `items` cannot all be appended; takes nothing."""
+        if self.max_length > 0:
+            for rid, n_new in items:
+                length = (self.requests[rid].length if rid in self.requests else 0) + n_new
+                if length > self.max_length:
+                    raise RequestTooLong(length, self.max_length)
         need = [0] * len(self.paged)
         new_requests = sum(1 for rid, _ in items if rid not in self.requests)
         for rid, n_new in items:
@@ -252,8 +280,9 @@ class CacheManager:
         req.length = length
 
     def block_table(self, rid, group: int) -> list:
-        """Page per logical block; pages already given back read as 0 (never dereferenced: the
-        window excludes their positions)."""
+        """Page per logical block; pages already given back read as 0.  No kernel dereferences
+        them: pages are released in runs of RELEASE_ALIGN keys, the largest key tile, so every
+        tile that still holds a key inside the window lies wholly in pages the request holds."""
         return [0 if b is None else b for b in self.requests[rid].tables[group]]
 
     def state_slot(self, rid) -> int:

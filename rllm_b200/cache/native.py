@@ -18,10 +18,10 @@ import torch
 
 from ..csrc import build
 from .allocator import OutOfPages
-from .manager import CacheManager
+from .manager import CacheManager, RequestTooLong
 
 OK, ERR_OUT_OF_PAGES, ERR_OUT_OF_SLOTS, ERR_UNKNOWN_REQUEST, ERR_BAD_ARG, ERR_DOUBLE_FREE, ERR_INVARIANT, \
-    ERR_LIVE_TWICE, ERR_BUFFER = range(9)
+    ERR_LIVE_TWICE, ERR_BUFFER, ERR_TOO_LONG = range(10)
 
 _lib = None
 
@@ -36,6 +36,7 @@ def host_lib():
         for name in ("has", "length", "state_slot"):
             getattr(lib, f"rllm_cache_{name}").argtypes = [c_void_p, c_int64]
         lib.rllm_cache_n_requests.argtypes = [c_void_p]
+        lib.rllm_cache_set_max_length.argtypes = [c_void_p, c_int]
         lib.rllm_cache_n_free_pages.argtypes = [c_void_p, c_int]
         lib.rllm_cache_n_free_slots.argtypes = [c_void_p]
         lib.rllm_cache_pages_needed.argtypes = [c_void_p, c_int64, c_int, POINTER(c_int)]
@@ -106,6 +107,10 @@ class NativeCacheManager(CacheManager):
             need, free = c_int(), c_int()
             host_lib().rllm_cache_last_refusal(self._h, need, free)
             raise OutOfPages(need.value, free.value, "pages" if code == ERR_OUT_OF_PAGES else "state slots")
+        if code == ERR_TOO_LONG:
+            need, limit = c_int(), c_int()
+            host_lib().rllm_cache_last_refusal(self._h, need, limit)
+            raise RequestTooLong(need.value, limit.value)
         if code == ERR_UNKNOWN_REQUEST:
             raise KeyError(what)
         if code == ERR_DOUBLE_FREE:
@@ -117,6 +122,10 @@ class NativeCacheManager(CacheManager):
         raise ValueError(f"{what}: bad argument")
 
     # ---- interface of CacheManager
+    def set_max_length(self, n: int) -> None:
+        self.max_length = int(n)
+        host_lib().rllm_cache_set_max_length(self._h, int(n))
+
     def has(self, rid) -> bool:
         return rid in self._ids
 

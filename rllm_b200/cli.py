@@ -10,7 +10,7 @@
   rllm perplexity MODEL TOKENS [--ctx 512] [--chunks N]
                                                   perplexity over a file of token ids, chunk by chunk
   rllm inspect MODEL                              configuration and tensor list
-  rllm random-model OUT --config FILE [--seed 0] [--dtype bfloat16]
+  rllm random-model OUT --config FILE [--seed 0] [--dtype bfloat16] [--shards 1]
   rllm replay ...                                 same as bin/trace_run
 
 The engine has no tokenizer: PROMPT is token ids separated by commas or spaces, or @FILE holding
@@ -235,9 +235,11 @@ def cmd_inspect(a) -> int:
     from .weights import SafetensorsFile
     cfg = load_config(a.model)
     print(cfg)
-    with SafetensorsFile(Path(a.model) / "model.safetensors") as f:
-        for n in sorted(f.names()):
-            print(f"{n:60s} {str(f.dtype(n)):16s} {list(f.shape(n))}")
+    from .weights import weight_files
+    for path in weight_files(a.model)[1]:
+        with SafetensorsFile(path) as f:
+            for n in sorted(f.names()):
+                print(f"{n:60s} {str(f.dtype(n)):16s} {str(list(f.shape(n))):20s} {path.name}")
     return 0
 
 
@@ -246,7 +248,7 @@ def cmd_random_model(a) -> int:
     from .config import config_from_dict
     from .weights import write_random_model
     cfg = config_from_dict(json.loads(Path(a.config).read_text()))
-    write_random_model(cfg, a.out, seed=a.seed,
+    write_random_model(cfg, a.out, seed=a.seed, shards=a.shards,
                        dtype={"bfloat16": torch.bfloat16, "float32": torch.float32}[a.dtype])
     print(a.out)
     return 0
@@ -308,6 +310,8 @@ def main(argv=None) -> int:
     p.add_argument("out"); p.add_argument("--config", required=True)
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    p.add_argument("--shards", type=int, default=1,
+                   help="write this many model-0000i-of-0000N.safetensors files and a weight map")
     p.set_defaults(fn=cmd_random_model)
 
     p = sub.add_parser("replay", add_help=False)

@@ -52,7 +52,12 @@ struct Group {
 };
 
 enum : int { OK = 0, ERR_OUT_OF_PAGES = 1, ERR_OUT_OF_SLOTS = 2, ERR_UNKNOWN_REQUEST = 3, ERR_BAD_ARG = 4,
-             ERR_DOUBLE_FREE = 5, ERR_INVARIANT = 6, ERR_LIVE_TWICE = 7, ERR_BUFFER = 8 };
+             ERR_DOUBLE_FREE = 5, ERR_INVARIANT = 6, ERR_LIVE_TWICE = 7, ERR_BUFFER = 8, ERR_TOO_LONG = 9 };
+
+// Pages of a windowed group are given back in runs of this many keys: the attention kernels
+// round the start of a window down to their key tile (at most 128 keys) and load whole tiles,
+// so a page is only handed to another request once no tile that is still read touches it.
+constexpr int RELEASE_ALIGN = 128;
 
 struct Cache {
     int block_size, n_blocks, max_requests;
@@ -60,6 +65,7 @@ struct Cache {
     std::vector<int> free_slots;
     std::unordered_map<int64_t, Request> requests;
     int last_need = 0, last_free = 0;        // of the most recent refusal
+    int max_length = 0;                      // most tokens a request may hold (0: no limit)
 
     Cache(int n_groups, const int* windows, int bs, int nb, int mr) : block_size(bs), n_blocks(nb), max_requests(mr) {
         for (int g = 0; g < n_groups; ++g) groups.emplace_back(windows[g], nb);
@@ -81,7 +87,10 @@ struct Cache {
         int new_requests = 0;
         for (int i = 0; i < n_items; ++i) {
             if (n_new[i] <= 0) return ERR_BAD_ARG;
-            if (!requests.count(rids[i])) ++new_requests;
+            auto it = requests.find(rids[i]);
+            if (it == requests.end()) ++new_requests;
+            const int length = (it == requests.end() ? 0 : it->second.length) + n_new[i];
+            if (max_length > 0 && length > max_length) { last_need = length; last_free = max_length; return ERR_TOO_LONG; }
             pages_needed(rids[i], n_new[i], one.data());
             for (size_t g = 0; g < groups.size(); ++g) need[g] += one[g];
         }
@@ -136,7 +145,7 @@ struct Cache {
         int count = 0;
         for (size_t g = 0; g < groups.size(); ++g) {
             if (groups[g].window <= 0) continue;
-            const int first = std::max(0, it->second.length + 1 - groups[g].window) / block_size;
+            const int first = std::max(0, it->second.length + 1 - groups[g].window) / RELEASE_ALIGN * RELEASE_ALIGN / block_size;
             auto& table = it->second.tables[g];
             for (int b = 0; b < std::min(first, (int)table.size()); ++b)
                 if (table[b] >= 0) {
@@ -211,6 +220,7 @@ API int rllm_cache_length(void* c, int64_t rid) {
     auto it = r.find(rid);
     return it == r.end() ? -1 : it->second.length;
 }
+API void rllm_cache_set_max_length(void* c, int n) { static_cast<Cache*>(c)->max_length = n; }
 API int rllm_cache_n_requests(void* c) { return (int)static_cast<Cache*>(c)->requests.size(); }
 API int rllm_cache_state_slot(void* c, int64_t rid) {
     auto& r = static_cast<Cache*>(c)->requests;

@@ -92,6 +92,9 @@ class Engine:
         manager = NativeCacheManager if native_host else CacheManager
         self.cache = manager(needs, cache_of, block_size, max_tokens, max_requests)
         self.cache.allocate_device(self.runtime.device, self.runtime.dtype)
+        # a request never grows beyond the positions the model has: the append that would take it
+        # there is refused before anything changes (RequestTooLong)
+        self.cache.set_max_length(int(getattr(model.spec, "max_position", 0) or 0))
         self.block_size = block_size
         self._windowed = any(g.need.window > 0 for g in self.cache.paged)     # only then do pages fall out of reach
         # RLLM_B200_NO_GRAPHS=1 turns graph replay off (the reference's RLLM_NO_GRAPHS); the profiling

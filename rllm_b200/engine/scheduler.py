@@ -228,3 +228,12 @@ class Scheduler:
         self.running = []
         self.done.extend(out)
         return out
+
+    def release_all(self) -> None:
+        """Frees what any request this scheduler knows still holds in the cache and forgets them
+        all (the end of a generate call, however it ended)."""
+        for s in list(self.running) + list(self.waiting):
+            if self.cache.has(s.rid):
+                self.cache.free(s.rid)
+        self.running = []
+        self.waiting.clear()

@@ -33,19 +33,29 @@ class LLM:
             self.config, self.model = load_model(model, dtype, device)
         else:
             self.config, self.model = None, model
+        limit = int(getattr(self.model.spec, "max_position", 0) or 0)
+        if limit and ctx > limit:
+            from .config.base import ConfigError
+            raise ConfigError(f"ctx {ctx} exceeds the model's max_position_embeddings ({limit}): positions beyond "
+                              f"it are outside what the model was made for")
         kv_tokens = max(kv_tokens or ctx * parallel, ctx)
         self.engine = Engine(self.model, block_size=block_size, max_tokens=kv_tokens,
                              max_requests=max(parallel, 1))
         self.ctx, self.prefill_chunk, self.parallel = ctx, prefill_chunk, parallel
         self.host_sampling = host_sampling
         self.last_stats = {}
+        self.last_errors = {}
 
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens=256, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, seed: int = 0, stop_ids: Sequence[int] = (),
                  return_reasons: bool = False, frequency_penalty: float = 0.0, presence_penalty: float = 0.0,
                  logit_bias=()):
         """Generates for every prompt (continuous batching); returns the generated ids per prompt,
-        in order.  max_tokens: one number, or one per prompt.  Request i samples with seed
+        in order.  A step that fails (an exception from the engine or the sampler, or a kernel that
+        gave up a bounded wait) fails the requests running in it and frees their pages; the waiting
+        ones still run.  Failed requests raise GenerationError at the end (its `results` hold
+        what the others generated), or, with return_reasons, come back with the reason "error" and
+        their message in `last_errors`.  max_tokens: one number, or one per prompt.  Request i samples with seed
         `seed + i`.  logit_bias: (token, delta) pairs or a
         {token: delta} mapping, added to the logits with the frequency and presence penalties over
         the tokens generated so far before the token is chosen."""
@@ -63,47 +73,78 @@ class LLM:
         results = {}
         host_samplers = {}
         steps = 0
-        while sched.has_work():
-            plan = sched.plan()
-            for f in sched.collect():
-                results[f.request_id] = f
-            if not plan:
-                continue
-            items = [StepItem(p.seq.rid, p.tokens, [p.take - 1] if p.want_last else []) for p in plan]
-            try:
-                logits = self.engine.step(items)
-            except Exception as e:           # a failed step fails the running requests, not the queue
-                for f in sched.fail_running(f"step failed: {e}"):
+        try:
+            while sched.has_work():
+                plan = sched.plan()
+                for f in sched.collect():
                     results[f.request_id] = f
-                sched.collect()
-                raise
-            wanted = [p for p in plan if p.want_last]
-            ids = []
-            if wanted:
-                if self.host_sampling:
-                    rows = logits.float().cpu().numpy()
-                    for r, p in enumerate(wanted):
-                        hs = host_samplers.setdefault(p.seq.rid, HostSampler(p.seq.req.params))
-                        ids.append(hs.sample(rows[r], p.seq.counts))
-                else:
-                    counters = [p.seq.cached + p.take for p in wanted]
-                    ids = sample_rows(logits, [p.seq.req.params for p in wanted], counters,
-                                      [p.seq.counts for p in wanted]).tolist()
-            sched.commit(plan, ids)
-            for f in sched.collect():
-                results[f.request_id] = f
-            steps += 1
-            if steps % 64 == 0:
-                self.engine.check_device_errors()     # the ids were just read: the device is idle
-        self.engine.check_device_errors()
+                if not plan:
+                    continue
+                try:
+                    ids = self._run_step(plan, host_samplers)
+                    steps += 1
+                    if steps % 64 == 0:
+                        self.engine.check_device_errors()     # the ids were just read: the device is idle
+                except Exception as e:
+                    # a failed step fails the requests that were running and frees what they hold; the
+                    # queue goes on (crates/rllm-server/src/engine.rs:569-578)
+                    sched.fail_running(f"step failed: {type(e).__name__}: {e}")
+                    for f in sched.collect():
+                        results[f.request_id] = f
+                    continue
+                sched.commit(plan, ids)
+                for f in sched.collect():
+                    results[f.request_id] = f
+            try:
+                self.engine.check_device_errors()
+            except Exception as e:
+                # which step the kernel belonged to is not known: nothing generated in this call is to be used
+                for i in range(len(prompts)):
+                    f = results.get(i)
+                    if f is None or f.reason != "error":
+                        results[i] = Finished(i, f.tokens if f else [], "error", f"{type(e).__name__}: {e}")
+        finally:
+            # whatever ended the loop (an interrupt included), nothing of this call stays in the cache:
+            # the next call numbers its requests from 0 again
+            sched.release_all()
         self.last_stats = dict(sched.stats)
         out = [results[i] for i in range(len(prompts))]
-        for f in out:
-            if f.reason == "error":
-                raise RuntimeError(f"request {f.request_id}: {f.error}")
+        self.last_errors = {f.request_id: f.error for f in out if f.reason == "error"}
         if return_reasons:
             return [(f.tokens, f.reason) for f in out]
+        if self.last_errors:
+            raise GenerationError(out)
         return [f.tokens for f in out]
+
+    def _run_step(self, plan, host_samplers) -> list:
+        """One engine step for the planned items and one sampled id per item that wants its last row."""
+        items = [StepItem(p.seq.rid, p.tokens, [p.take - 1] if p.want_last else []) for p in plan]
+        logits = self.engine.step(items)
+        wanted = [p for p in plan if p.want_last]
+        if not wanted:
+            return []
+        if self.host_sampling:
+            ids = []
+            rows = logits.float().cpu().numpy()
+            for r, p in enumerate(wanted):
+                hs = host_samplers.setdefault(p.seq.rid, HostSampler(p.seq.req.params))
+                ids.append(hs.sample(rows[r], p.seq.counts))
+            return ids
+        counters = [p.seq.cached + p.take for p in wanted]
+        return sample_rows(logits, [p.seq.req.params for p in wanted], counters,
+                           [p.seq.counts for p in wanted]).tolist()
+
+
+class GenerationError(RuntimeError):
+    """Some requests of a generate() call failed.  `results`: one scheduler record per prompt
+    (`tokens`, `reason`, `error`), the successful ones with their tokens; `errors`: index -> message."""
+
+    def __init__(self, results):
+        self.results = list(results)
+        self.errors = {f.request_id: f.error for f in self.results if f.reason == "error"}
+        first = next(iter(self.errors.items()))
+        more = f" (and {len(self.errors) - 1} more)" if len(self.errors) > 1 else ""
+        super().__init__(f"request {first[0]}: {first[1]}{more}")
 
 
 def generate(model, prompts, max_tokens: int = 256, temperature: float = 0.0, top_k: int = 0,

@@ -1,6 +1,6 @@
-from .loader import WeightMismatchError, load_checked
-from .random_init import random_tensors, write_random_model
+from .loader import WeightMismatchError, load_checked, weight_files
+from .random_init import random_tensors, write_random_model, write_sharded
 from .safetensors_io import SafetensorsFile, WeightFileError, write_safetensors
 
-__all__ = ["WeightMismatchError", "load_checked", "random_tensors", "write_random_model",
+__all__ = ["WeightMismatchError", "load_checked", "weight_files", "write_sharded", "random_tensors", "write_random_model",
            "SafetensorsFile", "WeightFileError", "write_safetensors"]

@@ -85,6 +85,33 @@ def test_trace_run_rejects_bad_model(tmp_path):
     assert proc.returncode != 0 and "unsupported architecture" in proc.stderr
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sharded_folder_gives_the_same_logits(tmp_path, dtype):
+    """Three shards and a weight map in place of model.safetensors: the same bits out of the engine,
+    and a request cannot grow beyond max_position_embeddings."""
+    from rllm_b200.cache import RequestTooLong
+    from rllm_b200.config import config_from_dict
+    from rllm_b200.engine import StepItem
+    from rllm_b200.weights import write_random_model
+    cfg = config_from_dict(dict(TINY["B"], max_position_embeddings=64))
+    one = write_random_model(cfg, tmp_path / "one", seed=3, dtype=getattr(torch, dtype), std=STD)
+    three = write_random_model(cfg, tmp_path / "three", seed=3, dtype=getattr(torch, dtype), std=STD, shards=3)
+    assert not (three / "model.safetensors").exists()
+    toks = helpers.random_tokens(60, TINY["B"]["vocab_size"], 8)
+    rows = []
+    for d in (one, three):
+        eng = engine(d, dtype, max_tokens=128, max_requests=2)
+        rows.append(eng.step([StepItem("a", toks, list(range(60)))]).float().cpu())
+    assert torch.equal(rows[0], rows[1])
+    pcfg, w = plain_impl.load_model(one)
+    assert rel_err(rows[1], plain_impl.forward(pcfg, w, toks)) <= (5e-6 if dtype == "float32" else 3e-2)
+    eng.step([StepItem("a", [1, 2, 3, 4], [])])                       # 64 tokens: the last position the model has
+    for more in ([5], [5, 6, 7]):                                     # the decode path and the portion path
+        with pytest.raises(RequestTooLong, match="max_position_embeddings"):
+            eng.step([StepItem("a", more, [0])])
+    assert eng.cache.length("a") == 64
+
+
 # ---------------------------------------------------------------- generation through the entry point
 
 @pytest.mark.parametrize("name", ["A", "B", "W", "F"])
@@ -695,6 +722,19 @@ def test_a_kernel_that_gave_up_a_wait_fails_the_generation(dirs):
     llm = LLM(dirs["A", "bfloat16"], dtype="bfloat16", device=DEV, ctx=64, parallel=1)
     assert len(llm.generate([[1, 2, 3]], max_tokens=3)[0]) == 3
     ops.error_word(DEV).fill_(2)
-    with pytest.raises(ops.KernelError, match="bounded wait"):
+    from rllm_b200.llm import GenerationError
+    with pytest.raises(GenerationError, match="bounded wait"):
         llm.generate([[1, 2, 3]], max_tokens=3)
     assert len(llm.generate([[1, 2, 3]], max_tokens=3)[0]) == 3          # cleared: the next call is clean
+    # the word is also read every 64 steps: the requests running then fail, nothing stays in the cache,
+    # and the next call (whose requests are numbered from 0 again) gives what a fresh engine gives
+    llm = LLM(dirs["A", "bfloat16"], dtype="bfloat16", device=DEV, ctx=256, parallel=1)
+    want = llm.generate([[4, 5, 6, 7]], max_tokens=100)[0]
+    assert len(want) == 100
+    ops.error_word(DEV).fill_(1)
+    with pytest.raises(GenerationError, match="bounded wait") as ei:
+        llm.generate([[9, 8, 7]], max_tokens=100)
+    assert ei.value.errors.keys() == {0}
+    assert not llm.engine.cache.requests
+    assert llm.engine.cache.n_free_pages(0) == llm.engine.cache.n_blocks
+    assert llm.generate([[4, 5, 6, 7]], max_tokens=100)[0] == want

@@ -14,6 +14,7 @@ import torch
 import helpers
 import plain_impl
 from rllm_b200.cache import BlockAllocator, CacheManager, OutOfPages
+from rllm_b200.cache.native import NativeCacheManager
 from rllm_b200.config import ConfigError, Qwen3Config, config_from_dict, load_config, supported_architectures
 from rllm_b200.engine.scheduler import Request, Scheduler
 from rllm_b200.parts import PagedKVNeed, StateNeed
@@ -139,6 +140,98 @@ def test_loader_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     assert set(load_checked(d, exp, ignorable={"lm_head.weight"})) == set(exp)
 
 
+def test_sharded_checkpoints(tmp_path):
+    """A folder with model.safetensors.index.json and model-0000i-of-0000N.safetensors shards loads to
+    the same tensors as the one-file folder; every way in which index and shards can disagree is an
+    error that names the file (the reference asks for each tensor by name and names it when it is
+    not there: crates/rllm-model/src/loader.rs:8-23)."""
+    import shutil
+    from rllm_b200.models.model import expected_tensors
+    from rllm_b200.weights import weight_files, write_sharded
+    cfg = config_from_dict(helpers.TINY_B)
+    exp = {n: s for n, (s, _) in expected_tensors(cfg.model_spec()).items()}
+    one = load_checked(write_random_model(cfg, tmp_path / "one", seed=5, dtype=torch.bfloat16), exp)
+    d = write_random_model(cfg, tmp_path / "three", seed=5, dtype=torch.bfloat16, shards=3)
+    files = sorted(p.name for p in d.glob("*.safetensors"))
+    assert files == [f"model-0000{i}-of-00003.safetensors" for i in (1, 2, 3)]
+    where, paths = weight_files(d)
+    assert len(paths) == 3 and set(where) == set(exp) and len(set(where.values())) == 3
+    got = load_checked(d, exp)
+    assert set(got) == set(one) and all(torch.equal(got[n], one[n]) for n in one)
+    index = json.loads((d / "model.safetensors.index.json").read_text())
+
+    def variant(name):
+        v = tmp_path / name
+        shutil.copytree(d, v)
+        return v
+
+    v = variant("missing_shard")
+    (v / files[1]).unlink()
+    with pytest.raises(WeightFileError, match=files[1] + ".*shard is missing"):
+        load_checked(v, exp)
+
+    v = variant("moved_tensor")                      # the index names a shard that does not hold the tensor
+    moved = next(n for n, f in index["weight_map"].items() if f == files[0])
+    idx = json.loads(json.dumps(index))
+    idx["weight_map"][moved] = files[2]
+    (v / "model.safetensors.index.json").write_text(json.dumps(idx))
+    with pytest.raises(WeightFileError, match=files[2] + ".*" + moved.replace(".", r"\.") + ".*does not hold it.*" + files[0]):
+        load_checked(v, exp)
+
+    v = variant("twice")                             # one tensor stored in two shards
+    with SafetensorsFile(v / files[0]) as f0, SafetensorsFile(v / files[1]) as f1:
+        t1 = {n: f1.tensor(n) for n in f1.names()}
+        dup = f0.names()[0]
+        t1[dup] = f0.tensor(dup)
+    write_safetensors(v / files[1], t1)
+    with pytest.raises(WeightFileError, match="stored here and in"):
+        load_checked(v, exp)
+
+    v = variant("lists")                             # missing, unexpected and wrong shapes across shards: one error
+    with SafetensorsFile(v / files[2]) as f2:
+        t2 = {n: f2.tensor(n) for n in f2.names()}
+    gone = sorted(t2)[0]
+    del t2[gone]
+    t2["model.extra.weight"] = torch.zeros(2)
+    write_safetensors(v / files[2], t2)
+    idx = json.loads(json.dumps(index))
+    del idx["weight_map"][gone]
+    idx["weight_map"]["model.extra.weight"] = files[2]
+    (v / "model.safetensors.index.json").write_text(json.dumps(idx))
+    with pytest.raises(WeightMismatchError) as e:
+        load_checked(v, exp)
+    assert e.value.missing == [gone] and e.value.unexpected == ["model.extra.weight"]
+    assert "model.safetensors.index.json" in str(e.value)
+
+    v = variant("bad_index")
+    (v / "model.safetensors.index.json").write_text("{\"weight_map\": 3}")
+    with pytest.raises(WeightFileError, match="not a weight map"):
+        load_checked(v, exp)
+    idx = json.loads(json.dumps(index))
+    idx["weight_map"][moved] = "../elsewhere.safetensors"
+    (v / "model.safetensors.index.json").write_text(json.dumps(idx))
+    with pytest.raises(WeightFileError, match="not a file name in this folder"):
+        load_checked(v, exp)
+    with pytest.raises(WeightFileError, match="neither model.safetensors nor"):
+        load_checked(tmp_path / "nowhere", exp)
+    # more shards than tensors: one tensor each, none empty
+    many = {f"t{i}": torch.full((i + 1,), float(i)) for i in range(3)}
+    assert len(write_sharded(tmp_path, many, 7)) == 3
+
+
+def test_ctx_beyond_the_models_positions_is_refused(tmp_path):
+    from rllm_b200.llm import LLM
+    from rllm_b200.config import ConfigError
+
+    class Spec:
+        max_position = 512
+
+    class Model:
+        spec = Spec()
+    with pytest.raises(ConfigError, match="max_position_embeddings"):
+        LLM(Model(), ctx=513)
+
+
 def test_loader_dtypes(tmp_path):
     t = {"a": torch.ones(2, 2, dtype=torch.float16), "b": torch.ones(2, dtype=torch.float32),
          "c": torch.arange(4, dtype=torch.int64), "d": torch.ones(3, dtype=torch.bfloat16)}
@@ -220,27 +313,50 @@ def test_cache_manager_slots_and_tables():
 
 
 def test_cache_groups_window_and_shared_cache():
-    full, win = PagedKVNeed(2, 16, 0), PagedKVNeed(2, 16, 6)
-    cm = CacheManager([full, win, win, win, StateNeed((3,)), None], [None, None, None, 1, None, None],
-                      block_size=4, max_tokens=64, max_requests=3)
-    assert len(cm.paged) == 2 and len(cm.stateful) == 1
-    assert cm.entry_place[3] == cm.entry_place[1]             # entry 3 reads entry 1's cache
-    assert cm.entry_place[5] is None
-    assert [len(g.entries) for g in cm.paged] == [1, 2]
-    cm.append("r", 10)
-    assert cm.release_passed("r") == 1                        # keys 0..3 are behind the window of position 10
-    cm.append("r", 1)
-    cm.release_passed("r")
-    assert cm.block_table("r", 0) == [0, 1, 2]
-    assert cm.requests["r"].tables[1] == [None, 1, 2]
-    # a long portion needs pages for all of its tokens at once, and gives most back after the step
-    free_before = cm.n_free_pages(1)
-    cm.append("r", 21)
-    assert cm.n_free_pages(1) == free_before - 5
-    assert cm.release_passed("r") == 5
-    cm.check_invariants()
+    full, win = PagedKVNeed(2, 16, 0), PagedKVNeed(2, 16, 40)
+    for manager in (CacheManager, NativeCacheManager):
+        cm = manager([full, win, win, win, StateNeed((3,)), None], [None, None, None, 1, None, None],
+                     block_size=16, max_tokens=1024, max_requests=3)
+        assert len(cm.paged) == 2 and len(cm.stateful) == 1
+        assert cm.entry_place[3] == cm.entry_place[1]             # entry 3 reads entry 1's cache
+        assert cm.entry_place[5] is None
+        assert [len(g.entries) for g in cm.paged] == [1, 2]
+        # Pages are given back in runs of 128 keys (the kernels' largest key tile: a tile that still holds a
+        # key inside the window is loaded whole).  After 166 tokens the next query sits at position 166 and
+        # reads keys from 127 on; one token later the window starts at 128 and keys 0..127 are out of reach.
+        cm.append("r", 166)
+        assert cm.release_passed("r") == 0
+        cm.append("r", 1)
+        assert cm.release_passed("r") == 8                        # keys 0..127: eight pages of 16
+        assert cm.block_table("r", 0) == list(range(11))          # the group without a window keeps everything
+        assert cm.block_table("r", 1)[:9] == [0] * 8 + [8]        # pages given back read as 0
+        # a long portion needs pages for all of its tokens at once, and gives most back after the step
+        free_before = cm.n_free_pages(1)
+        cm.append("r", 300)                                       # 167 -> 467 tokens: 30 pages where 11 were
+        assert cm.n_free_pages(1) == free_before - 19
+        assert cm.release_passed("r") == 16                       # the window now starts at 428: keys below 384 go
+        cm.check_invariants()
+        cm.free("r")
+        assert cm.n_free_pages(0) == cm.n_free_pages(1) == cm.n_blocks
     with pytest.raises(ValueError):
         CacheManager([full, win], [None, 0], 4, 64, 2)        # reading a cache of another kind
+
+
+def test_a_request_cannot_outgrow_the_models_positions():
+    from rllm_b200.cache import RequestTooLong
+    for manager in (CacheManager, NativeCacheManager):
+        cm = manager([PagedKVNeed(1, 16)], [None], 16, 1024, 4)
+        cm.set_max_length(100)
+        cm.append("a", 90)
+        assert cm.can_append([("a", 10)]) and not cm.can_append([("a", 11)])
+        with pytest.raises(RequestTooLong, match="max_position_embeddings") as e:
+            cm.append("a", 11)
+        assert (e.value.length, e.value.limit) == (101, 100)
+        with pytest.raises(RequestTooLong):
+            cm.check_append([("b", 5), ("c", 101)])
+        assert cm.length("a") == 90 and not cm.has("c")           # nothing changed
+        cm.append("a", 10)
+        cm.check_invariants()
 
 
 @pytest.mark.parametrize("seed", range(6))
@@ -381,6 +497,96 @@ def test_scheduler_failed_step_frees_running():
     assert not cache.requests
     drive(s, cache)                                            # the queue goes on
     assert [f.request_id for f in s.collect() if f.reason == "length"] == [2]
+
+
+class _FakeEngine:
+    """Stands in for the engine under LLM.generate: the host cache manager and a step that returns
+    logits naming token (number of tokens the request holds) % 50, or raises on the steps listed."""
+
+    def __init__(self, fail_steps=(), device_error_at=()):
+        self.cache = CacheManager([PagedKVNeed(1, 16)], [None], 16, 1024, 4)
+        self.calls, self.fail_steps, self.device_error_at = 0, set(fail_steps), set(device_error_at)
+        self.checks = 0
+
+    def step(self, items):
+        self.calls += 1
+        if self.calls in self.fail_steps:
+            raise RuntimeError(f"injected fault in step {self.calls}")
+        rows = []
+        for it in items:
+            self.cache.append(it.request_id, len(it.tokens))
+            for _ in it.want:
+                row = torch.zeros(50)
+                row[self.cache.length(it.request_id) % 50] = 1.0
+                rows.append(row)
+        return torch.stack(rows) if rows else None
+
+    def check_device_errors(self):
+        self.checks += 1
+        if self.checks in self.device_error_at:
+            raise RuntimeError("a kernel's bounded wait ran out (injected)")
+
+
+def _fake_llm(engine, parallel=2):
+    from rllm_b200.llm import LLM
+    llm = object.__new__(LLM)
+    llm.engine, llm.ctx, llm.prefill_chunk, llm.parallel = engine, 256, 512, parallel
+    llm.host_sampling, llm.last_stats, llm.last_errors = True, {}, {}
+    return llm
+
+
+def test_generate_goes_on_after_a_failed_step():
+    """A failed step fails the requests running in it and frees their pages; the waiting requests
+    still run, and the errors are reported per request (crates/rllm-server/src/engine.rs:569-578)."""
+    from rllm_b200.llm import GenerationError
+    prompts = [[1] * 5, [2] * 7, [3] * 4, [4] * 9]
+    good = _fake_llm(_FakeEngine()).generate(prompts, max_tokens=6)
+    assert good[0] == [(5 + i) % 50 for i in range(6)]
+    eng = _FakeEngine(fail_steps={3})                          # requests 0 and 1 run then, 2 and 3 wait
+    llm = _fake_llm(eng)
+    with pytest.raises(GenerationError, match="injected fault in step 3") as ei:
+        llm.generate(prompts, max_tokens=6)
+    err = ei.value
+    assert sorted(err.errors) == [0, 1]
+    assert [f.tokens for f in err.results[2:]] == good[2:] and all(f.reason == "length" for f in err.results[2:])
+    assert len(err.results[0].tokens) == 2                     # what it had generated before the fault
+    assert not eng.cache.requests and eng.cache.n_free_pages(0) == eng.cache.n_blocks
+    # with return_reasons nothing is raised: the failed requests come back with the reason "error"
+    eng = _FakeEngine(fail_steps={1})
+    llm = _fake_llm(eng)
+    out = llm.generate(prompts, max_tokens=6, return_reasons=True)
+    assert [r for _, r in out] == ["error", "error", "length", "length"] and sorted(llm.last_errors) == [0, 1]
+    assert [t for t, _ in out[2:]] == good[2:]
+    # the same engine again: numbered from 0 again, on a clean cache, the same tokens as a fresh one
+    assert llm.generate(prompts, max_tokens=6) == good
+
+
+def test_generate_leaves_nothing_in_the_cache_however_it_ends():
+    from rllm_b200.llm import GenerationError
+
+    class Interrupting(_FakeEngine):
+        def step(self, items):
+            if self.calls == 2:
+                raise KeyboardInterrupt
+            return super().step(items)
+
+    eng = Interrupting()
+    llm = _fake_llm(eng)
+    with pytest.raises(KeyboardInterrupt):
+        llm.generate([[1] * 5, [2] * 7], max_tokens=6)
+    assert not eng.cache.requests and eng.cache.n_free_pages(0) == eng.cache.n_blocks
+    # the device's error word read in the middle (every 64 steps) fails the running requests only
+    eng = _FakeEngine(device_error_at={1})
+    llm = _fake_llm(eng, parallel=1)
+    with pytest.raises(GenerationError, match="bounded wait") as ei:
+        llm.generate([[1] * 5, [2] * 7], max_tokens=80)
+    assert sorted(ei.value.errors) == [0] and len(ei.value.results[1].tokens) == 80
+    assert not eng.cache.requests
+    # read at the end, it fails everything the call generated
+    eng = _FakeEngine(device_error_at={1})
+    with pytest.raises(GenerationError) as ei:
+        _fake_llm(eng).generate([[1] * 5, [2] * 7], max_tokens=6)
+    assert sorted(ei.value.errors) == [0, 1]
 
 
 # ---------------------------------------------------------------- samplers and the plain implementation
