@@ -507,3 +507,5 @@ RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v
     }
     return rllm_launch(attention_tc_kernel, dim3(n_tiles, K), dim3(AT_THREADS), smem, stream, tq, tk, tv, p);
 }
+
+TC_DEFINE_WAIT_CONTROLS(rllm_attn_tc)

@@ -9,8 +9,9 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------ embedding
-// out[t, :] = table[tokens[t], :] as float32.  A token id outside [0, vocab) sets
-// *err and reads row 0 (the host checks ids before launch; this is the backstop).
+// out[t, :] = table[tokens[t], :] as float32.  A token id outside [0, vocab) writes code 4 to
+// *err (the error word that the entry points read) and reads row 0; the host checks ids before
+// launch, this is the backstop.
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int d, int vocab, int* err) {
@@ -19,7 +20,7 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
     const int t = blockIdx.x;
     int tok = tokens[t];
     if (tok < 0 || tok >= vocab) {
-        if (threadIdx.x == 0 && err) atomicExch(err, 1);
+        if (threadIdx.x == 0 && err) atomicExch(err, 4);
         tok = 0;
     }
     const TW* src = table + (size_t)tok * d;

@@ -656,3 +656,5 @@ RLLM_API int rllm_gemm_tc_swap(const void* W, const void* X, void* C, int c_dtyp
 #undef SWAP
     return (int)cudaErrorInvalidValue;
 }
+
+TC_DEFINE_WAIT_CONTROLS(rllm_tc)

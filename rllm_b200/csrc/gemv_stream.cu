@@ -435,3 +435,5 @@ RLLM_API int rllm_gemv_stream(const void* W, const void* X, void* C, int c_dtype
 #undef SV
     return (int)cudaErrorInvalidValue;
 }
+
+TC_DEFINE_WAIT_CONTROLS(rllm_stream)

@@ -298,6 +298,8 @@ def skinny_gemm(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
 
 
 _error_words: dict = {}
+ERROR_CODES_RANGE = {4: "a token id outside the vocabulary", 5: "a cache slot outside the pool",
+                     6: "a page outside the pool"}
 
 
 def error_word(device) -> torch.Tensor:
@@ -309,12 +311,36 @@ def error_word(device) -> torch.Tensor:
 
 
 def check_device_errors(device="cuda:0") -> None:
-    """Raises if a kernel reported a wait that ran out (reads one int from the device)."""
+    """Raises if a kernel reported a fault it caught itself: a bounded wait that ran out, or an
+    index that its range check refused (reads one int from the device)."""
     code = int(error_word(device).item())
     if code:
         error_word(device).zero_()
+        if code in ERROR_CODES_RANGE:
+            raise KernelError(f"a kernel refused an index (code {code}: {ERROR_CODES_RANGE[code]}); the access was "
+                              f"skipped, the step's results are not to be used")
         raise KernelError(f"a kernel's bounded wait ran out (code {code}: 1 operand tiles never arrived, "
                           f"2 a stage was never released, 3 the accumulator never completed)")
+
+
+_WAIT_LIBRARIES = {"tc": "rllm_tc", "stream": "rllm_stream", "attn_tc": "rllm_attn_tc"}
+
+
+def set_wait_cycles(cycles: int = 0, libraries=None) -> None:
+    """Limit, in clock cycles, of every bounded wait (mbarrier polls) in the kernels of the TMA
+    libraries; 0 restores the default of about a second."""
+    for name in (libraries or _WAIT_LIBRARIES):
+        fn = getattr(_lib(name), _WAIT_LIBRARIES[name] + "_set_wait_cycles")
+        fn.argtypes = [c_longlong]
+        _check(fn(c_longlong(int(cycles))), f"set_wait_cycles({name})", own=False)
+
+
+def wait_probe(library: str, code: int, device="cuda:0") -> None:
+    """Launches the library's probe kernel: one thread waits, with the library's limit, on an
+    mbarrier at which nothing arrives, gives up, writes `code` to the error word and returns."""
+    fn = getattr(_lib(library), _WAIT_LIBRARIES[library] + "_wait_probe")
+    with torch.cuda.device(device):
+        _check(fn(_ptr(error_word(device)), c_int(code), _stream()), f"wait_probe({library})")
 
 
 def _tc_ok(a, w) -> bool:
@@ -470,7 +496,21 @@ def _prefer_tc_swap(m: int, n: int, k: int, swiglu: bool = False) -> bool:
     return True
 
 
-def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None):
+class Preceding:
+    """The product launched directly before another one: its activation, its weight matrix and
+    whether it was the fused gate/up product.  Handed to `linear` as `follow`, so that the second
+    product takes the kernel family of the first where the shape allows it."""
+    __slots__ = ("a", "w", "swiglu")
+
+    def __init__(self, a, w, swiglu=False):
+        self.a, self.w, self.swiglu = a, w, swiglu
+
+    def took_stream(self) -> bool:
+        return (self.a.dtype == torch.bfloat16
+                and _prefer_stream(self.a, self.w, self.w.shape[0], swiglu=self.swiglu))
+
+
+def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None, follow=None):
     """out (+)= a . w^T, choosing the kernel by element type and shape.
 
     float32 operands always take the plain CUDA-core product (the true 32-bit path).
@@ -489,9 +529,12 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None):
         if a.dtype != w.dtype:
             raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
         return gemm_plain(a, w, out, accumulate)
+    if follow is not None and stream is None and follow.took_stream():
+        stream = True
     if _skinny_ok(a, w):
-        # stream: the caller's wish for the kernel family (a product that follows a gemv_stream launch
-        # directly should be one too, whatever its size: see _prefer_stream), where the shape allows it
+        # stream: the wish for the kernel family (a product that follows a gemv_stream launch directly
+        # should be one too, whatever its size: a launch of short-lived CTAs right behind the persistent
+        # ones is slow), where the shape allows it; `follow` describes the product before and decides it
         want_stream = _prefer_stream(a, w, n) if stream is None else (stream and _stream_ok(a, w))
         if want_stream:
             return gemv_stream(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)

@@ -35,9 +35,10 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(s_addr(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false when about a second has passed (TC_WAIT_CYCLES) or another thread raised the
-// abort flag.
+// Bounded wait: false when the limit has passed (tc_wait_cycles: about a second unless the library's
+// rllm_set_wait_cycles was called) or another thread raised the abort flag.
 #define TC_WAIT_CYCLES (2000000000ll)
+static __constant__ long long tc_wait_cycles = TC_WAIT_CYCLES;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
     if (mbar_test_wait(bar, parity)) return true;
     if (mbar_try_wait(bar, parity)) return true;
@@ -46,7 +47,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 63u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > TC_WAIT_CYCLES) return false;
+            if (clock64() - t0 > tc_wait_cycles) return false;
         }
     }
 }
@@ -155,3 +156,28 @@ static inline int tmap_encode_bf16(CUtensorMap* map, const void* base, int rank,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : 30000 + (int)r;
 }
+
+// Every library that includes this header exports, under a name of its own, a setter for the limit
+// of its bounded waits (clock cycles; 0 or less restores the default) and a probe: one CTA whose
+// thread 0 waits, with that limit, on an mbarrier at which nothing ever arrives.  The wait runs
+// out, the thread writes `code` to *err and the kernel returns: the path every bounded wait of the
+// library takes when its partner never comes.
+__global__ void tc_wait_probe_kernel(int* err, int code) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait(&bar, 0, &abort_flag)) atomicExch(err, code);
+    }
+}
+#define TC_DEFINE_WAIT_CONTROLS(prefix)                                                              \
+    RLLM_API int prefix##_set_wait_cycles(long long cycles) {                                        \
+        const long long v = cycles > 0 ? cycles : TC_WAIT_CYCLES;                                    \
+        return (int)cudaMemcpyToSymbol(tc_wait_cycles, &v, sizeof(v));                               \
+    }                                                                                                \
+    RLLM_API int prefix##_wait_probe(int* err, int code, cudaStream_t stream) {                      \
+        tc_wait_probe_kernel<<<1, 32, 0, stream>>>(err, code);                                        \
+        return RLLM_LAUNCH_STATUS();                                                                 \
+    }

@@ -20,18 +20,16 @@ class Embedding(Part):
         self.vocab_size = int(params["vocab_size"])
         self.hidden_size = int(params["hidden_size"])
         self.weight = None
-        self.err = None
 
     def expected_tensors(self):
         return {self.prefix + "weight": ((self.vocab_size, self.hidden_size), "matrix")}
 
     def load(self, tensors):
         self.weight = self._to_device(tensors[self.prefix + "weight"])
-        self.err = torch.zeros(1, dtype=torch.int32, device=self.runtime.device)
 
     def forward(self, tokens):
         out = torch.empty((tokens.numel(), self.hidden_size), dtype=torch.float32, device=tokens.device)
-        return ops.embed(self.weight, tokens, out, self.err)
+        return ops.embed(self.weight, tokens, out, ops.error_word(tokens.device))
 
 
 @register_part("lm_head", "lm_head")

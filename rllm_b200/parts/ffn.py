@@ -37,11 +37,10 @@ class SwiGLU(FeedForward):
         n = h.shape[0]
         act = torch.empty((n, self.intermediate_size), dtype=self.runtime.dtype, device=h.device)
         ops.gate_up_swiglu(h, self.w_gate_up, act)
-        # the down product follows the gate/up product directly: it takes the streaming kernel when that
-        # one did (a launch of short-lived CTAs right behind the persistent ones is slow), else as it likes
-        same = True if (act.dtype == torch.bfloat16 and
-                        ops._prefer_stream(h, self.w_gate_up, 2 * self.intermediate_size, swiglu=True)) else None
+        # the down product runs directly behind the gate/up product: ops is told so and keeps both on
+        # one kernel family
+        before = ops.Preceding(h, self.w_gate_up, swiglu=True)
         if residual is not None:
-            ops.linear(act, self.w_down, out=residual, accumulate=True, stream=same)
+            ops.linear(act, self.w_down, out=residual, accumulate=True, follow=before)
             return None
-        return ops.linear(act, self.w_down, out_dtype=torch.float32, stream=same)
+        return ops.linear(act, self.w_down, out_dtype=torch.float32, follow=before)

@@ -38,7 +38,7 @@ TINY_G = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_si
 TINY = {"A": TINY_A, "B": TINY_B, "W": TINY_W, "F": TINY_F, "G": TINY_G}
 
 
-def make_model_dir(path, cfg: dict, seed: int, dtype=torch.float32, std=0.02, norm_std=0.1, scale_attn=1.0):
+def make_model_dir(path, cfg: dict, seed: int, dtype=torch.float32, std=0.02, norm_std=0.1):
     """Writes config.json and model.safetensors with the package's random-weights mode."""
     from rllm_b200.config import config_from_dict
     from rllm_b200.weights import write_random_model

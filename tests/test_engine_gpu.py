@@ -738,3 +738,38 @@ def test_a_kernel_that_gave_up_a_wait_fails_the_generation(dirs):
     assert not llm.engine.cache.requests
     assert llm.engine.cache.n_free_pages(0) == llm.engine.cache.n_blocks
     assert llm.generate([[4, 5, 6, 7]], max_tokens=100)[0] == want
+
+
+@pytest.mark.parametrize("library", ["tc", "stream", "attn_tc"])
+def test_a_bounded_wait_runs_out_and_the_kernel_returns(library):
+    """A wait of the TMA kernels' own kind (mbar_wait, the library's limit) on a barrier at which
+    nothing ever arrives: with the limit set to 100,000 cycles the thread gives up within a
+    millisecond, writes its code to the error word and the kernel returns; the entry points' check
+    raises and clears the word, and the device is as usable as before."""
+    import time
+    from rllm_b200.csrc import ops
+    ops.check_device_errors(DEV)
+    ops.set_wait_cycles(100_000, [library])
+    try:
+        torch.cuda.synchronize()
+        t0 = time.time()
+        ops.wait_probe(library, 2, DEV)
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 0.5                  # far below the default limit of about a second
+        with pytest.raises(ops.KernelError, match="bounded wait ran out .code 2"):
+            ops.check_device_errors(DEV)
+        ops.check_device_errors(DEV)                   # cleared
+    finally:
+        ops.set_wait_cycles(0, [library])
+    # the library's product kernels still run, with the default limit back
+    a = torch.randn(24, 1024, device=DEV).bfloat16()
+    w = torch.randn(2048, 1024, device=DEV).bfloat16()
+    out = torch.empty(24, 2048, device=DEV)
+    if library == "tc":
+        ops.skinny_gemm_tc(a, w, out)
+    elif library == "stream":
+        ops.gemv_stream(a[:8], w, out[:8])
+        out, a = out[:8], a[:8]
+    if library != "attn_tc":
+        assert rel_err(out.cpu(), a.float().cpu() @ w.float().cpu().t()) < 1e-5
+    ops.check_device_errors(DEV)

@@ -5,8 +5,10 @@ loop that owns all GPU memory in its own pools and forbids cudaMalloc (which als
 stream of the device), or a C/C++ program that links the kernels without torch and so has no
 caching allocator.  For them `rllm_paged_flash_decode_static` keeps the split-key partials in a
 fixed array inside the library.  This test checks that it gives the same output as the regular
-entry point (which takes caller-allocated scratch), on two calls in a row that share the array,
-and that it refuses a problem larger than the array with a clear message.
+entry point (which takes caller-allocated scratch) and as the plain implementation of attention,
+on calls in a row that share the array (both decode kernels: tiles of 8 and of 16 rows), that the
+device's free memory does not move across its calls (it allocates nothing), and that it refuses a
+problem larger than the array with a clear message.
 
 The file is named to be collected last: a run that stops at the first failure has then already
 run every other test.
@@ -44,8 +46,8 @@ def make_case(seed, hd, H, K, bs, lens):
     return {k: v.to(DEV) for k, v in dict(q=q, kc=kc, vc=vc, table=table, pos=pos, cu=cu, tiles=tiles).items()}
 
 
-def call_static(lib, c, H, K, hd, bs, n_splits, split_keys=128):
-    out = torch.full_like(c["q"], float("nan"))
+def call_static(lib, c, H, K, hd, bs, n_splits, split_keys=128, out=None):
+    out = torch.full_like(c["q"], float("nan")) if out is None else out
     g = H // K
     p = lambda t: c_void_p(t.data_ptr())
     rc = lib.rllm_paged_flash_decode_static(
@@ -67,6 +69,22 @@ def call_regular(c, H, K, hd, bs, n_splits):
     return out
 
 
+def plain_decode_attention(c, H, K, hd, bs, lens):
+    """The plain implementation (whole sequences, no pages) on the keys and values gathered from
+    the pages of each request; the query of the last position is the one the kernels got."""
+    import plain_impl
+    q, kc, vc, table = (c[k].float().cpu() for k in ("q", "kc", "vc", "table"))
+    out = torch.zeros(len(lens), H * hd)
+    for r, L in enumerate(lens):
+        pages = [int(table[r, p // bs]) for p in range(L)]
+        k = torch.stack([kc[pages[p], :, p % bs, :] for p in range(L)])        # [L, K, hd]
+        v = torch.stack([vc[pages[p], :, p % bs, :] for p in range(L)])
+        qs = torch.zeros(L, H, hd)
+        qs[L - 1] = q[r].view(H, hd)
+        out[r] = plain_impl.attention(qs, k, v, 1.0 / math.sqrt(hd))[L - 1].reshape(-1)
+    return out
+
+
 def test_static_scratch_entry_point_matches_regular_one():
     from rllm_b200.csrc import build
     lib = ctypes.CDLL(str(build.build("attn")))
@@ -75,7 +93,9 @@ def test_static_scratch_entry_point_matches_regular_one():
 
     # two calls in a row on the shared array: a large problem, then a smaller one with other sizes,
     # so that anything read from the first call's leftovers would show
-    cases = [(31, 128, 8, 2, 16, [700, 129, 1, 333, 512]), (32, 64, 6, 2, 8, [90, 260, 17])]
+    # (the third has 16 query heads per key/value head: the decode kernel with 16-row tiles)
+    cases = [(31, 128, 8, 2, 16, [700, 129, 1, 333, 512]), (32, 64, 6, 2, 8, [90, 260, 17]),
+             (34, 128, 16, 1, 32, [301, 64, 150])]
     for seed, hd, H, K, bs, lens in cases:
         c = make_case(seed, hd, H, K, bs, lens)
         n_splits = -(-max(lens) // 128)
@@ -90,6 +110,20 @@ def test_static_scratch_entry_point_matches_regular_one():
         err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
         assert err <= 1.5e-2
         assert torch.equal(got, want)
+        # and against the plain implementation, within the tolerance of the attention kernel tests
+        plain = plain_decode_attention(c, H, K, hd, bs, lens)
+        assert float((got.float().cpu() - plain).abs().max() / plain.abs().max()) <= 1.5e-2
+        # it allocates nothing: across further calls (the first one looked the array's address up) into an
+        # output that exists already, the device's free memory stays where it was
+        again = torch.full_like(c["q"], float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        for _ in range(3):
+            rc, _ = call_static(lib, c, H, K, hd, bs, n_splits, out=again)
+            assert rc == 0
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.equal(again, want)
 
     # larger than the array: refused with a message, nothing launched
     c = make_case(33, 128, 8, 8, 16, [40] * 64)
