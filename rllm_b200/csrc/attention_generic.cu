@@ -20,8 +20,8 @@
 
 template <typename TQ, typename TC, typename TO>
 __global__ void __launch_bounds__(ATT_THREADS)
-paged_attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache,
-                               const TC* __restrict__ v_cache, TO* __restrict__ out,
+paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
+                               const TC* v_cache, TO* out,
                                const int* __restrict__ positions, const int* __restrict__ seq_ids,
                                const int* __restrict__ block_table, int table_stride, int H, int K,
                                int hd, int bs, float scale, int window) {

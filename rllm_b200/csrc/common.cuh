@@ -68,6 +68,8 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // depends on have completed and their writes are visible (a no-op for an ordinary launch);
 // `pdl_launch_dependents` lets the next kernel of the stream begin to launch early.  A kernel
 // launched with the attribute may only touch memory that earlier kernels write after its wait.
+// Pointers to such memory carry no __restrict__ and are never read with __ldg: a read-only load
+// (ld.global.nc) is "invariant" to the compiler, which may move it above the wait.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" :::); }
 

@@ -42,7 +42,7 @@ RLLM_API int rllm_embed(const void* table, int table_dtype, const int* tokens, f
 // if write_x the sum is stored back to x[src] (the residual stream);
 // out[r] = v * (1/sqrt(mean(v^2) + eps)) * w.   x is the float32 residual stream.
 template <typename TD, typename TO>
-__global__ void add_rms_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+__global__ void add_rms_norm_kernel(float* x, const TD* delta,
                                     const int* __restrict__ rows, const float* __restrict__ w,
                                     TO* __restrict__ out, int d, float eps, int write_x) {
     __shared__ float red[33];
@@ -84,7 +84,7 @@ template <> __device__ __forceinline__ void store2<bf16>(bf16* p, float a, float
 // lives in registers between the sum of squares and the scaling (float4 loads, 256 threads a row).
 template <typename TD, typename TO, int NV>
 __global__ void __launch_bounds__(256)
-add_rms_norm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, const int* __restrict__ rows,
+add_rms_norm_vec_kernel(float* x, const TD* delta, const int* __restrict__ rows,
                         const float* __restrict__ w, TO* __restrict__ out, int d, float eps, int write_x) {
     __shared__ float red[33];
     pdl_launch_dependents();          // as above
@@ -156,7 +156,7 @@ RLLM_API int rllm_add_rms_norm(float* x, const void* delta, int delta_dtype, con
 
 // Plain residual add x += delta (used after the last layer when no norm follows).
 template <typename TD>
-__global__ void add_inplace_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+__global__ void add_inplace_kernel(float* x, const TD* delta, size_t n) {
     pdl_wait();
     pdl_launch_dependents();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -175,7 +175,7 @@ RLLM_API int rllm_add_inplace(float* x, const void* delta, int delta_dtype, long
 // ------------------------------------------------------------------ SwiGLU
 // in [n, 2F] holds gate in columns [0,F) and up in [F,2F); out[t,j] = gate/(1+exp(-gate)) * up.
 template <typename TI, typename TO>
-__global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out, int F, size_t total) {
+__global__ void silu_mul_kernel(const TI* in, TO* out, int F, size_t total) {
     pdl_wait();
     pdl_launch_dependents();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -187,7 +187,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ in, TO* __restrict__ out,
     out[i] = from_f<TO>(g / (1.0f + expf(-g)) * u);
 }
 template <typename TI, typename TO>
-__global__ void silu_mul_vec2_kernel(const TI* __restrict__ in, TO* __restrict__ out, int F, size_t total2) {
+__global__ void silu_mul_vec2_kernel(const TI* in, TO* out, int F, size_t total2) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t i2 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // pairs of outputs
@@ -236,7 +236,7 @@ RLLM_API int rllm_silu_mul(const void* in, int in_dtype, void* out, int out_dtyp
 // stores are 8 and 4 bytes wide.
 template <typename TI, typename TO, typename TC>
 __global__ void __launch_bounds__(256)
-qk_norm_rope_store_token_kernel(const TI* __restrict__ qkv, const float* __restrict__ q_norm_w,
+qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_w,
                                 const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
                                 const int* __restrict__ positions, const int* __restrict__ slots,
                                 TO* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache, int H,

@@ -19,7 +19,7 @@
 
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
-gemm_plain_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, int m,
+gemm_plain_kernel(const TA* A, const TW* __restrict__ W, TC* C, int m,
                   int n, int k, int lda, int ldw, int ldc, int accumulate) {
     __shared__ float As[TK][TM + 1];
     __shared__ float Ws[TK][TN + 1];

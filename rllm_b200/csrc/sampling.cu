@@ -54,7 +54,7 @@ __device__ KeyIdx block_best(KeyIdx v, KeyIdx* sh) {
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_rows_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
+sample_rows_kernel(const float* logits, long long row_stride, int vocab,
                    const float* __restrict__ temperature, const int* __restrict__ top_k,
                    const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
                    const unsigned long long* __restrict__ counter, int* __restrict__ out) {

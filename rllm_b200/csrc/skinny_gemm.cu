@@ -37,8 +37,16 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+// The batch rows are written by the kernel before this one, which may still run when this kernel
+// starts (programmatic dependent launch).  They are therefore read with an ordinary, volatile load
+// that stays behind griddepcontrol.wait: a read-only load (__ldg, or a const __restrict__ pointer,
+// which the compiler turns into ld.global.nc) is "invariant" to the compiler, which may move it
+// above the wait, where it sees the values of the step before.
 __device__ __forceinline__ uint4 ldg_cached(const void* p) {
-    return __ldg(reinterpret_cast<const uint4*>(p));
+    uint4 v;
+    asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
 }
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
@@ -47,7 +55,7 @@ enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 // NT: batch columns / 8.  RT: weight row tiles per CTA (2 for SwiGLU).  U: k steps fetched ahead.
 template <int NT, int EPI, typename TC, int U>
 __global__ void __launch_bounds__(SG_THREADS)
-skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, TC* __restrict__ C, int m,
+skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* X, TC* C, int m,
                    int n, int k, int ldw, int ldx, int ldc, int up_row_offset) {
     constexpr int RT = (EPI == EPI_SWIGLU) ? 2 : 1;
     extern __shared__ float red[];          // [SG_WARPS][RT][16][NT*8]
