@@ -65,6 +65,29 @@ struct SvMaps {
     CUtensorMap x;
 };
 
+// An RMSNorm that stands between two products of a decode step, without a kernel of its own:
+//
+//   the product BEFORE the norm (accumulating into the float32 residual stream C) also writes, for
+//   every element it produces, xw = bfloat16(c * norm_weight[column]) and adds c^2 to a sum of
+//   squares per batch row; every CTA stores its sums in ssq_out[CTA][16] (fixed order inside the CTA);
+//
+//   the product AFTER the norm takes xw as its X operand, adds the n_parts partial sums of each batch
+//   row in a fixed order, and multiplies its result rows by r = 1 / sqrt(sum / d + eps) before they
+//   are stored or go through SwiGLU:  (x * w * r) . W^T  =  r * ((x * w) . W^T).
+//
+// The sums do not depend on the batch (a row's partials come from its own elements only).
+struct SvNorm {
+    // producer side (null: none)
+    bf16* xw_out;
+    const float* w_next;
+    float* ssq_out;
+    int ld_xw;
+    // consumer side (null: none)
+    const float* ssq_in;
+    int n_parts;
+    float inv_d, eps;
+};
+
 // The share of CTA `c` of `G`: granules [first, last).
 __device__ __forceinline__ void sv_share(int n_gran, int c, int G, int& first, int& last) {
     first = (int)(((long long)n_gran * c) / G);
@@ -83,7 +106,7 @@ __device__ __forceinline__ void sv_share(int n_gran, int c, int G, int& first, i
 template <int NT, int EPI, typename TC, int ATOMS, int STAGES>
 __global__ void __launch_bounds__(SV_THREADS)
 gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int ldc, int m, int n, int K,
-                   int up_row_offset, int* err) {
+                   int up_row_offset, int* err, const SvNorm nm) {
     constexpr int ROWS = 128 / ATOMS;
     constexpr int SLOTS = ROWS / 16;
     constexpr int BK = ATOMS * SV_ATOM;
@@ -99,6 +122,7 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
     __shared__ __align__(8) uint64_t full_bar[STAGES];
     __shared__ __align__(8) uint64_t empty_bar[STAGES];
     __shared__ volatile int abort_flag;
+    __shared__ float norm_red[8][16];         // partial sums of squares: [segment or warp][batch row]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_gran = (n + SV_GRAN - 1) / SV_GRAN;
@@ -192,8 +216,26 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
     const int b_row = lane & 7;
     const uint32_t b_off = (uint32_t)(b_row * 128 + (((2 * warp + ((lane >> 3) & 1)) ^ b_row) << 4));
 
+    // The rows' 1/rms for a deferred norm: thread (segment = tid / 16, b = tid % 16) adds every eighth
+    // partial sum of batch row b into shared memory here, while the first stages arrive; the eight
+    // segment sums are added in order at the end of the first chunk, behind that chunk's barrier.
+    float rscale[NT][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) rscale[j][0] = rscale[j][1] = 1.f;
+    bool waited = false, scaled = nm.ssq_in == nullptr;
+    if (nm.ssq_in) {
+        pdl_wait();                       // the sums come from the kernel before
+        waited = true;
+        const int b = tid & 15, seg = tid >> 4;
+        float ssum = 0.f;
+        for (int p = seg; p < nm.n_parts; p += 8) ssum += nm.ssq_in[(size_t)p * 16 + b];
+        norm_red[seg][b] = ssum;
+    }
+    float ssq[NT][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) ssq[j][0] = ssq[j][1] = 0.f;
+
     float acc[SLOTS][NT][4];
-    bool waited = false;
     int it = 0;
     for (int chunk = 0; chunk < n_chunks; ++chunk) {
         const int g0 = g_first + chunk * GRAN_PER_CHUNK;
@@ -230,11 +272,16 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
         // while the chunk streams (read at the chunk's end they cost a round trip to L2 each, one
         // after the other, at the end of the kernel).
         float c_old[NT][4];
+        float wn[2] = {0.f, 0.f};         // norm weights of this thread's two rows (deferred norm)
         if (EPI == SV_EPI_ACCUM) {
             if (!waited) { pdl_wait(); waited = true; }      // C belongs to the kernels before until here
             if (warp < n_slots) {
                 const int row_end = min(n, g_last * SV_GRAN);
                 const int r_lo = (g0 + 2 * warp) * SV_GRAN + g;
+                if (nm.w_next) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) wn[h] = r_lo + 8 * h < row_end ? nm.w_next[r_lo + 8 * h] : 0.f;
+                }
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -283,6 +330,18 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
                     make_float4(acc[sl][j][0], acc[sl][j][1], acc[sl][j][2], acc[sl][j][3]);
         consumer_sync();               // every consumer warp comes here, also after a wait that ran out
         if (abort_flag) break;
+        if (!scaled) {
+            scaled = true;
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    float tot = 0.f;
+#pragma unroll
+                    for (int sg = 0; sg < 8; ++sg) tot += norm_red[sg][8 * j + 2 * t + e];
+                    rscale[j][e] = 1.0f / sqrtf(tot * nm.inv_d + nm.eps);
+                }
+        }
         if (warp >= n_slots) continue;
         float v[NT][4];
 #pragma unroll
@@ -293,7 +352,8 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
                 const float4 p = *reinterpret_cast<const float4*>(buf + ((((size_t)src * SLOTS + warp) * NT + j) * 32 + lane) * 4);
                 sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
             }
-            v[j][0] = sum.x; v[j][1] = sum.y; v[j][2] = sum.z; v[j][3] = sum.w;
+            v[j][0] = sum.x * rscale[j][0]; v[j][1] = sum.y * rscale[j][1];
+            v[j][2] = sum.z * rscale[j][0]; v[j][3] = sum.w * rscale[j][1];
         }
         if (!waited) { pdl_wait(); waited = true; }      // C belongs to the kernels before until here
         // rows of this lane in slot `warp`: row g (sums 0, 1) and row g + 8 (sums 2, 3); batch columns 8j + 2t, + 1
@@ -326,11 +386,37 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
                         if (b < m) {
                             TC* c = C + (size_t)b * ldc + row;
                             const float val = v[j][2 * h + e];
-                            if (EPI == SV_EPI_ACCUM) *c = from_f<TC>(c_old[j][2 * h + e] + val);
-                            else *c = from_f<TC>(val);
+                            if (EPI == SV_EPI_ACCUM) {
+                                const float sum = c_old[j][2 * h + e] + val;
+                                *c = from_f<TC>(sum);
+                                if (nm.xw_out) {
+                                    nm.xw_out[(size_t)b * nm.ld_xw + row] = from_f<bf16>(sum * wn[h]);
+                                    ssq[j][e] += sum * sum;
+                                }
+                            } else *c = from_f<TC>(val);
                         }
                     }
             }
+        }
+    }
+    if (EPI == SV_EPI_ACCUM && nm.ssq_out) {
+        // this thread's sums -> the 8 lanes with equal t -> the four warps, in warp order
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float sq = ssq[j][e];
+                sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+                if (g == 0) norm_red[warp][8 * j + 2 * t + e] = sq;
+                else if (NT == 1 && g == 1) norm_red[warp][8 + 2 * t + e] = 0.f;
+            }
+        consumer_sync();
+        if (tid < 16) {
+            if (!waited) pdl_wait();
+            nm.ssq_out[(size_t)blockIdx.x * 16 + tid] =
+                norm_red[0][tid] + norm_red[1][tid] + norm_red[2][tid] + norm_red[3][tid];
         }
     }
 }
@@ -349,11 +435,12 @@ struct SvProblem {
     void* C;
     int m, n, K, ldw, ldx, ldc, up, grid, nt, w_rows, stages;
     int* err;
+    SvNorm nm;
 };
 
 template <int NT, int EPI, typename TC, int ATOMS, int STAGES>
 static int launch_sv_stages(const SvMaps& maps, void* C, int ldc, int m, int n, int K, int up, int grid, int* err,
-                            cudaStream_t stream) {
+                            const SvNorm& nm, cudaStream_t stream) {
     constexpr int SLOTS = 128 / ATOMS / 16;
     constexpr size_t smem = (size_t)STAGES * (SV_W_BYTES + ATOMS * NT * SV_GRAN_BYTES) +
                             2 * (SV_WARPS * SLOTS * NT * 32 * 4) * sizeof(float) + 1024;
@@ -364,7 +451,7 @@ static int launch_sv_stages(const SvMaps& maps, void* C, int ldc, int m, int n, 
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    return rllm_launch(kern, dim3(grid), dim3(SV_THREADS), smem, stream, maps, (TC*)C, ldc, m, n, K, up, err);
+    return rllm_launch(kern, dim3(grid), dim3(SV_THREADS), smem, stream, maps, (TC*)C, ldc, m, n, K, up, err, nm);
 }
 
 template <int NT, int EPI, typename TC, int ATOMS>
@@ -377,10 +464,10 @@ static int launch_sv_atoms(const SvProblem& p, cudaStream_t stream) {
     int st = sv_tmap(&maps.x, p.X, p.m, p.K, p.ldx, 8 * NT, ATOMS);
     if (st) return st;
     if (p.stages == 10 && ATOMS * NT <= 4)           // ten stages of the widest shapes do not fit; they get five
-        return launch_sv_stages<NT, EPI, TC, ATOMS, 10>(maps, p.C, p.ldc, p.m, p.n, p.K, p.up, p.grid, p.err, stream);
+        return launch_sv_stages<NT, EPI, TC, ATOMS, 10>(maps, p.C, p.ldc, p.m, p.n, p.K, p.up, p.grid, p.err, p.nm, stream);
     if (p.stages == 3)
-        return launch_sv_stages<NT, EPI, TC, ATOMS, 3>(maps, p.C, p.ldc, p.m, p.n, p.K, p.up, p.grid, p.err, stream);
-    return launch_sv_stages<NT, EPI, TC, ATOMS, 5>(maps, p.C, p.ldc, p.m, p.n, p.K, p.up, p.grid, p.err, stream);
+        return launch_sv_stages<NT, EPI, TC, ATOMS, 3>(maps, p.C, p.ldc, p.m, p.n, p.K, p.up, p.grid, p.err, p.nm, stream);
+    return launch_sv_stages<NT, EPI, TC, ATOMS, 5>(maps, p.C, p.ldc, p.m, p.n, p.K, p.up, p.grid, p.err, p.nm, stream);
 }
 
 // The stage shape follows the share of a CTA: few rows, more k-columns per stage.
@@ -399,8 +486,14 @@ static int launch_sv(const SvProblem& p, cudaStream_t stream) {
 // (3 CTAs of 3 stages, or 2 of 5, fit one SM; 10 falls back to 5 where it does not fit).  Requires k % 64 == 0, ldw % 8 == 0, ldx % 8 == 0 and
 // 16-byte aligned W and X; returns cudaErrorInvalidValue otherwise.  err: device int that receives
 // a code when a bounded wait runs out.
+// Deferred norm (see SvNorm), both optional.  Producing side, accumulate epilogue only: xw_out [m, ld_xw]
+// bfloat16, w_next [n] float32, ssq_out [CTAs of this launch][16] float32 (the launcher returns the
+// number of CTAs in *n_parts_out).  Consuming side, store and SwiGLU epilogues: ssq_in [n_parts_in][16],
+// norm_d the row length the sums run over, norm_eps.
 RLLM_API int rllm_gemv_stream(const void* W, const void* X, void* C, int c_dtype, int m, int n, int K, int ldw,
                               int ldx, int ldc, int epilogue, int up_row_offset, int grid, int stages, int* err,
+                              void* xw_out, int ld_xw, const float* w_next, float* ssq_out, int* n_parts_out,
+                              const float* ssq_in, int n_parts_in, int norm_d, float norm_eps,
                               cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 16 || K <= 0 || (K % SV_ATOM) || (ldw & 7) || (ldx & 7) || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) ||
@@ -418,6 +511,16 @@ RLLM_API int rllm_gemv_stream(const void* W, const void* X, void* C, int c_dtype
     p.W = W; p.X = X; p.C = C; p.m = m; p.n = n; p.K = K; p.ldw = ldw; p.ldx = ldx; p.ldc = ldc;
     p.up = up_row_offset; p.grid = grid; p.stages = stages; p.nt = m <= 8 ? 1 : 2; p.err = err;
     p.w_rows = epilogue == SV_EPI_SWIGLU ? up_row_offset + n : n;
+    p.nm = SvNorm{};
+    if (xw_out || ssq_out || w_next) {
+        if (epilogue != SV_EPI_ACCUM || !xw_out || !ssq_out || !w_next) return (int)cudaErrorInvalidValue;
+        p.nm.xw_out = (bf16*)xw_out; p.nm.w_next = w_next; p.nm.ssq_out = ssq_out; p.nm.ld_xw = ld_xw;
+        if (n_parts_out) *n_parts_out = grid;
+    }
+    if (ssq_in) {
+        if (epilogue == SV_EPI_ACCUM || n_parts_in <= 0 || norm_d <= 0) return (int)cudaErrorInvalidValue;
+        p.nm.ssq_in = ssq_in; p.nm.n_parts = n_parts_in; p.nm.inv_d = 1.0f / (float)norm_d; p.nm.eps = norm_eps;
+    }
     const int nt = p.nt;
 #define SV(NT_, EPI_, TC_) return launch_sv<NT_, EPI_, TC_>(p, stream)
     if (epilogue == SV_EPI_STORE) {

@@ -343,10 +343,11 @@ def wait_probe(library: str, code: int, device="cuda:0") -> None:
         _check(fn(_ptr(error_word(device)), c_int(code), _stream()), f"wait_probe({library})")
 
 
-def _tc_ok(a, w) -> bool:
+def _tc_ok(a, w, _meta=False) -> bool:
+    """_meta: `a` stands for a freshly allocated activation (contiguous, aligned)."""
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
-            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+            and (_meta or a.data_ptr() % 16 == 0) and w.data_ptr() % 16 == 0)
 
 
 def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
@@ -440,10 +441,41 @@ def stream_plan(n: int, k: int, swiglu: bool = False, n_sm: int = 148):
     return per_sm * n_sm, 3
 
 
-def gemv_stream(a, w, out, epilogue=EPI_STORE, up_row_offset=0, grid=None, stages=None):
+class NormedRows:
+    """Rows of the residual stream on their way through an RMSNorm whose division has not happened
+    yet: `xw` = bfloat16(x * norm weight) [m, d] and, per row, `n_parts` partial sums of squares of x
+    (`ssq` [n_parts, 16] float32, row b in column b).  The product that takes them as its input
+    multiplies its result rows by 1 / sqrt(sum / d + eps):  (x w r) . W^T = r ((x w) . W^T).
+    Made by an accumulating gemv_stream launch (`then_norm`), taken by `linear` and
+    `gate_up_swiglu` in place of a tensor."""
+    __slots__ = ("xw", "ssq", "n_parts", "d", "eps")
+
+    def __init__(self, xw, ssq, n_parts, d, eps):
+        self.xw, self.ssq, self.n_parts, self.d, self.eps = xw, ssq, n_parts, d, eps
+
+    @property
+    def shape(self):
+        return self.xw.shape
+
+    @property
+    def dtype(self):
+        return self.xw.dtype
+
+    @property
+    def device(self):
+        return self.xw.device
+
+
+def gemv_stream(a, w, out, epilogue=EPI_STORE, up_row_offset=0, grid=None, stages=None, then_norm=None):
     """out (+)= a . w^T for at most 16 rows of `a`: persistent CTAs stream their shares of w's rows
     through TMA rings (mma.sync consumers).  Epilogues as skinny_gemm.  grid, stages: number of CTAs
-    and ring depth (3, 5 or 10); by default from stream_plan."""
+    and ring depth (3, 5 or 10); by default from stream_plan.
+    `a` may be NormedRows (store and SwiGLU epilogues): the result rows are divided by the rows' rms.
+    then_norm = (norm weight [n] float32, eps), accumulate epilogue only: the launch also prepares
+    the RMSNorm of the sums it writes and returns them as NormedRows (else it returns `out`)."""
+    scale = a if isinstance(a, NormedRows) else None
+    if scale is not None:
+        a = scale.xw
     _need_cuda(a, w, out)
     m, k = a.shape
     n = out.shape[1]
@@ -455,12 +487,28 @@ def gemv_stream(a, w, out, epilogue=EPI_STORE, up_row_offset=0, grid=None, stage
         assert w.shape[0] == n
     assert out.stride(1) == 1 and w.shape[1] == k
     plan = stream_plan(n, k, epilogue == EPI_SWIGLU, sm_count(a.device))
+    n_ctas = plan[0] if grid is None else grid
+    xw = w_next = ssq_out = None
+    n_parts = c_int(0)
+    if then_norm is not None:
+        if epilogue != EPI_ACCUM or scale is not None:
+            raise KernelError("gemv_stream: then_norm goes with the accumulate epilogue")
+        w_next, eps_next = then_norm
+        assert w_next.dtype == torch.float32 and w_next.numel() == n and w_next.is_contiguous()
+        xw = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+        ssq_out = torch.empty((max(n_ctas, 1), 16), dtype=torch.float32, device=a.device)
+    if scale is not None and epilogue == EPI_ACCUM:
+        raise KernelError("gemv_stream: rows with a deferred norm go with the store and SwiGLU epilogues")
     st = _lib("stream").rllm_gemv_stream(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
         c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
-        c_int(plan[0] if grid is None else grid), c_int(plan[1] if stages is None else stages),
-        _ptr(error_word(a.device)), _stream())
+        c_int(n_ctas), c_int(plan[1] if stages is None else stages),
+        _ptr(error_word(a.device)), _ptr(xw), c_int(n), _ptr(w_next), _ptr(ssq_out), ctypes.byref(n_parts),
+        _ptr(scale.ssq if scale is not None else None), c_int(scale.n_parts if scale is not None else 0),
+        c_int(scale.d if scale is not None else 0), c_float(scale.eps if scale is not None else 0.0), _stream())
     _check(st, "gemv_stream")
+    if then_norm is not None:
+        return NormedRows(xw, ssq_out, n_parts.value, n, float(eps_next))
     return out
 
 
@@ -468,16 +516,16 @@ USE_STREAM = True
 STREAM_MIN_WEIGHTS = 1 << 23      # below 16 MB of weights the short-lived CTAs of skinny_gemm start faster
 
 
-def _stream_ok(a, w) -> bool:
-    return USE_STREAM and a.shape[0] <= 8 and a.shape[1] % 64 == 0 and _tc_ok(a, w)
+def _stream_ok(a, w, _meta=False) -> bool:
+    return USE_STREAM and a.shape[0] <= 8 and a.shape[1] % 64 == 0 and _tc_ok(a, w, _meta)
 
 
-def _prefer_stream(a, w, n: int, swiglu: bool = False) -> bool:
+def _prefer_stream(a, w, n: int, swiglu: bool = False, _meta=False) -> bool:
     """gemv_stream takes up to 8 rows always, and 9 to 16 rows for the layer's plain products; with
     9 to 16 rows the gate/up product and the LM head are faster on the tcgen05 kernel (measured
     inside the decode step at batch 9, 12 and 16: 3 to 7 % of the step)."""
     m, k = a.shape
-    if not USE_STREAM or k % 64 or n * k < STREAM_MIN_WEIGHTS or not _tc_ok(a, w):
+    if not USE_STREAM or k % 64 or n * k < STREAM_MIN_WEIGHTS or not _tc_ok(a, w, _meta):
         return False
     return m <= 8 or (m <= STREAM_MAX_ROWS and not swiglu and n * k < (1 << 27))
 
@@ -510,7 +558,25 @@ class Preceding:
                 and _prefer_stream(self.a, self.w, self.w.shape[0], swiglu=self.swiglu))
 
 
-def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None, follow=None):
+def defers_norm(m: int, w_before, w_after, swiglu_after: bool, w_lead=None, swiglu_lead: bool = False) -> bool:
+    """Whether the RMSNorm between the accumulating product with `w_before` and the product with
+    `w_after` (the fused gate/up product if swiglu_after) can do without a kernel of its own at `m`
+    rows: both products then run on gemv_stream, the first preparing the norm (`then_norm`), the
+    second dividing by the rms (NormedRows).  `w_lead`: the matrix of the product that runs directly
+    before the first one, if any (the first follows its kernel family)."""
+    if w_before.dtype != torch.bfloat16 or w_after.dtype != torch.bfloat16 or not 0 < m <= 8:
+        return False
+
+    def probe(w):
+        return torch.empty((m, w.shape[1]), dtype=torch.bfloat16, device="meta")
+    first = _prefer_stream(probe(w_before), w_before, w_before.shape[0], _meta=True)
+    if not first and w_lead is not None:
+        first = (_prefer_stream(probe(w_lead), w_lead, w_lead.shape[0], swiglu=swiglu_lead, _meta=True)
+                 and _stream_ok(probe(w_before), w_before, _meta=True))
+    return first and _prefer_stream(probe(w_after), w_after, w_after.shape[0], swiglu=swiglu_after, _meta=True)
+
+
+def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None, follow=None, then_norm=None):
     """out (+)= a . w^T, choosing the kernel by element type and shape.
 
     float32 operands always take the plain CUDA-core product (the true 32-bit path).
@@ -525,6 +591,10 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None, follow
         out = torch.empty((m, n), dtype=out_dtype or a.dtype, device=a.device)
     if m == 0:
         return out
+    if isinstance(a, NormedRows) or then_norm is not None:
+        # decided beforehand with defers_norm: both sides of a deferred norm run on gemv_stream
+        r = gemv_stream(a, w, out, EPI_ACCUM if accumulate else EPI_STORE, then_norm=then_norm)
+        return r
     if a.dtype == torch.float32 or w.dtype == torch.float32:
         if a.dtype != w.dtype:
             raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
@@ -555,6 +625,8 @@ def gate_up_swiglu(h, w_gate_up, out):
     float32 and odd shapes: a product followed by the activation kernel."""
     m = h.shape[0]
     F = out.shape[1]
+    if isinstance(h, NormedRows):
+        return gemv_stream(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
     if _skinny_ok(h, w_gate_up):
         if _prefer_stream(h, w_gate_up, 2 * F, swiglu=True):
             return gemv_stream(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)

@@ -76,7 +76,12 @@ class DecoderModel:
         x = self.embedding.forward(ctx.tokens)
         pending = None
         for i, e in enumerate(self.run_order):
-            pending = self.blocks[e.layer].forward(x, pending, ctx, views[i])
+            block = self.blocks[e.layer]
+            nxt = self.blocks[self.run_order[i + 1].layer] if i + 1 < len(self.run_order) else None
+            if getattr(block, "DEFERS_NORM", False) and getattr(nxt, "DEFERS_NORM", False):
+                pending = block.forward(x, pending, ctx, views[i], next_entry=nxt.entry())
+            else:
+                pending = block.forward(x, pending, ctx, views[i])
         if ctx.logit_rows is None or ctx.logit_rows.numel() == 0:
             return None
         h = self.final_norm.forward(x, pending, rows=ctx.logit_rows, write_x=False)

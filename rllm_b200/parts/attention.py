@@ -58,11 +58,21 @@ class Attention(Mixer):
             self.q_norm_w = self._to_device(tensors[p + "q_norm.weight"], torch.float32)
             self.k_norm_w = self._to_device(tensors[p + "k_norm.weight"], torch.float32)
 
-    def forward(self, h, ctx, cache, position, residual=None):
+    # A norm between two products may go without a kernel of its own (ops.NormedRows): the block asks the
+    # parts on both sides for the matrices of their last and first product.
+    def first_product(self):
+        return self.w_qkv, False
+
+    def last_product(self):
+        return self.w_o, None, False
+
+    def forward(self, h, ctx, cache, position, residual=None, then_norm=None):
+        """`h` may be ops.NormedRows; then_norm = (weight, eps): the output product also prepares the
+        norm that follows and the rows come back as ops.NormedRows (needs `residual`)."""
         n = h.shape[0]
         dt = self.runtime.dtype
         qkv = ops.linear(h, self.w_qkv, out_dtype=torch.float32)
-        q = torch.empty((n, self.H * self.hd), dtype=dt, device=h.device)
+        q = torch.empty((n, self.H * self.hd), dtype=dt, device=qkv.device)
         ops.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w,
                                position.table() if position is not None else None, ctx.positions,
                                cache.slots, q, cache.k, cache.v, self.H, self.K, self.hd,
@@ -71,6 +81,8 @@ class Attention(Mixer):
         ops.paged_attention(q, cache.k, cache.v, attn, ctx, cache.block_table, self.H, self.K, self.hd,
                             cache.block_size, self.scale, self.window)
         if residual is not None:
+            if then_norm is not None:
+                return ops.linear(attn, self.w_o, out=residual, accumulate=True, then_norm=then_norm)
             ops.linear(attn, self.w_o, out=residual, accumulate=True)
             return None
         return ops.linear(attn, self.w_o, out_dtype=torch.float32)

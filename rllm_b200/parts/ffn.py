@@ -33,14 +33,23 @@ class SwiGLU(FeedForward):
         self.w_gate_up = self._to_device(torch.cat([g.to(self.runtime.dtype), u.to(self.runtime.dtype)], 0))
         self.w_down = self._to_device(tensors[self.prefix + "down_proj.weight"])
 
-    def forward(self, h, ctx=None, residual=None):
+    def first_product(self):
+        return self.w_gate_up, True
+
+    def last_product(self):
+        return self.w_down, self.w_gate_up, True          # the down product follows the gate/up kernel
+
+    def forward(self, h, ctx=None, residual=None, then_norm=None):
+        """`h` may be ops.NormedRows; then_norm as for the attention part."""
         n = h.shape[0]
         act = torch.empty((n, self.intermediate_size), dtype=self.runtime.dtype, device=h.device)
         ops.gate_up_swiglu(h, self.w_gate_up, act)
         # the down product runs directly behind the gate/up product: ops is told so and keeps both on
         # one kernel family
-        before = ops.Preceding(h, self.w_gate_up, swiglu=True)
+        before = ops.Preceding(h.xw if isinstance(h, ops.NormedRows) else h, self.w_gate_up, swiglu=True)
         if residual is not None:
+            if then_norm is not None:
+                return ops.linear(act, self.w_down, out=residual, accumulate=True, then_norm=then_norm)
             ops.linear(act, self.w_down, out=residual, accumulate=True, follow=before)
             return None
         return ops.linear(act, self.w_down, out_dtype=torch.float32, follow=before)

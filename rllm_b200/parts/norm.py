@@ -28,6 +28,11 @@ class RMSNorm(Norm):
     def load(self, tensors):
         self.weight = self._to_device(tensors[self.prefix + "weight"], torch.float32)
 
+    def deferrable(self):
+        """(weight, eps) for a product kernel that prepares this norm in its epilogue (the division by
+        the rms then happens in the product after it: csrc/ops.NormedRows)."""
+        return self.weight, self.eps
+
     def forward(self, x, delta=None, rows=None, write_x=True):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=self.runtime.dtype, device=x.device)

@@ -460,6 +460,56 @@ def test_gemv_stream_swiglu(m, F, k, grid, stages):
     o.check_device_errors()
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 13])
+@pytest.mark.parametrize("d,k,F,grid", [(1024, 512, 768, None), (4096, 4096, 12288, None), (320, 192, 100, 7),
+                                        (960, 64, 520, 148)])
+def test_gemv_stream_deferred_norm(m, d, k, F, grid):
+    """An RMSNorm between two products without a kernel of its own: the accumulating product also
+    writes bfloat16(x * norm weight) and the rows' sums of squares in per-CTA partial sums, the
+    product behind it (plain, and fused gate/up) divides its result rows by the rms.  Against
+    rmsnorm(x) . W^T computed plainly; the partial sums against the sum of squares of the rows."""
+    o = ops()
+    eps = 1e-5
+    a = rnd(m, k, seed=51, dtype=torch.bfloat16)
+    w_before = rnd(d, k, seed=52, scale=0.1, dtype=torch.bfloat16)
+    base = rnd(m, d, seed=53)
+    norm_w = 1.0 + rnd(d, seed=54, scale=0.1)
+    w_after = rnd(2 * F, d, seed=55, scale=0.1, dtype=torch.bfloat16)
+    x = base + a.float() @ w_before.float().t()                      # the residual stream after the first product
+    resid = base.to(DEV)
+    rows = o.gemv_stream(a.to(DEV), w_before.to(DEV), resid, epilogue=o.EPI_ACCUM, grid=grid,
+                         then_norm=(norm_w.to(DEV), eps))
+    assert isinstance(rows, o.NormedRows) and rows.shape == (m, d) and rows.d == d
+    assert rel_err(resid.cpu(), x) < 1e-5
+    assert rel_err(rows.xw.float().cpu(), x * norm_w) < 5e-3         # one bfloat16 rounding
+    ssq = rows.ssq[:rows.n_parts].sum(0).cpu()
+    assert rel_err(ssq[:m], (x * x).sum(-1)) < 1e-5
+    assert (ssq[m:] == 0).all()
+    # what the norm kernel followed by the product would give, from the same bfloat16 xw
+    r = 1.0 / torch.sqrt((x * x).sum(-1, keepdim=True) / d + eps)
+    h = rows.xw.float().cpu() * r
+    ref = h @ w_after[:F].float().t()
+    out = torch.full((m, F), float("nan"), device=DEV)
+    o.gemv_stream(rows, w_after[:F].contiguous().to(DEV), out, grid=grid)
+    assert rel_err(out.cpu(), ref) < 2e-5
+    g, u = ref, h @ w_after[F:].float().t()
+    act = torch.full((m, F), float("nan"), device=DEV)
+    o.gemv_stream(rows, w_after.to(DEV), act, epilogue=o.EPI_SWIGLU, up_row_offset=F, grid=grid)
+    assert rel_err(act.cpu(), g / (1 + torch.exp(-g)) * u) < 2e-5
+    # against the norm itself (no bfloat16 hand-over in the plain formula): one rounding apart
+    plain = (x * r * norm_w) @ w_after[:F].float().t()
+    assert rel_err(out.cpu(), plain) < 5e-3
+    # a row's result does not depend on its batch-mates
+    if m > 1:
+        resid1 = base[m - 1:].to(DEV)
+        rows1 = o.gemv_stream(a[m - 1:].to(DEV), w_before.to(DEV), resid1, epilogue=o.EPI_ACCUM, grid=grid,
+                              then_norm=(norm_w.to(DEV), eps))
+        out1 = torch.empty(1, F, device=DEV)
+        o.gemv_stream(rows1, w_after[:F].contiguous().to(DEV), out1, grid=grid)
+        assert torch.equal(out1[0], out[m - 1])
+    o.check_device_errors()
+
+
 def test_gemv_stream_lm_head_size():
     """The largest matrix of the decode step (vocabulary 151,936 x 4,096): 444 CTAs, dozens of chunks each."""
     o = ops()
