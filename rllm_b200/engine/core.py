@@ -279,8 +279,15 @@ class Engine:
         return ctx, views
 
     # ------------------------------------------------------------------ the step
-    def step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
+    def step(self, items: Sequence[StepItem], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """`device_tokens` (int32 on the device, one entry per item; only for steps of one token per
+        item): the items' token ids are taken from there instead of from the items, whose `tokens`
+        are then placeholders: ids that an earlier step's sampler left on the device go into the
+        next step without a round trip over the host."""
         decode_only = bool(items) and all(len(it.tokens) == 1 for it in items)
+        if device_tokens is not None and (not decode_only or device_tokens.numel() < len(items)
+                                          or device_tokens.dtype != torch.int32):
+            raise StepError("device_tokens needs one int32 id per item and one token per item")
         # A decode-only step on the C++ host is checked there (token range, wanted places, a request
         # named twice, pages: all before anything changes); the Python check runs only to word the
         # error.  Anything that is not a plain int goes through the Python check first.
@@ -291,7 +298,7 @@ class Engine:
         self.stats["step_tokens"] += sum(len(it.tokens) for it in items)
         if self.use_graphs and decode_only and len(items) <= GRAPH_MAX_REQUESTS and not self.cache.stateful:
             try:
-                logits = self._graph_step(items)
+                logits = self._graph_step(items, device_tokens)
             except (ValueError, KeyError):
                 if light:
                     self._check_items(items)         # raises the StepError that names the fault
@@ -300,6 +307,8 @@ class Engine:
             host, layout, meta = self._build(items)
             dev = torch.empty(layout.total, dtype=torch.int32, device=self.runtime.device)
             self._copy_in(dev, host)
+            if device_tokens is not None:
+                dev[:len(items)].copy_(device_tokens[:len(items)])          # the tokens are the first array
             ctx, views = self._context(layout.views(dev), meta, bool(meta["rows"]))
             logits = self.model.forward(ctx, views)
         if self._windowed:
@@ -327,7 +336,7 @@ class Engine:
                 graph.capture_end()
         torch.cuda.current_stream().wait_stream(side)
 
-    def _graph_step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
+    def _graph_step(self, items: Sequence[StepItem], device_tokens=None) -> Optional[torch.Tensor]:
         R = len(items)
         B = _bucket(R)
         if self.native_host:
@@ -361,6 +370,8 @@ class Engine:
         elif layout is not None:
             assert layout.offsets == g.layout.offsets
         self._copy_in(g.static, host)
+        if device_tokens is not None:
+            g.static[:R].copy_(device_tokens[:R])                          # the tokens are the first array
         g.uses += 1
         g.last_used = self.stats["steps"]
         if g.uses == 1:

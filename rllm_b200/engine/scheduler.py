@@ -75,10 +75,18 @@ class PlannedItem:
     seq: _Seq
     take: int
     want_last: bool
+    ahead: int = 0          # tokens of the request that an uncommitted earlier step holds (plan_ahead)
 
     @property
     def tokens(self) -> list:
+        if self.ahead:
+            return [0] * self.take       # not known on the host yet: the step takes them from the device
         return self.seq.tokens[self.seq.cached:self.seq.cached + self.take]
+
+    @property
+    def counter(self) -> int:
+        """The request's length when this item's last token is in: the sampler's counter."""
+        return self.seq.cached + self.ahead + self.take
 
 
 class Scheduler:
@@ -186,6 +194,29 @@ class Scheduler:
                 continue
             self._preempt_newest()
 
+    def plan_ahead(self, plan: Sequence[PlannedItem]) -> Optional[list]:
+        """The step after `plan`, planned before `plan`'s sampled tokens are known on the host, so
+        that it can be launched while they are still on their way: every request of `plan` decodes
+        the token that `plan` samples for it.  Only when nothing else could happen in that step:
+        `plan` holds every running request and samples for each, none of them reaches its budget
+        with the token under way, none needs the host for its next token (penalties, bias), nothing
+        waits for admission that could be admitted, and the pages are there.  None otherwise (the
+        caller then commits `plan` first and plans as usual).  A request that `plan`'s token ends
+        (a stop id) has then run one token too far; its pages go back when `plan` is committed, and
+        its row of the step planned here is dropped."""
+        if not plan or len(plan) != len(self.running) or any(not p.want_last or p.ahead for p in plan):
+            return None
+        if self.waiting and len(self.running) < self.max_num_seqs:
+            return None
+        for p in plan:
+            s = p.seq
+            if s.req.params.adjusts or len(s.tokens) - s.n_prompt + 1 >= s.budget:
+                return None
+        if not self.cache.can_append([(p.seq.rid, 1) for p in plan]):
+            return None
+        self.stats["steps"] += 1
+        return [PlannedItem(p.seq, 1, True, ahead=p.take) for p in plan]
+
     # ------------------------------------------------------------------ after the step
     def commit(self, plan: Sequence[PlannedItem], sampled: Sequence[int]) -> list:
         """`sampled`: one token id per planned item with want_last, in plan order.  Returns the
@@ -194,6 +225,9 @@ class Scheduler:
         finished = []
         for p in plan:
             s = p.seq
+            if p.ahead and s not in self.running:
+                next(it)                 # the request ended with the step before: this token was one too far
+                continue
             if s.cached < s.n_prompt:
                 self.stats["prompt_tokens"] += min(p.take, s.n_prompt - s.cached)
             s.cached += p.take

@@ -73,28 +73,42 @@ class LLM:
         results = {}
         host_samplers = {}
         steps = 0
+        # A step whose sampled ids are still on the device: (plan, ids).  While they travel to the host
+        # the next step is planned and launched already where that is possible (Scheduler.plan_ahead),
+        # taking its tokens from the device; the host's work for a step then hides behind the GPU's.
+        pending = None
         try:
-            while sched.has_work():
-                plan = sched.plan()
-                for f in sched.collect():
-                    results[f.request_id] = f
-                if not plan:
-                    continue
+            while sched.has_work() or pending is not None:
                 try:
-                    ids = self._run_step(plan, host_samplers)
+                    if pending is None:
+                        plan = sched.plan()
+                        for f in sched.collect():
+                            results[f.request_id] = f
+                        if not plan:
+                            continue
+                        ids = self._run_step(plan, host_samplers)
+                        if isinstance(ids, torch.Tensor):
+                            pending = (plan, ids)
+                            continue
+                    else:
+                        plan, ids_dev = pending
+                        ahead = sched.plan_ahead(plan)
+                        ahead_ids = self._run_step(ahead, host_samplers, device_tokens=ids_dev) if ahead else None
+                        ids = ids_dev.tolist()
+                        pending = (ahead, ahead_ids) if ahead else None
+                    sched.commit(plan, ids)
+                    for f in sched.collect():
+                        results[f.request_id] = f
                     steps += 1
                     if steps % 64 == 0:
-                        self.engine.check_device_errors()     # the ids were just read: the device is idle
+                        self.engine.check_device_errors()
                 except Exception as e:
                     # a failed step fails the requests that were running and frees what they hold; the
                     # queue goes on (crates/rllm-server/src/engine.rs:569-578)
+                    pending = None
                     sched.fail_running(f"step failed: {type(e).__name__}: {e}")
                     for f in sched.collect():
                         results[f.request_id] = f
-                    continue
-                sched.commit(plan, ids)
-                for f in sched.collect():
-                    results[f.request_id] = f
             try:
                 self.engine.check_device_errors()
             except Exception as e:
@@ -116,10 +130,11 @@ class LLM:
             raise GenerationError(out)
         return [f.tokens for f in out]
 
-    def _run_step(self, plan, host_samplers) -> list:
-        """One engine step for the planned items and one sampled id per item that wants its last row."""
+    def _run_step(self, plan, host_samplers, device_tokens=None):
+        """One engine step for the planned items and one sampled id per item that wants its last row:
+        a list (no row wanted, or sampled on the host) or an int32 tensor still on the device."""
         items = [StepItem(p.seq.rid, p.tokens, [p.take - 1] if p.want_last else []) for p in plan]
-        logits = self.engine.step(items)
+        logits = self.engine.step(items, device_tokens=device_tokens)
         wanted = [p for p in plan if p.want_last]
         if not wanted:
             return []
@@ -130,9 +145,8 @@ class LLM:
                 hs = host_samplers.setdefault(p.seq.rid, HostSampler(p.seq.req.params))
                 ids.append(hs.sample(rows[r], p.seq.counts))
             return ids
-        counters = [p.seq.cached + p.take for p in wanted]
-        return sample_rows(logits, [p.seq.req.params for p in wanted], counters,
-                           [p.seq.counts for p in wanted]).tolist()
+        return sample_rows(logits, [p.seq.req.params for p in wanted], [p.counter for p in wanted],
+                           [p.seq.counts for p in wanted])
 
 
 class GenerationError(RuntimeError):

@@ -499,6 +499,64 @@ def test_scheduler_failed_step_frees_running():
     assert [f.request_id for f in s.collect() if f.reason == "length"] == [2]
 
 
+def drive_pipelined(sched, cache, pick, max_steps=10000):
+    """As `drive`, but the way LLM.generate runs with the sampler on the device: a step's tokens are
+    committed only after the next step has been planned (plan_ahead) and appended to the cache."""
+    pending, n_ahead = None, 0
+    while (sched.has_work() or pending is not None) and max_steps:
+        max_steps -= 1
+        if pending is None:
+            plan = sched.plan()
+            if not plan:
+                continue
+            for p in plan:
+                cache.append(p.seq.rid, p.take)
+            pending = plan
+            continue
+        plan = pending
+        ahead = sched.plan_ahead(plan)
+        if ahead:
+            n_ahead += 1
+            assert [p.seq for p in ahead] == [p.seq for p in plan] and all(p.tokens == [0] for p in ahead)
+            for p in ahead:
+                cache.append(p.seq.rid, p.take)
+        # the tokens of `plan` arrive: each from the request's history before it (an item planned ahead
+        # does not know its own input token yet, the history does once the step before is committed)
+        ids = [pick(p.seq.tokens) for p in plan if p.want_last and p.seq in sched.running]
+        it = iter(ids)
+        ids = [next(it) if p.seq in sched.running else -1 for p in plan if p.want_last]
+        sched.commit(plan, ids)
+        cache.check_invariants()
+        pending = ahead
+    return n_ahead
+
+
+def test_planning_ahead_changes_no_result():
+    def pick(t):
+        return (sum(t) * 31 + len(t)) % 1000
+
+    def run(pipelined, pool, stop=frozenset()):
+        cache = CacheManager([PagedKVNeed(1, 16)], [None], 16, pool, 8)
+        s = Scheduler(cache, ctx=400, max_num_seqs=3, prefill_chunk=64)
+        for i in range(5):
+            s.add(Request(i, [i + 1] * (20 + 7 * i), max_tokens=60 + 9 * i, stop_ids=stop))
+        n = drive_pipelined(s, cache, pick) if pipelined else (drive(s, cache, pick) and 0)
+        assert not cache.requests and cache.n_free_pages(0) == cache.n_blocks
+        return {f.request_id: (f.tokens, f.reason) for f in s.collect()}, n, s.stats["preemptions"]
+    plain, _, _ = run(False, 4096)
+    ahead, n, _ = run(True, 4096)
+    assert ahead == plain and n > 50                       # most decode steps were planned ahead
+    # stop ids end requests in the middle (the step planned ahead then ran one token too far for them)
+    some = sorted({t for toks, _ in plain.values() for t in toks[10:40]})[:25]
+    plain_stop, _, _ = run(False, 4096, frozenset(some))
+    ahead_stop, n, _ = run(True, 4096, frozenset(some))
+    assert ahead_stop == plain_stop and any(r == "stop" for _, r in plain_stop.values()) and n > 2
+    # a pool so small that requests are preempted: planning ahead steps back when pages are short
+    plain_tight, _, p0 = run(False, 208)
+    ahead_tight, _, p1 = run(True, 208)
+    assert ahead_tight == plain_tight == plain and p0 >= 1 and p1 >= 1
+
+
 class _FakeEngine:
     """Stands in for the engine under LLM.generate: the host cache manager and a step that returns
     logits naming token (number of tokens the request holds) % 50, or raises on the steps listed."""
@@ -508,7 +566,7 @@ class _FakeEngine:
         self.calls, self.fail_steps, self.device_error_at = 0, set(fail_steps), set(device_error_at)
         self.checks = 0
 
-    def step(self, items):
+    def step(self, items, device_tokens=None):
         self.calls += 1
         if self.calls in self.fail_steps:
             raise RuntimeError(f"injected fault in step {self.calls}")
@@ -565,10 +623,10 @@ def test_generate_leaves_nothing_in_the_cache_however_it_ends():
     from rllm_b200.llm import GenerationError
 
     class Interrupting(_FakeEngine):
-        def step(self, items):
+        def step(self, items, device_tokens=None):
             if self.calls == 2:
                 raise KeyboardInterrupt
-            return super().step(items)
+            return super().step(items, device_tokens)
 
     eng = Interrupting()
     llm = _fake_llm(eng)
