@@ -38,12 +38,24 @@ struct FlashParams {
     const int* tile_req;      // [tiles] request row of each tile
     const int* tile_tok0;     // [tiles] first flat token of each tile
     int table_stride;
+    int n_pages;              // pages of the pool: a table entry outside [0, n_pages) is refused (page 0 is read, *err set)
+    int* err;                 // the error word, or null
     int H, K, bs, window;
     int TT, GH, head_chunks;  // tokens per tile, heads per token in a tile, chunks of the GQA group
     int split_keys;           // 0: no split
     int part_rows;            // rows kept per partial (TT * GH)
     float scale_log2;         // softmax scale * log2(e)
 };
+
+// A table entry outside the pool is refused: page 0 is read in its place (its keys are masked or
+// not, the step's results are not to be used either way) and the error word says so.
+__device__ __forceinline__ int checked_page(const FlashParams& p, int page) {
+    if ((unsigned)page >= (unsigned)p.n_pages) {
+        if (p.err) atomicExch(p.err, RLLM_ERR_PAGE);
+        return 0;
+    }
+    return page;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -151,7 +163,7 @@ __global__ void __launch_bounds__(NW * 32) paged_flash_attention_kernel(const Fl
             const int key0 = kt + row0;
             const int blk = key0 / p.bs, off0 = key0 - blk * p.bs;
             const int rows_here = min(p.bs - off0, BN - row0);
-            const int page = table[min(blk, last_blk)];  // beyond the range: any valid address, zero fill
+            const int page = checked_page(p, table[min(blk, last_blk)]);  // beyond the range: any valid address, zero fill
             const size_t base = (((size_t)page * p.K + kvh) * p.bs + off0) * HD + my_chunk * 8;
             const bf16* ksrc = p.k_cache + base;
             const bf16* vsrc = p.v_cache + base;
@@ -391,7 +403,7 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
     auto load_tile = [&](int stage, int kt) {
         if (one_page) {
             const int blk = kt >> bs_shift, off0 = kt & (p.bs - 1);
-            const int page = table[min(blk, last_blk)];
+            const int page = checked_page(p, table[min(blk, last_blk)]);
             const size_t base = (((size_t)page * p.K + kvh) * p.bs + off0 + my_row0) * HD + my_chunk * 8;
             const bf16* ksrc = p.k_cache + base;
             const bf16* vsrc = p.v_cache + base;
@@ -413,7 +425,7 @@ __global__ void __launch_bounds__(32) paged_decode_attention_kernel(const FlashP
             const int key0 = kt + row0;
             const int blk = key0 / p.bs, off0 = key0 - blk * p.bs;
             const int rows_here = min(p.bs - off0, BN - row0);
-            const int page = table[min(blk, last_blk)];
+            const int page = checked_page(p, table[min(blk, last_blk)]);
             const size_t base = (((size_t)page * p.K + kvh) * p.bs + off0) * HD + my_chunk * 8;
             const bf16* ksrc = p.k_cache + base;
             const bf16* vsrc = p.v_cache + base;
@@ -691,7 +703,8 @@ RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, cons
                                         const int* block_table, int table_stride, const int* tile_req,
                                         const int* tile_tok0, int n_tiles, int H, int K, int hd, int bs,
                                         float scale, int window, int mode, int TT, int GH, int head_chunks,
-                                        int split_keys, int n_splits, cudaStream_t stream) {
+                                        int split_keys, int n_splits, long long n_pages, int* err,
+                                        cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     const int rows = mode == 0 ? 64 : 16;
     if (K <= 0 || H % K || TT <= 0 || GH <= 0 || TT * GH > rows || head_chunks * GH < H / K || bs <= 0)
@@ -702,6 +715,7 @@ RLLM_API int rllm_paged_flash_attention(const void* q, const void* k_cache, cons
     p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache; p.out = (bf16*)out;
     p.part_o = part_o; p.part_ml = part_ml; p.positions = positions; p.cu_q = cu_q; p.block_table = block_table;
     p.tile_req = tile_req; p.tile_tok0 = tile_tok0; p.table_stride = table_stride;
+    p.n_pages = (int)(n_pages > 0x7fffffffLL ? 0x7fffffffLL : n_pages); p.err = err;
     p.H = H; p.K = K; p.bs = bs; p.window = window; p.TT = TT; p.GH = GH; p.head_chunks = head_chunks;
     p.split_keys = mode == 0 ? 0 : split_keys; p.part_rows = TT * GH;
     p.scale_log2 = scale * 1.4426950408889634f;
@@ -761,5 +775,6 @@ RLLM_API int rllm_paged_flash_decode_static(const void* q, const void* k_cache, 
     float* part_ml = part_o + (size_t)RLLM_FLASH_STATIC_SCRATCH_ROWS * 128;
     return rllm_paged_flash_attention(q, k_cache, v_cache, out, part_o, part_ml, positions, cu_q, block_table,
                                       table_stride, tile_req, tile_tok0, n_tiles, H, K, hd, bs, scale, window,
-                                      /*mode=*/1, TT, GH, head_chunks, split_keys, n_splits, stream);
+                                      /*mode=*/1, TT, GH, head_chunks, split_keys, n_splits,
+                                      /*n_pages: the caller vouches for its table*/ 0x7fffffffLL, /*err=*/nullptr, stream);
 }

@@ -24,7 +24,7 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
                                const TC* v_cache, TO* out,
                                const int* __restrict__ positions, const int* __restrict__ seq_ids,
                                const int* __restrict__ block_table, int table_stride, int H, int K,
-                               int hd, int bs, float scale, int window) {
+                               int hd, int bs, float scale, int window, int n_pages, int* err) {
     extern __shared__ float smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -53,7 +53,11 @@ paged_attention_generic_kernel(const TQ* q, const TC* k_cache,
         const int p = c0 + tid;
         float s = -INFINITY;
         if (p <= pos) {
-            const int page = table[p / bs];
+            int page = table[p / bs];
+            if (page < 0 || page >= n_pages) {        // refused: read page 0, report
+                if (err) atomicExch(err, RLLM_ERR_PAGE);
+                page = 0;
+            }
             const size_t row = ((size_t)page * K + kvh) * bs + (p % bs);
             rowoff[tid] = (int)row;
             const TC* kr = k_cache + row * hd;
@@ -94,7 +98,7 @@ RLLM_API int rllm_paged_attention_generic(const void* q, int q_dtype, const void
                                           const void* v_cache, int cache_dtype, void* out,
                                           int out_dtype, const int* positions, const int* seq_ids,
                                           const int* block_table, int table_stride, int n, int H,
-                                          int K, int hd, int bs, float scale, int window,
+                                          int K, int hd, int bs, float scale, int window, int n_pages, int* err,
                                           cudaStream_t stream) {
     if (n <= 0) return 0;
     if (hd > ATT_THREADS * ATT_MAX_ACC || K <= 0 || H % K != 0 || bs <= 0) return (int)cudaErrorInvalidValue;
@@ -104,8 +108,8 @@ RLLM_API int rllm_paged_attention_generic(const void* q, int q_dtype, const void
     if (q_dtype == RLLM_F32)
         return rllm_launch(paged_attention_generic_kernel<float, float, float>, grid, dim3(ATT_THREADS), smem,
                            stream, (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out,
-                           positions, seq_ids, block_table, table_stride, H, K, hd, bs, scale, window);
+                           positions, seq_ids, block_table, table_stride, H, K, hd, bs, scale, window, n_pages, err);
     return rllm_launch(paged_attention_generic_kernel<bf16, bf16, bf16>, grid, dim3(ATT_THREADS), smem, stream,
                        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions,
-                       seq_ids, block_table, table_stride, H, K, hd, bs, scale, window);
+                       seq_ids, block_table, table_stride, H, K, hd, bs, scale, window, n_pages, err);
 }

@@ -65,6 +65,7 @@ struct AttnTcParams {
     const int* tile_req;        // [tiles]
     const int* tile_tok0;       // [tiles]
     int table_stride, H, K, bs, window, TT, g, n_tiles;
+    int n_pages;                // a table entry outside [0, n_pages) is refused (page 0 is read, RLLM_ERR_PAGE)
     float scale_log2;
     int* err;
 };
@@ -181,7 +182,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         auto page_row = [&](int j) {                                // first cache row of this lane's page of tile j
             const int rel = min(j * pages + lane, n_blk - 1);      // pages past the context: the last valid page, masked
             if (lane >= pages) return 0;
-            const int page = rel < AT_TABLE_SMEM ? s_table[rel] : table[first_blk + rel];
+            int page = rel < AT_TABLE_SMEM ? s_table[rel] : table[first_blk + rel];
+            if ((unsigned)page >= (unsigned)p.n_pages) {           // (a box outside the tensor map would read as zeros anyway)
+                atomicExch(p.err, RLLM_ERR_PAGE);
+                page = 0;
+            }
             return (page * p.K + kvh) * p.bs;
         };
         auto load_k = [&](int j) -> bool {
@@ -498,6 +503,7 @@ RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v
     p.out = (bf16*)out; p.positions = positions; p.cu_q = cu_q; p.block_table = block_table; p.tile_req = tile_req;
     p.tile_tok0 = tile_tok0; p.table_stride = table_stride; p.H = H; p.K = K; p.bs = bs; p.window = window; p.TT = TT;
     p.g = g; p.n_tiles = n_tiles; p.scale_log2 = scale * 1.4426950408889634f; p.err = err;
+    p.n_pages = (int)(n_pages > 0x7fffffffLL ? 0x7fffffffLL : n_pages);
     constexpr int smem = (1 + AT_KS + AT_VS) * AT_TILE_BYTES + 1024;
     static bool attr_set = false;
     if (!attr_set) {

@@ -8,6 +8,10 @@
 
 #define RLLM_API extern "C" __attribute__((visibility("default")))
 
+// Codes that kernels write to the error word when a range check refuses an index (the access is then
+// skipped or redirected to page 0 and the step's results are not to be used; nothing traps).
+enum : int { RLLM_ERR_TOKEN = 4, RLLM_ERR_SLOT = 5, RLLM_ERR_PAGE = 6 };
+
 // Element type codes shared with the Python wrappers.
 enum : int { RLLM_F32 = 0, RLLM_BF16 = 1 };
 

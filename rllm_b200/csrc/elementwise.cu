@@ -227,7 +227,8 @@ RLLM_API int rllm_silu_mul(const void* in, int in_dtype, void* out, int out_dtyp
 //               then rotate-half rotary with angle = position * inv_freq[i] on pairs (i, i+hd/2)
 //               (inv_freq has hd/2 entries; a null inv_freq means no rotation);
 //   q -> q_out[t, h, :];  k, v -> the paged cache at slot = slots[t]
-//   (page = slot / bs, offset = slot % bs, layout [page][kv_head][bs][hd]); slot < 0 writes nothing.
+//   (page = slot / bs, offset = slot % bs, layout [page][kv_head][bs][hd]); slot < 0 writes nothing;
+//   a slot beyond the pool (>= n_slots) writes nothing and sets the error word (RLLM_ERR_SLOT).
 // write_kv == 0 skips the cache (a layer that reads another layer's cache).
 //
 // One block per token and group of 8 heads (head size a multiple of 4, at most 256): the
@@ -240,7 +241,7 @@ qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_
                                 const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
                                 const int* __restrict__ positions, const int* __restrict__ slots,
                                 TO* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache, int H,
-                                int K, int hd, int bs, float eps, int write_kv) {
+                                int K, int hd, int bs, float eps, int write_kv, int n_slots, int* err) {
     __shared__ float2 cs[128];                    // (cos, sin) of pair j at this token's position
     // The attention kernel that follows may start at once: before its own wait (which ends when this
     // grid has completed, and so the product before it) it reads only the step's index arrays and
@@ -257,7 +258,11 @@ qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_
     }
     __syncthreads();
     const int n_heads = write_kv ? H + 2 * K : H;
-    const int slot = slots[t];
+    int slot = slots[t];
+    if (slot >= n_slots) {
+        if (tid == 0 && blockIdx.y == 0 && err) atomicExch(err, RLLM_ERR_SLOT);
+        slot = -1;
+    }
     const size_t width = (size_t)(H + 2 * K) * hd;
     const int units = half >> 1;                  // float2 units per half head
     const int hx = blockIdx.y * 8 + warp;          // one head per warp
@@ -314,7 +319,8 @@ RLLM_API int rllm_qk_norm_rope_store(const void* qkv, int in_dtype, const float*
                                      const float* k_norm_w, const float* inv_freq,
                                      const int* positions, const int* slots, void* q_out, int q_dtype,
                                      void* k_cache, void* v_cache, int cache_dtype, int n, int H, int K,
-                                     int hd, int bs, float eps, int write_kv, cudaStream_t stream) {
+                                     int hd, int bs, float eps, int write_kv, long long n_slots, int* err,
+                                     cudaStream_t stream) {
     if (n <= 0) return 0;
     if (hd % 4 != 0 || hd > 256 || ((uintptr_t)qkv & 7) || ((uintptr_t)q_out & 7) || ((uintptr_t)k_cache & 7) ||
         ((uintptr_t)v_cache & 7))
@@ -323,7 +329,8 @@ RLLM_API int rllm_qk_norm_rope_store(const void* qkv, int in_dtype, const float*
 #define LAUNCH(TI, TO, TC)                                                                            \
     return rllm_launch(qk_norm_rope_store_token_kernel<TI, TO, TC>, grid, dim3(256), 0, stream,       \
                        (const TI*)qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, (TO*)q_out,    \
-                       (TC*)k_cache, (TC*)v_cache, H, K, hd, bs, eps, write_kv)
+                       (TC*)k_cache, (TC*)v_cache, H, K, hd, bs, eps, write_kv,                       \
+                       (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots), err)
     if (q_dtype != cache_dtype) return (int)cudaErrorInvalidValue;
     if (in_dtype == RLLM_F32 && q_dtype == RLLM_F32) { LAUNCH(float, float, float); }
     if (in_dtype == RLLM_F32 && q_dtype == RLLM_BF16) { LAUNCH(float, bf16, bf16); }

@@ -170,7 +170,8 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_ou
         _ptr(qkv), c_int(_code(qkv)), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq), _ptr(positions),
         _ptr(slots), _ptr(q_out), c_int(_code(q_out)), _ptr(k_cache), _ptr(v_cache), c_int(_code(k_cache)),
         c_int(n), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(eps),
-        c_int(1 if write_kv else 0), _stream()), "qk_norm_rope_store")
+        c_int(1 if write_kv else 0), c_longlong(k_cache.shape[0] * block_size), _ptr(error_word(qkv.device)),
+        _stream()), "qk_norm_rope_store")
     return q_out
 
 
@@ -193,7 +194,7 @@ def paged_attention_generic(q, k_cache, v_cache, out, positions, seq_ids, block_
         _ptr(q), c_int(_code(q)), _ptr(k_cache), _ptr(v_cache), c_int(_code(k_cache)), _ptr(out),
         c_int(_code(out)), _ptr(positions), _ptr(seq_ids), _ptr(block_table), c_int(block_table.stride(0)),
         c_int(n), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
-        _stream()), "paged_attention_generic")
+        c_int(min(k_cache.shape[0], 0x7fffffff)), _ptr(error_word(q.device)), _stream()), "paged_attention_generic")
     return out
 
 
@@ -721,7 +722,7 @@ def paged_flash_attention(q, k_cache, v_cache, out, positions, cu_q, block_table
         _ptr(cu_q), _ptr(block_table), c_int(block_table.stride(0)), _ptr(tile_req), _ptr(tile_tok0),
         c_int(n_tiles), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(scale), c_int(window),
         c_int(mode), c_int(TT), c_int(GH), c_int(head_chunks), c_int(split_keys), c_int(n_splits),
-        _stream()), "paged_flash_attention")
+        c_longlong(k_cache.shape[0]), _ptr(error_word(q.device)), _stream()), "paged_flash_attention")
     global _launches
     if mode == 1:
         _launches += 1                         # the combine kernel

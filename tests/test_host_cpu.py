@@ -384,6 +384,10 @@ def test_cache_manager_random_orders(seed):
                 del live[victim]
             else:
                 assert all(len(s) == n for s in slots)
+                # what the kernels' range checks hold the host to: every slot lies inside the pool
+                # (rows = pages x page size), every table entry names a page of the pool
+                assert all(0 <= x < cm.n_blocks * cm.block_size for s in slots for x in s)
+                assert all(0 <= b < cm.n_blocks for g in range(len(cm.paged)) for b in cm.block_table(rid, g))
                 live[rid] += n
                 assert cm.length(rid) == live[rid]
                 cm.release_passed(rid)
