@@ -259,10 +259,13 @@ API int rllm_cache_block_table(void* c, int64_t rid, int group, int* out, int ca
 // entries): tokens[n], positions[n], seq_ids[n], cu_q[R+1], ctx_lens[R], state_slots[R],
 // logit_rows[m], then per group slots[n], then per group block_table[R, width].
 // Appends every item's tokens to its request first (all-or-nothing: on an error nothing changed).
-// pad_requests > 0: the step holds one token per request and is padded to that many requests
-// (padding rows: token 0, position 0, slot -1) with all n rows as logit rows and tables of
-// pad_width columns.  `offsets` receives the start of each array, `meta` = {n, R, m, width, total}.
-// `new_flags[i]` tells whether item i created its request (its state slot must be zeroed).
+// pad_requests > 0 gives the step the padded shape of a captured graph: the items with one token
+// are padded to that many requests (padding rows: token 0, position 0, slot -1, context 1), the
+// tables to pad_width columns.  Every item may have one token (a decode step: all n rows are logit
+// rows), or all but the LAST, which is then a portion of a prompt and comes behind the padding
+// rows: [one-token items][padding][portion]; the logit rows are the pad_requests one-token rows and
+// the portion's last row.  `offsets` receives the start of each array, `meta` = {n, R, m, width,
+// total, longest}.  `new_flags[i]` tells whether item i created its request (its state slot must be zeroed).
 API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n_tok, const int* tokens_flat,
                         const int* n_want, const int* want_flat, int vocab, int pad_requests, int pad_width,
                         int pad_quantum, int32_t* out, int out_cap, int* offsets, int* meta, int* new_flags) {
@@ -280,12 +283,20 @@ API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n
             n_real += n_tok[i]; m += n_want[i];
         }
     }
+    // the padded shape: one-token items first, at most one portion, and that one last
+    const bool portion = pad_requests > 0 && n_tok[n_items - 1] > 1;
+    const int n_single = portion ? n_items - 1 : n_items;
+    if (pad_requests > 0) {
+        for (int i = 0; i < n_single; ++i) if (n_tok[i] != 1) return ERR_BAD_ARG;
+        if (n_single > pad_requests) return ERR_BAD_ARG;
+    }
     int st = c->check_append(n_items, rids, n_tok);
     if (st) return st;
     const int G = (int)c->groups.size();
-    const int R = std::max(n_items, pad_requests);
-    const int n = n_real + (R - n_items);
-    if (pad_requests) m = n;
+    const int n_pad = pad_requests > 0 ? pad_requests - n_single : 0;      // padding rows (and requests)
+    const int R = n_items + n_pad;
+    const int n = n_real + n_pad;
+    if (pad_requests) m = pad_requests + (portion ? 1 : 0);
     // table width after the append
     int width = std::max(1, pad_width), longest = 0;
     for (int i = 0; i < n_items; ++i) {
@@ -309,9 +320,18 @@ API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n
     if (total > out_cap) return ERR_BUFFER;           // nothing appended yet: the caller grows the buffer and retries
     std::memset(out, 0, sizeof(int32_t) * total);
     std::vector<int> slots;
-    int base = 0, t = 0, w = 0, row = 0;
+    int base = 0, t = 0, w = 0, row = 0, r = 0;      // r: the request's row in the step
     out[o_cu] = 0;
     for (int i = 0; i < n_items; ++i) {
+        if (i == n_single) {
+            // padding rows, behind the one-token items (and before the portion, if there is one)
+            for (int q = 0; q < n_pad; ++q, ++r, ++base) {
+                out[o_seq + base] = r;
+                for (int g = 0; g < G; ++g) out[o_slots[g] + base] = -1;
+                out[o_cu + r + 1] = base + 1;
+                out[o_ctx + r] = 1;
+            }
+        }
         const int cnt = n_tok[i];
         auto it = c->requests.find(rids[i]);
         const int start = it == c->requests.end() ? 0 : it->second.length;
@@ -321,29 +341,32 @@ API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n
         for (int j = 0; j < cnt; ++j) {
             out[o_tok + base + j] = tokens_flat[t + j];
             out[o_pos + base + j] = start + j;
-            out[o_seq + base + j] = i;
+            out[o_seq + base + j] = r;
             for (int g = 0; g < G; ++g) out[o_slots[g] + base + j] = slots[(size_t)g * cnt + j];
         }
         if (!pad_requests)
             for (int j = 0; j < n_want[i]; ++j) out[o_rows + row++] = base + want_flat[w + j];
-        out[o_cu + i + 1] = base + cnt;
-        out[o_ctx + i] = start + cnt;
-        const Request& r = c->requests[rids[i]];
-        out[o_state + i] = r.state_slot;
+        out[o_cu + r + 1] = base + cnt;
+        out[o_ctx + r] = start + cnt;
+        const Request& rq = c->requests[rids[i]];
+        out[o_state + r] = rq.state_slot;
         for (int g = 0; g < G; ++g) {
-            const auto& tab = r.tables[g];
-            for (size_t b = 0; b < tab.size(); ++b) out[o_tab[g] + i * width + (int)b] = std::max(tab[b], 0);
+            const auto& tab = rq.tables[g];
+            for (size_t b = 0; b < tab.size(); ++b) out[o_tab[g] + r * width + (int)b] = std::max(tab[b], 0);
         }
         base += cnt; t += cnt; w += n_want[i];
+        ++r;
     }
-    for (int i = n_items; i < R; ++i) {                 // padding rows
-        out[o_seq + base] = i;
-        for (int g = 0; g < G; ++g) out[o_slots[g] + base] = -1;
-        out[o_cu + i + 1] = base + 1;
-        out[o_ctx + i] = 1;
-        ++base;
+    if (n_single == n_items)
+        for (int q = 0; q < n_pad; ++q, ++r, ++base) {  // padding rows at the end of a decode step
+            out[o_seq + base] = r;
+            for (int g = 0; g < G; ++g) out[o_slots[g] + base] = -1;
+            out[o_cu + r + 1] = base + 1;
+            out[o_ctx + r] = 1;
+        }
+    if (pad_requests) {
+        for (int j = 0; j < pad_requests; ++j) out[o_rows + j] = j;
+        if (portion) out[o_rows + pad_requests] = n - 1;
     }
-    if (pad_requests)
-        for (int j = 0; j < n; ++j) { out[o_rows + j] = j; out[o_seq + j] = j; }
     return OK;
 }

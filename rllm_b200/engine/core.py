@@ -10,6 +10,10 @@ given back after the step; `finish(request)` gives back everything a request hol
 Steps that hold one token per request (decode) are replayed from CUDA graphs: one graph per
 (padded number of requests, padded context length), captured the second time a shape is seen,
 with the step's index arrays copied into the graph's fixed input buffer before each replay.
+So are steps of one-token items followed by ONE portion of a prompt (what the scheduler makes of
+decoding requests beside the short tail of a prompt, and a lone short portion too; up to
+GRAPH_MAX_PORTION tokens): the shape then also holds the portion's length.  Other steps launch
+their kernels one by one from Python, about 17 us of host time each.
 
 AxiomOperator/rllm: ``KvPool::step_sampled`` (crates/rllm-model/src/generate.rs:85-139) with
 the same pre-checks before any mutation (86-100); graph replay keyed by the step's shape
@@ -37,7 +41,14 @@ class StepError(ValueError):
 
 GRAPH_MAX_REQUESTS = 64
 GRAPH_CTX_QUANTUM = 256          # context lengths are padded to a multiple of this many tokens
-GRAPH_CACHE_MAX = 48             # captured decode shapes kept per engine
+GRAPH_CACHE_MAX = 48             # captured shapes kept per engine
+GRAPH_PORTION_CAPTURE_AT = 4     # a shape with a prompt portion is captured when it comes for this many-th time
+# Longest prompt portion of a step that is replayed from a graph (0: only decode steps are).  The
+# reference replays steps of up to 8 tokens (crates/rllm-model/src/lib.rs:80-87).  Longer portions
+# work the same way (the tests run them), but do not pay: their shapes repeat seldom, and padding the
+# decoding requests beside them to a power of two can push the products over a tile boundary (measured
+# on the 8B serving workload with portions of 512: 4.7 % slower than launching those steps one by one).
+GRAPH_MAX_PORTION = int(os.environ.get("RLLM_B200_GRAPH_MAX_PORTION", "8"))
 
 
 def _bucket(n: int) -> int:
@@ -296,13 +307,16 @@ class Engine:
             self._check_items(items)
         self.stats["steps"] += 1
         self.stats["step_tokens"] += sum(len(it.tokens) for it in items)
-        if self.use_graphs and decode_only and len(items) <= GRAPH_MAX_REQUESTS and not self.cache.stateful:
+        graphable = self.use_graphs and not self.cache.stateful
+        if graphable and decode_only and len(items) <= GRAPH_MAX_REQUESTS:
             try:
                 logits = self._graph_step(items, device_tokens)
             except (ValueError, KeyError):
                 if light:
                     self._check_items(items)         # raises the StepError that names the fault
                 raise
+        elif graphable and self.native_host and self._one_portion_last(items):
+            logits = self._graph_step(items, None, portion=len(items[-1].tokens))
         else:
             host, layout, meta = self._build(items)
             dev = torch.empty(layout.total, dtype=torch.int32, device=self.runtime.device)
@@ -315,6 +329,17 @@ class Engine:
             for it in items:
                 self.cache.release_passed(it.request_id)
         return logits
+
+    @staticmethod
+    def _one_portion_last(items) -> bool:
+        """One-token items (at most GRAPH_MAX_REQUESTS, possibly none) and then one portion of
+        2 to GRAPH_MAX_PORTION tokens of which at most the last one's logits are wanted."""
+        last = items[-1]
+        k = len(last.tokens)
+        return (1 < k <= GRAPH_MAX_PORTION and len(items) - 1 <= GRAPH_MAX_REQUESTS
+                and all(len(it.tokens) == 1 for it in items[:-1])
+                and all(int(w) == k - 1 for w in last.want) and len(last.want) <= 1
+                and all(len(it.want) <= 1 for it in items[:-1]))
 
     @contextlib.contextmanager
     def _capture(self, graph):
@@ -336,14 +361,16 @@ class Engine:
                 graph.capture_end()
         torch.cuda.current_stream().wait_stream(side)
 
-    def _graph_step(self, items: Sequence[StepItem], device_tokens=None) -> Optional[torch.Tensor]:
-        R = len(items)
+    def _graph_step(self, items: Sequence[StepItem], device_tokens=None, portion: int = 0) -> Optional[torch.Tensor]:
+        """portion: 0 for a decode step; else the last item is a portion of that many tokens and the
+        items before it have one token each (padded to a power of two, the portion behind them)."""
+        R = len(items) - (1 if portion else 0)             # one-token items
         B = _bucket(R)
         if self.native_host:
             # the C++ builder finds the longest request and pads the tables itself: one call per step
             buf, offsets, m = self._build_native(items, B, 0, GRAPH_CTX_QUANTUM)
             ctx_pad = -(-m[5] // GRAPH_CTX_QUANTUM) * GRAPH_CTX_QUANTUM
-            key = (B, ctx_pad)
+            key = (B, portion, ctx_pad)
             g = self._graphs.get(key)
             if g is None:
                 host, layout, meta = self._finish_build(items, B, buf, offsets, m)
@@ -354,7 +381,7 @@ class Engine:
             longest = max((self.cache.length(it.request_id) if self.cache.has(it.request_id) else 0) + 1
                           for it in items)
             ctx_pad = -(-longest // GRAPH_CTX_QUANTUM) * GRAPH_CTX_QUANTUM
-            key = (B, ctx_pad)
+            key = (B, 0, ctx_pad)
             host, layout, meta = self._build(items, pad_requests=B, pad_width=-(-ctx_pad // self.block_size))
             g = self._graphs.get(key)
         if g is None:
@@ -365,7 +392,11 @@ class Engine:
             g.layout = layout
             g.static = torch.zeros(g.layout.total, dtype=torch.int32, device=self.runtime.device)
             # host-side shape of the step as the graph sees it: every request at the padded length
-            meta_pad = dict(meta, start_pos=[ctx_pad - 1] * B, ctx_lens=[ctx_pad] * B, q_lens=[1] * B)
+            if portion:
+                meta_pad = dict(meta, start_pos=[ctx_pad - 1] * B + [ctx_pad - portion], ctx_lens=[ctx_pad] * (B + 1),
+                                q_lens=[1] * B + [portion])
+            else:
+                meta_pad = dict(meta, start_pos=[ctx_pad - 1] * B, ctx_lens=[ctx_pad] * B, q_lens=[1] * B)
             g.ctx, g.views = self._context(g.layout.views(g.static), meta_pad, True)
         elif layout is not None:
             assert layout.offsets == g.layout.offsets
@@ -374,8 +405,10 @@ class Engine:
             g.static[:R].copy_(device_tokens[:R])                          # the tokens are the first array
         g.uses += 1
         g.last_used = self.stats["steps"]
-        if g.uses == 1:
-            # first time: run the padded step eagerly (loads kernels, builds the dispatch plans)
+        if g.uses == 1 or (portion and g.uses < GRAPH_PORTION_CAPTURE_AT and g.graph is None):
+            # first time: run the padded step eagerly (loads kernels, builds the dispatch plans).  Shapes
+            # with a portion come in many more kinds than decode shapes, and most come once or twice: they
+            # are captured (which costs more than running them) only when they have come a few times.
             g.logits = self.model.forward(g.ctx, g.views)
         else:
             if g.graph is None:
@@ -389,11 +422,14 @@ class Engine:
                 ops.add_launches(g.launches)
             g.graph.replay()
             self.stats["graph_replays"] += 1
-        rows = [i for i, it in enumerate(items) for _ in it.want]      # one token each: its row is the item's index
+        # the graph's logit rows: one per (padded) one-token item, then the portion's last row
+        rows = [i for i, it in enumerate(items[:R]) for _ in it.want]
+        if portion and items[-1].want:
+            rows.append(B)
         if not rows:
             return None
-        if rows == list(range(R)):
-            return g.logits[:R]
+        if rows == list(range(len(rows))) and (not portion or not items[-1].want):
+            return g.logits[:len(rows)]
         return g.logits[torch.tensor(rows, dtype=torch.long, device=self.runtime.device)]
 
     def check_device_errors(self) -> None:

@@ -855,6 +855,35 @@ def test_native_step_builder_arrays():
     off, meta3, _ = nat.build_step([StepItem("a", [3], [0]), StepItem("b", [4], [])], 100, buf, pad_requests=2,
                                    pad_quantum=32)
     assert meta3[5] == 11 and meta3[3] == 32 // 4
+    # padded step with a portion: [one-token items][padding][portion]; logit rows: the padded one-token rows
+    # and the portion's last row
+    la, lc = nat.length("a"), nat.length("c")
+    off, (n, R, m, width, total, longest), _ = nat.build_step(
+        [StepItem("a", [3], [0]), StepItem("b", [4], []), StepItem("c", [7, 8, 9], [2])], 100, buf, pad_requests=4,
+        pad_quantum=16)
+    a = buf.numpy()
+    assert (n, R, m, longest) == (7, 5, 5, max(la + 1, lc + 3))
+    assert a[off[0]:off[0] + n].tolist() == [3, 4, 0, 0, 7, 8, 9]
+    assert a[off[1]:off[1] + n].tolist() == [la, nat.length("b") - 1, 0, 0, lc, lc + 1, lc + 2]
+    assert a[off[2]:off[2] + n].tolist() == [0, 1, 2, 3, 4, 4, 4]
+    assert a[off[3]:off[3] + R + 1].tolist() == [0, 1, 2, 3, 4, 7]
+    assert a[off[4]:off[4] + R].tolist() == [la + 1, nat.length("b"), 1, 1, lc + 3]
+    assert a[off[6]:off[6] + m].tolist() == [0, 1, 2, 3, 6]
+    for g in range(2):
+        slots = a[off[7 + g]:off[7 + g] + n]
+        tab = a[off[9 + g]:off[9 + g] + R * width].reshape(R, width)
+        assert slots[2] == slots[3] == -1 and (tab[2] == 0).all() and (tab[3] == 0).all()
+        t = nat.block_table("c", g)
+        assert tab[4, :len(t)].tolist() == t
+        assert all(slots[4 + j] == tab[4, (lc + j) // 4] * 4 + (lc + j) % 4 for j in range(3))
+    # a lone portion is padded with one one-token row
+    off, (n, R, m, width, total, longest), _ = nat.build_step([StepItem("c", [1, 2], [])], 100, buf, pad_requests=1)
+    a = buf.numpy()
+    assert (n, R, m) == (3, 2, 2) and a[off[2]:off[2] + 3].tolist() == [0, 1, 1] and a[off[6]:off[6] + 2].tolist() == [0, 2]
+    # a portion anywhere but last, or two of them, is no padded shape
+    for bad in ([StepItem("c", [1, 2], []), StepItem("a", [3], [])], [StepItem("a", [1, 2], []), StepItem("c", [1, 2], [])]):
+        with pytest.raises(ValueError):
+            nat.build_step(bad, 100, buf, pad_requests=4)
     nat.check_invariants()
 
 

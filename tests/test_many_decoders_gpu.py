@@ -113,7 +113,7 @@ def test_many_decoders_tiny(tiny_refs, name, dtype, block_size):
     for n in (12, 20, 40, 64, 70):
         eng = make_engine(d, dtype, max_tokens=pool_tokens(seqs, n, block_size), block_size=block_size, max_requests=n)
         run_rounds(eng, seqs, n, refs, dtype, f"tiny {name} pages of {block_size}")
-        buckets = {k[0] for k in eng._graphs}
+        buckets = {k[0] for k in eng._graphs if k[1] == 0}            # decode shapes (k[1]: a portion's length)
         assert buckets == ({{12: 16, 20: 32, 40: 64, 64: 64}[n]} if n <= 64 else set())
         if n <= 64:
             assert eng.stats["graph_replays"] >= 2 * (DECODE_STEPS - 2)
@@ -122,7 +122,9 @@ def test_many_decoders_tiny(tiny_refs, name, dtype, block_size):
 
 
 def tail_schedule(seqs):
-    """30 requests decode while request 30 brings its prompt in portions whose last has two tokens."""
+    """30 requests decode while request 30 brings its prompt in portions, the later ones of two tokens.
+    The two-token portions want their last row only: such steps (one-token items, then one portion) are
+    run from the padded layout of a graph (and are captured when their shape has come a few times)."""
     steps = [{"entries": [{"id": i, "tokens": seqs[i][:len(seqs[i]) - DECODE_STEPS - 1], "want": []}
                           for i in range(lo, min(lo + 10, 30))]} for lo in range(0, 30, 10)]
     late = seqs[30]
@@ -131,7 +133,7 @@ def tail_schedule(seqs):
         entries = [{"id": i, "tokens": [seqs[i][len(seqs[i]) - DECODE_STEPS - 1 + j]], "want": [0]} for i in range(30)]
         if j < len(cuts) - 1:
             part = late[cuts[j]:cuts[j + 1]]
-            entries.insert(7, {"id": 30, "tokens": part, "want": list(range(len(part)))[-2:]})
+            entries.append({"id": 30, "tokens": part, "want": [len(part) - 1]})
         else:
             entries.append({"id": 30, "tokens": [late[cuts[-1] + j - (len(cuts) - 1)]], "want": [0]})
         steps.append({"entries": entries})
@@ -150,6 +152,7 @@ def test_two_token_tail_beside_thirty_decoders(tiny_refs, name, dtype):
     check(out, {i: refs[i] for i in range(31)}, dtype, f"tiny {name}: 2-token tail beside 30 decoding")
     eng.cache.check_invariants()
     assert eng.cache.n_free_pages(0) == eng.cache.n_blocks
+    assert any(k[:2] == (32, 2) for k in eng._graphs)
 
 
 # ---------------------------------------------------------------- the layer sizes of Qwen3-8B
@@ -192,7 +195,7 @@ def test_many_decoders_at_8b_layer_sizes_bfloat16(big_refs, block_size):
         eng = make_engine(d, "bfloat16", max_tokens=pool_tokens(seqs, n, block_size), block_size=block_size, max_requests=n)
         with Spy() as spy:
             run_rounds(eng, seqs, n, refs, "bfloat16", f"8B sizes, pages of {block_size}")
-        buckets = {k[0] for k in eng._graphs}
+        buckets = {k[0] for k in eng._graphs if k[1] == 0}
         if n == 12:
             # 9 to 16 rows: the streaming kernel for QKV, O and down, the swapped tcgen05 kernel for gate/up and the head
             assert 16 in spy.rows("gemv_stream") and 16 in spy.rows("skinny_gemm_tc") and buckets == {16}
@@ -219,4 +222,58 @@ def test_two_token_tail_beside_thirty_decoders_at_8b_layer_sizes(big_refs):
         eng = make_engine(d, "bfloat16", max_tokens=31 * 96, block_size=block_size, max_requests=31)
         out = helpers.run_steps(eng, tail_schedule(seqs))
         check(out, {i: refs[i] for i in range(31)}, "bfloat16", f"8B sizes: 2-token tail beside 30 decoding, pages of {block_size}")
+        eng.cache.check_invariants()
+
+
+def portion_schedule(seqs, n_dec, k, late):
+    """n_dec requests decode, one token each per step, while the requests `late` bring their prompts one
+    after the other in portions of exactly k tokens (the rest in a last, shorter portion): the shape
+    (decoders, portion of k) repeats, so that it is captured and replayed."""
+    steps = [{"entries": [{"id": i, "tokens": seqs[i][:len(seqs[i]) - DECODE_STEPS - 1], "want": []}
+                          for i in range(lo, min(lo + 8, n_dec))]} for lo in range(0, n_dec, 8)]
+    j = 0
+    for rid in late:
+        toks, cut = seqs[rid], 0
+        while cut < len(toks):
+            part = toks[cut:cut + k]
+            entries = [{"id": i, "tokens": [seqs[i][len(seqs[i]) - DECODE_STEPS - 1 + j]], "want": [0]} for i in range(n_dec)]
+            entries.append({"id": rid, "tokens": part, "want": [len(part) - 1] if len(part) > 1 else [0]})
+            steps.append({"entries": entries})
+            cut += len(part)
+            j += 1
+            assert j <= DECODE_STEPS
+    steps[-1]["end"] = list(range(n_dec)) + list(late)
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_portions_beside_decoders_from_graphs(tiny_refs, name, dtype, monkeypatch):
+    from rllm_b200.engine import core
+    monkeypatch.setattr(core, "GRAPH_MAX_PORTION", 1024)      # the default keeps graphs to portions of up to 8 tokens
+    d, seqs, refs = tiny_refs[name, dtype]
+    for n_dec, k in ((5, 12), (0, 16), (11, 9), (20, 5)):
+        late = [40, 41, 42]
+        eng = make_engine(d, dtype, max_tokens=(n_dec + 3) * 96, block_size=16, max_requests=n_dec + 3)
+        steps = portion_schedule(seqs, n_dec, k, late)
+        out = helpers.run_steps(eng, steps)
+        check(out, {i: refs[i] for i in list(range(n_dec)) + late}, dtype,
+              f"tiny {name}: portions of {k} beside {n_dec} decoding")
+        eng.cache.check_invariants()
+        assert eng.cache.n_free_pages(0) == eng.cache.n_blocks
+        hit = [key for key, g in eng._graphs.items() if key[1] == k and g.graph is not None]
+        assert hit and eng.stats["graph_replays"] >= 3, (sorted(eng._graphs), eng.stats)
+
+
+def test_portions_beside_decoders_from_graphs_at_8b_layer_sizes(big_refs, monkeypatch):
+    from rllm_b200.engine import core
+    monkeypatch.setattr(core, "GRAPH_MAX_PORTION", 1024)
+    d, seqs, refs = big_refs["bfloat16"]
+    for block_size, n_dec, k in ((16, 6, 20), (32, 0, 24)):
+        late = [50, 51, 52]
+        eng = make_engine(d, "bfloat16", max_tokens=(n_dec + 3) * 96, block_size=block_size, max_requests=n_dec + 3)
+        out = helpers.run_steps(eng, portion_schedule(seqs, n_dec, k, late))
+        check(out, {i: refs[i] for i in list(range(n_dec)) + late}, "bfloat16",
+              f"8B sizes: portions of {k} beside {n_dec} decoding, pages of {block_size}")
+        assert [key for key, g in eng._graphs.items() if key[1] == k and g.graph is not None]
         eng.cache.check_invariants()
