@@ -143,7 +143,9 @@ class CacheManager:
             grp.pool = torch.zeros((len(grp.entries), 2, self.n_blocks, n.num_kv_heads, self.block_size,
                                     n.head_dim), dtype=dtype, device=device)
         for grp in self.stateful:
-            grp.state = torch.zeros((len(grp.entries), self.max_requests, *grp.need.shape),
+            # one slot more than requests: the last one belongs to nobody; the padding rows of a step
+            # that is replayed from a CUDA graph read and write it
+            grp.state = torch.zeros((len(grp.entries), self.max_requests + 1, *grp.need.shape),
                                     dtype=grp.need.dtype, device=device)
 
     def device_bytes(self) -> int:

@@ -330,6 +330,7 @@ API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n
                 for (int g = 0; g < G; ++g) out[o_slots[g] + base] = -1;
                 out[o_cu + r + 1] = base + 1;
                 out[o_ctx + r] = 1;
+                out[o_state + r] = c->max_requests;     // the state slot that belongs to no request
             }
         }
         const int cnt = n_tok[i];
@@ -363,6 +364,7 @@ API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n
             for (int g = 0; g < G; ++g) out[o_slots[g] + base] = -1;
             out[o_cu + r + 1] = base + 1;
             out[o_ctx + r] = 1;
+            out[o_state + r] = c->max_requests;
         }
     if (pad_requests) {
         for (int j = 0; j < pad_requests; ++j) out[o_rows + j] = j;

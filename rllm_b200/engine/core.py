@@ -110,7 +110,8 @@ class Engine:
         self._windowed = any(g.need.window > 0 for g in self.cache.paged)     # only then do pages fall out of reach
         # RLLM_B200_NO_GRAPHS=1 turns graph replay off (the reference's RLLM_NO_GRAPHS); the profiling
         # switch does too: events cannot be recorded into a capture
-        self.use_graphs = (use_graphs and not profiler.enabled()
+        # and a model one of whose parts does not declare itself safe to capture (CAPTURE_SAFE) runs eagerly
+        self.use_graphs = (use_graphs and not profiler.enabled() and getattr(model, "capture_safe", False)
                            and os.environ.get("RLLM_B200_NO_GRAPHS", "0") in ("", "0"))
         self._graphs: dict = {}
         self._graph_pool = None
@@ -249,6 +250,7 @@ class Engine:
             base += k
         for r in range(R_real, R):
             cu_q[r + 1] = cu_q[r] + 1
+            state_slots[r] = cache.max_requests          # the state slot that belongs to no request
             q_lens.append(1)
             start_pos.append(0)
         tables = []
@@ -307,7 +309,7 @@ class Engine:
             self._check_items(items)
         self.stats["steps"] += 1
         self.stats["step_tokens"] += sum(len(it.tokens) for it in items)
-        graphable = self.use_graphs and not self.cache.stateful
+        graphable = self.use_graphs
         if graphable and decode_only and len(items) <= GRAPH_MAX_REQUESTS:
             try:
                 logits = self._graph_step(items, device_tokens)

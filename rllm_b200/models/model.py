@@ -26,6 +26,8 @@ class DecoderModel:
             if not 0 <= e.layer < len(self.blocks):
                 raise ValueError(f"run entry {i} names layer {e.layer}, but there are {len(self.blocks)}")
         self.loaded = False
+        # decode steps of this model may be captured into CUDA graphs: every part says it can be
+        self.capture_safe = all(getattr(p, "CAPTURE_SAFE", False) for p in self._weighted_parts() + self.blocks)
 
     # ------------------------------------------------------------------ tensors
     def _weighted_parts(self):

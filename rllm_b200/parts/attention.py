@@ -21,6 +21,8 @@ from .base import Mixer, PagedKVNeed, PartError, register_part
 
 @register_part("mixer", "attention")
 class Attention(Mixer):
+    CAPTURE_SAFE = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         p = params
@@ -73,10 +75,15 @@ class Attention(Mixer):
         dt = self.runtime.dtype
         qkv = ops.linear(h, self.w_qkv, out_dtype=torch.float32)
         q = torch.empty((n, self.H * self.hd), dtype=dt, device=qkv.device)
-        ops.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w,
-                               position.table() if position is not None else None, ctx.positions,
-                               cache.slots, q, cache.k, cache.v, self.H, self.K, self.hd,
-                               cache.block_size, self.qk_norm_eps, write_kv=cache.write)
+        if position is not None and hasattr(position, "apply_and_store"):
+            # the position part does it all: q/k norm, its own encoding, queries out, keys and values stored
+            position.apply_and_store(qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, ctx.positions, cache, q,
+                                     self.H, self.K, self.hd)
+        else:
+            ops.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w,
+                                   position.table() if position is not None else None, ctx.positions,
+                                   cache.slots, q, cache.k, cache.v, self.H, self.K, self.hd,
+                                   cache.block_size, self.qk_norm_eps, write_kv=cache.write)
         attn = torch.empty_like(q)
         ops.paged_attention(q, cache.k, cache.v, attn, ctx, cache.block_table, self.H, self.K, self.hd,
                             cache.block_size, self.scale, self.window)

@@ -80,6 +80,13 @@ class StateNeed:
 class Part:
     """Base of all parts."""
 
+    # True for a part whose `forward` may be captured into a CUDA graph and replayed for another step
+    # of the same padded shape: it launches kernels and torch operations on device tensors only, reads
+    # nothing back to the host, and takes from the step's host copies (`ctx.q_lens`, `ctx.start_pos`,
+    # ...) no more than the shape.  Padding rows of such a step have slot -1 in the pages and the last
+    # state slot, which belongs to no request.  A model with a part that does not say so runs eagerly.
+    CAPTURE_SAFE = False
+
     def __init__(self, params: Mapping[str, Any], prefix: str, runtime: Runtime):
         self.params = dict(params)
         self.prefix = prefix

@@ -56,6 +56,7 @@ class PreNormBlock:
         return ps
 
     DEFERS_NORM = True
+    CAPTURE_SAFE = True
 
     def entry(self):
         return self.norm_mixer, self.mixer

@@ -15,6 +15,8 @@ from .base import Part, register_part
 
 @register_part("embedding", "embedding")
 class Embedding(Part):
+    CAPTURE_SAFE = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.vocab_size = int(params["vocab_size"])
@@ -34,6 +36,8 @@ class Embedding(Part):
 
 @register_part("lm_head", "lm_head")
 class LMHead(Part):
+    CAPTURE_SAFE = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.vocab_size = int(params["vocab_size"])

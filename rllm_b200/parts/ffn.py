@@ -14,6 +14,8 @@ from .base import FeedForward, register_part
 
 @register_part("ffn", "swiglu")
 class SwiGLU(FeedForward):
+    CAPTURE_SAFE = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.hidden_size = int(params["hidden_size"])

@@ -16,6 +16,8 @@ from .base import Norm, register_part
 
 @register_part("norm", "rms_norm")
 class RMSNorm(Norm):
+    CAPTURE_SAFE = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.size = int(params["size"])

@@ -6,8 +6,19 @@ crates/rllm-cpu/src/lib.rs:256-290).  The part owns the inv_freq table; the rota
 is applied inside the mixer's fused kernel, which receives the table.
 Parameters: head_dim, theta.  No tensors.
 
-A position part's interface: ``table()`` returns what the mixer's kernel needs (here the
-float32 inv_freq vector of head_dim/2 entries).
+A position part's interface, either of:
+
+``apply_and_store(qkv, q_norm_w, k_norm_w, eps, positions, cache, q_out, H, K, head_dim)``: the
+part itself turns the fused projection rows ``qkv`` [n, (H + 2K) * head_dim] (float32) into the
+queries ``q_out`` [n, H * head_dim] and writes keys and values to ``cache`` (a PagedKVView: ``k``,
+``v``, ``slots``, ``block_size``, ``write``) at the step's slots, applying the per-head q/k norm
+(if the weights are given) before its own encoding.  Any scheme can be written this way, with
+kernels of its own or on top of ``ops.qk_norm_rope_store`` (which, without a table, norms and
+stores without rotating).
+
+``table()``: for schemes of the form "rotate pairs (i, i + head_dim/2) by position * table[i]":
+the float32 vector of head_dim/2 entries that the fused kernel takes; the mixer then calls the
+kernel itself.  This part offers both.
 """
 from __future__ import annotations
 
@@ -18,6 +29,8 @@ from .base import Part, PartError, register_part
 
 @register_part("position", "rotary_neox")
 class RotaryNeox(Part):
+    CAPTURE_SAFE = True
+
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
         self.head_dim = int(params["head_dim"])
@@ -30,3 +43,8 @@ class RotaryNeox(Part):
 
     def table(self):
         return self.inv_freq
+
+    def apply_and_store(self, qkv, q_norm_w, k_norm_w, eps, positions, cache, q_out, H, K, head_dim):
+        from ..csrc import ops
+        return ops.qk_norm_rope_store(qkv, q_norm_w, k_norm_w, self.inv_freq, positions, cache.slots, q_out,
+                                      cache.k, cache.v, H, K, head_dim, cache.block_size, eps, write_kv=cache.write)

@@ -414,28 +414,50 @@ def test_toy_stateful_mixer_registers_and_steps(tmp_path):
                 cache.state[slot] = st
             return out
 
+    @register_part("mixer", "toy_decay_sum_on_device")
+    class ToyDecaySumOnDevice(ToyDecaySum):
+        """The same mixer written so that a step may be captured into a CUDA graph and replayed: device
+        operations only, the state slots taken from the device array, from the host no more than the
+        step's shape (the number of requests and of tokens of each)."""
+        CAPTURE_SAFE = True
+
+        def forward(self, h, ctx, cache, position, residual=None):
+            u = h.float() @ self.w_in.t()
+            out = torch.empty(h.shape[0], self.d, device=h.device)
+            lo = 0
+            for r in range(ctx.n_requests):
+                slot = cache.slots[r:r + 1].long()                   # stays on the device
+                st = cache.state.index_select(0, slot)[0]
+                for t in range(lo, lo + ctx.q_lens[r]):
+                    st = self.decay * st + u[t]
+                    out[t] = self.w_out @ st
+                cache.state.index_copy_(0, slot, st[None])
+                lo += ctx.q_lens[r]
+            return out
+
     @dataclass(frozen=True)
     class ToyConfig(ModelConfig):
         hidden: int
         vocab: int
         state: int
         decay: float
+        mixer_kind: str = "toy_decay_sum"
         architecture: str = "ToyForCausalLM"
 
         @classmethod
         def from_dict(cls, d):
-            return cls(d["hidden"], d["vocab"], d["state"], d["decay"])
+            return cls(d["hidden"], d["vocab"], d["state"], d["decay"], d.get("mixer_kind", "toy_decay_sum"))
 
         def to_dict(self):
             return dict(architectures=[self.architecture], hidden=self.hidden, vocab=self.vocab,
-                        state=self.state, decay=self.decay)
+                        state=self.state, decay=self.decay, mixer_kind=self.mixer_kind)
 
         def model_spec(self):
             norm = lambda p: PartSpec("rms_norm", {"size": self.hidden, "eps": 1e-6}, p)
             ffn = lambda p: PartSpec("swiglu", {"hidden_size": self.hidden, "intermediate_size": 2 * self.hidden}, p)
             attn = lambda p: PartSpec("attention", {"hidden_size": self.hidden, "num_heads": 2, "num_kv_heads": 1,
                                                     "head_dim": 16, "qk_norm": False, "window": 0, "scale": 0.25}, p)
-            toy = lambda p: PartSpec("toy_decay_sum", {"hidden_size": self.hidden, "state_size": self.state,
+            toy = lambda p: PartSpec(self.mixer_kind, {"hidden_size": self.hidden, "state_size": self.state,
                                                        "decay": self.decay}, p)
             layers = []
             for i, mixer in enumerate([attn, toy, attn]):
@@ -470,7 +492,7 @@ def test_toy_stateful_mixer_registers_and_steps(tmp_path):
     def run(schedule):
         eng = Engine(model, block_size=4, max_tokens=64, max_requests=2)
         assert len(eng.cache.paged) == 1 and len(eng.cache.paged[0].entries) == 1     # one shared plane
-        assert eng.cache.stateful[0].state.shape == (2, 2, 6)                          # two entries, two slots
+        assert eng.cache.stateful[0].state.shape == (2, 3, 6)                          # two entries, two slots and the one for padding rows
         return helpers.run_steps(eng, schedule)
 
     whole = run([{"entries": [{"id": r, "tokens": t, "want": list(range(len(t)))}], "end": [r]} for r, t in toks.items()])
@@ -490,14 +512,45 @@ def test_toy_stateful_mixer_registers_and_steps(tmp_path):
     first = helpers.run_steps(eng, [{"entries": [{"id": "x", "tokens": a, "want": [20]}], "end": ["x"]}])
     again = helpers.run_steps(eng, [{"entries": [{"id": "y", "tokens": a, "want": [20]}], "end": ["y"]}])
     assert rel_err(again["y", 20], first["x", 20]) < 1e-6
+    assert not eng.use_graphs                       # the toy reads its slots back to the host: never captured
+
+    # The same mixer written with device operations only declares itself safe to capture: the model's
+    # decode steps are then replayed from CUDA graphs although it holds state (three requests padded to
+    # four: the padding row reads and writes the state slot that belongs to nobody), with the results of
+    # the eager toy.
+    d2 = tmp_path / "toy_on_device"
+    d2.mkdir()
+    (d2 / "config.json").write_text(json.dumps(dict(cfg.to_dict(), mixer_kind="toy_decay_sum_on_device")))
+    write_safetensors(d2 / "model.safetensors", tensors)
+    _, model2 = load_model(d2, "float32", DEV)
+    assert model2.capture_safe and not model.capture_safe
+    toks["c"] = helpers.random_tokens(15, 50, 3)
+    whole3 = helpers.run_steps(Engine(model, block_size=4, max_tokens=64, max_requests=3),
+                               [{"entries": [{"id": r, "tokens": t, "want": list(range(len(t)))}], "end": [r]}
+                                for r, t in toks.items()])
+    eng2 = Engine(model2, block_size=4, max_tokens=64, max_requests=3)
+    steps = [{"entries": [{"id": r, "tokens": t[:3], "want": [0, 1, 2]} for r, t in toks.items()]}]
+    for j in range(3, 9):
+        steps.append({"entries": [{"id": r, "tokens": [t[j]], "want": [0]} for r, t in toks.items()]})
+    steps[-1]["end"] = list(toks)
+    got = helpers.run_steps(eng2, steps)
+    assert eng2.use_graphs and eng2.stats["graph_replays"] >= 4
+    for key, row in got.items():
+        assert rel_err(row, whole3[key]) < 1e-5, key
+    # and a request that then takes a slot starts from zero: nothing of the padding row's state leaks
+    after = helpers.run_steps(eng2, [{"entries": [{"id": "z", "tokens": a, "want": [20]}], "end": ["z"]}])
+    assert rel_err(after["z", 20], first["x", 20]) < 1e-5
 
 
 def test_toy_routed_ffn_and_other_position_encoding(tmp_path):
-    """A feed-forward that routes every token to one of several experts, and a position encoding
-    other than the model family's (rotary with interpolated positions), both defined here:
+    """A feed-forward that routes every token to one of several experts, and two position encodings
+    other than the model family's (rotary with interpolated positions through the table interface,
+    and a partial rotation that does its own step), all defined here:
     registered, chosen by a configuration layer by layer beside the framework's own parts, built,
     loaded from a model folder and stepped, with no change to the framework's files.  Never a
-    model of anyone's: two layers of toys."""
+    model of anyone's: two layers of toys.  (Toys have no plain implementation under tests/: the engine
+    cut into portions and mixed with another request is compared with the engine on whole prompts,
+    and each toy part is shown to matter by replacing it.)"""
     from rllm_b200.config import (LayerSpec, ModelConfig, ModelSpec, PartSpec, RunEntry, load_config,
                                   register_architecture)
     from rllm_b200.engine import Engine
@@ -550,21 +603,51 @@ def test_toy_routed_ffn_and_other_position_encoding(tmp_path):
         def table(self):
             return self.inv_freq
 
+    @register_part("position", "toy_partial_rotary")
+    class ToyPartialRotary(Part):
+        """Rotates only the first `rot` dims of a head, in pairs (i, i + rot/2), and leaves the rest: not
+        a table the fused kernel could take, so the part does the whole step itself (`apply_and_store`):
+        q/k norm and rotation with torch operations, then the package's kernel, without a table, to
+        write the queries out and the keys and values into the pages."""
+
+        def __init__(self, params, prefix, runtime):
+            super().__init__(params, prefix, runtime)
+            self.rot = params["rot"]
+            i = torch.arange(0, self.rot, 2, dtype=torch.float32)
+            self.inv_freq = (1.0 / torch.pow(torch.tensor(float(params["theta"])), i / self.rot)).to(runtime.device)
+
+        def apply_and_store(self, qkv, q_norm_w, k_norm_w, eps, positions, cache, q_out, H, K, head_dim):
+            from rllm_b200.csrc import ops
+            n, half = qkv.shape[0], self.rot // 2
+            x = qkv.float().view(n, H + 2 * K, head_dim).clone()
+            if q_norm_w is not None:
+                for lo, hi, w in ((0, H, q_norm_w), (H, H + K, k_norm_w)):
+                    t = x[:, lo:hi]
+                    x[:, lo:hi] = t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w
+            ang = positions.float()[:, None] * self.inv_freq[None, :]
+            c, sn = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            a, b = x[:, :H + K, :half].clone(), x[:, :H + K, half:self.rot].clone()
+            x[:, :H + K, :half] = a * c - b * sn
+            x[:, :H + K, half:self.rot] = a * sn + b * c
+            ops.qk_norm_rope_store(x.view(n, -1), None, None, None, positions, cache.slots, q_out, cache.k, cache.v,
+                                   H, K, head_dim, cache.block_size, eps, write_kv=cache.write)
+
     @dataclass(frozen=True)
     class Toy2Config(ModelConfig):
         hidden: int
         vocab: int
         experts: int
         factor: float
+        rot: int = 8
         architecture: str = "Toy2ForCausalLM"
 
         @classmethod
         def from_dict(cls, d):
-            return cls(d["hidden"], d["vocab"], d["experts"], d["factor"])
+            return cls(d["hidden"], d["vocab"], d["experts"], d["factor"], d.get("rot", 8))
 
         def to_dict(self):
             return dict(architectures=[self.architecture], hidden=self.hidden, vocab=self.vocab,
-                        experts=self.experts, factor=self.factor)
+                        experts=self.experts, factor=self.factor, rot=self.rot)
 
         def model_spec(self):
             norm = lambda p: PartSpec("rms_norm", {"size": self.hidden, "eps": 1e-5}, p)
@@ -575,6 +658,7 @@ def test_toy_routed_ffn_and_other_position_encoding(tmp_path):
                                                              "num_experts": self.experts}, p)
             dense = lambda p: PartSpec("swiglu", {"hidden_size": self.hidden, "intermediate_size": 40}, p)
             pos = [PartSpec("toy_rotary_interpolated", {"head_dim": 16, "theta": 1e4, "factor": self.factor}),
+                   PartSpec("toy_partial_rotary", {"rot": self.rot, "theta": 1e4}) if self.rot < 16 else
                    PartSpec("rotary_neox", {"head_dim": 16, "theta": 1e4})]
             layers = tuple(LayerSpec("pre_norm", attn(f"l.{i}.mix."), (routed if i == 0 else dense)(f"l.{i}.mlp."),
                                      {"mixer": norm(f"l.{i}.n1."), "ffn": norm(f"l.{i}.n2.")}, pos[i]) for i in range(2))
@@ -586,8 +670,8 @@ def test_toy_routed_ffn_and_other_position_encoding(tmp_path):
 
     register_architecture("Toy2ForCausalLM", Toy2Config)
 
-    def build(factor, sub):
-        cfg = Toy2Config(hidden=48, vocab=61, experts=4, factor=factor)
+    def build(factor, sub, rot=8):
+        cfg = Toy2Config(hidden=48, vocab=61, experts=4, factor=factor, rot=rot)
         d = tmp_path / sub
         d.mkdir()
         (d / "config.json").write_text(json.dumps(cfg.to_dict()))
@@ -619,6 +703,12 @@ def test_toy_routed_ffn_and_other_position_encoding(tmp_path):
                                   [{"entries": [{"id": "a", "tokens": a, "want": [0, 20, 36]}], "end": ["a"]}])
     assert rel_err(plain_pos["a", 0], whole["a", 0]) < 1e-6
     assert rel_err(plain_pos["a", 20], whole["a", 20]) > 1e-3 and rel_err(plain_pos["a", 36], whole["a", 36]) > 1e-3
+    # and so is the second layer's (the part that does its own step): with all 16 dims rotated by the family's
+    # part the logits differ again; rotating all 16 dims through the toy (rot = 16 is not offered) is not needed
+    full_rot = helpers.run_steps(Engine(build(4.0, "toy2_rot16", rot=16), block_size=8, max_tokens=64, max_requests=1),
+                                 [{"entries": [{"id": "a", "tokens": a, "want": [0, 20, 36]}], "end": ["a"]}])
+    assert rel_err(full_rot["a", 0], whole["a", 0]) < 1e-6
+    assert rel_err(full_rot["a", 20], whole["a", 20]) > 1e-3
 
 
 # ---------------------------------------------------------------- the command line

@@ -454,6 +454,31 @@ def test_long_context(long_dirs, dtype):
     ops.check_device_errors()
 
 
+def test_bfloat16_bounds_tell_a_one_percent_fault_from_rounding(long_dirs):
+    """The bfloat16 bounds are wide because one flipped bfloat16 ulp moves a whole logits row; this shows
+    that they are still tight enough to catch a fault of one percent: with attention as sharp as in this
+    configuration, the plain implementation with its softmax scale 1 % off (query norm weights times 1.01)
+    lies several times farther from the right one than the engine does, and outside the bound on the mean
+    that `check_long` applies to the engine."""
+    import plain_impl
+    n = 640
+    toks = helpers.random_tokens(n, LONG["vocab_size"], 700)
+    cfg, w = plain_impl.load_model(long_dirs["bfloat16"], torch.float32)
+    right = plain_impl.forward(cfg, w, toks, storage=torch.bfloat16)
+    off = dict(w)
+    for name in off:
+        if name.endswith("q_norm.weight"):
+            off[name] = off[name] * 1.01
+    wrong = plain_impl.forward(cfg, off, toks, storage=torch.bfloat16)
+    places = list(range(100, n, 9))
+    eng = make_engine(long_dirs["bfloat16"], "bfloat16", max_tokens=n + 64, max_requests=1)
+    out = helpers.run_steps(eng, [{"entries": [{"id": "a", "tokens": toks, "want": places}], "end": ["a"]}])
+    engine_err = sum(rel_err(out["a", p], right[p]) for p in places) / len(places)
+    fault_err = sum(rel_err(wrong[p], right[p]) for p in places) / len(places)
+    assert fault_err > 1.5e-2, f"the one-percent fault moves the rows by {fault_err:.2e} on average"
+    assert engine_err < 0.5 * fault_err, f"engine {engine_err:.2e}, a fault of one percent {fault_err:.2e}"
+
+
 def test_down_product_follows_the_gate_up_kernel(tmp_path):
     """A feed-forward whose gate/up matrix is large enough for the streaming product and whose down
     matrix alone would not be: both take gemv_stream in a decode step (the down product directly
