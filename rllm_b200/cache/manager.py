@@ -53,7 +53,7 @@ class _Request:
 
 class PagedGroup:
     def __init__(self, need: PagedKVNeed, entries: list, n_blocks: int, block_size: int):
-        self.need, self.entries, self.block_size = need, entries, block_size
+        self.need, self.entries, self.block_size, self.n_blocks = need, entries, block_size, n_blocks
         self.allocator = BlockAllocator(n_blocks)
         self.pool = None                               # device tensor, see CacheManager.allocate_device
 
@@ -90,7 +90,11 @@ class CacheManager:
     the earlier entry whose cache entry i reads instead of owning one (None: its own)."""
 
     def __init__(self, needs: Sequence, cache_of: Sequence, block_size: int, max_tokens: int,
-                 max_requests: int):
+                 max_requests: int, max_step_tokens: Optional[int] = None):
+        """max_step_tokens: the most tokens of one request that a step brings, if the caller keeps to
+        one (a scheduler's portion size).  A group whose layers read a window of keys only then gets a
+        smaller pool: a request never holds more of its pages than the window, a step's tokens and the
+        alignment of the release take (see RELEASE_ALIGN).  None: every group has pages for max_tokens."""
         if block_size <= 0:
             raise ValueError("block_size must be positive")
         self.block_size = block_size
@@ -114,7 +118,7 @@ class CacheManager:
             elif isinstance(need, PagedKVNeed):
                 g = next((j for j, grp in enumerate(self.paged) if grp.need == need), None)
                 if g is None:
-                    self.paged.append(PagedGroup(need, [], self.n_blocks, block_size))
+                    self.paged.append(PagedGroup(need, [], self._group_blocks(need, max_step_tokens), block_size))
                     g = len(self.paged) - 1
                 self.paged[g].entries.append(i)
                 self.entry_place.append(("kv", g, len(self.paged[g].entries) - 1))
@@ -132,6 +136,12 @@ class CacheManager:
         self.requests: dict = {}
         self.max_length = 0          # most tokens a request may hold (0: no limit); see set_max_length
 
+    def _group_blocks(self, need: PagedKVNeed, max_step_tokens) -> int:
+        if need.window <= 0 or max_step_tokens is None:
+            return self.n_blocks
+        per_request = -(-(need.window + int(max_step_tokens) + RELEASE_ALIGN) // self.block_size) + 1
+        return min(self.n_blocks, self.max_requests * per_request)
+
     def set_max_length(self, n: int) -> None:
         """Appends that would take a request beyond `n` tokens raise RequestTooLong (0: no limit)."""
         self.max_length = int(n)
@@ -140,7 +150,7 @@ class CacheManager:
     def allocate_device(self, device, dtype) -> None:
         for grp in self.paged:
             n = grp.need
-            grp.pool = torch.zeros((len(grp.entries), 2, self.n_blocks, n.num_kv_heads, self.block_size,
+            grp.pool = torch.zeros((len(grp.entries), 2, grp.n_blocks, n.num_kv_heads, self.block_size,
                                     n.head_dim), dtype=dtype, device=device)
         for grp in self.stateful:
             # one slot more than requests: the last one belongs to nobody; the padding rows of a step

@@ -31,7 +31,7 @@ def host_lib():
     if _lib is None:
         lib = build.load("host")
         lib.rllm_cache_create.restype = c_void_p
-        lib.rllm_cache_create.argtypes = [c_int, POINTER(c_int), c_int, c_int, c_int]
+        lib.rllm_cache_create.argtypes = [c_int, POINTER(c_int), c_int, c_int, c_int, POINTER(c_int)]
         lib.rllm_cache_destroy.argtypes = [c_void_p]
         for name in ("has", "length", "state_slot"):
             getattr(lib, f"rllm_cache_{name}").argtypes = [c_void_p, c_int64]
@@ -72,11 +72,14 @@ class _Slots:
 class NativeCacheManager(CacheManager):
     """Same construction and interface as CacheManager; the bookkeeping lives in C++."""
 
-    def __init__(self, needs: Sequence, cache_of: Sequence, block_size: int, max_tokens: int, max_requests: int):
-        super().__init__(needs, cache_of, block_size, max_tokens, max_requests)    # groups, entry_place
+    def __init__(self, needs: Sequence, cache_of: Sequence, block_size: int, max_tokens: int, max_requests: int,
+                 max_step_tokens=None):
+        super().__init__(needs, cache_of, block_size, max_tokens, max_requests, max_step_tokens)    # groups, entry_place
         lib = host_lib()
         windows = (c_int * max(1, len(self.paged)))(*[g.need.window for g in self.paged])
-        self._h = c_void_p(lib.rllm_cache_create(len(self.paged), windows, block_size, self.n_blocks, max_requests))
+        group_blocks = (c_int * max(1, len(self.paged)))(*[g.n_blocks for g in self.paged])
+        self._h = c_void_p(lib.rllm_cache_create(len(self.paged), windows, block_size, self.n_blocks, max_requests,
+                                                 group_blocks))
         if not self._h:
             raise ValueError("cache manager: bad sizes")
         self._ids: dict = {}

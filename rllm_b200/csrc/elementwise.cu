@@ -72,6 +72,11 @@ __global__ void add_rms_norm_kernel(float* x, const TD* delta,
     }
 }
 
+template <typename T> __device__ __forceinline__ float2 load2(const T* p);
+template <> __device__ __forceinline__ float2 load2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 load2<bf16>(const bf16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
 template <typename T> __device__ __forceinline__ void store2(T* p, float a, float b);
 template <> __device__ __forceinline__ void store2<float>(float* p, float a, float b) {
     *reinterpret_cast<float2*>(p) = make_float2(a, b);
@@ -224,25 +229,25 @@ RLLM_API int rllm_silu_mul(const void* in, int in_dtype, void* out, int out_dtyp
 // ------------------------------------------------------------------ q/k norm + rotary + paged KV write
 // Over the fused projection row qkv[t] = [q (H*hd) | k (K*hd) | v (K*hd)]:
 //   q, k heads: optional RMSNorm over the head (weight of hd entries shared by all heads),
-//               then rotate-half rotary with angle = position * inv_freq[i] on pairs (i, i+hd/2)
-//               (inv_freq has hd/2 entries; a null inv_freq means no rotation);
+//               then rotate-half rotary on pairs (i, i+hd/2) with the (cos, sin) of the token's angles
+//               from cs_table [n, hd/2] (rope_table below: angle = position * inv_freq[i], worked out
+//               once per step for all layers; a null table means no rotation);
 //   q -> q_out[t, h, :];  k, v -> the paged cache at slot = slots[t]
 //   (page = slot / bs, offset = slot % bs, layout [page][kv_head][bs][hd]); slot < 0 writes nothing;
 //   a slot beyond the pool (>= n_slots) writes nothing and sets the error word (RLLM_ERR_SLOT).
 // write_kv == 0 skips the cache (a layer that reads another layer's cache).
 //
-// One block per token and group of 8 heads (head size a multiple of 4, at most 256): the
-// token's cos/sin table is computed once in shared memory, each warp then takes one head,
-// a lane holding two neighbouring pairs (j, j + hd/2), (j + 1, j + 1 + hd/2) so that loads and
-// stores are 8 and 4 bytes wide.
+// One block per token and group of 8 heads (head size a multiple of 4, at most 256): each warp
+// takes one head, a lane holding two neighbouring pairs (j, j + hd/2), (j + 1, j + 1 + hd/2) so
+// that loads and stores are 8 and 4 bytes wide.  No shared memory, no barrier: a warp's loads are
+// all in flight at once.
 template <typename TI, typename TO, typename TC>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_w,
-                                const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
+                                const float* __restrict__ k_norm_w, const float2* cs_table,
                                 const int* __restrict__ positions, const int* __restrict__ slots,
                                 TO* __restrict__ q_out, TC* __restrict__ k_cache, TC* __restrict__ v_cache, int H,
                                 int K, int hd, int bs, float eps, int write_kv, int n_slots, int* err) {
-    __shared__ float2 cs[128];                    // (cos, sin) of pair j at this token's position
     // The attention kernel that follows may start at once: before its own wait (which ends when this
     // grid has completed, and so the product before it) it reads only the step's index arrays and
     // keys of earlier steps, and that part of it then runs beside this kernel and the end of the one before.
@@ -251,24 +256,40 @@ qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid < half) {
-        float sn = 0.f, c = 1.f;
-        if (inv_freq) sincosf((float)positions[t] * inv_freq[tid], &sn, &c);
-        cs[tid] = make_float2(c, sn);
-    }
-    __syncthreads();
     const int n_heads = write_kv ? H + 2 * K : H;
+    const size_t width = (size_t)(H + 2 * K) * hd;
+    const int units = half >> 1;                  // float2 units per half head
+    const int hx = blockIdx.y * 8 + warp;          // one head per warp
+    // this warp's head is asked for first: its values arrive while the token's angles are worked out
+    float a[2][2], b[2][2];
+    float2 cs[2][2];                              // (cos, sin) of this lane's pairs
+    const bool rotates = cs_table != nullptr && hx < H + K;
+    if (hx < n_heads) {
+        const TI* src = qkv + (size_t)t * width + (size_t)hx * hd;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int j = (lane + 32 * u) * 2;
+            a[u][0] = a[u][1] = b[u][0] = b[u][1] = 0.f;
+            cs[u][0] = cs[u][1] = make_float2(1.f, 0.f);
+            if (lane + 32 * u < units) {
+                const float2 lo = load2<TI>(src + j), hi = load2<TI>(src + j + half);
+                a[u][0] = lo.x; a[u][1] = lo.y;
+                b[u][0] = hi.x; b[u][1] = hi.y;
+                if (rotates) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + j);
+                    cs[u][0] = make_float2(c4.x, c4.y);
+                    cs[u][1] = make_float2(c4.z, c4.w);
+                }
+            }
+        }
+    }
     int slot = slots[t];
     if (slot >= n_slots) {
         if (tid == 0 && blockIdx.y == 0 && err) atomicExch(err, RLLM_ERR_SLOT);
         slot = -1;
     }
-    const size_t width = (size_t)(H + 2 * K) * hd;
-    const int units = half >> 1;                  // float2 units per half head
-    const int hx = blockIdx.y * 8 + warp;          // one head per warp
     if (hx < n_heads) {
         const int kind = hx < H ? 0 : (hx < H + K ? 1 : 2);
-        const TI* src = qkv + (size_t)t * width + (size_t)hx * hd;
         TO* qdst = nullptr;
         TC* cdst = nullptr;
         if (kind == 0) {
@@ -277,18 +298,10 @@ qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_
             const int kvh = kind == 1 ? hx - H : hx - H - K;
             cdst = (kind == 1 ? k_cache : v_cache) + (((size_t)(slot / bs) * K + kvh) * bs + (slot % bs)) * hd;
         }
-        float a[2][2], b[2][2];
         float ss = 0.f;
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int j = (lane + 32 * u) * 2;
-            a[u][0] = a[u][1] = b[u][0] = b[u][1] = 0.f;
-            if (lane + 32 * u < units) {
-                a[u][0] = to_f<TI>(src[j]); a[u][1] = to_f<TI>(src[j + 1]);
-                b[u][0] = to_f<TI>(src[j + half]); b[u][1] = to_f<TI>(src[j + half + 1]);
-                ss += a[u][0] * a[u][0] + a[u][1] * a[u][1] + b[u][0] * b[u][0] + b[u][1] * b[u][1];
-            }
-        }
+        for (int u = 0; u < 2; ++u)
+            ss += a[u][0] * a[u][0] + a[u][1] * a[u][1] + b[u][0] * b[u][0] + b[u][1] * b[u][1];
         const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
         float rs = 1.f;
         if (nw) rs = 1.0f / sqrtf(warp_sum(ss) / (float)hd + eps);
@@ -302,7 +315,7 @@ qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_
                 float av = a[u][e], bv = b[u][e];
                 if (nw) { av = av * rs * nw[j + e]; bv = bv * rs * nw[j + e + half]; }
                 if (kind != 2) {
-                    const float2 c = cs[j + e];
+                    const float2 c = cs[u][e];
                     const float a2 = av * c.x - bv * c.y, b2 = av * c.y + bv * c.x;
                     av = a2; bv = b2;
                 }
@@ -315,20 +328,41 @@ qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_
     }
 }
 
+// cs_table[t, i] = (cos, sin) of position[t] * inv_freq[i], float32, accurate sincosf: the angles of
+// a step's tokens, worked out once for all layers that share a rotary table.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ out, int half, int total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float sn, c;
+    sincosf((float)positions[i / half] * inv_freq[i % half], &sn, &c);
+    out[i] = make_float2(c, sn);
+}
+
+RLLM_API int rllm_rope_table(const int* positions, const float* inv_freq, void* out, int n, int half,
+                             cudaStream_t stream) {
+    if (n <= 0 || half <= 0) return 0;
+    const int total = n * half;
+    return rllm_launch(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, positions, inv_freq,
+                       (float2*)out, half, total);
+}
+
 RLLM_API int rllm_qk_norm_rope_store(const void* qkv, int in_dtype, const float* q_norm_w,
-                                     const float* k_norm_w, const float* inv_freq,
+                                     const float* k_norm_w, const void* cs_table,
                                      const int* positions, const int* slots, void* q_out, int q_dtype,
                                      void* k_cache, void* v_cache, int cache_dtype, int n, int H, int K,
                                      int hd, int bs, float eps, int write_kv, long long n_slots, int* err,
                                      cudaStream_t stream) {
     if (n <= 0) return 0;
     if (hd % 4 != 0 || hd > 256 || ((uintptr_t)qkv & 7) || ((uintptr_t)q_out & 7) || ((uintptr_t)k_cache & 7) ||
-        ((uintptr_t)v_cache & 7))
+        ((uintptr_t)v_cache & 7) || ((uintptr_t)cs_table & 15))
         return (int)cudaErrorInvalidValue;
     const dim3 grid(n, ((write_kv ? H + 2 * K : H) + 7) / 8);
 #define LAUNCH(TI, TO, TC)                                                                            \
     return rllm_launch(qk_norm_rope_store_token_kernel<TI, TO, TC>, grid, dim3(256), 0, stream,       \
-                       (const TI*)qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, (TO*)q_out,    \
+                       (const TI*)qkv, q_norm_w, k_norm_w, (const float2*)cs_table, positions, slots, (TO*)q_out,    \
                        (TC*)k_cache, (TC*)v_cache, H, K, hd, bs, eps, write_kv,                       \
                        (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots), err)
     if (q_dtype != cache_dtype) return (int)cudaErrorInvalidValue;

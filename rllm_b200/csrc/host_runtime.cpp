@@ -48,7 +48,8 @@ struct Request {
 struct Group {
     int window;
     Allocator alloc;
-    Group(int w, int n_blocks) : window(w), alloc(n_blocks) {}
+    int n_blocks;                    // pages of this group's pool
+    Group(int w, int nb) : window(w), alloc(nb), n_blocks(nb) {}
 };
 
 enum : int { OK = 0, ERR_OUT_OF_PAGES = 1, ERR_OUT_OF_SLOTS = 2, ERR_UNKNOWN_REQUEST = 3, ERR_BAD_ARG = 4,
@@ -67,8 +68,10 @@ struct Cache {
     int last_need = 0, last_free = 0;        // of the most recent refusal
     int max_length = 0;                      // most tokens a request may hold (0: no limit)
 
-    Cache(int n_groups, const int* windows, int bs, int nb, int mr) : block_size(bs), n_blocks(nb), max_requests(mr) {
-        for (int g = 0; g < n_groups; ++g) groups.emplace_back(windows[g], nb);
+    // group_blocks: pages of each group's pool (null: nb for all; a windowed group may have fewer)
+    Cache(int n_groups, const int* windows, int bs, int nb, int mr, const int* group_blocks = nullptr)
+        : block_size(bs), n_blocks(nb), max_requests(mr) {
+        for (int g = 0; g < n_groups; ++g) groups.emplace_back(windows[g], group_blocks ? group_blocks[g] : nb);
         for (int s = mr - 1; s >= 0; --s) free_slots.push_back(s);
     }
     int blocks_for(int tokens) const { return (tokens + block_size - 1) / block_size; }
@@ -184,13 +187,14 @@ struct Cache {
     }
     int check_invariants() const {
         for (size_t g = 0; g < groups.size(); ++g) {
-            std::vector<int> seen(n_blocks, 0);
+            const int nb = groups[g].n_blocks;
+            std::vector<int> seen(nb, 0);
             int held = 0;
             for (auto& kv : requests)
                 for (int b : kv.second.tables[g])
-                    if (b >= 0) { if (b >= n_blocks || seen[b]++) return ERR_INVARIANT; ++held; }
-            for (int b : groups[g].alloc.free_list) { if (b < 0 || b >= n_blocks || seen[b]++) return ERR_INVARIANT; }
-            if (held + groups[g].alloc.n_free() != n_blocks) return ERR_INVARIANT;
+                    if (b >= 0) { if (b >= nb || seen[b]++) return ERR_INVARIANT; ++held; }
+            for (int b : groups[g].alloc.free_list) { if (b < 0 || b >= nb || seen[b]++) return ERR_INVARIANT; }
+            if (held + groups[g].alloc.n_free() != nb) return ERR_INVARIANT;
         }
         std::vector<int> slot_seen(max_requests, 0);
         for (auto& kv : requests) {
@@ -209,9 +213,10 @@ inline int round4(int n) { return (n + 3) / 4 * 4; }
 
 #define API extern "C" __attribute__((visibility("default")))
 
-API void* rllm_cache_create(int n_groups, const int* windows, int block_size, int n_blocks, int max_requests) {
+API void* rllm_cache_create(int n_groups, const int* windows, int block_size, int n_blocks, int max_requests,
+                            const int* group_blocks) {
     if (n_groups < 0 || block_size <= 0 || n_blocks < 0 || max_requests < 0) return nullptr;
-    return new Cache(n_groups, windows, block_size, n_blocks, max_requests);
+    return new Cache(n_groups, windows, block_size, n_blocks, max_requests, group_blocks);
 }
 API void rllm_cache_destroy(void* c) { delete static_cast<Cache*>(c); }
 API int rllm_cache_has(void* c, int64_t rid) { return (int)static_cast<Cache*>(c)->requests.count(rid); }

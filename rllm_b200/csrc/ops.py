@@ -151,9 +151,23 @@ def silu_mul(gate_up, out):
     return out
 
 
+def rope_table(positions, inv_freq):
+    """(cos, sin) of positions[t] * inv_freq[i] as float32 [n, head_dim/2, 2]: the rotation angles of a
+    step's tokens, worked out once and read by every layer's qk_norm_rope_store."""
+    _need_cuda(positions, inv_freq)
+    n, half = positions.numel(), inv_freq.numel()
+    assert positions.dtype == torch.int32 and inv_freq.dtype == torch.float32 and inv_freq.is_contiguous()
+    out = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
+    _check(core().rllm_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(out), c_int(n), c_int(half), _stream()),
+           "rope_table")
+    return out
+
+
 def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_out, k_cache, v_cache,
-                       H, K, hd, block_size, eps, write_kv=True):
-    """Fused per-head q/k RMSNorm, rotary embedding and paged K/V write; see elementwise.cu."""
+                       H, K, hd, block_size, eps, write_kv=True, cs_table=None):
+    """Fused per-head q/k RMSNorm, rotary embedding and paged K/V write; see elementwise.cu.
+    The rotation takes its angles from `cs_table` (rope_table: made once per step and shared by the
+    layers); given `inv_freq` alone, the table is made here; neither: no rotation."""
     _need_cuda(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_out, k_cache, v_cache)
     _need_contig(qkv=qkv, q_out=q_out, k_cache=k_cache, v_cache=v_cache, positions=positions, slots=slots)
     n = qkv.shape[0]
@@ -166,8 +180,12 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, positions, slots, q_ou
         assert w is None or (w.dtype == torch.float32 and w.numel() == hd)
     assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == hd // 2)
     assert k_cache.dtype == q_out.dtype == v_cache.dtype
+    if cs_table is None and inv_freq is not None:
+        cs_table = rope_table(positions, inv_freq)
+    assert cs_table is None or (cs_table.dtype == torch.float32 and cs_table.shape == (n, hd // 2, 2)
+                                and cs_table.is_contiguous())
     _check(core().rllm_qk_norm_rope_store(
-        _ptr(qkv), c_int(_code(qkv)), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq), _ptr(positions),
+        _ptr(qkv), c_int(_code(qkv)), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cs_table), _ptr(positions),
         _ptr(slots), _ptr(q_out), c_int(_code(q_out)), _ptr(k_cache), _ptr(v_cache), c_int(_code(k_cache)),
         c_int(n), c_int(H), c_int(K), c_int(hd), c_int(block_size), c_float(eps),
         c_int(1 if write_kv else 0), c_longlong(k_cache.shape[0] * block_size), _ptr(error_word(qkv.device)),

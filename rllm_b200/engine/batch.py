@@ -40,4 +40,5 @@ class StepContext:
     max_q_len: int = 0
     max_ctx_len: int = 0
     state_slots: Optional[torch.Tensor] = None   # [R] slot of each request's fixed-size state
-    plans: dict = field(default_factory=dict)    # per-step scratch of the kernels' dispatchers
+    plans: dict = field(default_factory=dict)    # per-step scratch of the kernels' dispatchers (what depends on the step's shape only)
+    scratch: dict = field(default_factory=dict)  # emptied at the start of every forward pass: results that the layers of one pass share

@@ -87,9 +87,11 @@ class _DecodeGraph:
 
 class Engine:
     def __init__(self, model, block_size: int = 32, max_tokens: int = 4096, max_requests: int = 64,
-                 use_graphs: bool = True, native_host: bool = True):
+                 use_graphs: bool = True, native_host: bool = True, max_step_tokens: Optional[int] = None):
         """`native_host`: page accounting and the step's index arrays are built by the C++ host
-        runtime (default); False keeps them in Python (same results, slower)."""
+        runtime (default); False keeps them in Python (same results, slower).  `max_step_tokens`: a
+        promise that no step brings more tokens of one request than this (a scheduler's portion size);
+        layers that read a window of keys then share a smaller pool of pages (see CacheManager)."""
         if not model.loaded:
             raise ValueError("the model has no weights loaded")
         self.model = model
@@ -101,7 +103,7 @@ class Engine:
         needs, cache_of = model.cache_needs()
         self.native_host = native_host
         manager = NativeCacheManager if native_host else CacheManager
-        self.cache = manager(needs, cache_of, block_size, max_tokens, max_requests)
+        self.cache = manager(needs, cache_of, block_size, max_tokens, max_requests, max_step_tokens)
         self.cache.allocate_device(self.runtime.device, self.runtime.dtype)
         # a request never grows beyond the positions the model has: the append that would take it
         # there is refused before anything changes (RequestTooLong)

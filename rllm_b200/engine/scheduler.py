@@ -204,7 +204,7 @@ class Scheduler:
         caller then commits `plan` first and plans as usual).  A request that `plan`'s token ends
         (a stop id) has then run one token too far; its pages go back when `plan` is committed, and
         its row of the step planned here is dropped."""
-        if not plan or len(plan) != len(self.running) or any(not p.want_last or p.ahead for p in plan):
+        if not plan or len(plan) != len(self.running) or any(not p.want_last for p in plan):
             return None
         if self.waiting and len(self.running) < self.max_num_seqs:
             return None

@@ -24,6 +24,29 @@ from .sampling.host import HostSampler
 from .sampling.params import SamplingParams
 
 
+class _SampledIds:
+    """The ids a step's sampler left on the device, on their way to the host.  The copy runs on a
+    stream of its own, as soon as the sampler is done: on the engine's stream it would queue behind
+    the NEXT step, which has been launched by the time the ids are read (Scheduler.plan_ahead), and
+    the host would see them a whole step late."""
+
+    def __init__(self, ids: torch.Tensor, copy_stream):
+        self.device_ids = ids
+        self.host = torch.empty(ids.shape, dtype=ids.dtype, pin_memory=True)
+        ready = torch.cuda.Event()
+        ready.record()                                   # the sampler, on the engine's stream
+        ids.record_stream(copy_stream)
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(ready)
+            self.host.copy_(ids, non_blocking=True)
+            self.done = torch.cuda.Event()
+            self.done.record(copy_stream)
+
+    def tolist(self) -> list:
+        self.done.synchronize()
+        return self.host.tolist()
+
+
 class LLM:
     def __init__(self, model, dtype="bfloat16", device="cuda:0", ctx: int = 4096, block_size: int = 32,
                  prefill_chunk: int = 512, parallel: int = 4, kv_tokens: Optional[int] = None,
@@ -40,11 +63,12 @@ class LLM:
                               f"it are outside what the model was made for")
         kv_tokens = max(kv_tokens or ctx * parallel, ctx)
         self.engine = Engine(self.model, block_size=block_size, max_tokens=kv_tokens,
-                             max_requests=max(parallel, 1))
+                             max_requests=max(parallel, 1), max_step_tokens=prefill_chunk)
         self.ctx, self.prefill_chunk, self.parallel = ctx, prefill_chunk, parallel
         self.host_sampling = host_sampling
         self.last_stats = {}
         self.last_errors = {}
+        self._copy_stream = None
 
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens=256, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, seed: int = 0, stop_ids: Sequence[int] = (),
@@ -87,14 +111,15 @@ class LLM:
                         if not plan:
                             continue
                         ids = self._run_step(plan, host_samplers)
-                        if isinstance(ids, torch.Tensor):
+                        if isinstance(ids, _SampledIds):
                             pending = (plan, ids)
                             continue
                     else:
-                        plan, ids_dev = pending
+                        plan, sampled = pending
                         ahead = sched.plan_ahead(plan)
-                        ahead_ids = self._run_step(ahead, host_samplers, device_tokens=ids_dev) if ahead else None
-                        ids = ids_dev.tolist()
+                        ahead_ids = (self._run_step(ahead, host_samplers, device_tokens=sampled.device_ids)
+                                     if ahead else None)
+                        ids = sampled.tolist()
                         pending = (ahead, ahead_ids) if ahead else None
                     sched.commit(plan, ids)
                     for f in sched.collect():
@@ -132,7 +157,7 @@ class LLM:
 
     def _run_step(self, plan, host_samplers, device_tokens=None):
         """One engine step for the planned items and one sampled id per item that wants its last row:
-        a list (no row wanted, or sampled on the host) or an int32 tensor still on the device."""
+        a list (no row wanted, or sampled on the host) or the ids still on the device (_SampledIds)."""
         items = [StepItem(p.seq.rid, p.tokens, [p.take - 1] if p.want_last else []) for p in plan]
         logits = self.engine.step(items, device_tokens=device_tokens)
         wanted = [p for p in plan if p.want_last]
@@ -145,8 +170,11 @@ class LLM:
                 hs = host_samplers.setdefault(p.seq.rid, HostSampler(p.seq.req.params))
                 ids.append(hs.sample(rows[r], p.seq.counts))
             return ids
-        return sample_rows(logits, [p.seq.req.params for p in wanted], [p.counter for p in wanted],
-                           [p.seq.counts for p in wanted])
+        ids = sample_rows(logits, [p.seq.req.params for p in wanted], [p.counter for p in wanted],
+                          [p.seq.counts for p in wanted])
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=ids.device)
+        return _SampledIds(ids, self._copy_stream)
 
 
 class GenerationError(RuntimeError):

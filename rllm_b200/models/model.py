@@ -75,6 +75,7 @@ class DecoderModel:
     def forward(self, ctx, views):
         """Runs the step's tokens through the run order; returns float32 logits [wanted, vocab]
         (None when no row is wanted).  `views[i]` is run entry i's cache view."""
+        ctx.scratch = {}                 # what the layers of this pass share (a captured pass makes its own again)
         x = self.embedding.forward(ctx.tokens)
         pending = None
         for i, e in enumerate(self.run_order):

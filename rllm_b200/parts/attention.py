@@ -77,7 +77,7 @@ class Attention(Mixer):
         q = torch.empty((n, self.H * self.hd), dtype=dt, device=qkv.device)
         if position is not None and hasattr(position, "apply_and_store"):
             # the position part does it all: q/k norm, its own encoding, queries out, keys and values stored
-            position.apply_and_store(qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, ctx.positions, cache, q,
+            position.apply_and_store(qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, ctx, cache, q,
                                      self.H, self.K, self.hd)
         else:
             ops.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w,

@@ -8,11 +8,13 @@ Parameters: head_dim, theta.  No tensors.
 
 A position part's interface, either of:
 
-``apply_and_store(qkv, q_norm_w, k_norm_w, eps, positions, cache, q_out, H, K, head_dim)``: the
+``apply_and_store(qkv, q_norm_w, k_norm_w, eps, ctx, cache, q_out, H, K, head_dim)``: the
 part itself turns the fused projection rows ``qkv`` [n, (H + 2K) * head_dim] (float32) into the
 queries ``q_out`` [n, H * head_dim] and writes keys and values to ``cache`` (a PagedKVView: ``k``,
 ``v``, ``slots``, ``block_size``, ``write``) at the step's slots, applying the per-head q/k norm
-(if the weights are given) before its own encoding.  Any scheme can be written this way, with
+(if the weights are given) before its own encoding; ``ctx`` is the step's StepContext (positions in
+``ctx.positions``; ``ctx.scratch`` is a dictionary that lives for one forward pass, for what the
+layers of the pass can share).  Any scheme can be written this way, with
 kernels of its own or on top of ``ops.qk_norm_rope_store`` (which, without a table, norms and
 stores without rotating).
 
@@ -44,7 +46,13 @@ class RotaryNeox(Part):
     def table(self):
         return self.inv_freq
 
-    def apply_and_store(self, qkv, q_norm_w, k_norm_w, eps, positions, cache, q_out, H, K, head_dim):
+    def apply_and_store(self, qkv, q_norm_w, k_norm_w, eps, ctx, cache, q_out, H, K, head_dim):
         from ..csrc import ops
-        return ops.qk_norm_rope_store(qkv, q_norm_w, k_norm_w, self.inv_freq, positions, cache.slots, q_out,
-                                      cache.k, cache.v, H, K, head_dim, cache.block_size, eps, write_kv=cache.write)
+        # the angles of the step's tokens are the same in every layer with this table: once per pass
+        key = ("rotary_neox", self.head_dim, self.theta)
+        table = ctx.scratch.get(key)
+        if table is None:
+            table = ctx.scratch[key] = ops.rope_table(ctx.positions, self.inv_freq)
+        return ops.qk_norm_rope_store(qkv, q_norm_w, k_norm_w, None, ctx.positions, cache.slots, q_out,
+                                      cache.k, cache.v, H, K, head_dim, cache.block_size, eps, write_kv=cache.write,
+                                      cs_table=table)

@@ -616,8 +616,9 @@ def test_toy_routed_ffn_and_other_position_encoding(tmp_path):
             i = torch.arange(0, self.rot, 2, dtype=torch.float32)
             self.inv_freq = (1.0 / torch.pow(torch.tensor(float(params["theta"])), i / self.rot)).to(runtime.device)
 
-        def apply_and_store(self, qkv, q_norm_w, k_norm_w, eps, positions, cache, q_out, H, K, head_dim):
+        def apply_and_store(self, qkv, q_norm_w, k_norm_w, eps, ctx, cache, q_out, H, K, head_dim):
             from rllm_b200.csrc import ops
+            positions = ctx.positions
             n, half = qkv.shape[0], self.rot // 2
             x = qkv.float().view(n, H + 2 * K, head_dim).clone()
             if q_norm_w is not None:

@@ -342,6 +342,26 @@ def test_cache_groups_window_and_shared_cache():
         CacheManager([full, win], [None, 0], 4, 64, 2)        # reading a cache of another kind
 
 
+def test_windowed_groups_get_smaller_pools_when_the_step_size_is_promised():
+    full, win = PagedKVNeed(2, 16, 0), PagedKVNeed(2, 16, 40)
+    for manager in (CacheManager, NativeCacheManager):
+        cm = manager([full, win], [None, None], block_size=16, max_tokens=4096, max_requests=2, max_step_tokens=64)
+        assert cm.paged[0].n_blocks == 256
+        assert cm.paged[1].n_blocks == 2 * (-(-(40 + 64 + 128) // 16) + 1) == 32      # window + step + release alignment
+        for _ in range(20):                                   # 1,280 tokens in portions of 64: the small pool suffices
+            cm.append("a", 64)
+            cm.release_passed("a")
+            cm.append("b", 64)
+            cm.release_passed("b")
+            cm.check_invariants()
+        assert cm.n_free_pages(0) == 256 - 2 * 80 and cm.n_free_pages(1) >= 32 - 2 * 16
+        with pytest.raises(OutOfPages):                       # a portion beyond the promise: refused, nothing taken
+            cm.append("a", 600)
+        cm.check_invariants()
+        cm.free("a"); cm.free("b")
+        assert cm.n_free_pages(0) == 256 and cm.n_free_pages(1) == 32
+
+
 def test_a_request_cannot_outgrow_the_models_positions():
     from rllm_b200.cache import RequestTooLong
     for manager in (CacheManager, NativeCacheManager):
