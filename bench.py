@@ -110,7 +110,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: Qwen3-8B (default), 0.6B or 32B")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--block-size", type=int, default=32, help="tokens per page of the KV cache")
+    ap.add_argument("--block-size", type=int, default=16, help="tokens per page of the KV cache (16: the reference's default)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
