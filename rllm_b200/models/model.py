@@ -5,6 +5,7 @@ crates/rllm-model/src/qwen3.rs:162-234, written once per architecture there.
 """
 from __future__ import annotations
 
+import os
 from pathlib import Path
 
 import torch
@@ -12,6 +13,62 @@ import torch
 from ..config import ModelConfig, ModelSpec, load_config
 from ..parts import Runtime, build_part, part_class
 from ..weights.loader import load_checked
+
+
+TRACE_LAYERS = os.environ.get("RLLM_B200_NO_LAYER_TRACE", "0") in ("", "0")
+
+
+def _tensors_of(obj) -> dict:
+    """attribute name -> device tensor of an object (a part's weights, a cache view's planes)."""
+    return {k: v for k, v in vars(obj).items() if isinstance(v, torch.Tensor) and v.is_cuda}
+
+
+class _LayerTrace:
+    """The launches of one run entry, recorded, with what a replay for another entry of the same
+    build has to swap: the tensors of the block's parts, of the entry's cache view, of the norm
+    that follows the block (a product may prepare it), and the rows that came in."""
+
+    def __init__(self, trace, block, view, nxt, pending_in, pending_out):
+        self.trace, self.pending_out = trace, pending_out
+        self.fixed = self._fixed_roles(block, nxt)            # [address, ...] in a fixed order
+        self.view = self._view_roles(view)
+        self.inputs = self._pending_pointers(pending_in)
+        trace.freeze(self.fixed + self.view + self.inputs)
+
+    @staticmethod
+    def _fixed_roles(block, nxt) -> list:
+        """Addresses of the tensors of the block's parts and of the norm behind it; they never change,
+        so they are worked out once per (block, follower)."""
+        cache = block.__dict__.setdefault("_role_addresses", {})
+        key = id(nxt)
+        out = cache.get(key)
+        if out is None:
+            out = []
+            for part in block.parts() + ([nxt.entry()[0]] if nxt is not None else []):
+                out += [t.data_ptr() for _, t in sorted(_tensors_of(part).items())]
+            cache[key] = out
+        return out
+
+    @staticmethod
+    def _view_roles(view) -> list:
+        if view is None:
+            return []
+        return [t.data_ptr() for _, t in sorted(_tensors_of(view).items())]
+
+    @staticmethod
+    def _pending_pointers(pending) -> list:
+        from ..csrc import ops
+        if isinstance(pending, ops.NormedRows):
+            return [pending.xw.data_ptr(), pending.ssq.data_ptr()]
+        if isinstance(pending, torch.Tensor):
+            return [pending.data_ptr()]
+        return []
+
+    def replay(self, block, view, nxt, pending_in):
+        old = self.fixed + self.view + self.inputs
+        new = self._fixed_roles(block, nxt) + self._view_roles(view) + self._pending_pointers(pending_in)
+        self.trace.replay({o: n for o, n in zip(old, new) if o != n})
+        return self.pending_out
 
 
 class DecoderModel:
@@ -28,6 +85,19 @@ class DecoderModel:
         self.loaded = False
         # decode steps of this model may be captured into CUDA graphs: every part says it can be
         self.capture_safe = all(getattr(p, "CAPTURE_SAFE", False) for p in self._weighted_parts() + self.blocks)
+        # The layers of a step that launches from Python are traced once per build and replayed for the
+        # other layers of that build (ops.Trace).  A block's build: its class, its parts' kinds and
+        # parameters; only blocks all of whose parts launch through ops alone (TRACEABLE) take part.
+        self._builds = [self._build_key(b) for b in self.blocks]
+
+    @staticmethod
+    def _build_key(block):
+        if not getattr(block, "TRACEABLE", False) or not hasattr(block, "entry"):
+            return None
+        parts = block.parts()
+        if not all(getattr(p, "TRACEABLE", False) for p in parts):
+            return None
+        return (type(block).__name__,) + tuple((type(p).__name__, repr(sorted(p.params.items()))) for p in parts)
 
     # ------------------------------------------------------------------ tensors
     def _weighted_parts(self):
@@ -78,10 +148,31 @@ class DecoderModel:
         ctx.scratch = {}                 # what the layers of this pass share (a captured pass makes its own again)
         x = self.embedding.forward(ctx.tokens)
         pending = None
+        from ..csrc import ops
+        traces = {} if (TRACE_LAYERS and x.is_cuda and ops.can_trace()) else None
         for i, e in enumerate(self.run_order):
             block = self.blocks[e.layer]
             nxt = self.blocks[self.run_order[i + 1].layer] if i + 1 < len(self.run_order) else None
-            if getattr(block, "DEFERS_NORM", False) and getattr(nxt, "DEFERS_NORM", False):
+            defers = getattr(block, "DEFERS_NORM", False) and getattr(nxt, "DEFERS_NORM", False)
+            key = None
+            if traces is not None and self._builds[e.layer] is not None:
+                view = views[i]
+                # entries replay one another when they are built alike, read and write caches of the same
+                # kind through the same table, got rows of the same kind and are followed alike
+                key = (self._builds[e.layer], type(view).__name__, getattr(view, "group", None),
+                       getattr(view, "write", None), type(pending).__name__,
+                       self._builds[self.run_order[i + 1].layer] if defers else None)
+                rec = traces.get(key)
+                if rec is not None:
+                    pending = rec.replay(block, view, nxt if defers else None, pending)
+                    continue
+            if key is not None:
+                with ops.tracing() as trace:
+                    out = (block.forward(x, pending, ctx, views[i], next_entry=nxt.entry()) if defers
+                           else block.forward(x, pending, ctx, views[i]))
+                traces[key] = _LayerTrace(trace, block, views[i], nxt if defers else None, pending, out)
+                pending = out
+            elif defers:
                 pending = block.forward(x, pending, ctx, views[i], next_entry=nxt.entry())
             else:
                 pending = block.forward(x, pending, ctx, views[i])

@@ -22,6 +22,7 @@ from .base import Mixer, PagedKVNeed, PartError, register_part
 @register_part("mixer", "attention")
 class Attention(Mixer):
     CAPTURE_SAFE = True
+    TRACEABLE = True
 
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)

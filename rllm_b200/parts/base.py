@@ -87,6 +87,11 @@ class Part:
     # state slot, which belongs to no request.  A model with a part that does not say so runs eagerly.
     CAPTURE_SAFE = False
 
+    # True for a part that touches device memory through the launchers of csrc/ops only (no torch
+    # operation of its own on tensors): the launches of a layer of such parts can be recorded once and
+    # replayed for the other layers of the same build (models/model.py, ops.Trace).
+    TRACEABLE = False
+
     def __init__(self, params: Mapping[str, Any], prefix: str, runtime: Runtime):
         self.params = dict(params)
         self.prefix = prefix

@@ -57,6 +57,7 @@ class PreNormBlock:
 
     DEFERS_NORM = True
     CAPTURE_SAFE = True
+    TRACEABLE = True
 
     def entry(self):
         return self.norm_mixer, self.mixer

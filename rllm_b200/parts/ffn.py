@@ -15,6 +15,7 @@ from .base import FeedForward, register_part
 @register_part("ffn", "swiglu")
 class SwiGLU(FeedForward):
     CAPTURE_SAFE = True
+    TRACEABLE = True
 
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)

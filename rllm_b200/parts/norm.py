@@ -17,6 +17,7 @@ from .base import Norm, register_part
 @register_part("norm", "rms_norm")
 class RMSNorm(Norm):
     CAPTURE_SAFE = True
+    TRACEABLE = True
 
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)

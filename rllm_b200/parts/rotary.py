@@ -32,6 +32,7 @@ from .base import Part, PartError, register_part
 @register_part("position", "rotary_neox")
 class RotaryNeox(Part):
     CAPTURE_SAFE = True
+    TRACEABLE = True
 
     def __init__(self, params, prefix, runtime):
         super().__init__(params, prefix, runtime)
@@ -52,7 +53,8 @@ class RotaryNeox(Part):
         key = ("rotary_neox", self.head_dim, self.theta)
         table = ctx.scratch.get(key)
         if table is None:
-            table = ctx.scratch[key] = ops.rope_table(ctx.positions, self.inv_freq)
+            with ops.untraced():                  # once per pass, not once per layer that replays this one
+                table = ctx.scratch[key] = ops.rope_table(ctx.positions, self.inv_freq)
         return ops.qk_norm_rope_store(qkv, q_norm_w, k_norm_w, None, ctx.positions, cache.slots, q_out,
                                       cache.k, cache.v, H, K, head_dim, cache.block_size, eps, write_kv=cache.write,
                                       cs_table=table)
