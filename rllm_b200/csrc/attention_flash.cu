@@ -778,3 +778,6 @@ RLLM_API int rllm_paged_flash_decode_static(const void* q, const void* k_cache, 
                                       /*mode=*/1, TT, GH, head_chunks, split_keys, n_splits,
                                       /*n_pages: the caller vouches for its table*/ 0x7fffffffLL, /*err=*/nullptr, stream);
 }
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_paged_flash_attention)

@@ -113,3 +113,6 @@ RLLM_API int rllm_paged_attention_generic(const void* q, int q_dtype, const void
                        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions,
                        seq_ids, block_table, table_stride, H, K, hd, bs, scale, window, n_pages, err);
 }
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_paged_attention_generic)

@@ -515,3 +515,6 @@ RLLM_API int rllm_attention_tc(const void* q, const void* k_cache, const void* v
 }
 
 TC_DEFINE_WAIT_CONTROLS(rllm_attn_tc)
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_attention_tc)

@@ -136,3 +136,33 @@ static inline int rllm_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 bl
 }
 
 #define RLLM_LAUNCH_STATUS() ((int)cudaGetLastError())
+
+// Every launcher also has a form that takes its arguments packed into 64-bit words, one per argument
+// in order (pointers and integers as they are, a float as its 32 bits): `name_packed(words)`.  The
+// host runtime replays recorded launches through these without knowing a launcher's signature.
+#include <cstring>
+#include <utility>
+template <typename T> struct RllmWord {
+    static T get(unsigned long long w) { return (T)(long long)w; }
+};
+template <typename T> struct RllmWord<T*> {
+    static T* get(unsigned long long w) { return reinterpret_cast<T*>((uintptr_t)w); }
+};
+template <> struct RllmWord<float> {
+    static float get(unsigned long long w) {
+        const uint32_t bits = (uint32_t)w;
+        float f;
+        memcpy(&f, &bits, sizeof f);
+        return f;
+    }
+};
+template <typename R, typename... A, size_t... I>
+static inline R rllm_call_packed_impl(R (*fn)(A...), const unsigned long long* w, std::index_sequence<I...>) {
+    return fn(RllmWord<A>::get(w[I])...);
+}
+template <typename R, typename... A>
+static inline R rllm_call_packed(R (*fn)(A...), const unsigned long long* w) {
+    return rllm_call_packed_impl(fn, w, std::index_sequence_for<A...>{});
+}
+#define RLLM_PACKED(name) \
+    RLLM_API int name##_packed(const unsigned long long* w) { return rllm_call_packed(&name, w); }

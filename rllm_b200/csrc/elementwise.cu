@@ -372,3 +372,11 @@ RLLM_API int rllm_qk_norm_rope_store(const void* qkv, int in_dtype, const float*
     LAUNCH(bf16, float, float);
 #undef LAUNCH
 }
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_embed)
+RLLM_PACKED(rllm_add_rms_norm)
+RLLM_PACKED(rllm_add_inplace)
+RLLM_PACKED(rllm_silu_mul)
+RLLM_PACKED(rllm_rope_table)
+RLLM_PACKED(rllm_qk_norm_rope_store)

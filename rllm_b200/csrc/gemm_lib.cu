@@ -48,3 +48,6 @@ RLLM_API int rllm_gemm_lib(const void* A, const void* W, void* C, int c_dtype, i
                                     ldc, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
     return s == CUBLAS_STATUS_SUCCESS ? 0 : 10000 + (int)s;
 }
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_gemm_lib)

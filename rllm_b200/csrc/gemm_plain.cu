@@ -100,3 +100,6 @@ RLLM_API int rllm_gemm_plain(const void* A, int a_dtype, const void* W, int w_dt
 #undef LAUNCH
     return 0;
 }
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_gemm_plain)

@@ -658,3 +658,7 @@ RLLM_API int rllm_gemm_tc_swap(const void* W, const void* X, void* C, int c_dtyp
 }
 
 TC_DEFINE_WAIT_CONTROLS(rllm_tc)
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_gemm_tc)
+RLLM_PACKED(rllm_gemm_tc_swap)

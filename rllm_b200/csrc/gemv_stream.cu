@@ -540,3 +540,6 @@ RLLM_API int rllm_gemv_stream(const void* W, const void* X, void* C, int c_dtype
 }
 
 TC_DEFINE_WAIT_CONTROLS(rllm_stream)
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_gemv_stream)

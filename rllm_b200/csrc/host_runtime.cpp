@@ -377,3 +377,58 @@ API int rllm_step_build(void* cv, int n_items, const int64_t* rids, const int* n
     }
     return OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Replay of recorded launches.  A step that is not replayed from a CUDA graph launches the kernels
+// of one layer from Python and records them (ops.Trace); the other layers of the same build launch
+// the same kernels with their own weights and cache planes.  The record comes here as a list of
+// calls: for each, the packed-argument form of its launcher (`name_packed` in the kernel libraries:
+// one 64-bit word per argument) and its words.  `rllm_trace_replay` makes all the calls again with
+// the words that hold a layer's addresses replaced: `swap_at[i]` is the index of such a word,
+// `swap_role[i]` which of the layer's addresses (in the order the caller keeps) stands there.
+namespace {
+typedef int (*PackedFn)(const unsigned long long*);
+struct Recorded {
+    std::vector<PackedFn> fns;
+    std::vector<int> first;                 // index of a call's first word
+    std::vector<unsigned long long> words;
+    std::vector<int> swap_at, swap_role;
+};
+}  // namespace
+
+API void* rllm_trace_create(int n_calls, void* const* fns, const int* n_args, const unsigned long long* words,
+                            int n_swap, const int* swap_at, const int* swap_role) {
+    if (n_calls < 0 || n_swap < 0) return nullptr;
+    Recorded* r = new Recorded;
+    int total = 0;
+    for (int i = 0; i < n_calls; ++i) {
+        r->fns.push_back(reinterpret_cast<PackedFn>(fns[i]));
+        r->first.push_back(total);
+        total += n_args[i];
+    }
+    r->words.assign(words, words + total);
+    r->swap_at.assign(swap_at, swap_at + n_swap);
+    r->swap_role.assign(swap_role, swap_role + n_swap);
+    for (int i = 0; i < n_swap; ++i)
+        if (swap_at[i] < 0 || swap_at[i] >= total || swap_role[i] < 0) { delete r; return nullptr; }
+    return r;
+}
+API void rllm_trace_destroy(void* t) { delete static_cast<Recorded*>(t); }
+
+// Makes the recorded calls with the layer's addresses `roles[0 .. n_roles)` in their places.
+// Returns 0, or the first launcher status that was not 0, with the call's index in *failed_call.
+API int rllm_trace_replay(void* t, const unsigned long long* roles, int n_roles, int* failed_call) {
+    Recorded* r = static_cast<Recorded*>(t);
+    for (size_t i = 0; i < r->swap_at.size(); ++i) {
+        if (r->swap_role[i] >= n_roles) return ERR_BAD_ARG;
+        r->words[r->swap_at[i]] = roles[r->swap_role[i]];
+    }
+    for (size_t i = 0; i < r->fns.size(); ++i) {
+        const int st = r->fns[i](r->words.data() + r->first[i]);
+        if (st) {
+            if (failed_call) *failed_call = (int)i;
+            return st;
+        }
+    }
+    return OK;
+}

@@ -8,6 +8,7 @@ cannot be built and loaded, raises.
 from __future__ import annotations
 
 import ctypes
+import struct
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -49,33 +50,82 @@ _trace = None
 
 
 class Trace:
-    """The launches recorded between `tracing()` and its end: (launcher, arguments) in order."""
+    """The launches recorded between `tracing()` and its end: (launcher, arguments) in order.
+    `freeze(addresses)` names the addresses that belong to the layer, in the order in which
+    `replay(addresses of another layer)` gives theirs; the calls then live in the C++ host runtime
+    (host_runtime.cpp, rllm_trace_replay), which makes them again through the launchers'
+    packed-argument forms, one call from Python for the whole layer."""
 
     def __init__(self):
-        self.calls: list = []             # [launcher function, [ctypes arguments]]
-        self.keep: list = []              # tensors whose memory the arguments name
+        self.calls: list = []             # [library, launcher name, [ctypes arguments]]
+        self.keep: list = []              # tensors (and ctypes objects) whose memory the arguments name
         self.own_launches = 0
-        self._swappable = None
+        self._native = None
+        self._n_roles = 0
 
-    def freeze(self, pointers) -> None:
-        """`pointers`: every address that a replay may swap.  Notes where they stand in the calls."""
-        pointers = set(pointers)
-        self._swappable = [[i for i, a in enumerate(args) if isinstance(a, c_void_p) and a.value in pointers]
-                           for _, args in self.calls]
+    @staticmethod
+    def _word(a) -> int:
+        if isinstance(a, c_void_p):
+            return a.value or 0
+        if isinstance(a, c_float):
+            return struct.unpack("<I", struct.pack("<f", a.value))[0]
+        if isinstance(a, (c_int, c_longlong)):
+            return a.value & 0xFFFFFFFFFFFFFFFF
+        if isinstance(a, int):
+            return a & 0xFFFFFFFFFFFFFFFF
+        return ctypes.cast(a, c_void_p).value or 0          # byref(...) of an out parameter, a ctypes pointer
 
-    def replay(self, swap: dict) -> None:
-        """Launches the recorded calls again; `swap`: address in the trace -> address to use now."""
-        for (fn, args), places in zip(self.calls, self._swappable):
-            if places:
-                args = list(args)
-                for i in places:
-                    new = swap.get(args[i].value)
-                    if new is not None:
-                        args[i] = c_void_p(new)
-            status = fn(*args)
-            if status:
-                raise KernelError(f"replayed launch {getattr(fn, '__name__', fn)}: status {status}")
+    def freeze(self, addresses) -> None:
+        role_of = {}
+        for i, addr in enumerate(addresses):
+            role_of.setdefault(addr, i)
+        self._n_roles = len(addresses)
+        fns, n_args, words, swap_at, swap_role = [], [], [], [], []
+        for lib, name, args in self.calls:
+            fn = getattr(lib, name + "_packed")
+            fns.append(ctypes.cast(fn, c_void_p).value)
+            n_args.append(len(args))
+            for a in args:
+                if isinstance(a, c_void_p) and a.value in role_of:
+                    swap_at.append(len(words))
+                    swap_role.append(role_of[a.value])
+                words.append(self._word(a))
+        self.keep.append([a for _, _, args in self.calls for a in args])     # out parameters stay alive
+        host = build.load("host")
+        host.rllm_trace_create.restype = c_void_p
+        host.rllm_trace_create.argtypes = [c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int),
+                                           ctypes.POINTER(ctypes.c_ulonglong), c_int, ctypes.POINTER(c_int),
+                                           ctypes.POINTER(c_int)]
+        host.rllm_trace_replay.argtypes = [c_void_p, ctypes.POINTER(ctypes.c_ulonglong), c_int, ctypes.POINTER(c_int)]
+        host.rllm_trace_destroy.argtypes = [c_void_p]
+        n = len(fns)
+        self._host = host
+        self._native = host.rllm_trace_create(
+            n, (c_void_p * max(n, 1))(*fns), (c_int * max(n, 1))(*n_args),
+            (ctypes.c_ulonglong * max(len(words), 1))(*words), len(swap_at),
+            (c_int * max(len(swap_at), 1))(*swap_at), (c_int * max(len(swap_role), 1))(*swap_role))
+        if not self._native:
+            raise KernelError("the host runtime refused a trace of launches")
+
+    def replay(self, addresses) -> None:
+        """Launches the recorded calls again with `addresses` (same order as at `freeze`) in place."""
+        if len(addresses) != self._n_roles:
+            raise KernelError("replay: other addresses than the trace was frozen with")
+        failed = c_int(-1)
+        status = self._host.rllm_trace_replay(self._native, (ctypes.c_ulonglong * max(self._n_roles, 1))(*addresses),
+                                              self._n_roles, ctypes.byref(failed))
+        if status:
+            name = self.calls[failed.value][1] if 0 <= failed.value < len(self.calls) else "?"
+            raise KernelError(f"replayed launch {name}: status {status}")
         add_launches(self.own_launches)
+
+    def __del__(self):
+        try:
+            if self._native:
+                self._host.rllm_trace_destroy(self._native)
+                self._native = None
+        except Exception:
+            pass
 
 
 class _RecordingLibrary:
@@ -83,11 +133,11 @@ class _RecordingLibrary:
         self._lib, self._trace = lib, trace
 
     def __getattr__(self, name):
-        fn = getattr(self._lib, name)
-        trace = self._trace
+        lib, trace = self._lib, self._trace
+        fn = getattr(lib, name)
 
         def call(*args):
-            trace.calls.append((fn, list(args)))
+            trace.calls.append((lib, name, list(args)))
             return fn(*args)
         return call
 

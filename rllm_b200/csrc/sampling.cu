@@ -158,3 +158,7 @@ RLLM_API int rllm_sample_rows(const float* logits, long long row_stride, int row
     return rllm_launch(sample_rows_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride, vocab,
                        temperature, top_k, top_p, seed, counter, out);
 }
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_logit_adjust)
+RLLM_PACKED(rllm_sample_rows)

@@ -202,3 +202,6 @@ RLLM_API int rllm_skinny_gemm(const void* W, const void* X, void* C, int c_dtype
     }
     return (int)cudaErrorInvalidValue;
 }
+
+// the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
+RLLM_PACKED(rllm_skinny_gemm)

@@ -65,9 +65,7 @@ class _LayerTrace:
         return []
 
     def replay(self, block, view, nxt, pending_in):
-        old = self.fixed + self.view + self.inputs
-        new = self._fixed_roles(block, nxt) + self._view_roles(view) + self._pending_pointers(pending_in)
-        self.trace.replay({o: n for o, n in zip(old, new) if o != n})
+        self.trace.replay(self._fixed_roles(block, nxt) + self._view_roles(view) + self._pending_pointers(pending_in))
         return self.pending_out
 
 
