@@ -14,6 +14,7 @@ scheduler in the loop), timed by the wall clock as the difference between two ge
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -182,6 +183,7 @@ def main():
         for b in range(batch):
             eng.finish(b)
         del eng
+        gc.collect()                                 # the graphs of the engine hold memory pools
         torch.cuda.empty_cache()
         return {"ms": ms, "tok_s": batch * 1000.0 / ms, "bytes": wbytes + kv_bytes, "launches": launches,
                 "h2d": staging, "d2h": 4 * batch}
@@ -213,6 +215,7 @@ def main():
         ms = (long_ - short) * 1000.0 / (3 * steps)
         staging = llm.engine.last_upload_bytes
         del llm
+        gc.collect()
         torch.cuda.empty_cache()
         return {"ms": ms, "tok_s": batch * 1000.0 / ms, "h2d": staging, "d2h": 4 * batch}
 

@@ -351,10 +351,28 @@ __device__ __forceinline__ void cluster_row_sums(uint32_t red_addr, uint32_t ele
     }
 }
 
+// An RMSNorm whose kernel this product saves (the contract of gemv_stream.cu's SvNorm, with 64
+// columns per part).  Producer side, accumulate epilogue: beside the sums x it writes into C, the
+// launch writes bfloat16(x * w_next) and, per CTA, the sums of squares of the x it wrote (row b of
+// the batch in column b of part tile * splits + split; a CTA that writes nothing writes zeros).
+// Consumer side, store and SwiGLU epilogues: the rows that came in are such x * w; the result rows
+// are multiplied by 1 / sqrt(sum of the parts / d + eps).  The parts are added in a fixed order.
+struct SwapNorm {
+    bf16* xw_out;
+    const float* w_next;
+    float* ssq_out;
+    int ld_xw;
+    const float* ssq_in;
+    int n_parts;
+    float inv_d, eps;
+};
+#define SWAP_NORM_COLS 64
+
 template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(TC_THREADS, STAGES > 4 ? 1 : 2)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                    TC* __restrict__ C, int ldc, int m, int n, int K, int up_row_offset, int* __restrict__ err) {
+                    TC* __restrict__ C, int ldc, int m, int n, int K, int up_row_offset, int* __restrict__ err,
+                    const SwapNorm nrm) {
     constexpr int A_BYTES = TC_BM * TC_BK * 2;          // 128 weight rows x 64 k
     constexpr int B_BYTES = BN * TC_BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -366,7 +384,13 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     __shared__ __align__(8) uint64_t acc_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int abort_flag;
+    __shared__ float norm_part[8][SWAP_NORM_COLS];          // consumer side of a deferred norm: partial sums,
+    __shared__ float norm_rs[SWAP_NORM_COLS];               // and 1 / rms per batch row
     float* red = reinterpret_cast<float*>(smem);            // exchange buffer: the stages are free once the MMAs are done
+    float* sq = red + BN * TC_BM;                           // producer side: squares [weight row][BN + 1]
+    const bool norm_out = EPI == TC_EPI_ACCUM && nrm.ssq_out != nullptr;
+    const bool norm_in = EPI != TC_EPI_ACCUM && nrm.ssq_in != nullptr;
+    float wn = 0.f;                                         // the following norm's weight at this thread's column
     float v[BN];                                            // this thread's accumulator row (epilogue warps)
     float c_old[EPI == TC_EPI_ACCUM ? BN : 1];              // and the values of C it adds to
 #pragma unroll
@@ -471,6 +495,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
                 for (int i = 0; i < BN / 2; ++i)
                     if (i < sc_cols && sc_b0 + i < m) c_old[i] = to_f<TC>(C[(size_t)(sc_b0 + i) * ldc + n0 + sc_row]);
+                if (norm_out) wn = nrm.w_next[n0 + sc_row];
             }
         } else if (EPI == TC_EPI_ACCUM && split == 0) {
             const int out_col = n0 + quarter * 32 + lane;
@@ -478,7 +503,40 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
                 for (int b = 0; b < BN; ++b)
                     if (b < m) c_old[b] = to_f<TC>(C[(size_t)b * ldc + out_col]);
+                if (norm_out) wn = nrm.w_next[out_col];
             }
+        }
+        if (norm_in) {
+            // 1 / rms of the rows that came in, from the parts the kernel before left (ordinary loads:
+            // they are its output), also while the MMAs run: 16 threads take the 64 columns four at a
+            // time, 8 such groups share the parts, four loads in flight each
+            const int t = quarter * 32 + lane, c4 = (t & 15) * 4, g = t >> 4;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c4 < BN) {
+                for (int p0 = g; p0 < nrm.n_parts; p0 += 32) {
+                    float4 f[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int p = p0 + 8 * u;
+                        f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (p < nrm.n_parts)
+                            asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(f[u].x), "=f"(f[u].y), "=f"(f[u].z), "=f"(f[u].w)
+                                         : "l"(nrm.ssq_in + (size_t)p * SWAP_NORM_COLS + c4) : "memory");
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) { a.x += f[u].x; a.y += f[u].y; a.z += f[u].z; a.w += f[u].w; }
+                }
+            }
+            norm_part[g][c4] = a.x; norm_part[g][c4 + 1] = a.y; norm_part[g][c4 + 2] = a.z; norm_part[g][c4 + 3] = a.w;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (t < SWAP_NORM_COLS) {
+                float tot = 0.f;
+#pragma unroll
+                for (int gg = 0; gg < 8; ++gg) tot += norm_part[gg][t];
+                norm_rs[t] = 1.0f / sqrtf(tot * nrm.inv_d + nrm.eps);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
         }
         if (my_kb > 0) {
             ep_ok = mbar_wait(&acc_bar, 0, &abort_flag);
@@ -526,13 +584,29 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         else if (n_splits == 4) cluster_row_sums<BN, 4>(s_addr(red), off, acc);
         else cluster_row_sums<BN, 8>(s_addr(red), off, acc);
         const int out_col = n0 + sc_row;
-        if (ep_ok && out_col < n) {
+        const bool row_ok = ep_ok && out_col < n;
+        const int rl = sc_t & (sc_rows - 1);
 #pragma unroll
-            for (int i = 0; i < BN / 2; ++i)
-                if (i < sc_cols && sc_b0 + i < m) {
-                    const float o = (EPI == TC_EPI_ACCUM) ? acc[i] + c_old[i] : acc[i];
-                    C[(size_t)(sc_b0 + i) * ldc + out_col] = from_f<TC>(o);
+        for (int i = 0; i < BN / 2; ++i)
+            if (i < sc_cols) {
+                const int b = sc_b0 + i;
+                const bool ok = row_ok && b < m;
+                float o = (EPI == TC_EPI_ACCUM) ? acc[i] + c_old[i] : acc[i];
+                if (norm_in) o *= norm_rs[b];
+                if (ok) C[(size_t)b * ldc + out_col] = from_f<TC>(o);
+                if (norm_out) {
+                    if (ok) nrm.xw_out[(size_t)b * nrm.ld_xw + out_col] = __float2bfloat16(o * wn);
+                    sq[rl * (BN + 1) + b] = ok ? o * o : 0.f;
                 }
+            }
+        if (norm_out) {
+            // this CTA's part: for every batch row the squares of its sc_rows weight rows, in row order
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (sc_t < BN) {
+                float tot = 0.f;
+                for (int r = 0; r < sc_rows; ++r) tot += sq[r * (BN + 1) + sc_t];
+                nrm.ssq_out[(size_t)(tile * n_splits + split) * SWAP_NORM_COLS + sc_t] = tot;
+            }
         }
     } else if (warp >= 2 && split == 0) {
         // ---- epilogue, second half (the cluster's leader): add the followers' sums in rank order, write out
@@ -565,19 +639,40 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
                 for (int b = 0; b < BN; ++b)
                     if (b < m) {
-                        const float g = v[b];
-                        C[(size_t)b * ldc + out_col] = from_f<TC>(__fdividef(g, 1.0f + __expf(-g)) * red[b * 64 + row]);
+                        const float rs = norm_in ? norm_rs[b] : 1.0f;
+                        const float g = v[b] * rs;
+                        C[(size_t)b * ldc + out_col] = from_f<TC>(__fdividef(g, 1.0f + __expf(-g)) * (red[b * 64 + row] * rs));
                     }
             }
-        } else if (ep_ok && col_ok) {
+        } else {
+            const bool row_ok = ep_ok && col_ok;
             if (EPI == TC_EPI_ACCUM) {
 #pragma unroll
                 for (int b = 0; b < BN; ++b) v[b] += c_old[b];
             }
 #pragma unroll
-            for (int b = 0; b < BN; ++b)
-                if (b < m) C[(size_t)b * ldc + out_col] = from_f<TC>(v[b]);
+            for (int b = 0; b < BN; ++b) {
+                const bool ok = row_ok && b < m;
+                if (norm_in) v[b] *= norm_rs[b];
+                if (ok) C[(size_t)b * ldc + out_col] = from_f<TC>(v[b]);
+                if (norm_out) {
+                    if (ok) nrm.xw_out[(size_t)b * nrm.ld_xw + out_col] = __float2bfloat16(v[b] * wn);
+                    sq[row * (BN + 1) + b] = ok ? v[b] * v[b] : 0.f;
+                }
+            }
+            if (norm_out) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (row < BN) {
+                    float tot = 0.f;
+                    for (int r = 0; r < TC_BM; ++r) tot += sq[r * (BN + 1) + row];
+                    nrm.ssq_out[(size_t)(tile * n_splits + split) * SWAP_NORM_COLS + row] = tot;
+                }
+            }
         }
+    } else if (warp >= 2 && norm_out) {
+        // a follower of a cluster whose leader writes everything: its part is empty
+        const int t = (warp & 3) * 32 + lane;
+        if (t < BN) nrm.ssq_out[(size_t)(tile * n_splits + split) * SWAP_NORM_COLS + t] = 0.f;
     }
     if (n_splits > 1) {
         // #2: the leader has read the followers' shared memory; they may exit
@@ -589,7 +684,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 
 template <int BN, int EPI, typename TC, int STAGES>
 static int launch_swap_stages(const CUtensorMap& tw, const CUtensorMap& tx, void* C, int ldc, int m, int n, int K, int up,
-                              int n_splits, int* err, cudaStream_t stream) {
+                              int n_splits, int* err, const SwapNorm& nrm, cudaStream_t stream) {
     constexpr int ROWS_OUT = (EPI == TC_EPI_SWIGLU) ? TC_BM / 2 : TC_BM;
     constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
     auto kern = gemm_tc_swap_kernel<BN, STAGES, EPI, TC>;
@@ -601,14 +696,14 @@ static int launch_swap_stages(const CUtensorMap& tw, const CUtensorMap& tx, void
     }
     dim3 grid((n + ROWS_OUT - 1) / ROWS_OUT, n_splits);
     return rllm_launch_cluster(kern, grid, dim3(TC_THREADS), smem, stream, n_splits, tw, tx, (TC*)C, ldc, m, n, K, up,
-                               err);
+                               err, nrm);
 }
 
 // At most one CTA per SM: a ring of 8 stages, so that a single CTA keeps 190 KB in flight.  More
 // CTAs than SMs: 4 stages, two CTAs share an SM and one streams while the other starts or ends.
 template <int BN, int EPI, typename TC>
 static int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, void* C, int ldc, int m, int n, int K, int up,
-                       int n_splits, int* err, cudaStream_t stream) {
+                       int n_splits, int* err, const SwapNorm& nrm, cudaStream_t stream) {
     constexpr int ROWS_OUT = (EPI == TC_EPI_SWIGLU) ? TC_BM / 2 : TC_BM;
     const int ctas = ((n + ROWS_OUT - 1) / ROWS_OUT) * n_splits;
     static int n_sm = 0;
@@ -618,15 +713,20 @@ static int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, void* C, in
             n_sm = 148;
     }
     if (ctas <= n_sm)
-        return launch_swap_stages<BN, EPI, TC, 8>(tw, tx, C, ldc, m, n, K, up, n_splits, err, stream);
-    return launch_swap_stages<BN, EPI, TC, 4>(tw, tx, C, ldc, m, n, K, up, n_splits, err, stream);
+        return launch_swap_stages<BN, EPI, TC, 8>(tw, tx, C, ldc, m, n, K, up, n_splits, err, nrm, stream);
+    return launch_swap_stages<BN, EPI, TC, 4>(tw, tx, C, ldc, m, n, K, up, n_splits, err, nrm, stream);
 }
 
 // C[m,n] (+)= X[m,k] . W[n,k]^T for m <= 64 with W as the streamed operand (see above).
 // n_splits (1..8) CTAs of a cluster share each tile's K range.
+// A deferred RMSNorm (SwapNorm above).  Producer, accumulate epilogue, xw_out != null: xw_out
+// [m, ld_xw] bfloat16, w_next [n] float32, ssq_out [ceil(n / 128) * n_splits, 64] float32.
+// Consumer, other epilogues, ssq_in != null: n_parts_in parts of 64 columns, norm_d the length of
+// the rows that were squared, norm_eps.
 RLLM_API int rllm_gemm_tc_swap(const void* W, const void* X, void* C, int c_dtype, int m, int n, int K, int ldw,
                                int ldx, int ldc, int epilogue, int up_row_offset, int n_splits, int* err,
-                               cudaStream_t stream) {
+                               void* xw_out, int ld_xw, const float* w_next, float* ssq_out, const float* ssq_in,
+                               int n_parts_in, int norm_d, float norm_eps, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 64 || K <= 0 || (K & 7) || (ldw & 7) || (ldx & 7) || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) || !err ||
         n_splits < 1 || n_splits > 8)
@@ -639,8 +739,18 @@ RLLM_API int rllm_gemm_tc_swap(const void* W, const void* X, void* C, int c_dtyp
     const int bn = m <= 32 ? 32 : 64;
     st = make_tmap(&tx, X, m, K, ldx, bn);
     if (st) return st;
+    SwapNorm nrm = {};
+    if (xw_out) {
+        if (epilogue != TC_EPI_ACCUM || !w_next || !ssq_out || ld_xw < n) return (int)cudaErrorInvalidValue;
+        nrm.xw_out = (bf16*)xw_out; nrm.w_next = w_next; nrm.ssq_out = ssq_out; nrm.ld_xw = ld_xw;
+    }
+    if (ssq_in) {
+        if (epilogue == TC_EPI_ACCUM || n_parts_in <= 0 || norm_d <= 0 || ((uintptr_t)ssq_in & 15))
+            return (int)cudaErrorInvalidValue;
+        nrm.ssq_in = ssq_in; nrm.n_parts = n_parts_in; nrm.inv_d = 1.0f / (float)norm_d; nrm.eps = norm_eps;
+    }
 #define SWAP(BN_, EPI_, TC_) \
-    return launch_swap<BN_, EPI_, TC_>(tw, tx, C, ldc, m, n, K, up_row_offset, n_splits, err, stream)
+    return launch_swap<BN_, EPI_, TC_>(tw, tx, C, ldc, m, n, K, up_row_offset, n_splits, err, nrm, stream)
     if (epilogue == TC_EPI_STORE) {
         if (c_dtype == RLLM_F32) { if (bn == 32) { SWAP(32, TC_EPI_STORE, float); } SWAP(64, TC_EPI_STORE, float); }
         if (bn == 32) { SWAP(32, TC_EPI_STORE, bf16); }

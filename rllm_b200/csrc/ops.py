@@ -558,10 +558,16 @@ def tc_swap_splits(n_tiles: int, k: int, swiglu: bool = False, n_sm: int = 148) 
     return splits
 
 
-def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None):
+def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None, then_norm=None):
     """out (+)= a . w^T for at most 64 rows of a on the tcgen05 tensor cores with the weights as
     the streamed M operand (TMA ring), the K range split over the CTAs of a cluster where the weight
-    matrix has few rows."""
+    matrix has few rows.  `a` as NormedRows and `then_norm`: as for gemv_stream (parts of 64 columns)."""
+    scale = a if isinstance(a, NormedRows) else None
+    if scale is not None:
+        a = scale.xw
+        if scale.cols != TC_SWAP_NORM_COLS or epilogue == EPI_ACCUM:
+            raise KernelError("skinny_gemm_tc: rows with a deferred norm must come from skinny_gemm_tc and go "
+                              "with the store and SwiGLU epilogues")
     _need_cuda(a, w, out)
     if not _tc_ok(a, w) or a.shape[0] > 64:
         raise KernelError("skinny_gemm_tc needs bfloat16 operands, at most 64 rows, k a multiple of 8 and "
@@ -574,17 +580,31 @@ def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None
     if n_splits is None:
         n_splits = tc_swap_splits(n_tiles, k, epilogue == EPI_SWIGLU, sm_count(a.device))
     n_splits = max(1, min(int(n_splits), 8))
+    xw = w_next = ssq_out = None
+    if then_norm is not None:
+        if epilogue != EPI_ACCUM or scale is not None:
+            raise KernelError("skinny_gemm_tc: then_norm goes with the accumulate epilogue")
+        w_next, eps_next = then_norm
+        assert w_next.dtype == torch.float32 and w_next.numel() == n and w_next.is_contiguous()
+        xw = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+        ssq_out = torch.empty((n_tiles * n_splits, TC_SWAP_NORM_COLS), dtype=torch.float32, device=a.device)
     st = _lib("tc").rllm_gemm_tc_swap(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
         c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), c_int(n_splits),
-        _ptr(error_word(a.device)), _stream())
+        _ptr(error_word(a.device)), _ptr(xw), c_int(n), _ptr(w_next), _ptr(ssq_out),
+        _ptr(scale.ssq if scale is not None else None), c_int(scale.n_parts if scale is not None else 0),
+        c_int(scale.d if scale is not None else 0), c_float(scale.eps if scale is not None else 0.0), _stream())
     if st >= 30000:
         raise KernelError(f"skinny_gemm_tc: tensor map encoding failed (CUresult {st - 30000})")
     _check(st, "skinny_gemm_tc")
+    if then_norm is not None:
+        return NormedRows(xw, ssq_out, n_tiles * n_splits, n, float(eps_next), cols=TC_SWAP_NORM_COLS)
     return out
 
 
 STREAM_MAX_ROWS = 16
+TC_SWAP_NORM_COLS = 64            # columns of a part of sums of squares that skinny_gemm_tc writes and reads
+USE_TC_SWAP_NORM = True           # norms between two skinny_gemm_tc products are deferred into them
 _n_sm: dict = {}
 
 
@@ -609,14 +629,15 @@ def stream_plan(n: int, k: int, swiglu: bool = False, n_sm: int = 148):
 class NormedRows:
     """Rows of the residual stream on their way through an RMSNorm whose division has not happened
     yet: `xw` = bfloat16(x * norm weight) [m, d] and, per row, `n_parts` partial sums of squares of x
-    (`ssq` [n_parts, 16] float32, row b in column b).  The product that takes them as its input
+    (`ssq` [n_parts, cols] float32, row b in column b).  The product that takes them as its input
     multiplies its result rows by 1 / sqrt(sum / d + eps):  (x w r) . W^T = r ((x w) . W^T).
-    Made by an accumulating gemv_stream launch (`then_norm`), taken by `linear` and
-    `gate_up_swiglu` in place of a tensor."""
-    __slots__ = ("xw", "ssq", "n_parts", "d", "eps")
+    Made by an accumulating gemv_stream (16 columns) or skinny_gemm_tc (64 columns) launch
+    (`then_norm`), taken by `linear` and `gate_up_swiglu` in place of a tensor; the product that
+    takes them is of the kernel family that made them."""
+    __slots__ = ("xw", "ssq", "n_parts", "d", "eps", "cols")
 
-    def __init__(self, xw, ssq, n_parts, d, eps):
-        self.xw, self.ssq, self.n_parts, self.d, self.eps = xw, ssq, n_parts, d, eps
+    def __init__(self, xw, ssq, n_parts, d, eps, cols=16):
+        self.xw, self.ssq, self.n_parts, self.d, self.eps, self.cols = xw, ssq, n_parts, d, eps, cols
 
     @property
     def shape(self):
@@ -729,11 +750,18 @@ def defers_norm(m: int, w_before, w_after, swiglu_after: bool, w_lead=None, swig
     rows: both products then run on gemv_stream, the first preparing the norm (`then_norm`), the
     second dividing by the rms (NormedRows).  `w_lead`: the matrix of the product that runs directly
     before the first one, if any (the first follows its kernel family)."""
-    if w_before.dtype != torch.bfloat16 or w_after.dtype != torch.bfloat16 or not 0 < m <= 8:
+    if w_before.dtype != torch.bfloat16 or w_after.dtype != torch.bfloat16 or m <= 0:
         return False
 
     def probe(w):
         return torch.empty((m, w.shape[1]), dtype=torch.bfloat16, device="meta")
+    if STREAM_MAX_ROWS < m <= 64:
+        # both on the tcgen05 weight-streaming kernel
+        return (USE_TC_SWAP_NORM and _tc_ok(probe(w_before), w_before, True) and _tc_ok(probe(w_after), w_after, True)
+                and _prefer_tc_swap(m, w_before.shape[0], w_before.shape[1])
+                and _prefer_tc_swap(m, w_after.shape[0], w_after.shape[1], swiglu_after))
+    if m > 8:
+        return False
     first = _prefer_stream(probe(w_before), w_before, w_before.shape[0], _meta=True)
     if not first and w_lead is not None:
         first = (_prefer_stream(probe(w_lead), w_lead, w_lead.shape[0], swiglu=swiglu_lead, _meta=True)
@@ -757,9 +785,10 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None, follow
     if m == 0:
         return out
     if isinstance(a, NormedRows) or then_norm is not None:
-        # decided beforehand with defers_norm: both sides of a deferred norm run on gemv_stream
-        r = gemv_stream(a, w, out, EPI_ACCUM if accumulate else EPI_STORE, then_norm=then_norm)
-        return r
+        # decided beforehand with defers_norm: both sides of a deferred norm run on the same kernel
+        # family, gemv_stream up to 8 rows, skinny_gemm_tc from 17 rows on
+        family = gemv_stream if (a.cols == 16 if isinstance(a, NormedRows) else m <= STREAM_MAX_ROWS) else skinny_gemm_tc
+        return family(a, w, out, EPI_ACCUM if accumulate else EPI_STORE, then_norm=then_norm)
     if a.dtype == torch.float32 or w.dtype == torch.float32:
         if a.dtype != w.dtype:
             raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
@@ -791,7 +820,8 @@ def gate_up_swiglu(h, w_gate_up, out):
     m = h.shape[0]
     F = out.shape[1]
     if isinstance(h, NormedRows):
-        return gemv_stream(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
+        family = gemv_stream if h.cols == 16 else skinny_gemm_tc
+        return family(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
     if _skinny_ok(h, w_gate_up):
         if _prefer_stream(h, w_gate_up, 2 * F, swiglu=True):
             return gemv_stream(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)

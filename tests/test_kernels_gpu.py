@@ -510,6 +510,71 @@ def test_gemv_stream_deferred_norm(m, d, k, F, grid):
     o.check_device_errors()
 
 
+@pytest.mark.parametrize("m", [17, 32, 40, 64])
+@pytest.mark.parametrize("d,k,F,splits", [(1024, 512, 768, None), (4096, 4096, 12288, None), (320, 192, 100, 1),
+                                          (960, 512, 520, 3), (600, 1024, 136, 2), (520, 2048, 72, 8)])
+def test_skinny_gemm_tc_deferred_norm(m, d, k, F, splits):
+    """The same contract on the tcgen05 weight-streaming kernel (17 to 64 rows): every way its
+    epilogue is shared by a cluster (1 CTA; 2, 4, 8 CTAs that each write a share of the rows; 3 CTAs
+    whose leader writes all), widths that are no multiple of the 128-row tile."""
+    o = ops()
+    eps = 1e-5
+    a = rnd(m, k, seed=61, dtype=torch.bfloat16)
+    w_before = rnd(d, k, seed=62, scale=0.1, dtype=torch.bfloat16)
+    base = rnd(m, d, seed=63)
+    norm_w = 1.0 + rnd(d, seed=64, scale=0.1)
+    w_after = rnd(2 * F, d, seed=65, scale=0.1, dtype=torch.bfloat16)
+    x = base + a.float() @ w_before.float().t()
+    resid = base.to(DEV)
+    rows = o.skinny_gemm_tc(a.to(DEV), w_before.to(DEV), resid, epilogue=o.EPI_ACCUM, n_splits=splits,
+                            then_norm=(norm_w.to(DEV), eps))
+    assert isinstance(rows, o.NormedRows) and rows.shape == (m, d) and rows.d == d and rows.cols == 64
+    assert rel_err(resid.cpu(), x) < 1e-5
+    assert rel_err(rows.xw.float().cpu(), x * norm_w) < 5e-3         # one bfloat16 rounding
+    ssq = rows.ssq[:rows.n_parts].sum(0).cpu()
+    assert rel_err(ssq[:m], (x * x).sum(-1)) < 1e-5
+    assert (ssq[m:(32 if m <= 32 else 64)] == 0).all()
+    r = 1.0 / torch.sqrt((x * x).sum(-1, keepdim=True) / d + eps)
+    h = rows.xw.float().cpu() * r
+    ref = h @ w_after[:F].float().t()
+    for dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 5e-3)):
+        out = torch.full((m, F), float("nan"), device=DEV, dtype=dt)
+        o.skinny_gemm_tc(rows, w_after[:F].contiguous().to(DEV), out, n_splits=splits)
+        assert rel_err(out.float().cpu(), ref) < tol
+        g, u = ref, h @ w_after[F:].float().t()
+        act = torch.full((m, F), float("nan"), device=DEV, dtype=dt)
+        o.skinny_gemm_tc(rows, w_after.to(DEV), act, epilogue=o.EPI_SWIGLU, up_row_offset=F)
+        assert rel_err(act.float().cpu(), g / (1 + torch.exp(-g)) * u) < tol
+    out = torch.full((m, F), float("nan"), device=DEV)
+    o.skinny_gemm_tc(rows, w_after[:F].contiguous().to(DEV), out, n_splits=splits)
+    plain = (x * r * norm_w) @ w_after[:F].float().t()
+    assert rel_err(out.cpu(), plain) < 5e-3
+    # through the dispatch: linear and gate_up_swiglu take the rows to the kernel that made them
+    out2 = o.linear(rows, w_after[:F].contiguous().to(DEV), out_dtype=torch.float32)
+    assert rel_err(out2.cpu(), ref) < 2e-5
+    # a row's result does not depend on its batch-mates
+    resid1 = base[m - 1:].to(DEV)
+    rows1 = o.skinny_gemm_tc(a[m - 1:].to(DEV), w_before.to(DEV), resid1, epilogue=o.EPI_ACCUM, n_splits=splits,
+                             then_norm=(norm_w.to(DEV), eps))
+    out1 = torch.empty(1, F, device=DEV)
+    o.skinny_gemm_tc(rows1, w_after[:F].contiguous().to(DEV), out1, n_splits=splits)
+    assert torch.equal(out1[0], out[m - 1])
+    o.check_device_errors()
+
+
+def test_defers_norm_names_one_family_for_both_products():
+    """Which kernel family a deferred norm lies between is decided from the sizes alone: up to 8
+    rows the TMA-ring kernel, 17 to 64 rows the tcgen05 weight-streaming kernel, nothing between
+    (the plain products and the gate/up product take different kernels there) or above."""
+    o = ops()
+    w_o = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV)
+    w_gu = torch.empty(2 * 12288, 4096, dtype=torch.bfloat16, device=DEV)
+    for m, want in ((1, True), (8, True), (9, False), (16, False), (17, True), (64, True), (65, False)):
+        assert o.defers_norm(m, w_o, w_gu, True) == want, m
+    small = torch.empty(256, 128, dtype=torch.bfloat16, device=DEV)
+    assert not o.defers_norm(32, small, small, False)
+
+
 def test_gemv_stream_lm_head_size():
     """The largest matrix of the decode step (vocabulary 151,936 x 4,096): 444 CTAs, dozens of chunks each."""
     o = ops()
