@@ -191,12 +191,15 @@ def main():
     def generate_run(batch, steps, warmup):
         """The same decode steps through the entry point a user calls, LLM.generate: token ids in
         on the host, token ids out on the host, every step (the step's index arrays go up from
-        pinned memory, the sampled ids come back and decide the next step's input).  All prompts
-        are prefilled in one step, so that the `batch` requests decode in lockstep; the time of a
-        decode step is the difference between a run that generates warmup + steps tokens and one
-        that generates warmup tokens, over `steps` (wall clock, synchronized on both sides)."""
+        pinned memory, the sampled ids come back and decide the next step's input).  The prompts
+        are prefilled whole, 16 to a step at most (the activations of more would not fit beside
+        the largest shape), so the requests start and end at most three steps apart; the time of
+        a decode step is the difference between a run that generates warmup + 3 * steps tokens and
+        one that generates warmup tokens, over 3 * steps: the steps the long run has more are steps
+        in which all `batch` requests decode (wall clock, synchronized on both sides)."""
         from rllm_b200 import LLM
-        llm = LLM(model, ctx=CTX, block_size=a.block_size, prefill_chunk=batch * PROMPT, parallel=batch, kv_tokens=batch * CTX)
+        llm = LLM(model, ctx=CTX, block_size=a.block_size, prefill_chunk=min(batch, 16) * PROMPT, parallel=batch,
+                  kv_tokens=batch * CTX)
         prompts = [torch.randint(0, V, (PROMPT,), generator=g).tolist() for _ in range(batch)]
 
         def timed(n_tokens):

@@ -699,7 +699,10 @@ def gemv_stream(a, w, out, epilogue=EPI_STORE, up_row_offset=0, grid=None, stage
 
 
 USE_STREAM = True
-STREAM_MIN_WEIGHTS = 1 << 23      # below 16 MB of weights the short-lived CTAs of skinny_gemm start faster
+STREAM_MIN_WEIGHTS = 1 << 23      # below 16 MB of weights the short-lived CTAs of skinny_gemm start faster,
+STREAM_MIN_WEIGHTS_4_ROWS = 1 << 21   # but with 4 to 8 rows the norm kernels that gemv_stream saves count for more
+                                  # (decode step at the 0.6B layer sizes, all four products of 4 to 12 MB on
+                                  # gemv_stream against skinny_gemm: batch 1 -0.5 %, 2 -1.4 %, 4 +2.5 %, 8 +6.8 %)
 
 
 def _stream_ok(a, w, _meta=False) -> bool:
@@ -711,7 +714,8 @@ def _prefer_stream(a, w, n: int, swiglu: bool = False, _meta=False) -> bool:
     9 to 16 rows the gate/up product and the LM head are faster on the tcgen05 kernel (measured
     inside the decode step at batch 9, 12 and 16: 3 to 7 % of the step)."""
     m, k = a.shape
-    if not USE_STREAM or k % 64 or n * k < STREAM_MIN_WEIGHTS or not _tc_ok(a, w, _meta):
+    least = STREAM_MIN_WEIGHTS_4_ROWS if 4 <= m <= 8 else STREAM_MIN_WEIGHTS
+    if not USE_STREAM or k % 64 or n * k < least or not _tc_ok(a, w, _meta):
         return False
     return m <= 8 or (m <= STREAM_MAX_ROWS and not swiglu and n * k < (1 << 27))
 
