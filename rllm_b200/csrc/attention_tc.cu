@@ -144,6 +144,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (warp == 1) {
         tmem_alloc(&tmem_base_slot, 512);
         tmem_relinquish();
+    } else if (warp >= 2) {
+        // The request's block table goes to shared memory once (the lookups would otherwise be a
+        // chain of dependent global loads in front of every tile).  It was uploaded before the
+        // step's first kernel, so it is fetched here, beside the set-up of barriers and tensor
+        // memory and before the wait for the kernel before this one.
+        const int* table = p.block_table + (size_t)req * p.table_stride;
+        const int first_blk = kb / p.bs, n_blk = pos_last / p.bs - first_blk + 1;
+        for (int i = tid - 64; i < min(n_blk, AT_TABLE_SMEM); i += AT_THREADS - 64) s_table[i] = table[first_blk + i];
     }
     tc_fence_before();
     __syncthreads();
@@ -161,17 +169,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // tile wait in line behind the value tile before it, which itself waits for a product two
         // tiles back to release its stage.
         const bool keys = warp == 0;
-        // The request's block table goes to shared memory once (the lookups would otherwise be a
-        // chain of dependent global loads in front of every tile); lane pg then issues the two boxes
-        // (one per 64-dim half) of page pg of a tile.
+        // Lane pg issues the two boxes (one per 64-dim half) of page pg of a tile; the pages come
+        // from the table in shared memory (above).
         const int* table = p.block_table + (size_t)req * p.table_stride;
         const int pages = AT_BN / p.bs;                      // pages per key tile (<= 16)
         const int last_blk = pos_last / p.bs;                // last block that exists for this request
         const int first_blk = kb / p.bs;
         const int n_blk = last_blk - first_blk + 1;
-        if (keys)
-            for (int i = lane; i < min(n_blk, AT_TABLE_SMEM); i += 32) s_table[i] = table[first_blk + i];
-        asm volatile("bar.sync 10, 64;" ::: "memory");              // the two producer warps: the table is in place
         if (keys && lane == 0) {
             mbar_expect_tx(&q_full, AT_TILE_BYTES);
             tma_load_3d(sQ, &tmQ, 0, head0, tok0, &q_full);
