@@ -363,7 +363,7 @@ struct SwapNorm {
     float* ssq_out;
     int ld_xw;
     const float* ssq_in;
-    int n_parts;
+    int n_parts, stride;      // parts of `stride` columns: 64 from this kernel, 16 from gemv_stream and skinny_gemm
     float inv_d, eps;
 };
 #define SWAP_NORM_COLS 64
@@ -512,7 +512,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             // time, 8 such groups share the parts, four loads in flight each
             const int t = quarter * 32 + lane, c4 = (t & 15) * 4, g = t >> 4;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c4 < BN) {
+            if (c4 < BN && c4 < nrm.stride) {
                 for (int p0 = g; p0 < nrm.n_parts; p0 += 32) {
                     float4 f[4];
 #pragma unroll
@@ -522,7 +522,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                         if (p < nrm.n_parts)
                             asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
                                          : "=f"(f[u].x), "=f"(f[u].y), "=f"(f[u].z), "=f"(f[u].w)
-                                         : "l"(nrm.ssq_in + (size_t)p * SWAP_NORM_COLS + c4) : "memory");
+                                         : "l"(nrm.ssq_in + (size_t)p * nrm.stride + c4) : "memory");
                     }
 #pragma unroll
                     for (int u = 0; u < 4; ++u) { a.x += f[u].x; a.y += f[u].y; a.z += f[u].z; a.w += f[u].w; }
@@ -721,12 +721,12 @@ static int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, void* C, in
 // n_splits (1..8) CTAs of a cluster share each tile's K range.
 // A deferred RMSNorm (SwapNorm above).  Producer, accumulate epilogue, xw_out != null: xw_out
 // [m, ld_xw] bfloat16, w_next [n] float32, ssq_out [ceil(n / 128) * n_splits, 64] float32.
-// Consumer, other epilogues, ssq_in != null: n_parts_in parts of 64 columns, norm_d the length of
-// the rows that were squared, norm_eps.
+// Consumer, other epilogues, ssq_in != null: n_parts_in parts of ssq_stride_in columns (>= m, a
+// multiple of 4), norm_d the length of the rows that were squared, norm_eps.
 RLLM_API int rllm_gemm_tc_swap(const void* W, const void* X, void* C, int c_dtype, int m, int n, int K, int ldw,
                                int ldx, int ldc, int epilogue, int up_row_offset, int n_splits, int* err,
                                void* xw_out, int ld_xw, const float* w_next, float* ssq_out, const float* ssq_in,
-                               int n_parts_in, int norm_d, float norm_eps, cudaStream_t stream) {
+                               int n_parts_in, int ssq_stride_in, int norm_d, float norm_eps, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 64 || K <= 0 || (K & 7) || (ldw & 7) || (ldx & 7) || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) || !err ||
         n_splits < 1 || n_splits > 8)
@@ -745,9 +745,12 @@ RLLM_API int rllm_gemm_tc_swap(const void* W, const void* X, void* C, int c_dtyp
         nrm.xw_out = (bf16*)xw_out; nrm.w_next = w_next; nrm.ssq_out = ssq_out; nrm.ld_xw = ld_xw;
     }
     if (ssq_in) {
-        if (epilogue == TC_EPI_ACCUM || n_parts_in <= 0 || norm_d <= 0 || ((uintptr_t)ssq_in & 15))
+        // the rows' columns are read four at a time: parts of a multiple of 4 columns, all of the batch's
+        if (epilogue == TC_EPI_ACCUM || n_parts_in <= 0 || norm_d <= 0 || ((uintptr_t)ssq_in & 15) ||
+            (ssq_stride_in & 3) || ssq_stride_in < m)
             return (int)cudaErrorInvalidValue;
-        nrm.ssq_in = ssq_in; nrm.n_parts = n_parts_in; nrm.inv_d = 1.0f / (float)norm_d; nrm.eps = norm_eps;
+        nrm.ssq_in = ssq_in; nrm.n_parts = n_parts_in; nrm.stride = ssq_stride_in; nrm.inv_d = 1.0f / (float)norm_d;
+        nrm.eps = norm_eps;
     }
 #define SWAP(BN_, EPI_, TC_) \
     return launch_swap<BN_, EPI_, TC_>(tw, tx, C, ldc, m, n, K, up_row_offset, n_splits, err, nrm, stream)

@@ -84,7 +84,7 @@ struct SvNorm {
     int ld_xw;
     // consumer side (null: none)
     const float* ssq_in;
-    int n_parts;
+    int n_parts, stride;      // parts of `stride` columns (16 from this kernel and skinny_gemm, 64 from gemm_tc_swap)
     float inv_d, eps;
 };
 
@@ -228,7 +228,7 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
         waited = true;
         const int b = tid & 15, seg = tid >> 4;
         float ssum = 0.f;
-        for (int p = seg; p < nm.n_parts; p += 8) ssum += nm.ssq_in[(size_t)p * 16 + b];
+        for (int p = seg; p < nm.n_parts; p += 8) ssum += nm.ssq_in[(size_t)p * nm.stride + b];
         norm_red[seg][b] = ssum;
     }
     float ssq[NT][2];
@@ -493,7 +493,7 @@ static int launch_sv(const SvProblem& p, cudaStream_t stream) {
 RLLM_API int rllm_gemv_stream(const void* W, const void* X, void* C, int c_dtype, int m, int n, int K, int ldw,
                               int ldx, int ldc, int epilogue, int up_row_offset, int grid, int stages, int* err,
                               void* xw_out, int ld_xw, const float* w_next, float* ssq_out, int* n_parts_out,
-                              const float* ssq_in, int n_parts_in, int norm_d, float norm_eps,
+                              const float* ssq_in, int n_parts_in, int ssq_stride_in, int norm_d, float norm_eps,
                               cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 16 || K <= 0 || (K % SV_ATOM) || (ldw & 7) || (ldx & 7) || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) ||
@@ -518,8 +518,9 @@ RLLM_API int rllm_gemv_stream(const void* W, const void* X, void* C, int c_dtype
         if (n_parts_out) *n_parts_out = grid;
     }
     if (ssq_in) {
-        if (epilogue == SV_EPI_ACCUM || n_parts_in <= 0 || norm_d <= 0) return (int)cudaErrorInvalidValue;
-        p.nm.ssq_in = ssq_in; p.nm.n_parts = n_parts_in; p.nm.inv_d = 1.0f / (float)norm_d; p.nm.eps = norm_eps;
+        if (epilogue == SV_EPI_ACCUM || n_parts_in <= 0 || norm_d <= 0 || ssq_stride_in < 16) return (int)cudaErrorInvalidValue;
+        p.nm.ssq_in = ssq_in; p.nm.n_parts = n_parts_in; p.nm.stride = ssq_stride_in; p.nm.inv_d = 1.0f / (float)norm_d;
+        p.nm.eps = norm_eps;
     }
     const int nt = p.nt;
 #define SV(NT_, EPI_, TC_) return launch_sv<NT_, EPI_, TC_>(p, stream)

@@ -440,10 +440,14 @@ def _skinny_ok(a, w) -> bool:
             and a.stride(1) == 1 and w.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def skinny_gemm(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
+def skinny_gemm(a, w, out, epilogue=EPI_STORE, up_row_offset=0, then_norm=None):
     """out (+)= a . w^T for at most 64 rows of a, streaming w once (tensor-core kernel for decode).
     epilogue EPI_SWIGLU: w holds gate rows then (from up_row_offset) up rows; out[b, j] =
-    silu(gate_j) * up_j with out [m, n], n = number of gate rows."""
+    silu(gate_j) * up_j with out [m, n], n = number of gate rows.
+    `a` as NormedRows and `then_norm`: as for gemv_stream."""
+    scale = a if isinstance(a, NormedRows) else None
+    if scale is not None:
+        a = scale.xw
     _need_cuda(a, w, out)
     if not _skinny_ok(a, w):
         raise KernelError("skinny_gemm needs bfloat16 operands, at most 64 rows, k a multiple of 8 and "
@@ -455,11 +459,40 @@ def skinny_gemm(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
         assert w.shape[0] >= up_row_offset + n
     else:
         assert w.shape[0] == n
+    xw, w_next, ssq_out, cols, eps_next = _norm_producer(then_norm, epilogue, scale, m, n, -(-n // 16),
+                                                         16 if m <= 16 else 64, a.device, "skinny_gemm")
     _check(_lib("fast").rllm_skinny_gemm(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
-        c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), _stream()),
+        c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
+        _ptr(xw), c_int(n), _ptr(w_next), _ptr(ssq_out), *_norm_consumer(scale, epilogue, m, "skinny_gemm"), _stream()),
         "skinny_gemm")
+    if then_norm is not None:
+        return NormedRows(xw, ssq_out, -(-n // 16), n, eps_next, cols=cols)
     return out
+
+
+def _norm_producer(then_norm, epilogue, scale, m, n, n_parts, cols, device, who):
+    """Buffers of the producing side of a deferred norm: (xw, norm weight, parts, columns of a part, eps)."""
+    if then_norm is None:
+        return None, None, None, cols, 0.0
+    if epilogue != EPI_ACCUM or scale is not None:
+        raise KernelError(f"{who}: then_norm goes with the accumulate epilogue")
+    w_next, eps_next = then_norm
+    assert w_next.dtype == torch.float32 and w_next.numel() == n and w_next.is_contiguous()
+    xw = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+    ssq_out = torch.empty((max(n_parts, 1), cols), dtype=torch.float32, device=device)
+    return xw, w_next, ssq_out, cols, float(eps_next)
+
+
+def _norm_consumer(scale, epilogue, m, who):
+    """Arguments of the consuming side of a deferred norm: parts, their number and width, d, eps."""
+    if scale is None:
+        return _ptr(None), c_int(0), c_int(0), c_int(0), c_float(0.0)
+    if epilogue == EPI_ACCUM:
+        raise KernelError(f"{who}: rows with a deferred norm go with the store and SwiGLU epilogues")
+    if scale.cols < m:
+        raise KernelError(f"{who}: parts of {scale.cols} columns for {m} rows")
+    return _ptr(scale.ssq), c_int(scale.n_parts), c_int(scale.cols), c_int(scale.d), c_float(scale.eps)
 
 
 _error_words: dict = {}
@@ -565,9 +598,6 @@ def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None
     scale = a if isinstance(a, NormedRows) else None
     if scale is not None:
         a = scale.xw
-        if scale.cols != TC_SWAP_NORM_COLS or epilogue == EPI_ACCUM:
-            raise KernelError("skinny_gemm_tc: rows with a deferred norm must come from skinny_gemm_tc and go "
-                              "with the store and SwiGLU epilogues")
     _need_cuda(a, w, out)
     if not _tc_ok(a, w) or a.shape[0] > 64:
         raise KernelError("skinny_gemm_tc needs bfloat16 operands, at most 64 rows, k a multiple of 8 and "
@@ -580,31 +610,24 @@ def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None
     if n_splits is None:
         n_splits = tc_swap_splits(n_tiles, k, epilogue == EPI_SWIGLU, sm_count(a.device))
     n_splits = max(1, min(int(n_splits), 8))
-    xw = w_next = ssq_out = None
-    if then_norm is not None:
-        if epilogue != EPI_ACCUM or scale is not None:
-            raise KernelError("skinny_gemm_tc: then_norm goes with the accumulate epilogue")
-        w_next, eps_next = then_norm
-        assert w_next.dtype == torch.float32 and w_next.numel() == n and w_next.is_contiguous()
-        xw = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
-        ssq_out = torch.empty((n_tiles * n_splits, TC_SWAP_NORM_COLS), dtype=torch.float32, device=a.device)
+    xw, w_next, ssq_out, cols, eps_next = _norm_producer(then_norm, epilogue, scale, m, n, n_tiles * n_splits,
+                                                         TC_SWAP_NORM_COLS, a.device, "skinny_gemm_tc")
     st = _lib("tc").rllm_gemm_tc_swap(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
         c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset), c_int(n_splits),
         _ptr(error_word(a.device)), _ptr(xw), c_int(n), _ptr(w_next), _ptr(ssq_out),
-        _ptr(scale.ssq if scale is not None else None), c_int(scale.n_parts if scale is not None else 0),
-        c_int(scale.d if scale is not None else 0), c_float(scale.eps if scale is not None else 0.0), _stream())
+        *_norm_consumer(scale, epilogue, m, "skinny_gemm_tc"), _stream())
     if st >= 30000:
         raise KernelError(f"skinny_gemm_tc: tensor map encoding failed (CUresult {st - 30000})")
     _check(st, "skinny_gemm_tc")
     if then_norm is not None:
-        return NormedRows(xw, ssq_out, n_tiles * n_splits, n, float(eps_next), cols=TC_SWAP_NORM_COLS)
+        return NormedRows(xw, ssq_out, n_tiles * n_splits, n, eps_next, cols=cols)
     return out
 
 
 STREAM_MAX_ROWS = 16
 TC_SWAP_NORM_COLS = 64            # columns of a part of sums of squares that skinny_gemm_tc writes and reads
-USE_TC_SWAP_NORM = True           # norms between two skinny_gemm_tc products are deferred into them
+DEFER_NORMS = True                # a norm between two products of at most 64 rows is deferred into them
 _n_sm: dict = {}
 
 
@@ -631,9 +654,10 @@ class NormedRows:
     yet: `xw` = bfloat16(x * norm weight) [m, d] and, per row, `n_parts` partial sums of squares of x
     (`ssq` [n_parts, cols] float32, row b in column b).  The product that takes them as its input
     multiplies its result rows by 1 / sqrt(sum / d + eps):  (x w r) . W^T = r ((x w) . W^T).
-    Made by an accumulating gemv_stream (16 columns) or skinny_gemm_tc (64 columns) launch
-    (`then_norm`), taken by `linear` and `gate_up_swiglu` in place of a tensor; the product that
-    takes them is of the kernel family that made them."""
+    Made by an accumulating launch of one of the few-row kernels (`then_norm`; gemv_stream and
+    skinny_gemm up to 16 rows write parts of 16 columns, skinny_gemm above that and skinny_gemm_tc
+    parts of 64), taken by `linear` and `gate_up_swiglu` in place of a tensor; each of the three
+    kernels reads parts of either width."""
     __slots__ = ("xw", "ssq", "n_parts", "d", "eps", "cols")
 
     def __init__(self, xw, ssq, n_parts, d, eps, cols=16):
@@ -674,27 +698,18 @@ def gemv_stream(a, w, out, epilogue=EPI_STORE, up_row_offset=0, grid=None, stage
     assert out.stride(1) == 1 and w.shape[1] == k
     plan = stream_plan(n, k, epilogue == EPI_SWIGLU, sm_count(a.device))
     n_ctas = plan[0] if grid is None else grid
-    xw = w_next = ssq_out = None
     n_parts = c_int(0)
-    if then_norm is not None:
-        if epilogue != EPI_ACCUM or scale is not None:
-            raise KernelError("gemv_stream: then_norm goes with the accumulate epilogue")
-        w_next, eps_next = then_norm
-        assert w_next.dtype == torch.float32 and w_next.numel() == n and w_next.is_contiguous()
-        xw = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
-        ssq_out = torch.empty((max(n_ctas, 1), 16), dtype=torch.float32, device=a.device)
-    if scale is not None and epilogue == EPI_ACCUM:
-        raise KernelError("gemv_stream: rows with a deferred norm go with the store and SwiGLU epilogues")
+    xw, w_next, ssq_out, cols, eps_next = _norm_producer(then_norm, epilogue, scale, m, n, n_ctas, 16, a.device,
+                                                         "gemv_stream")
     st = _lib("stream").rllm_gemv_stream(
         _ptr(w), _ptr(a), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(w.stride(0)),
         c_int(a.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
         c_int(n_ctas), c_int(plan[1] if stages is None else stages),
         _ptr(error_word(a.device)), _ptr(xw), c_int(n), _ptr(w_next), _ptr(ssq_out), ctypes.byref(n_parts),
-        _ptr(scale.ssq if scale is not None else None), c_int(scale.n_parts if scale is not None else 0),
-        c_int(scale.d if scale is not None else 0), c_float(scale.eps if scale is not None else 0.0), _stream())
+        *_norm_consumer(scale, epilogue, 16, "gemv_stream"), _stream())
     _check(st, "gemv_stream")
     if then_norm is not None:
-        return NormedRows(xw, ssq_out, n_parts.value, n, float(eps_next))
+        return NormedRows(xw, ssq_out, n_parts.value, n, eps_next, cols=cols)
     return out
 
 
@@ -748,29 +763,18 @@ class Preceding:
                 and _prefer_stream(self.a, self.w, self.w.shape[0], swiglu=self.swiglu))
 
 
-def defers_norm(m: int, w_before, w_after, swiglu_after: bool, w_lead=None, swiglu_lead: bool = False) -> bool:
+def defers_norm(m: int, w_before, w_after, swiglu_after: bool = False, w_lead=None, swiglu_lead: bool = False) -> bool:
     """Whether the RMSNorm between the accumulating product with `w_before` and the product with
-    `w_after` (the fused gate/up product if swiglu_after) can do without a kernel of its own at `m`
-    rows: both products then run on gemv_stream, the first preparing the norm (`then_norm`), the
-    second dividing by the rms (NormedRows).  `w_lead`: the matrix of the product that runs directly
-    before the first one, if any (the first follows its kernel family)."""
-    if w_before.dtype != torch.bfloat16 or w_after.dtype != torch.bfloat16 or m <= 0:
+    `w_after` can do without a kernel of its own at `m` rows: both products then run on one of the
+    few-row kernels (gemv_stream, skinny_gemm, skinny_gemm_tc; `linear` and `gate_up_swiglu` choose
+    as always), the first preparing the norm (`then_norm`), the second dividing by the rms
+    (NormedRows).  The three kernels write and read the same parts of sums of squares, so any of
+    them may stand on either side.  (w_lead, swiglu_lead, swiglu_after: what the caller knows of the
+    products around; the answer does not depend on them.)"""
+    if not DEFER_NORMS or not 0 < m <= SKINNY_MAX_ROWS:
         return False
-
-    def probe(w):
-        return torch.empty((m, w.shape[1]), dtype=torch.bfloat16, device="meta")
-    if STREAM_MAX_ROWS < m <= 64:
-        # both on the tcgen05 weight-streaming kernel
-        return (USE_TC_SWAP_NORM and _tc_ok(probe(w_before), w_before, True) and _tc_ok(probe(w_after), w_after, True)
-                and _prefer_tc_swap(m, w_before.shape[0], w_before.shape[1])
-                and _prefer_tc_swap(m, w_after.shape[0], w_after.shape[1], swiglu_after))
-    if m > 8:
-        return False
-    first = _prefer_stream(probe(w_before), w_before, w_before.shape[0], _meta=True)
-    if not first and w_lead is not None:
-        first = (_prefer_stream(probe(w_lead), w_lead, w_lead.shape[0], swiglu=swiglu_lead, _meta=True)
-                 and _stream_ok(probe(w_before), w_before, _meta=True))
-    return first and _prefer_stream(probe(w_after), w_after, w_after.shape[0], swiglu=swiglu_after, _meta=True)
+    return all(w.dtype == torch.bfloat16 and w.dim() == 2 and w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0
+               and w.stride(1) == 1 and w.data_ptr() % 16 == 0 for w in (w_before, w_after))
 
 
 def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None, follow=None, then_norm=None):
@@ -788,27 +792,27 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None, follow
         out = torch.empty((m, n), dtype=out_dtype or a.dtype, device=a.device)
     if m == 0:
         return out
-    if isinstance(a, NormedRows) or then_norm is not None:
-        # decided beforehand with defers_norm: both sides of a deferred norm run on the same kernel
-        # family, gemv_stream up to 8 rows, skinny_gemm_tc from 17 rows on
-        family = gemv_stream if (a.cols == 16 if isinstance(a, NormedRows) else m <= STREAM_MAX_ROWS) else skinny_gemm_tc
-        return family(a, w, out, EPI_ACCUM if accumulate else EPI_STORE, then_norm=then_norm)
-    if a.dtype == torch.float32 or w.dtype == torch.float32:
-        if a.dtype != w.dtype:
-            raise KernelError(f"linear: activation {a.dtype} and weight {w.dtype} differ")
+    rows = a.xw if isinstance(a, NormedRows) else a          # what the rules below look at
+    if rows.dtype == torch.float32 or w.dtype == torch.float32:
+        if rows.dtype != w.dtype:
+            raise KernelError(f"linear: activation {rows.dtype} and weight {w.dtype} differ")
         return gemm_plain(a, w, out, accumulate)
     if follow is not None and stream is None and follow.took_stream():
         stream = True
-    if _skinny_ok(a, w):
+    if _skinny_ok(rows, w):
         # stream: the wish for the kernel family (a product that follows a gemv_stream launch directly
         # should be one too, whatever its size: a launch of short-lived CTAs right behind the persistent
         # ones is slow), where the shape allows it; `follow` describes the product before and decides it
-        want_stream = _prefer_stream(a, w, n) if stream is None else (stream and _stream_ok(a, w))
+        epilogue = EPI_ACCUM if accumulate else EPI_STORE
+        want_stream = _prefer_stream(rows, w, n) if stream is None else (stream and _stream_ok(rows, w))
         if want_stream:
-            return gemv_stream(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
+            return gemv_stream(a, w, out, epilogue, then_norm=then_norm)
         if _prefer_tc_swap(m, n, k) and out.data_ptr() % 16 == 0:
-            return skinny_gemm_tc(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
-        return skinny_gemm(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
+            return skinny_gemm_tc(a, w, out, epilogue, then_norm=then_norm)
+        return skinny_gemm(a, w, out, epilogue, then_norm=then_norm)
+    if isinstance(a, NormedRows) or then_norm is not None:
+        raise KernelError("linear: a deferred norm needs a product that one of the few-row kernels takes "
+                          "(ask defers_norm first)")
     aligned = (a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
                and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
                and out.stride(0) % (4 if out.dtype == torch.float32 else 8) == 0)
@@ -823,15 +827,15 @@ def gate_up_swiglu(h, w_gate_up, out):
     float32 and odd shapes: a product followed by the activation kernel."""
     m = h.shape[0]
     F = out.shape[1]
-    if isinstance(h, NormedRows):
-        family = gemv_stream if h.cols == 16 else skinny_gemm_tc
-        return family(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
-    if _skinny_ok(h, w_gate_up):
-        if _prefer_stream(h, w_gate_up, 2 * F, swiglu=True):
+    rows = h.xw if isinstance(h, NormedRows) else h
+    if _skinny_ok(rows, w_gate_up):
+        if _prefer_stream(rows, w_gate_up, 2 * F, swiglu=True):
             return gemv_stream(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
         if _prefer_tc_swap(m, 2 * F, h.shape[1], swiglu=True):
             return skinny_gemm_tc(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
         return skinny_gemm(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
+    if isinstance(h, NormedRows):
+        raise KernelError("gate_up_swiglu: a deferred norm needs a product that one of the few-row kernels takes")
     if _tc_ok(h, w_gate_up) and out.data_ptr() % 16 == 0:
         return gemm_tc(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)     # tcgen05, activation in the epilogue
     gu = linear(h, w_gate_up, out_dtype=torch.float32)     # same rounding points as the fused kernels

@@ -51,17 +51,52 @@ __device__ __forceinline__ uint4 ldg_cached(const void* p) {
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 
+// An RMSNorm whose kernel this product saves (the contract of gemv_stream.cu's SvNorm).  Producer
+// side, accumulate epilogue: beside the sums x it leaves in C, the launch writes bfloat16(x * w_next)
+// and, per CTA, the sums of squares of its 16 columns of x: ssq_out [CTAs][16 or 64] (16 up to 16
+// batch rows), batch row b in column b.  Consumer side, other epilogues: the rows that came in are
+// such x * w; the result rows are multiplied by 1 / sqrt(sum of the parts / d + eps), the parts
+// ssq_in [n_parts][stride] added in a fixed order that does not depend on the batch.
+struct SgNorm {
+    bf16* xw_out;
+    const float* w_next;
+    float* ssq_out;
+    int ld_xw;
+    const float* ssq_in;
+    int n_parts, stride;
+    float inv_d, eps;
+};
+
 
 // NT: batch columns / 8.  RT: weight row tiles per CTA (2 for SwiGLU).  U: k steps fetched ahead.
 template <int NT, int EPI, typename TC, int U>
 __global__ void __launch_bounds__(SG_THREADS)
 skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* X, TC* C, int m,
-                   int n, int k, int ldw, int ldx, int ldc, int up_row_offset) {
+                   int n, int k, int ldw, int ldx, int ldc, int up_row_offset, const SgNorm nm) {
     constexpr int RT = (EPI == EPI_SWIGLU) ? 2 : 1;
+    constexpr int NCOL = NT <= 2 ? 16 : 64;             // columns of a part of sums of squares
+    constexpr int NPG = 4;                              // thread groups that share the parts: the same for every
+                                                        // batch size, so that a row's sum is added in one order
     extern __shared__ float red[];          // [SG_WARPS][RT][16][NT*8]
+    __shared__ float nred[NPG][NCOL];       // consumer side of a deferred norm: partial sums [group][batch row]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int r0 = blockIdx.x * 16;
+    const bool norm_out = EPI == EPI_ACCUM && nm.ssq_out != nullptr;
+    const bool norm_in = EPI != EPI_ACCUM && nm.ssq_in != nullptr;
+    // the following norm's weight at the output column this thread writes (a weight: no need to wait for it)
+    const float wn = (norm_out && r0 + (threadIdx.x & 15) < n) ? nm.w_next[r0 + (threadIdx.x & 15)] : 0.f;
+    float nsum = 0.f;
+    bool norm_loaded = false;
+    // the parts of the rows' sums of squares, left by the kernel before (so: after the wait): thread
+    // (group, column) adds every NPG-th part of its column
+    auto load_norm = [&]() {
+        if (!norm_in || norm_loaded) return;
+        norm_loaded = true;
+        const int col = threadIdx.x % NCOL, pg = threadIdx.x / NCOL;
+        if (col < nm.stride && pg < NPG)
+            for (int p = pg; p < nm.n_parts; p += NPG) nsum += __ldcg(nm.ssq_in + (size_t)p * nm.stride + col);
+    };
     // rows beyond n are clamped for loading and dropped at the store
     const bf16* wrow[RT][2];
 #pragma unroll
@@ -103,7 +138,10 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* X, TC* C, int m,
         // The weights do not depend on the kernel before this one, the activations do: with a
         // programmatic dependent launch the first weight loads are already in flight while the
         // previous kernel drains.  (Without that launch attribute the wait returns at once.)
-        if (s0 == warp) pdl_wait();
+        if (s0 == warp) {
+            pdl_wait();
+            load_norm();               // beside the batch rows' loads, while the weights arrive
+        }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int kk = (s0 + u * SG_WARPS) << 5;
@@ -121,6 +159,8 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* X, TC* C, int m,
     }
     pdl_wait();                 // warps that had no k step still have to wait before they write
     pdl_launch_dependents();    // the next kernel may start to fill the SMs that this one leaves
+    load_norm();
+    if (norm_in && threadIdx.x / NCOL < NPG) nred[threadIdx.x / NCOL][threadIdx.x % NCOL] = nsum;
     // partial sums -> shared memory [warp][rt][row 0..15][batch 0..NT*8)
     constexpr int NB = NT * 8;
 #pragma unroll
@@ -135,9 +175,10 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* X, TC* C, int m,
         }
     __syncthreads();
     // outputs: 16 rows x NB batch columns; consecutive threads take consecutive rows (contiguous in C)
+    // (16 * NB is a multiple of 32: a warp is in the loop with all its lanes or not at all)
     for (int o = threadIdx.x; o < 16 * NB; o += SG_THREADS) {
         const int row = o & 15, b = o >> 4;
-        if (b >= m || r0 + row >= n) continue;
+        const bool ok = b < m && r0 + row < n;
         float v[RT];
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt) {
@@ -146,16 +187,37 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* X, TC* C, int m,
             for (int w = 0; w < SG_WARPS; ++w) s += red[((size_t)(w * RT + rt) * 16 + row) * NB + b];
             v[rt] = s;
         }
-        TC* c = C + (size_t)b * ldc + r0 + row;
-        if (EPI == EPI_STORE) *c = from_f<TC>(v[0]);
-        else if (EPI == EPI_ACCUM) *c = from_f<TC>(to_f<TC>(*c) + v[0]);
-        else *c = from_f<TC>(v[0] / (1.0f + expf(-v[0])) * v[RT - 1]);
+        if (norm_in) {
+            float tot = 0.f;
+#pragma unroll
+            for (int pg = 0; pg < NPG; ++pg) tot += nred[pg][b];
+            const float rs = 1.0f / sqrtf(tot * nm.inv_d + nm.eps);
+#pragma unroll
+            for (int rt = 0; rt < RT; ++rt) v[rt] *= rs;
+        }
+        TC* c = C + (size_t)(ok ? b : 0) * ldc + (ok ? r0 + row : 0);
+        float x_new = 0.f;
+        if (ok) {
+            if (EPI == EPI_STORE) *c = from_f<TC>(v[0]);
+            else if (EPI == EPI_ACCUM) { x_new = to_f<TC>(*c) + v[0]; *c = from_f<TC>(x_new); }
+            else *c = from_f<TC>(v[0] / (1.0f + expf(-v[0])) * v[RT - 1]);
+        }
+        if (norm_out) {
+            if (ok) nm.xw_out[(size_t)b * nm.ld_xw + r0 + row] = __float2bfloat16(x_new * wn);
+            // the 16 lanes of a half-warp hold the 16 rows of batch column b
+            float sq = x_new * x_new;
+            sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+            if (row == 0) nm.ssq_out[(size_t)blockIdx.x * NCOL + b] = sq;
+        }
     }
 }
 
 template <int NT, int EPI, typename TC>
 static int launch_sg(const bf16* W, const bf16* X, void* C, int m, int n, int k, int ldw, int ldx, int ldc,
-                     int up_row_offset, cudaStream_t stream) {
+                     int up_row_offset, const SgNorm& nm, cudaStream_t stream) {
     constexpr int RT = (EPI == EPI_SWIGLU) ? 2 : 1;
     // k steps fetched ahead: 16 weight loads of 16 bytes in flight per thread where registers allow
     constexpr int U = (NT * RT >= 8) ? 2 : (NT >= 2 ? 4 : 8 / RT);
@@ -166,39 +228,55 @@ static int launch_sg(const bf16* W, const bf16* X, void* C, int m, int n, int k,
         if (e != cudaSuccess) return (int)e;
     }
     return rllm_launch(kern, dim3((n + 15) / 16), dim3(SG_THREADS), smem, stream, W, X, (TC*)C, m, n, k, ldw, ldx,
-                       ldc, up_row_offset);
+                       ldc, up_row_offset, nm);
 }
 
 template <int EPI, typename TC>
 static int dispatch_nt(const bf16* W, const bf16* X, void* C, int m, int n, int k, int ldw, int ldx, int ldc,
-                       int up, cudaStream_t s) {
-    if (m <= 8) return launch_sg<1, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, s);
-    if (m <= 16) return launch_sg<2, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, s);
-    if (m <= 32) return launch_sg<4, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, s);
-    return launch_sg<8, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, s);
+                       int up, const SgNorm& nm, cudaStream_t s) {
+    if (m <= 8) return launch_sg<1, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, nm, s);
+    if (m <= 16) return launch_sg<2, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, nm, s);
+    if (m <= 32) return launch_sg<4, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, nm, s);
+    return launch_sg<8, EPI, TC>(W, X, C, m, n, k, ldw, ldx, ldc, up, nm, s);
 }
 
 // epilogue: 0 store, 1 accumulate into float32 C, 2 SwiGLU (W holds n gate rows then, from row
 // up_row_offset on, n up rows; C is [m, n]).  Requires m <= 64, k % 8 == 0, ldw % 8 == 0,
 // ldx % 8 == 0 and 16-byte aligned W and X; returns cudaErrorInvalidValue otherwise.
+// A deferred RMSNorm (SgNorm above).  Producer, accumulate epilogue, xw_out != null: xw_out [m, ld_xw]
+// bfloat16, w_next [n] float32, ssq_out [ceil(n / 16)][m <= 16 ? 16 : 64] float32.  Consumer, other
+// epilogues, ssq_in != null: n_parts_in parts of ssq_stride_in (>= m) columns, norm_d the length of the
+// rows that were squared, norm_eps.
 RLLM_API int rllm_skinny_gemm(const void* W, const void* X, void* C, int c_dtype, int m, int n, int k,
                               int ldw, int ldx, int ldc, int epilogue, int up_row_offset,
-                              cudaStream_t stream) {
+                              void* xw_out, int ld_xw, const float* w_next, float* ssq_out, const float* ssq_in,
+                              int n_parts_in, int ssq_stride_in, int norm_d, float norm_eps, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 64 || k <= 0 || (k & 7) || (ldw & 7) || (ldx & 7) || ((uintptr_t)W & 15) || ((uintptr_t)X & 15))
         return (int)cudaErrorInvalidValue;
     if (epilogue == EPI_ACCUM && c_dtype != RLLM_F32) return (int)cudaErrorInvalidValue;
+    SgNorm nm = {};
+    if (xw_out) {
+        if (epilogue != EPI_ACCUM || !w_next || !ssq_out || ld_xw < n) return (int)cudaErrorInvalidValue;
+        nm.xw_out = (bf16*)xw_out; nm.w_next = w_next; nm.ssq_out = ssq_out; nm.ld_xw = ld_xw;
+    }
+    if (ssq_in) {
+        if (epilogue == EPI_ACCUM || n_parts_in <= 0 || norm_d <= 0 || ssq_stride_in < m)
+            return (int)cudaErrorInvalidValue;
+        nm.ssq_in = ssq_in; nm.n_parts = n_parts_in; nm.stride = ssq_stride_in; nm.inv_d = 1.0f / (float)norm_d;
+        nm.eps = norm_eps;
+    }
     const bf16* w = (const bf16*)W;
     const bf16* x = (const bf16*)X;
     if (epilogue == EPI_STORE) {
-        return c_dtype == RLLM_F32 ? dispatch_nt<EPI_STORE, float>(w, x, C, m, n, k, ldw, ldx, ldc, 0, stream)
-                                   : dispatch_nt<EPI_STORE, bf16>(w, x, C, m, n, k, ldw, ldx, ldc, 0, stream);
+        return c_dtype == RLLM_F32 ? dispatch_nt<EPI_STORE, float>(w, x, C, m, n, k, ldw, ldx, ldc, 0, nm, stream)
+                                   : dispatch_nt<EPI_STORE, bf16>(w, x, C, m, n, k, ldw, ldx, ldc, 0, nm, stream);
     } else if (epilogue == EPI_ACCUM) {
-        return dispatch_nt<EPI_ACCUM, float>(w, x, C, m, n, k, ldw, ldx, ldc, 0, stream);
+        return dispatch_nt<EPI_ACCUM, float>(w, x, C, m, n, k, ldw, ldx, ldc, 0, nm, stream);
     } else if (epilogue == EPI_SWIGLU) {
         return c_dtype == RLLM_F32
-                   ? dispatch_nt<EPI_SWIGLU, float>(w, x, C, m, n, k, ldw, ldx, ldc, up_row_offset, stream)
-                   : dispatch_nt<EPI_SWIGLU, bf16>(w, x, C, m, n, k, ldw, ldx, ldc, up_row_offset, stream);
+                   ? dispatch_nt<EPI_SWIGLU, float>(w, x, C, m, n, k, ldw, ldx, ldc, up_row_offset, nm, stream)
+                   : dispatch_nt<EPI_SWIGLU, bf16>(w, x, C, m, n, k, ldw, ldx, ldc, up_row_offset, nm, stream);
     }
     return (int)cudaErrorInvalidValue;
 }

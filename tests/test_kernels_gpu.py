@@ -562,17 +562,86 @@ def test_skinny_gemm_tc_deferred_norm(m, d, k, F, splits):
     o.check_device_errors()
 
 
-def test_defers_norm_names_one_family_for_both_products():
-    """Which kernel family a deferred norm lies between is decided from the sizes alone: up to 8
-    rows the TMA-ring kernel, 17 to 64 rows the tcgen05 weight-streaming kernel, nothing between
-    (the plain products and the gate/up product take different kernels there) or above."""
+def test_defers_norm_rule():
+    """A norm between two products is deferred whenever both can run on a few-row kernel: bfloat16
+    matrices with rows of a multiple of 8 elements, at most 64 batch rows."""
     o = ops()
     w_o = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV)
     w_gu = torch.empty(2 * 12288, 4096, dtype=torch.bfloat16, device=DEV)
-    for m, want in ((1, True), (8, True), (9, False), (16, False), (17, True), (64, True), (65, False)):
+    for m, want in ((1, True), (8, True), (9, True), (16, True), (17, True), (64, True), (65, False), (0, False)):
         assert o.defers_norm(m, w_o, w_gu, True) == want, m
     small = torch.empty(256, 128, dtype=torch.bfloat16, device=DEV)
-    assert not o.defers_norm(32, small, small, False)
+    assert o.defers_norm(32, small, small)
+    assert not o.defers_norm(8, small, torch.empty(64, 100, dtype=torch.bfloat16, device=DEV))      # rows of 100 elements
+    assert not o.defers_norm(8, small.float(), small)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 13, 16, 17, 40, 64])
+@pytest.mark.parametrize("d,k,F", [(320, 192, 100), (1024, 2048, 3072), (72, 40, 56)])
+def test_skinny_gemm_deferred_norm(m, d, k, F):
+    """The same contract on the mma.sync kernel of short-lived CTAs (small matrices, any row count
+    up to 64): parts of 16 columns up to 16 rows, of 64 above."""
+    o = ops()
+    eps = 1e-5
+    a = rnd(m, k, seed=71, dtype=torch.bfloat16)
+    w_before = rnd(d, k, seed=72, scale=0.1, dtype=torch.bfloat16)
+    base = rnd(m, d, seed=73)
+    norm_w = 1.0 + rnd(d, seed=74, scale=0.1)
+    w_after = rnd(2 * F, d, seed=75, scale=0.1, dtype=torch.bfloat16)
+    x = base + a.float() @ w_before.float().t()
+    resid = base.to(DEV)
+    rows = o.skinny_gemm(a.to(DEV), w_before.to(DEV), resid, epilogue=o.EPI_ACCUM, then_norm=(norm_w.to(DEV), eps))
+    assert isinstance(rows, o.NormedRows) and rows.shape == (m, d) and rows.cols == (16 if m <= 16 else 64)
+    assert rows.n_parts == -(-d // 16)
+    assert rel_err(resid.cpu(), x) < 1e-5
+    assert rel_err(rows.xw.float().cpu(), x * norm_w) < 5e-3
+    ssq = rows.ssq[:rows.n_parts].sum(0).cpu()
+    assert rel_err(ssq[:m], (x * x).sum(-1)) < 1e-5
+    r = 1.0 / torch.sqrt((x * x).sum(-1, keepdim=True) / d + eps)
+    h = rows.xw.float().cpu() * r
+    ref = h @ w_after[:F].float().t()
+    out = torch.full((m, F), float("nan"), device=DEV)
+    o.skinny_gemm(rows, w_after[:F].contiguous().to(DEV), out)
+    assert rel_err(out.cpu(), ref) < 2e-5
+    g, u = ref, h @ w_after[F:].float().t()
+    act = torch.full((m, F), float("nan"), device=DEV, dtype=torch.bfloat16)
+    o.skinny_gemm(rows, w_after.to(DEV), act, epilogue=o.EPI_SWIGLU, up_row_offset=F)
+    assert rel_err(act.float().cpu(), g / (1 + torch.exp(-g)) * u) < 5e-3
+    # a row's result does not depend on its batch-mates
+    resid1 = base[m - 1:].to(DEV)
+    rows1 = o.skinny_gemm(a[m - 1:].to(DEV), w_before.to(DEV), resid1, epilogue=o.EPI_ACCUM,
+                          then_norm=(norm_w.to(DEV), eps))
+    out1 = torch.empty(1, F, device=DEV)
+    o.skinny_gemm(rows1, w_after[:F].contiguous().to(DEV), out1)
+    assert torch.equal(out1[0], out[m - 1])
+    o.check_device_errors()
+
+
+@pytest.mark.parametrize("m", [2, 8, 12, 16, 24, 64])
+def test_deferred_norm_across_kernels(m):
+    """Any of the three few-row kernels may prepare a norm and any may finish it: the parts they
+    leave differ only in their width (16 or 64 columns), which every reader is told."""
+    o = ops()
+    eps, d, k, F = 1e-6, 1024, 512, 640
+    a = rnd(m, k, seed=81, dtype=torch.bfloat16)
+    w_before = rnd(d, k, seed=82, scale=0.1, dtype=torch.bfloat16).to(DEV)
+    base = rnd(m, d, seed=83)
+    norm_w = (1.0 + rnd(d, seed=84, scale=0.1)).to(DEV)
+    w_after = rnd(F, d, seed=85, scale=0.1, dtype=torch.bfloat16).to(DEV)
+    x = base + a.float() @ w_before.float().cpu().t()
+    r = 1.0 / torch.sqrt((x * x).sum(-1, keepdim=True) / d + eps)
+    kernels = {"skinny": o.skinny_gemm, "swap": o.skinny_gemm_tc}
+    if m <= 16:
+        kernels["stream"] = o.gemv_stream
+    for pname, producer in kernels.items():
+        resid = base.to(DEV)
+        rows = producer(a.to(DEV), w_before, resid, epilogue=o.EPI_ACCUM, then_norm=(norm_w, eps))
+        ref = (rows.xw.float().cpu() * r) @ w_after.float().cpu().t()
+        for cname, consumer in kernels.items():
+            out = torch.full((m, F), float("nan"), device=DEV)
+            consumer(rows, w_after, out)
+            assert rel_err(out.cpu(), ref) < 2e-5, (pname, cname)
+    o.check_device_errors()
 
 
 def test_gemv_stream_lm_head_size():

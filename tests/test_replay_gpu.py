@@ -492,9 +492,9 @@ def test_down_product_follows_the_gate_up_kernel(tmp_path):
     seen = []
     real = ops.gemv_stream
 
-    def spy(a, w, out, epilogue=0, up_row_offset=0, grid=None, stages=None):
+    def spy(a, w, out, epilogue=0, up_row_offset=0, grid=None, stages=None, then_norm=None):
         seen.append((tuple(w.shape), epilogue))
-        return real(a, w, out, epilogue, up_row_offset, grid, stages)
+        return real(a, w, out, epilogue, up_row_offset, grid, stages, then_norm)
 
     ops.gemv_stream = spy
     try:
