@@ -75,8 +75,11 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* X, TC* C, int m,
                    int n, int k, int ldw, int ldx, int ldc, int up_row_offset, const SgNorm nm) {
     constexpr int RT = (EPI == EPI_SWIGLU) ? 2 : 1;
     constexpr int NCOL = NT <= 2 ? 16 : 64;             // columns of a part of sums of squares
-    constexpr int NPG = 4;                              // thread groups that share the parts: the same for every
-                                                        // batch size, so that a row's sum is added in one order
+    constexpr int NPG = 16;                             // groups that share the parts (part p belongs to group p % 16):
+                                                        // the same for every batch size, so that a row's sum is
+                                                        // added in one order
+    constexpr int TG = SG_THREADS / NCOL;               // thread groups (16 or 4), each takes NPG / TG groups of parts
+    constexpr int GPT = NPG / TG;
     extern __shared__ float red[];          // [SG_WARPS][RT][16][NT*8]
     __shared__ float nred[NPG][NCOL];       // consumer side of a deferred norm: partial sums [group][batch row]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,16 +89,31 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* X, TC* C, int m,
     const bool norm_in = EPI != EPI_ACCUM && nm.ssq_in != nullptr;
     // the following norm's weight at the output column this thread writes (a weight: no need to wait for it)
     const float wn = (norm_out && r0 + (threadIdx.x & 15) < n) ? nm.w_next[r0 + (threadIdx.x & 15)] : 0.f;
-    float nsum = 0.f;
+    float nsum[GPT];
+#pragma unroll
+    for (int j = 0; j < GPT; ++j) nsum[j] = 0.f;
     bool norm_loaded = false;
     // the parts of the rows' sums of squares, left by the kernel before (so: after the wait): thread
-    // (group, column) adds every NPG-th part of its column
+    // (thread group, column) adds the parts of its groups, four loads in flight per group
     auto load_norm = [&]() {
         if (!norm_in || norm_loaded) return;
         norm_loaded = true;
-        const int col = threadIdx.x % NCOL, pg = threadIdx.x / NCOL;
-        if (col < nm.stride && pg < NPG)
-            for (int p = pg; p < nm.n_parts; p += NPG) nsum += __ldcg(nm.ssq_in + (size_t)p * nm.stride + col);
+        const int col = threadIdx.x % NCOL, tg = threadIdx.x / NCOL;
+        if (col >= nm.stride) return;
+        for (int p0 = 0; p0 < nm.n_parts; p0 += 4 * NPG) {
+            float f[GPT][4];
+#pragma unroll
+            for (int j = 0; j < GPT; ++j)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int p = p0 + u * NPG + tg * GPT + j;
+                    f[j][u] = p < nm.n_parts ? __ldcg(nm.ssq_in + (size_t)p * nm.stride + col) : 0.f;
+                }
+#pragma unroll
+            for (int j = 0; j < GPT; ++j)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) nsum[j] += f[j][u];
+        }
     };
     // rows beyond n are clamped for loading and dropped at the store
     const bf16* wrow[RT][2];
@@ -160,7 +178,10 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* X, TC* C, int m,
     pdl_wait();                 // warps that had no k step still have to wait before they write
     pdl_launch_dependents();    // the next kernel may start to fill the SMs that this one leaves
     load_norm();
-    if (norm_in && threadIdx.x / NCOL < NPG) nred[threadIdx.x / NCOL][threadIdx.x % NCOL] = nsum;
+    if (norm_in) {
+#pragma unroll
+        for (int j = 0; j < GPT; ++j) nred[(threadIdx.x / NCOL) * GPT + j][threadIdx.x % NCOL] = nsum[j];
+    }
     // partial sums -> shared memory [warp][rt][row 0..15][batch 0..NT*8)
     constexpr int NB = NT * 8;
 #pragma unroll
