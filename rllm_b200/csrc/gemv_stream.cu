@@ -228,7 +228,18 @@ gemv_stream_kernel(const __grid_constant__ SvMaps maps, TC* __restrict__ C, int 
         waited = true;
         const int b = tid & 15, seg = tid >> 4;
         float ssum = 0.f;
-        for (int p = seg; p < nm.n_parts; p += 8) ssum += nm.ssq_in[(size_t)p * nm.stride + b];
+        // eight loads in flight at a time, added in the order of the parts (one after the other, each
+        // load would wait for the round trip of the one before)
+        for (int p0 = seg; p0 < nm.n_parts; p0 += 64) {
+            float f[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int p = p0 + 8 * u;
+                f[u] = p < nm.n_parts ? __ldcg(nm.ssq_in + (size_t)p * nm.stride + b) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) ssum += f[u];
+        }
         norm_red[seg][b] = ssum;
     }
     float ssq[NT][2];
