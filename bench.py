@@ -313,6 +313,13 @@ def main():
                      "frac": round(main_run["bytes"] / main_run["ms"] / 1e6 / pk["hbm_gbs"], 4)},
     }
     if not a.skip_points:
+        # decode at batch 1 and 64, device-timed like the main run and directly behind it
+        steps = max(8, a.steps // 2)
+        points, fracs, e2es = {}, {}, {}
+        for b in (1, 64):
+            r = decode_run(b, steps, a.warmup)
+            points[f"decode_b{b}"] = round(r["tok_s"], 2)
+            fracs[f"decode_b{b}"] = round(r["bytes"] / r["ms"] / 1e6 / pk["hbm_gbs"], 4)
         # prefill of 2,048 tokens in one step
         toks = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
 
@@ -350,12 +357,7 @@ def main():
                           "ms": round(ms, 3), "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
                           "peak_tflops": pk["bf16_tflops_sustained"]}
         out["prefill_ms_warm"] = {f"block{b}": round(v, 3) for b, v in by_block.items()}
-        steps = max(8, a.steps // 2)
-        points, fracs, e2es = {}, {}, {}
         for b in (1, 64):
-            r = decode_run(b, steps, a.warmup)
-            points[f"decode_b{b}"] = round(r["tok_s"], 2)
-            fracs[f"decode_b{b}"] = round(r["bytes"] / r["ms"] / 1e6 / pk["hbm_gbs"], 4)
             e2es[f"decode_b{b}"] = round(generate_run(b, max(8, steps // 2), a.warmup)["tok_s"], 2)
         out["points"] = points
         out["points_frac"] = fracs              # achieved share of the HBM roofline (weights once + live cache) / time

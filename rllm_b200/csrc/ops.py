@@ -8,6 +8,7 @@ cannot be built and loaded, raises.
 from __future__ import annotations
 
 import ctypes
+import os
 import struct
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
@@ -627,7 +628,8 @@ def skinny_gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0, n_splits=None
 
 STREAM_MAX_ROWS = 16
 TC_SWAP_NORM_COLS = 64            # columns of a part of sums of squares that skinny_gemm_tc writes and reads
-DEFER_NORMS = True                # a norm between two products of at most 64 rows is deferred into them
+# a norm between two products of at most 64 rows is deferred into them (RLLM_B200_NO_DEFER_NORMS=1: never)
+DEFER_NORMS = os.environ.get("RLLM_B200_NO_DEFER_NORMS", "0") in ("", "0")
 _n_sm: dict = {}
 
 
