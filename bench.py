@@ -314,7 +314,7 @@ def main():
     }
     if not a.skip_points:
         # decode at batch 1 and 64, device-timed like the main run and directly behind it
-        steps = max(8, a.steps // 2)
+        steps = a.steps
         points, fracs, e2es = {}, {}, {}
         for b in (1, 64):
             r = decode_run(b, steps, a.warmup)

@@ -36,6 +36,7 @@ LIBRARIES = {
     "fast": (["skinny_gemm.cu"], []),
     "attn": (["attention_flash.cu"], []),
     "tc": (["gemm_tc.cu"], []),
+    "tc2": (["gemm_tc2.cu"], []),
     "stream": (["gemv_stream.cu"], []),
     "attn_tc": (["attention_tc.cu"], []),
     "host": (["host_runtime.cpp"], []),

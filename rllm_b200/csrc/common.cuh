@@ -107,10 +107,10 @@ static inline int rllm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     return (int)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
-// The same with the CTAs of grid dimension y grouped into thread-block clusters of `cluster_y`.
+// The same with the CTAs grouped into thread-block clusters of `cluster` CTAs along each dimension.
 template <typename... KArgs, typename... Args>
-static inline int rllm_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                      int cluster_y, Args... args) {
+static inline int rllm_launch_clusters(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                       dim3 cluster, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -123,16 +123,23 @@ static inline int rllm_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 bl
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
-    if (cluster_y > 1) {
+    if (cluster.x * cluster.y * cluster.z > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 1;
-        attr[n].val.clusterDim.y = (unsigned)cluster_y;
-        attr[n].val.clusterDim.z = 1;
+        attr[n].val.clusterDim.x = cluster.x;
+        attr[n].val.clusterDim.y = cluster.y;
+        attr[n].val.clusterDim.z = cluster.z;
         ++n;
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
     return (int)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// Clusters of `cluster_y` CTAs along grid dimension y.
+template <typename... KArgs, typename... Args>
+static inline int rllm_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      int cluster_y, Args... args) {
+    return rllm_launch_clusters(kern, grid, block, smem, stream, dim3(1, cluster_y > 1 ? cluster_y : 1, 1), args...);
 }
 
 #define RLLM_LAUNCH_STATUS() ((int)cudaGetLastError())

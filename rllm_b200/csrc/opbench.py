@@ -63,7 +63,7 @@ def time_product(op: str, m: int, n: int, k: int, epilogue: str = "store", launc
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--op", required=True, choices=["skinny_gemm", "skinny_gemm_tc", "gemv_stream", "gemm_tc", "gemm_lib"])
+    ap.add_argument("--op", required=True, choices=["skinny_gemm", "skinny_gemm_tc", "gemv_stream", "gemm_tc", "gemm_tc2", "gemm_lib"])
     ap.add_argument("--m", type=int, required=True)
     ap.add_argument("--n", type=int, required=True)
     ap.add_argument("--k", type=int, required=True)

@@ -522,7 +522,7 @@ def check_device_errors(device="cuda:0") -> None:
                           f"2 a stage was never released, 3 the accumulator never completed)")
 
 
-_WAIT_LIBRARIES = {"tc": "rllm_tc", "stream": "rllm_stream", "attn_tc": "rllm_attn_tc"}
+_WAIT_LIBRARIES = {"tc": "rllm_tc", "tc2": "rllm_tc2", "stream": "rllm_stream", "attn_tc": "rllm_attn_tc"}
 
 
 def set_wait_cycles(cycles: int = 0, libraries=None) -> None:
@@ -569,6 +569,30 @@ def gemm_tc(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
     if st >= 30000:
         raise KernelError(f"gemm_tc: tensor map encoding failed (CUresult {st - 30000}) for m={m} n={n} k={k}")
     _check(st, "gemm_tc")
+    return out
+
+
+def gemm_tc2(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
+    """out (+)= a . w^T on the tcgen05 tensor cores with two SMs per 256 x 256 tile
+    (tcgen05.mma.cta_group::2; each CTA of the pair stages half of the operands).  Arguments as
+    gemm_tc.  See gemm_tc2.cu."""
+    _need_cuda(a, w, out)
+    if not _tc_ok(a, w):
+        raise KernelError("gemm_tc2 needs bfloat16 operands, k a multiple of 8 and 16-byte aligned rows")
+    m, k = a.shape
+    n = out.shape[1]
+    assert out.shape[0] == m and out.stride(1) == 1
+    if epilogue == EPI_SWIGLU:
+        assert w.shape[0] >= up_row_offset + n
+    else:
+        assert w.shape[0] == n
+    st = _lib("tc2").rllm_gemm_tc2(
+        _ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
+        c_int(w.stride(0)), c_int(out.stride(0)), c_int(epilogue), c_int(up_row_offset),
+        _ptr(error_word(a.device)), _stream())
+    if st >= 30000:
+        raise KernelError(f"gemm_tc2: tensor map encoding failed (CUresult {st - 30000}) for m={m} n={n} k={k}")
+    _check(st, "gemm_tc2")
     return out
 
 
@@ -823,6 +847,16 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None, follow
     return gemm_plain(a, w, out, accumulate)
 
 
+def _prefer_tc2(m: int) -> bool:
+    """The two-SM kernel takes 256 rows per tile: it wins unless half of a pair's tile is padding and
+    the tiles are few."""
+    tiles128 = -(-m // 128)
+    return USE_TC2 and (tiles128 % 2 == 0 or tiles128 >= 16)
+
+
+USE_TC2 = True
+
+
 def gate_up_swiglu(h, w_gate_up, out):
     """out[m, F] = silu(h . Wg^T) * (h . Wu^T) with w_gate_up = [Wg; Wu] stacked ([2F, k]).
     bfloat16: one kernel (the weight-streaming kernel up to 64 rows, the tcgen05 kernel above);
@@ -839,7 +873,10 @@ def gate_up_swiglu(h, w_gate_up, out):
     if isinstance(h, NormedRows):
         raise KernelError("gate_up_swiglu: a deferred norm needs a product that one of the few-row kernels takes")
     if _tc_ok(h, w_gate_up) and out.data_ptr() % 16 == 0:
-        return gemm_tc(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)     # tcgen05, activation in the epilogue
+        # tcgen05, activation in the epilogue; two SMs per tile where the rows fill pairs of 128-row tiles
+        # (2,048 x 24,576 x 4,096: 270 us against 290; 384 rows, one and a half pair tiles: 96 against 71)
+        many = gemm_tc2 if _prefer_tc2(m) else gemm_tc
+        return many(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
     gu = linear(h, w_gate_up, out_dtype=torch.float32)     # same rounding points as the fused kernels
     return silu_mul(gu, out)
 

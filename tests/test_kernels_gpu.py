@@ -366,6 +366,50 @@ def test_gemm_tc_swiglu(m, F, k):
     o.check_device_errors()
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (65, 40, 8), (200, 300, 264), (1000, 1111, 1096), (2048, 512, 4096),
+                                   (300, 700, 136), (4096, 1024, 128)])
+def test_gemm_tc2(m, n, k):
+    """The product with two SMs per tile (tcgen05.mma.cta_group::2): tiles cut by every edge, K that
+    ends inside a stage of 128 and inside a block of 64, more tiles than pairs (both accumulator
+    buffers in turn)."""
+    o = ops()
+    a, w = rnd(m, k, seed=24, dtype=torch.bfloat16), rnd(n, k, seed=25, scale=0.1, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    for _ in range(2):
+        out = torch.full((m, n), float("nan"), device=DEV)
+        o.gemm_tc2(a.to(DEV), w.to(DEV), out)
+        torch.cuda.synchronize()
+        o.check_device_errors()
+        assert rel_err(out.cpu(), ref) < 1e-5
+    out16 = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc2(a.to(DEV), w.to(DEV), out16)
+    assert rel_err(out16.float().cpu(), ref) < 5e-3
+    base = rnd(m, n, seed=26)
+    acc = base.to(DEV)
+    o.gemm_tc2(a.to(DEV), w.to(DEV), acc, epilogue=o.EPI_ACCUM)
+    assert rel_err(acc.cpu(), ref + base) < 1e-5
+    one = torch.empty(m, n, device=DEV)
+    o.gemm_tc(a.to(DEV), w.to(DEV), one)
+    assert rel_err(out.cpu(), one.cpu()) < 1e-6          # the one-CTA kernel adds in the same order
+    o.check_device_errors()
+
+
+@pytest.mark.parametrize("m,F,k", [(65, 224, 96), (300, 1000, 264), (1024, 3072, 1024), (2048, 1536, 512)])
+def test_gemm_tc2_swiglu(m, F, k):
+    o = ops()
+    a = rnd(m, k, seed=27, dtype=torch.bfloat16)
+    w = rnd(2 * F, k, seed=28, scale=0.2, dtype=torch.bfloat16)
+    g, u = a.float() @ w[:F].float().t(), a.float() @ w[F:].float().t()
+    ref = g / (1 + torch.exp(-g)) * u
+    out = torch.full((m, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc2(a.to(DEV), w.to(DEV), out, epilogue=o.EPI_SWIGLU, up_row_offset=F)
+    assert rel_err(out.float().cpu(), ref) < 5e-3
+    out32 = torch.full((m, F), float("nan"), device=DEV)
+    o.gemm_tc2(a.to(DEV), w.to(DEV), out32, epilogue=o.EPI_SWIGLU, up_row_offset=F)
+    assert rel_err(out32.cpu(), ref) < 1e-5
+    o.check_device_errors()
+
+
 @pytest.mark.parametrize("m", [1, 8, 17, 32, 33, 64])
 @pytest.mark.parametrize("n,k,splits", [(96, 512, None), (37, 264, 1), (4096, 4096, None), (1000, 1096, 3), (300, 8, 1),
                                         (130, 2048, 4), (640, 4096, 8), (200, 1024, 2)])
