@@ -307,7 +307,7 @@ def test_layer_sizes_of_the_large_models(tmp_path, size, dtype):
     else:
         check = globals()["check"]
     seen = set()
-    real_stream, real_swap = ops.gemv_stream, ops.skinny_gemm_tc
+    real_stream, real_swap, real_tc2 = ops.gemv_stream, ops.skinny_gemm_tc, ops.gemm_tc2
 
     def spy_stream(a, w, out, *args, **kw):
         seen.add(("stream", tuple(w.shape)))
@@ -317,7 +317,11 @@ def test_layer_sizes_of_the_large_models(tmp_path, size, dtype):
         seen.add(("swap", tuple(w.shape)))
         return real_swap(a, w, out, *args, **kw)
 
-    ops.gemv_stream, ops.skinny_gemm_tc = spy_stream, spy_swap
+    def spy_tc2(a, w, out, *args, **kw):
+        seen.add(("tc2", tuple(w.shape)))
+        return real_tc2(a, w, out, *args, **kw)
+
+    ops.gemv_stream, ops.skinny_gemm_tc, ops.gemm_tc2 = spy_stream, spy_swap, spy_tc2
     try:
         # whole prompts
         for rid, toks in reqs.items():
@@ -353,10 +357,11 @@ def test_layer_sizes_of_the_large_models(tmp_path, size, dtype):
         again = helpers.run_steps(eng, steps)
         assert all(torch.equal(again[key], out[key]) for key in out)
     finally:
-        ops.gemv_stream, ops.skinny_gemm_tc = real_stream, real_swap
+        ops.gemv_stream, ops.skinny_gemm_tc, ops.gemm_tc2 = real_stream, real_swap, real_tc2
     if dtype == "bfloat16":
         for shape in BIG_PRODUCTS[size]:
             assert ("stream", shape) in seen and ("swap", shape) in seen, (shape, sorted(seen))
+        assert ("tc2", BIG_PRODUCTS[size][2]) in seen          # the whole prompt of 210 tokens: two SMs per tile
     else:
         assert not seen
     eng.cache.check_invariants()
