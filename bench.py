@@ -222,6 +222,10 @@ def main():
         torch.cuda.empty_cache()
         return {"ms": ms, "tok_s": batch * 1000.0 / ms, "h2d": staging, "d2h": 4 * batch}
 
+    def idle(seconds=2.0):
+        torch.cuda.synchronize()
+        time.sleep(seconds)
+
     def serving_run():
         """Continuous batching through the entry point: requests of mixed lengths wait, are admitted
         as others finish, prompts go in portions beside decoded tokens.  Wall clock around the
@@ -313,10 +317,14 @@ def main():
                      "frac": round(main_run["bytes"] / main_run["ms"] / 1e6 / pk["hbm_gbs"], 4)},
     }
     if not a.skip_points:
-        # decode at batch 1 and 64, device-timed like the main run and directly behind it
+        # Decode at batch 1 and 64, device-timed like the main run.  What ran before decides the clock a
+        # measurement starts with (after seconds at the power cap it stays low for a while; a prefill
+        # behind the batch-64 steps took 24.8 ms, behind two idle seconds 23.8), so each of the
+        # measurements below starts from a device that has idled for two seconds, and warms up by itself.
         steps = a.steps
         points, fracs, e2es = {}, {}, {}
         for b in (1, 64):
+            idle()
             r = decode_run(b, steps, a.warmup)
             points[f"decode_b{b}"] = round(r["tok_s"], 2)
             fracs[f"decode_b{b}"] = round(r["bytes"] / r["ms"] / 1e6 / pk["hbm_gbs"], 4)
@@ -339,6 +347,7 @@ def main():
             del eng
             torch.cuda.empty_cache()
             return min(times)
+        idle()
         ms = prefill_ms(a.block_size)
         # The two page sizes against each other (16 is the reference's default): a prefill runs at the
         # power cap and the clock settles lower from run to run, so they are measured in turn, after the
