@@ -104,6 +104,7 @@ def weight_bytes(model):
 
 
 def main():
+    global PROMPT, CTX
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -112,6 +113,8 @@ def main():
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: Qwen3-8B (default), 0.6B or 32B")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--block-size", type=int, default=16, help="tokens per page of the KV cache (16: the reference's default)")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of every prompt (the context the decode steps start from)")
+    ap.add_argument("--ctx", type=int, default=None, help="tokens a request may hold (default: twice the prompt)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
@@ -130,6 +133,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     a.warmup = max(a.warmup, 3)
+    PROMPT = a.prompt_len
+    CTX = a.ctx if a.ctx is not None else 2 * PROMPT
 
     import torch
     from rllm_b200.config import config_from_dict
@@ -296,7 +301,8 @@ def main():
     e2e_run = generate_run(a.batch, a.steps, a.warmup)
 
     out = {
-        "metric": METRIC.replace("Qwen3-8B", f"Qwen3-{a.shape.upper()}").replace("batch 8", f"batch {a.batch}"), "value": round(main_run["tok_s"], 2), "unit": "tok/s", "n_gpus": 1,
+        "metric": METRIC.replace("Qwen3-8B", f"Qwen3-{a.shape.upper()}").replace("batch 8", f"batch {a.batch}")
+                        .replace("2,048-token", f"{PROMPT:,}-token").replace("ctx 4,096", f"ctx {CTX:,}"), "value": round(main_run["tok_s"], 2), "unit": "tok/s", "n_gpus": 1,
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(main_run["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids", "impl": "ours",
