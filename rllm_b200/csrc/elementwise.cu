@@ -237,11 +237,14 @@ RLLM_API int rllm_silu_mul(const void* in, int in_dtype, void* out, int out_dtyp
 //   a slot beyond the pool (>= n_slots) writes nothing and sets the error word (RLLM_ERR_SLOT).
 // write_kv == 0 skips the cache (a layer that reads another layer's cache).
 //
-// One block per token and group of 8 heads (head size a multiple of 4, at most 256): each warp
-// takes one head, a lane holding two neighbouring pairs (j, j + hd/2), (j + 1, j + 1 + hd/2) so
-// that loads and stores are 8 and 4 bytes wide.  No shared memory, no barrier: a warp's loads are
-// all in flight at once.
-template <typename TI, typename TO, typename TC>
+// One block per token and group of 8 * HPW heads (head size a multiple of 4, at most 256): each warp
+// takes HPW heads (8 apart), a lane holding two neighbouring pairs (j, j + hd/2), (j + 1, j + 1 + hd/2)
+// of each so that loads and stores are 8 and 4 bytes wide (U = 1: head sizes up to 128, one unit a
+// lane; U = 2: up to 256).  No shared memory, no barrier: the loads of
+// all of a warp's heads are in flight at once, and the token's angles are fetched once per lane.  A
+// head's arithmetic does not depend on HPW: a decode step (HPW = 1: most blocks, shortest chain) and
+// a prompt step (two heads a warp) give the same bits.
+template <typename TI, typename TO, typename TC, int HPW, int U>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_w,
                                 const float* __restrict__ k_norm_w, const float2* cs_table,
@@ -259,27 +262,29 @@ qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_
     const int n_heads = write_kv ? H + 2 * K : H;
     const size_t width = (size_t)(H + 2 * K) * hd;
     const int units = half >> 1;                  // float2 units per half head
-    const int hx = blockIdx.y * 8 + warp;          // one head per warp
-    // this warp's head is asked for first: its values arrive while the token's angles are worked out
-    float a[2][2], b[2][2];
-    float2 cs[2][2];                              // (cos, sin) of this lane's pairs
-    const bool rotates = cs_table != nullptr && hx < H + K;
-    if (hx < n_heads) {
-        const TI* src = qkv + (size_t)t * width + (size_t)hx * hd;
+    // this warp's heads are asked for first: their values arrive while the rest is worked out
+    float a[HPW][U][2], b[HPW][U][2];
+    float2 cs[U][2];                              // (cos, sin) of this lane's pairs
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int j = (lane + 32 * u) * 2;
-            a[u][0] = a[u][1] = b[u][0] = b[u][1] = 0.f;
-            cs[u][0] = cs[u][1] = make_float2(1.f, 0.f);
-            if (lane + 32 * u < units) {
-                const float2 lo = load2<TI>(src + j), hi = load2<TI>(src + j + half);
-                a[u][0] = lo.x; a[u][1] = lo.y;
-                b[u][0] = hi.x; b[u][1] = hi.y;
-                if (rotates) {
-                    const float4 c4 = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + j);
-                    cs[u][0] = make_float2(c4.x, c4.y);
-                    cs[u][1] = make_float2(c4.z, c4.w);
-                }
+    for (int u = 0; u < U; ++u) {
+        cs[u][0] = cs[u][1] = make_float2(1.f, 0.f);
+        if (cs_table != nullptr && lane + 32 * u < units) {
+            const float4 c4 = *reinterpret_cast<const float4*>(cs_table + (size_t)t * half + (lane + 32 * u) * 2);
+            cs[u][0] = make_float2(c4.x, c4.y);
+            cs[u][1] = make_float2(c4.z, c4.w);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < HPW; ++i) {
+        const int hx = (blockIdx.y * HPW + i) * 8 + warp;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            a[i][u][0] = a[i][u][1] = b[i][u][0] = b[i][u][1] = 0.f;
+            if (hx < n_heads && lane + 32 * u < units) {
+                const TI* src = qkv + (size_t)t * width + (size_t)hx * hd + (lane + 32 * u) * 2;
+                const float2 lo = load2<TI>(src), hi = load2<TI>(src + half);
+                a[i][u][0] = lo.x; a[i][u][1] = lo.y;
+                b[i][u][0] = hi.x; b[i][u][1] = hi.y;
             }
         }
     }
@@ -288,7 +293,10 @@ qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_
         if (tid == 0 && blockIdx.y == 0 && err) atomicExch(err, RLLM_ERR_SLOT);
         slot = -1;
     }
-    if (hx < n_heads) {
+#pragma unroll
+    for (int i = 0; i < HPW; ++i) {
+        const int hx = (blockIdx.y * HPW + i) * 8 + warp;
+        if (hx >= n_heads) continue;              // warp-uniform
         const int kind = hx < H ? 0 : (hx < H + K ? 1 : 2);
         TO* qdst = nullptr;
         TC* cdst = nullptr;
@@ -300,29 +308,29 @@ qk_norm_rope_store_token_kernel(const TI* qkv, const float* __restrict__ q_norm_
         }
         float ss = 0.f;
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
-            ss += a[u][0] * a[u][0] + a[u][1] * a[u][1] + b[u][0] * b[u][0] + b[u][1] * b[u][1];
+        for (int u = 0; u < U; ++u)
+            ss += a[i][u][0] * a[i][u][0] + a[i][u][1] * a[i][u][1] + b[i][u][0] * b[i][u][0] + b[i][u][1] * b[i][u][1];
         const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
         float rs = 1.f;
         if (nw) rs = 1.0f / sqrtf(warp_sum(ss) / (float)hd + eps);
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < U; ++u) {
             const int j = (lane + 32 * u) * 2;
             if (lane + 32 * u < units) {
-            float o[4];
+                float o[4];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                float av = a[u][e], bv = b[u][e];
-                if (nw) { av = av * rs * nw[j + e]; bv = bv * rs * nw[j + e + half]; }
-                if (kind != 2) {
-                    const float2 c = cs[u][e];
-                    const float a2 = av * c.x - bv * c.y, b2 = av * c.y + bv * c.x;
-                    av = a2; bv = b2;
+                for (int e = 0; e < 2; ++e) {
+                    float av = a[i][u][e], bv = b[i][u][e];
+                    if (nw) { av = av * rs * nw[j + e]; bv = bv * rs * nw[j + e + half]; }
+                    if (kind != 2) {
+                        const float2 c = cs[u][e];
+                        const float a2 = av * c.x - bv * c.y, b2 = av * c.y + bv * c.x;
+                        av = a2; bv = b2;
+                    }
+                    o[e] = av; o[2 + e] = bv;
                 }
-                o[e] = av; o[2 + e] = bv;
-            }
-            if (qdst) { store2<TO>(qdst + j, o[0], o[1]); store2<TO>(qdst + j + half, o[2], o[3]); }
-            if (cdst) { store2<TC>(cdst + j, o[0], o[1]); store2<TC>(cdst + j + half, o[2], o[3]); }
+                if (qdst) { store2<TO>(qdst + j, o[0], o[1]); store2<TO>(qdst + j + half, o[2], o[3]); }
+                if (cdst) { store2<TC>(cdst + j, o[0], o[1]); store2<TC>(cdst + j + half, o[2], o[3]); }
             }
         }
     }
@@ -359,18 +367,36 @@ RLLM_API int rllm_qk_norm_rope_store(const void* qkv, int in_dtype, const float*
     if (hd % 4 != 0 || hd > 256 || ((uintptr_t)qkv & 7) || ((uintptr_t)q_out & 7) || ((uintptr_t)k_cache & 7) ||
         ((uintptr_t)v_cache & 7) || ((uintptr_t)cs_table & 15))
         return (int)cudaErrorInvalidValue;
-    const dim3 grid(n, ((write_kv ? H + 2 * K : H) + 7) / 8);
+    // heads per warp: one for the few tokens of a decode step (most blocks, shortest chain), two for a
+    // prompt step (2,048 tokens of 48 heads, back to back over inputs larger than L2: 22.7 us with one,
+    // 20.1 with two, 22.8 with four, 22.6 with six; 11.5 at the copy peak)
+    const int n_heads = write_kv ? H + 2 * K : H;
+    const int hpw = n > 64 ? 2 : 1;
+    const dim3 grid(n, (n_heads + 8 * hpw - 1) / (8 * hpw));
+#define LAUNCH_H(TI, TO, TC, HPW)                                                                     \
+    do {                                                                                              \
+        if (hd <= 128)                                                                                \
+            return rllm_launch(qk_norm_rope_store_token_kernel<TI, TO, TC, HPW, 1>, grid, dim3(256), 0, stream,      \
+                               (const TI*)qkv, q_norm_w, k_norm_w, (const float2*)cs_table, positions, slots,        \
+                               (TO*)q_out, (TC*)k_cache, (TC*)v_cache, H, K, hd, bs, eps, write_kv,   \
+                               (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots), err);          \
+        return rllm_launch(qk_norm_rope_store_token_kernel<TI, TO, TC, HPW, 2>, grid, dim3(256), 0, stream,          \
+                           (const TI*)qkv, q_norm_w, k_norm_w, (const float2*)cs_table, positions, slots,            \
+                           (TO*)q_out, (TC*)k_cache, (TC*)v_cache, H, K, hd, bs, eps, write_kv,       \
+                           (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots), err);              \
+    } while (0)
 #define LAUNCH(TI, TO, TC)                                                                            \
-    return rllm_launch(qk_norm_rope_store_token_kernel<TI, TO, TC>, grid, dim3(256), 0, stream,       \
-                       (const TI*)qkv, q_norm_w, k_norm_w, (const float2*)cs_table, positions, slots, (TO*)q_out,    \
-                       (TC*)k_cache, (TC*)v_cache, H, K, hd, bs, eps, write_kv,                       \
-                       (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots), err)
+    do {                                                                                              \
+        if (hpw == 1) { LAUNCH_H(TI, TO, TC, 1); }                                                    \
+        LAUNCH_H(TI, TO, TC, 2);                                                                      \
+    } while (0)
     if (q_dtype != cache_dtype) return (int)cudaErrorInvalidValue;
     if (in_dtype == RLLM_F32 && q_dtype == RLLM_F32) { LAUNCH(float, float, float); }
     if (in_dtype == RLLM_F32 && q_dtype == RLLM_BF16) { LAUNCH(float, bf16, bf16); }
     if (in_dtype == RLLM_BF16 && q_dtype == RLLM_BF16) { LAUNCH(bf16, bf16, bf16); }
     LAUNCH(bf16, float, float);
 #undef LAUNCH
+#undef LAUNCH_H
 }
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches

@@ -99,6 +99,42 @@ def test_qk_norm_rope_store(hd, H, K, dtype):
             assert float(kc[s // bs, :, s % bs].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("hd,H,K", [(128, 32, 8), (128, 16, 8), (128, 64, 8), (48, 5, 1), (64, 3, 2)])
+def test_qk_norm_rope_store_many_tokens(hd, H, K):
+    """A prompt step takes two heads per warp, a decode step
+    one: the same tokens through both give the same bits, and both agree with the plain formulas."""
+    o = ops()
+    n, bs, theta, eps = 200, 16, 1e6, 1e-6
+    pages = -(-n // bs) + 1
+    qkv = rnd(n, (H + 2 * K) * hd, seed=16)
+    qw, kw = 1 + 0.1 * rnd(hd, seed=17), 1 + 0.1 * rnd(hd, seed=18)
+    g = torch.Generator().manual_seed(19)
+    positions = torch.randint(0, 5000, (n,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * bs, generator=g)[:n].to(torch.int32)
+    inv = (1.0 / torch.pow(torch.tensor(theta), torch.arange(0, hd, 2).float() / hd)).to(DEV)
+    outs = []
+    for chunk in (n, 50):                       # one launch of 200 tokens; four of 50
+        kc = torch.zeros(pages, K, bs, hd, dtype=torch.bfloat16, device=DEV)
+        vc = torch.zeros_like(kc)
+        q_out = torch.zeros(n, H * hd, dtype=torch.bfloat16, device=DEV)
+        for t0 in range(0, n, chunk):
+            sl = slice(t0, t0 + chunk)
+            o.qk_norm_rope_store(qkv[sl].to(DEV), qw.to(DEV), kw.to(DEV), inv, positions[sl].to(DEV),
+                                 slots[sl].to(DEV), q_out[sl], kc, vc, H, K, hd, bs, eps)
+        outs.append((q_out.cpu(), kc.cpu(), vc.cpu()))
+    for x, y in zip(*outs):
+        assert torch.equal(x, y)
+    q = qkv[:, :H * hd].view(n, H, hd)
+    k = qkv[:, H * hd:(H + K) * hd].view(n, K, hd)
+    q_ref = plain_impl.rope_neox(plain_impl.rms_norm(q, qw, eps), positions.tolist(), theta)
+    k_ref = plain_impl.rope_neox(plain_impl.rms_norm(k, kw, eps), positions.tolist(), theta)
+    assert rel_err(outs[0][0].float().view(n, H, hd), q_ref) < 1e-2
+    for t in (0, 57, 199):
+        sl = int(slots[t])
+        assert rel_err(outs[0][1][sl // bs, :, sl % bs].float(), k_ref[t]) < 1e-2
+    o.check_device_errors()
+
+
 def paged_case(hd, H, K, bs, lens, q_lens, seed, dtype, window=0, spike=False):
     """Builds a scattered paged cache for requests of `lens` tokens whose last `q_lens` tokens are
     the step's queries; returns kernel inputs and the plain reference output."""
