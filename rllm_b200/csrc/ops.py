@@ -847,11 +847,18 @@ def linear(a, w, out=None, out_dtype=None, accumulate=False, stream=None, follow
     return gemm_plain(a, w, out, accumulate)
 
 
-def _prefer_tc2(m: int) -> bool:
-    """The two-SM kernel takes 256 rows per tile: it wins unless half of a pair's tile is padding and
-    the tiles are few."""
+def _prefer_tc2(m: int, n_col_tiles: int, n_sm: int = 148) -> bool:
+    """Which of the two many-row kernels finishes the product in fewer waves: the one-CTA kernel
+    walks 128-row tiles on n_sm CTAs, the two-SM kernel 256-row tiles on n_sm / 2 pairs, whose wave
+    takes 0.93 of the other's (2,048 x 24,576 x 4,096: 270 us against 290 in 11 waves each).
+    Measured at 12,288 x 4,096 with SwiGLU: 544 rows 116 us (two SMs) against 121, 672 rows 118
+    against 128, 896 rows 160 against 141, 1,152 rows 185 against 171."""
+    if not USE_TC2:
+        return False
     tiles128 = -(-m // 128)
-    return USE_TC2 and (tiles128 % 2 == 0 or tiles128 >= 16)
+    waves_one = -(-(tiles128 * n_col_tiles) // n_sm)
+    waves_two = -(-(-(-tiles128 // 2) * n_col_tiles) // (n_sm // 2))
+    return 0.93 * waves_two < waves_one
 
 
 USE_TC2 = True
@@ -873,9 +880,8 @@ def gate_up_swiglu(h, w_gate_up, out):
     if isinstance(h, NormedRows):
         raise KernelError("gate_up_swiglu: a deferred norm needs a product that one of the few-row kernels takes")
     if _tc_ok(h, w_gate_up) and out.data_ptr() % 16 == 0:
-        # tcgen05, activation in the epilogue; two SMs per tile where the rows fill pairs of 128-row tiles
-        # (2,048 x 24,576 x 4,096: 270 us against 290; 384 rows, one and a half pair tiles: 96 against 71)
-        many = gemm_tc2 if _prefer_tc2(m) else gemm_tc
+        # tcgen05, activation in the epilogue; two SMs per tile where that takes fewer waves
+        many = gemm_tc2 if _prefer_tc2(m, -(-F // 128), sm_count(h.device)) else gemm_tc
         return many(h, w_gate_up, out, EPI_SWIGLU, up_row_offset=F)
     gu = linear(h, w_gate_up, out_dtype=torch.float32)     # same rounding points as the fused kernels
     return silu_mul(gu, out)
