@@ -23,6 +23,11 @@
 //   SwiGLU: the leader's half of B holds 128 gate rows, the peer's the 128 up rows of the same
 //   index, so that a thread finds gate and up of an output column in its own accumulator row.
 //
+// The last, partial wave: when the tiles left over after the full waves would keep at most half (a
+// quarter) of the pairs busy, each of them is cut into two (four) slices of columns (MMAs of N = 128
+// or 64), so that the wave takes half (a quarter) of a tile's time; a product with fewer tiles than
+// pairs is cut the same way.  A work item is a tile or a slice of one.
+//
 // No TMA load is multicast.  Every wait on an mbarrier is bounded (tcgen05.cuh); the two barriers
 // that have no limit are the cluster barriers at the start and the end, which every thread of both
 // CTAs reaches whatever happened between them.
@@ -116,13 +121,28 @@ template <> __device__ __forceinline__ void t2_store_row32<bf16>(bf16* dst, cons
     }
 }
 
+struct T2Maps {
+    CUtensorMap a;          // boxes of 64 x 128 rows
+    CUtensorMap b[3];       // boxes of 64 x 128, 64 and 32 rows: a CTA's half of a whole, half and quarter B tile
+};
+
+// Work item -> (tile, slice, log2 of the slices its tile is cut into): the first `head` items are
+// whole tiles, the others the slices of the `tail` tiles behind them.
+__device__ __forceinline__ void t2_item(int item, int head, int tail_log2, int& tile, int& slice, int& sl_log2) {
+    if (item < head) { tile = item; slice = 0; sl_log2 = 0; return; }
+    const int j = item - head;
+    tile = head + (j >> tail_log2);
+    slice = j & ((1 << tail_log2) - 1);
+    sl_log2 = tail_log2;
+}
+
 // grid (2 * pairs), clusters of two along x (a kernel with cta_group::2 instructions is refused with
 // "invalid cluster size" when its clusters are not even along x): CTAs 2p and 2p + 1 are pair p,
 // which takes tiles p, p + pairs, ... (m fastest, as in gemm_tc.cu).
 template <int EPI, typename TC, int STAGES>
 __global__ void __launch_bounds__(T2_THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TC* __restrict__ C,
-                int ldc, int M, int N, int K, int up_row_offset, int* __restrict__ err) {
+gemm_tc2_kernel(const __grid_constant__ T2Maps maps, TC* __restrict__ C, int ldc, int M, int N, int K,
+                int up_row_offset, int* __restrict__ err, int tail_tiles, int tail_log2) {
     constexpr int BN_OUT = (EPI == T2_EPI_SWIGLU) ? T2_BN / 2 : T2_BN;      // output columns per tile
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -138,11 +158,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int nkb = (K + T2_KH * T2_BK - 1) / (T2_KH * T2_BK);      // stages along K
     const int m_tiles = (M + 2 * T2_BM - 1) / (2 * T2_BM), n_tiles = (N + BN_OUT - 1) / BN_OUT;
     const int total_tiles = m_tiles * n_tiles;
+    const int head = total_tiles - tail_tiles;                   // whole tiles; then the slices of the others
+    const int total_items = head + (tail_tiles << tail_log2);
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
 
     if (tid == 0) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.b[0]) : "memory");
+        if (tail_tiles) asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.b[tail_log2]) : "memory");
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }   // 4 warps of 2 CTAs
         abort_flag = 0;
@@ -164,9 +187,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // ---- TMA producer of this CTA: its rows of A and its half of B, bytes counted by the leader
         int it = 0, issued = 0;
         bool ok = true;
-        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-            const int m0 = (tile % m_tiles) * (2 * T2_BM) + (int)rank * T2_BM, n0 = (tile / m_tiles) * BN_OUT;
-            const int b_row = (EPI == T2_EPI_SWIGLU) ? (rank == 0 ? n0 : up_row_offset + n0) : n0 + (int)rank * 128;
+        for (int item = pair; item < total_items && ok; item += n_pairs) {
+            int tile, slice, sl;
+            t2_item(item, head, tail_log2, tile, slice, sl);
+            const int m0 = (tile % m_tiles) * (2 * T2_BM) + (int)rank * T2_BM;
+            const int n0 = (tile / m_tiles) * BN_OUT + slice * (BN_OUT >> sl);      // first output column of the item
+            const int b_row = (EPI == T2_EPI_SWIGLU) ? (rank == 0 ? n0 : up_row_offset + n0) : n0 + (int)rank * (128 >> sl);
+            const uint32_t stage_tx = 2 * T2_KH * (T2_HALF_BYTES + (T2_HALF_BYTES >> sl));     // both CTAs' bytes
             for (int kb = 0; kb < nkb; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
@@ -177,11 +204,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 unsigned char* a_s = smem + (size_t)s * T2_STAGE_BYTES;
                 const uint32_t full = cluster_addr(&full_bar[s], 0);
-                if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * T2_STAGE_BYTES);
+                if (rank == 0) mbar_expect_tx(&full_bar[s], stage_tx);
 #pragma unroll
                 for (int h = 0; h < T2_KH; ++h) {
-                    tma_load_2d_pair(a_s + h * T2_HALF_BYTES, &tmA, (kb * T2_KH + h) * T2_BK, m0, full);
-                    tma_load_2d_pair(a_s + (T2_KH + h) * T2_HALF_BYTES, &tmB, (kb * T2_KH + h) * T2_BK, b_row, full);
+                    tma_load_2d_pair(a_s + h * T2_HALF_BYTES, &maps.a, (kb * T2_KH + h) * T2_BK, m0, full);
+                    tma_load_2d_pair(a_s + (T2_KH + h) * T2_HALF_BYTES, &maps.b[sl], (kb * T2_KH + h) * T2_BK, b_row, full);
                 }
                 issued = it + 1;
             }
@@ -195,11 +222,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ---- MMA issuer of the pair
-        constexpr uint32_t idesc = idesc_bf16(2 * T2_BM, T2_BN);
         int it = 0, local = 0;
         bool ok = true;
-        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
+        for (int item = pair; item < total_items && ok; item += n_pairs, ++local) {
             const int buf = local & 1;
+            const uint32_t idesc = idesc_bf16(2 * T2_BM, T2_BN >> (item < head ? 0 : tail_log2));
             if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, &abort_flag)) {
                 if (!abort_flag) { atomicExch(err, T2_ERR_ACC); abort_flag = 1; }
                 break;
@@ -234,25 +261,29 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int row = quarter * 32 + lane;
         int local = 0;
         bool first = true;
-        for (int tile = pair; tile < total_tiles; tile += n_pairs, ++local) {
+        for (int item = pair; item < total_items; item += n_pairs, ++local) {
             const int buf = local & 1;
-            const int m0 = (tile % m_tiles) * (2 * T2_BM) + (int)rank * T2_BM, n0 = (tile / m_tiles) * BN_OUT;
+            int tile, slice, sl;
+            t2_item(item, head, tail_log2, tile, slice, sl);
+            const int cols_out = BN_OUT >> sl;                     // output columns of the item (at least 32)
+            const int m0 = (tile % m_tiles) * (2 * T2_BM) + (int)rank * T2_BM;
+            const int n0 = (tile / m_tiles) * BN_OUT + slice * cols_out;
             const int gm = m0 + row;
             bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, &abort_flag);
             if (!ok && !abort_flag) { atomicExch(err, T2_ERR_ACC); abort_flag = 1; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            if (first && tile + n_pairs >= total_tiles) { pdl_launch_dependents(); first = false; }
+            if (first && item + n_pairs >= total_items) { pdl_launch_dependents(); first = false; }
             const uint32_t taddr = tmem_base + buf * T2_BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
+            for (int c0 = 0; c0 < cols_out; c0 += 32) {
                 uint32_t r[32];
                 float v[32];
                 tmem_ld32(taddr + c0, r);
                 if (EPI == T2_EPI_SWIGLU) {
                     uint32_t u[32];
-                    tmem_ld32(taddr + T2_BN / 2 + c0, u);
+                    tmem_ld32(taddr + cols_out + c0, u);          // the up columns follow the item's gate columns
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -264,7 +295,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
                 }
-                if (c0 + 32 >= BN_OUT) {                     // all of this warp's TMEM reads of the tile are done
+                if (c0 + 32 >= cols_out) {                   // all of this warp's TMEM reads of the item are done
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[buf], 0));
@@ -298,12 +329,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 // ---------------------------------------------------------------- host side
-static int t2_make_tmap(CUtensorMap* map, const void* base, int rows, int cols, int ld) {
+static int t2_make_tmap(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows = 128) {
     TmapEncodeFn enc = tmap_encoder();
     if (!enc) return 30001;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {T2_BK, 128};
+    cuuint32_t box[2] = {T2_BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -312,8 +343,7 @@ static int t2_make_tmap(CUtensorMap* map, const void* base, int rows, int cols, 
 }
 
 template <int EPI, typename TC, int STAGES>
-static int launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int ldc, int M, int N, int K, int up,
-                      int* err, cudaStream_t stream) {
+static int launch_tc2(const T2Maps& maps, void* C, int ldc, int M, int N, int K, int up, int* err, cudaStream_t stream) {
     constexpr int BN_OUT = (EPI == T2_EPI_SWIGLU) ? T2_BN / 2 : T2_BN;
     constexpr size_t smem = (size_t)STAGES * T2_STAGE_BYTES + 1024;
     auto kern = gemm_tc2_kernel<EPI, TC, STAGES>;
@@ -331,9 +361,17 @@ static int launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int
         if (n_sm <= 0) n_sm = 148;
     }
     const int tiles = ((M + 2 * T2_BM - 1) / (2 * T2_BM)) * ((N + BN_OUT - 1) / BN_OUT);
-    const int pairs = tiles < n_sm / 2 ? tiles : n_sm / 2;
-    return rllm_launch_clusters(kern, dim3(2 * pairs), dim3(T2_THREADS), smem, stream, dim3(2, 1, 1), ta, tb, (TC*)C, ldc,
-                                M, N, K, up, err);
+    // the tiles of the last, partial wave are cut into 4 or 2 slices when that fits the pairs
+    const int all_pairs = n_sm / 2;
+    const int rem = tiles % all_pairs;
+    int tail_log2 = 0;
+    if (rem > 0 && rem * 4 <= all_pairs) tail_log2 = 2;
+    else if (rem > 0 && rem * 2 <= all_pairs) tail_log2 = 1;
+    const int tail_tiles = tail_log2 ? rem : 0;
+    const int items = tiles - tail_tiles + (tail_tiles << tail_log2);
+    const int pairs = items < all_pairs ? items : all_pairs;
+    return rllm_launch_clusters(kern, dim3(2 * pairs), dim3(T2_THREADS), smem, stream, dim3(2, 1, 1), maps, (TC*)C, ldc,
+                                M, N, K, up, err, tail_tiles, tail_log2);
 }
 
 // C[M,N] (+)= A[M,K] . B[N,K]^T with two SMs per 256 x 256 tile.  Arguments, epilogues and return
@@ -344,20 +382,23 @@ RLLM_API int rllm_gemm_tc2(const void* A, const void* B, void* C, int c_dtype, i
     if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || !err)
         return (int)cudaErrorInvalidValue;
     if (epilogue == T2_EPI_ACCUM && c_dtype != RLLM_F32) return (int)cudaErrorInvalidValue;
-    CUtensorMap ta, tb;
-    int st = t2_make_tmap(&ta, A, M, K, lda);
+    T2Maps maps;
+    int st = t2_make_tmap(&maps.a, A, M, K, lda);
     if (st) return st;
-    st = t2_make_tmap(&tb, B, epilogue == T2_EPI_SWIGLU ? up_row_offset + N : N, K, ldb);
-    if (st) return st;
+    const int b_rows = epilogue == T2_EPI_SWIGLU ? up_row_offset + N : N;
+    for (int i = 0; i < 3; ++i) {
+        st = t2_make_tmap(&maps.b[i], B, b_rows, K, ldb, 128 >> i);
+        if (st) return st;
+    }
     if (epilogue == T2_EPI_STORE) {
-        return c_dtype == RLLM_F32 ? launch_tc2<T2_EPI_STORE, float, 3>(ta, tb, C, ldc, M, N, K, 0, err, stream)
-                                   : launch_tc2<T2_EPI_STORE, bf16, 3>(ta, tb, C, ldc, M, N, K, 0, err, stream);
+        return c_dtype == RLLM_F32 ? launch_tc2<T2_EPI_STORE, float, 3>(maps, C, ldc, M, N, K, 0, err, stream)
+                                   : launch_tc2<T2_EPI_STORE, bf16, 3>(maps, C, ldc, M, N, K, 0, err, stream);
     } else if (epilogue == T2_EPI_ACCUM) {
-        return launch_tc2<T2_EPI_ACCUM, float, 3>(ta, tb, C, ldc, M, N, K, 0, err, stream);
+        return launch_tc2<T2_EPI_ACCUM, float, 3>(maps, C, ldc, M, N, K, 0, err, stream);
     } else if (epilogue == T2_EPI_SWIGLU) {
         return c_dtype == RLLM_F32
-                   ? launch_tc2<T2_EPI_SWIGLU, float, 3>(ta, tb, C, ldc, M, N, K, up_row_offset, err, stream)
-                   : launch_tc2<T2_EPI_SWIGLU, bf16, 3>(ta, tb, C, ldc, M, N, K, up_row_offset, err, stream);
+                   ? launch_tc2<T2_EPI_SWIGLU, float, 3>(maps, C, ldc, M, N, K, up_row_offset, err, stream)
+                   : launch_tc2<T2_EPI_SWIGLU, bf16, 3>(maps, C, ldc, M, N, K, up_row_offset, err, stream);
     }
     return (int)cudaErrorInvalidValue;
 }
