@@ -928,3 +928,22 @@ def test_launch_plans_of_the_few_row_products():
     assert ops.stream_plan(4096, 4096) == (296, 3)
     assert ops.stream_plan(12288, 4096, swiglu=True) == (444, 3)
     assert ops.stream_plan(151936, 4096) == (444, 3)
+
+
+def test_which_many_row_kernel_and_which_norms_are_deferred():
+    """The two-SM product is taken where it needs fewer waves than the one-CTA kernel; a norm is
+    deferred whenever both products around it can run on a few-row kernel.  Plain functions of
+    shapes and types."""
+    from rllm_b200.csrc import ops
+    cols_8b = 12288 // 128
+    want = {70: False, 128: False, 200: True, 256: True, 384: False, 544: True, 672: True, 896: False,
+            1152: False, 2048: True, 4096: True}
+    for m, two in want.items():
+        assert ops._prefer_tc2(m, cols_8b) == two, m
+    assert ops._prefer_tc2(2048, 3072 // 128) and ops._prefer_tc2(210, 25600 // 128)
+    w_o = torch.empty(256, 128, dtype=torch.bfloat16)
+    w_gu = torch.empty(512, 256, dtype=torch.bfloat16)
+    for m, yes in ((0, False), (1, True), (8, True), (9, True), (16, True), (17, True), (64, True), (65, False)):
+        assert ops.defers_norm(m, w_o, w_gu, True) == yes, m
+    assert not ops.defers_norm(8, w_o.float(), w_gu)                                     # the 32-bit path
+    assert not ops.defers_norm(8, w_o, torch.empty(64, 100, dtype=torch.bfloat16))       # rows of 100 elements
