@@ -90,11 +90,16 @@ class PlannedItem:
 
 
 class Scheduler:
-    def __init__(self, cache, ctx: int = 4096, max_num_seqs: int = 4, prefill_chunk: int = 512):
-        if max_num_seqs <= 0 or prefill_chunk <= 0 or ctx <= 0:
+    def __init__(self, cache, ctx: int = 4096, max_num_seqs: int = 4, prefill_chunk: int = 512, row_quantum: int = 0):
+        """row_quantum: the rows of a tile of the many-row kernels (0: none).  A step that holds prompt
+        tokens beside decoding requests is then trimmed to a whole number of tiles where that costs
+        at most an eighth of its prompt tokens: 512 prompt tokens beside 32 decoding requests are 544
+        rows, five tiles of 128 of which the last is a quarter full; 480 beside 32 are four."""
+        if max_num_seqs <= 0 or prefill_chunk <= 0 or ctx <= 0 or row_quantum < 0:
             raise ValueError("ctx, max_num_seqs and prefill_chunk must be positive")
         self.cache, self.ctx = cache, ctx
         self.max_num_seqs, self.prefill_chunk = max_num_seqs, prefill_chunk
+        self.row_quantum = row_quantum
         self.waiting: deque = deque()
         self.running: list = []
         self._order = 0
@@ -159,6 +164,14 @@ class Scheduler:
                 continue
             left -= take
             plan.append(PlannedItem(s, take, s.cached + take == len(s.tokens)))
+        q = self.row_quantum
+        if q and len(plan) > len(decoders):
+            rows = sum(p.take for p in plan)
+            prompt_rows = rows - len(decoders)
+            over = rows % q
+            last = plan[-1]
+            if rows > q and 0 < over <= prompt_rows // 8 and over < last.take:
+                plan[-1] = PlannedItem(last.seq, last.take - over, False)
         return plan
 
     def _preempt_newest(self) -> Optional[_Seq]:

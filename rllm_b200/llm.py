@@ -65,6 +65,8 @@ class LLM:
         self.engine = Engine(self.model, block_size=block_size, max_tokens=kv_tokens,
                              max_requests=max(parallel, 1), max_step_tokens=prefill_chunk)
         self.ctx, self.prefill_chunk, self.parallel = ctx, prefill_chunk, parallel
+        # steps with prompt tokens are trimmed to whole 128-row tiles of the many-row kernels (Scheduler)
+        self.row_quantum = 128 if self.engine.runtime.dtype == torch.bfloat16 else 0
         self.host_sampling = host_sampling
         self.last_stats = {}
         self.last_errors = {}
@@ -89,7 +91,7 @@ class LLM:
         if len(limits) != len(prompts):
             raise ValueError(f"max_tokens: {len(limits)} numbers for {len(prompts)} prompts")
         sched = Scheduler(self.engine.cache, ctx=self.ctx, max_num_seqs=self.parallel,
-                          prefill_chunk=self.prefill_chunk)
+                          prefill_chunk=self.prefill_chunk, row_quantum=getattr(self, "row_quantum", 0))
         for i, p in enumerate(prompts):
             sched.add(Request(i, list(p), int(limits[i]),
                               SamplingParams(temperature, top_k, top_p, seed + i, frequency_penalty,

@@ -947,3 +947,25 @@ def test_which_many_row_kernel_and_which_norms_are_deferred():
         assert ops.defers_norm(m, w_o, w_gu, True) == yes, m
     assert not ops.defers_norm(8, w_o.float(), w_gu)                                     # the 32-bit path
     assert not ops.defers_norm(8, w_o, torch.empty(64, 100, dtype=torch.bfloat16))       # rows of 100 elements
+
+
+def test_scheduler_trims_mixed_steps_to_whole_tiles():
+    """With a row quantum, a step of decoding requests and prompt tokens is cut to a whole number of
+    tiles when that costs at most an eighth of its prompt tokens; the tokens come in the next step."""
+    def run(quantum):
+        cache = CacheManager([PagedKVNeed(1, 16)], [None], 16, 8192, 8)
+        s = Scheduler(cache, ctx=2048, max_num_seqs=4, prefill_chunk=512, row_quantum=quantum)
+        for i, n in enumerate((20, 30, 1000)):
+            s.add(Request(i, list(range(1, n + 1)), max_tokens=50))
+        return [[(rid, take) for rid, take, _ in step] for step in drive(s, cache)]
+
+    seen = run(128)
+    # step 0: 20 + 30 + 462 prompt tokens = 512 rows: nothing to trim
+    assert seen[0] == [(0, 20), (1, 30), (2, 462)]
+    # step 1: two decoding requests beside 512 prompt tokens are 514 rows: the portion gives up two
+    assert seen[1] == [(0, 1), (1, 1), (2, 510)]
+    # step 2: the rest of the prompt (28 tokens) beside two: 30 rows, under one tile: as it is
+    assert seen[2] == [(0, 1), (1, 1), (2, 28)]
+    assert all(take == 1 for step in seen[3:] for _, take in step)
+    # without a quantum nothing is trimmed
+    assert run(0)[1] == [(0, 1), (1, 1), (2, 512)]
