@@ -294,15 +294,22 @@ class Engine:
         return ctx, views
 
     # ------------------------------------------------------------------ the step
-    def step(self, items: Sequence[StepItem], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
-        """`device_tokens` (int32 on the device, one entry per item; only for steps of one token per
-        item): the items' token ids are taken from there instead of from the items, whose `tokens`
-        are then placeholders: ids that an earlier step's sampler left on the device go into the
-        next step without a round trip over the host."""
+    def step(self, items: Sequence[StepItem], device_tokens: Optional[torch.Tensor] = None,
+             n_device: Optional[int] = None) -> Optional[torch.Tensor]:
+        """`device_tokens` (int32 on the device): the token ids of the first `n_device` items (all of
+        them by default), which have one token each, are taken from there instead of from the items,
+        whose `tokens` are then placeholders: ids that an earlier step's sampler left on the device go
+        into the next step without a round trip over the host."""
         decode_only = bool(items) and all(len(it.tokens) == 1 for it in items)
-        if device_tokens is not None and (not decode_only or device_tokens.numel() < len(items)
-                                          or device_tokens.dtype != torch.int32):
-            raise StepError("device_tokens needs one int32 id per item and one token per item")
+        n_dev = 0
+        if device_tokens is not None:
+            n_dev = len(items) if n_device is None else int(n_device)
+            if (not 0 <= n_dev <= len(items) or any(len(it.tokens) != 1 for it in items[:n_dev])
+                    or device_tokens.numel() < n_dev or device_tokens.dtype != torch.int32):
+                raise StepError("device_tokens needs one int32 id for each of the first n_device items, "
+                                "which have one token each")
+            if n_dev == 0:
+                device_tokens = None
         # A decode-only step on the C++ host is checked there (token range, wanted places, a request
         # named twice, pages: all before anything changes); the Python check runs only to word the
         # error.  Anything that is not a plain int goes through the Python check first.
@@ -314,19 +321,19 @@ class Engine:
         graphable = self.use_graphs
         if graphable and decode_only and len(items) <= GRAPH_MAX_REQUESTS:
             try:
-                logits = self._graph_step(items, device_tokens)
+                logits = self._graph_step(items, device_tokens, n_dev=n_dev)
             except (ValueError, KeyError):
                 if light:
                     self._check_items(items)         # raises the StepError that names the fault
                 raise
         elif graphable and self.native_host and self._one_portion_last(items):
-            logits = self._graph_step(items, None, portion=len(items[-1].tokens))
+            logits = self._graph_step(items, device_tokens, portion=len(items[-1].tokens), n_dev=n_dev)
         else:
             host, layout, meta = self._build(items)
             dev = torch.empty(layout.total, dtype=torch.int32, device=self.runtime.device)
             self._copy_in(dev, host)
             if device_tokens is not None:
-                dev[:len(items)].copy_(device_tokens[:len(items)])          # the tokens are the first array
+                dev[:n_dev].copy_(device_tokens[:n_dev])                    # the tokens are the first array, in item order
             ctx, views = self._context(layout.views(dev), meta, bool(meta["rows"]))
             logits = self.model.forward(ctx, views)
         if self._windowed:
@@ -365,7 +372,7 @@ class Engine:
                 graph.capture_end()
         torch.cuda.current_stream().wait_stream(side)
 
-    def _graph_step(self, items: Sequence[StepItem], device_tokens=None, portion: int = 0) -> Optional[torch.Tensor]:
+    def _graph_step(self, items: Sequence[StepItem], device_tokens=None, portion: int = 0, n_dev: int = 0) -> Optional[torch.Tensor]:
         """portion: 0 for a decode step; else the last item is a portion of that many tokens and the
         items before it have one token each (padded to a power of two, the portion behind them)."""
         R = len(items) - (1 if portion else 0)             # one-token items
@@ -406,7 +413,7 @@ class Engine:
             assert layout.offsets == g.layout.offsets
         self._copy_in(g.static, host)
         if device_tokens is not None:
-            g.static[:R].copy_(device_tokens[:R])                          # the tokens are the first array
+            g.static[:n_dev].copy_(device_tokens[:n_dev])                  # the tokens are the first array, one-token items first
         g.uses += 1
         g.last_used = self.stats["steps"]
         if g.uses == 1 or (portion and g.uses < GRAPH_PORTION_CAPTURE_AT and g.graph is None):

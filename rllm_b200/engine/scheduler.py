@@ -76,12 +76,14 @@ class PlannedItem:
     take: int
     want_last: bool
     ahead: int = 0          # tokens of the request that an uncommitted earlier step holds (plan_ahead)
+    sampled: bool = False   # its one token is what that earlier step samples: still on the device
 
     @property
     def tokens(self) -> list:
-        if self.ahead:
+        if self.sampled:
             return [0] * self.take       # not known on the host yet: the step takes them from the device
-        return self.seq.tokens[self.seq.cached:self.seq.cached + self.take]
+        first = self.seq.cached + self.ahead
+        return self.seq.tokens[first:first + self.take]
 
     @property
     def counter(self) -> int:
@@ -164,14 +166,18 @@ class Scheduler:
                 continue
             left -= take
             plan.append(PlannedItem(s, take, s.cached + take == len(s.tokens)))
+        return self._trim(plan, len(decoders))
+
+    def _trim(self, plan: list, n_decoders: int) -> list:
+        """A step with prompt tokens, cut to a whole number of tiles (row_quantum) where that is cheap."""
         q = self.row_quantum
-        if q and len(plan) > len(decoders):
+        if q and len(plan) > n_decoders:
             rows = sum(p.take for p in plan)
-            prompt_rows = rows - len(decoders)
+            prompt_rows = rows - n_decoders
             over = rows % q
             last = plan[-1]
             if rows > q and 0 < over <= prompt_rows // 8 and over < last.take:
-                plan[-1] = PlannedItem(last.seq, last.take - over, False)
+                plan[-1] = PlannedItem(last.seq, last.take - over, False, ahead=last.ahead)
         return plan
 
     def _preempt_newest(self) -> Optional[_Seq]:
@@ -209,26 +215,38 @@ class Scheduler:
 
     def plan_ahead(self, plan: Sequence[PlannedItem]) -> Optional[list]:
         """The step after `plan`, planned before `plan`'s sampled tokens are known on the host, so
-        that it can be launched while they are still on their way: every request of `plan` decodes
-        the token that `plan` samples for it.  Only when nothing else could happen in that step:
-        `plan` holds every running request and samples for each, none of them reaches its budget
-        with the token under way, none needs the host for its next token (penalties, bias), nothing
-        waits for admission that could be admitted, and the pages are there.  None otherwise (the
-        caller then commits `plan` first and plans as usual).  A request that `plan`'s token ends
-        (a stop id) has then run one token too far; its pages go back when `plan` is committed, and
-        its row of the step planned here is dropped."""
-        if not plan or len(plan) != len(self.running) or any(not p.want_last for p in plan):
+        that it can be launched while they are still on their way: every request for which `plan`
+        samples decodes that token (it is taken from the device), every request that `plan` leaves in
+        the middle of its prompt goes on with it.  Only when nothing else could happen in that step:
+        `plan` holds every running request, none reaches its budget with the token under way, none
+        needs the host for its next token (penalties, bias), nothing waits for admission that could
+        be admitted, and the pages are there.  None otherwise (the caller then commits `plan` first
+        and plans as usual).  The decoding requests come first, in the order in which `plan` samples
+        for them.  A request that `plan`'s token ends (a stop id) has then run one token too far; its
+        pages go back when `plan` is committed, and its row of the step planned here is dropped."""
+        if not plan or len(plan) != len(self.running):
             return None
         if self.waiting and len(self.running) < self.max_num_seqs:
             return None
         for p in plan:
             s = p.seq
-            if s.req.params.adjusts or len(s.tokens) - s.n_prompt + 1 >= s.budget:
+            if p.want_last and (s.req.params.adjusts or len(s.tokens) - s.n_prompt + 1 >= s.budget):
                 return None
-        if not self.cache.can_append([(p.seq.rid, 1) for p in plan]):
+        nxt = [PlannedItem(p.seq, 1, True, ahead=p.take, sampled=True) for p in plan if p.want_last]
+        n_decoders = len(nxt)
+        left = self.prefill_chunk
+        for p in sorted((p for p in plan if not p.want_last), key=lambda p: p.seq.order):
+            s = p.seq
+            take = min(s.todo() - p.take, left)          # what is left of the prompt behind plan's portion
+            if take <= 0:
+                continue
+            left -= take
+            nxt.append(PlannedItem(s, take, s.cached + p.take + take == len(s.tokens), ahead=p.take))
+        nxt = self._trim(nxt, n_decoders)
+        if not self.cache.can_append([(p.seq.rid, p.take) for p in nxt]):
             return None
         self.stats["steps"] += 1
-        return [PlannedItem(p.seq, 1, True, ahead=p.take) for p in plan]
+        return nxt
 
     # ------------------------------------------------------------------ after the step
     def commit(self, plan: Sequence[PlannedItem], sampled: Sequence[int]) -> list:
@@ -239,7 +257,8 @@ class Scheduler:
         for p in plan:
             s = p.seq
             if p.ahead and s not in self.running:
-                next(it)                 # the request ended with the step before: this token was one too far
+                if p.want_last:
+                    next(it)             # the request ended with the step before: this token was one too far
                 continue
             if s.cached < s.n_prompt:
                 self.stats["prompt_tokens"] += min(p.take, s.n_prompt - s.cached)

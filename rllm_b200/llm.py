@@ -161,7 +161,8 @@ class LLM:
         """One engine step for the planned items and one sampled id per item that wants its last row:
         a list (no row wanted, or sampled on the host) or the ids still on the device (_SampledIds)."""
         items = [StepItem(p.seq.rid, p.tokens, [p.take - 1] if p.want_last else []) for p in plan]
-        logits = self.engine.step(items, device_tokens=device_tokens)
+        logits = self.engine.step(items, device_tokens=device_tokens,
+                                  n_device=sum(1 for p in plan if p.sampled) if device_tokens is not None else None)
         wanted = [p for p in plan if p.want_last]
         if not wanted:
             return []

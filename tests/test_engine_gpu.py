@@ -125,6 +125,31 @@ def test_greedy_generation_matches_plain(dirs, name):
     assert llm.engine.cache.n_free_pages(0) == llm.engine.cache.n_blocks
 
 
+def test_steps_with_prompt_portions_are_planned_ahead(dirs, monkeypatch):
+    """Steps that hold the next portion of a prompt beside decoding requests are launched before the
+    tokens of the step before are on the host (the decoding requests' ids come from the device, the
+    portion's from the host): they happen, and the tokens are the plain implementation's."""
+    from rllm_b200 import LLM
+    from rllm_b200.engine import scheduler
+    cfg, w = plain_impl.load_model(dirs["B", "float32"])
+    prompts = [helpers.random_tokens(n, cfg["vocab_size"], 70 + n) for n in (5, 61, 47, 30, 52)]
+    want = [plain_impl.greedy_generate(cfg, w, p, 12) for p in prompts]
+    mixed = [0]
+    real = scheduler.Scheduler.plan_ahead
+
+    def counted(self, plan):
+        nxt = real(self, plan)
+        if nxt and any(not p.sampled for p in nxt) and any(p.sampled for p in nxt):
+            mixed[0] += 1
+        return nxt
+
+    monkeypatch.setattr(scheduler.Scheduler, "plan_ahead", counted)
+    llm = LLM(dirs["B", "float32"], dtype="float32", device=DEV, ctx=128, parallel=3, prefill_chunk=8)
+    assert llm.generate(prompts, max_tokens=12) == want
+    assert mixed[0] >= 5
+    assert llm.engine.cache.n_free_pages(0) == llm.engine.cache.n_blocks
+
+
 def test_bfloat16_generation_follows_plain_argmax(dirs):
     """bfloat16 greedy tokens agree with the plain implementation wherever its top two logits are
     further apart than the bfloat16 error bound."""

@@ -541,7 +541,17 @@ def drive_pipelined(sched, cache, pick, max_steps=10000):
         ahead = sched.plan_ahead(plan)
         if ahead:
             n_ahead += 1
-            assert [p.seq for p in ahead] == [p.seq for p in plan] and all(p.tokens == [0] for p in ahead)
+            # the requests that `plan` samples for decode that token (a placeholder until it is known), first
+            # and in `plan`'s order; the others go on with their prompts, whose tokens are known
+            n_dec = sum(p.want_last for p in plan)
+            assert [p.seq for p in ahead[:n_dec]] == [p.seq for p in plan if p.want_last]
+            assert all(p.sampled and p.tokens == [0] for p in ahead[:n_dec])
+            for p in ahead[n_dec:]:
+                mine = next(q for q in plan if q.seq is p.seq)
+                first = p.seq.cached + mine.take
+                assert not p.sampled and not mine.want_last and p.tokens == p.seq.tokens[first:first + p.take]
+            if len(ahead) > n_dec:
+                drive_pipelined.mixed += 1
             for p in ahead:
                 cache.append(p.seq.rid, p.take)
         # the tokens of `plan` arrive: each from the request's history before it (an item planned ahead
@@ -553,6 +563,9 @@ def drive_pipelined(sched, cache, pick, max_steps=10000):
         cache.check_invariants()
         pending = ahead
     return n_ahead
+
+
+drive_pipelined.mixed = 0
 
 
 def test_planning_ahead_changes_no_result():
@@ -580,6 +593,25 @@ def test_planning_ahead_changes_no_result():
     ahead_tight, _, p1 = run(True, 208)
     assert ahead_tight == plain_tight == plain and p0 >= 1 and p1 >= 1
 
+    # long prompts in portions beside decoding requests: those steps are planned ahead too
+    def run_long(pipelined, quantum=0):
+        cache = CacheManager([PagedKVNeed(1, 16)], [None], 16, 8192, 8)
+        s = Scheduler(cache, ctx=2048, max_num_seqs=3, prefill_chunk=64, row_quantum=quantum)
+        for i in range(6):
+            s.add(Request(i, [(i * 7 + j) % 50 + 1 for j in range(150 + 90 * i)], max_tokens=20 + 5 * i))
+        drive_pipelined.mixed = 0
+        if pipelined:
+            drive_pipelined(s, cache, pick)
+        else:
+            drive(s, cache, pick)
+        assert not cache.requests and cache.n_free_pages(0) == cache.n_blocks
+        return {f.request_id: (f.tokens, f.reason) for f in s.collect()}, drive_pipelined.mixed
+    plain_long, _ = run_long(False)
+    ahead_long, mixed = run_long(True)
+    assert ahead_long == plain_long and mixed > 10
+    trimmed, mixed = run_long(True, quantum=32)
+    assert trimmed == plain_long and mixed > 10
+
 
 class _FakeEngine:
     """Stands in for the engine under LLM.generate: the host cache manager and a step that returns
@@ -590,7 +622,7 @@ class _FakeEngine:
         self.calls, self.fail_steps, self.device_error_at = 0, set(fail_steps), set(device_error_at)
         self.checks = 0
 
-    def step(self, items, device_tokens=None):
+    def step(self, items, device_tokens=None, n_device=None):
         self.calls += 1
         if self.calls in self.fail_steps:
             raise RuntimeError(f"injected fault in step {self.calls}")
@@ -647,7 +679,7 @@ def test_generate_leaves_nothing_in_the_cache_however_it_ends():
     from rllm_b200.llm import GenerationError
 
     class Interrupting(_FakeEngine):
-        def step(self, items, device_tokens=None):
+        def step(self, items, device_tokens=None, n_device=None):
             if self.calls == 2:
                 raise KeyboardInterrupt
             return super().step(items, device_tokens)
