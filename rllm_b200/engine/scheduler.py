@@ -91,6 +91,11 @@ class PlannedItem:
         return self.seq.cached + self.ahead + self.take
 
 
+def _wants(plan, seq) -> bool:
+    """Whether `plan` samples for `seq`."""
+    return any(p.seq is seq and p.want_last for p in plan)
+
+
 class Scheduler:
     def __init__(self, cache, ctx: int = 4096, max_num_seqs: int = 4, prefill_chunk: int = 512, row_quantum: int = 0):
         """row_quantum: the rows of a tile of the many-row kernels (0: none).  A step that holds prompt
@@ -217,31 +222,40 @@ class Scheduler:
         """The step after `plan`, planned before `plan`'s sampled tokens are known on the host, so
         that it can be launched while they are still on their way: every request for which `plan`
         samples decodes that token (it is taken from the device), every request that `plan` leaves in
-        the middle of its prompt goes on with it.  Only when nothing else could happen in that step:
-        `plan` holds every running request, none reaches its budget with the token under way, none
-        needs the host for its next token (penalties, bias), nothing waits for admission that could
-        be admitted, and the pages are there.  None otherwise (the caller then commits `plan` first
-        and plans as usual).  The decoding requests come first, in the order in which `plan` samples
-        for them.  A request that `plan`'s token ends (a stop id) has then run one token too far; its
-        pages go back when `plan` is committed, and its row of the step planned here is dropped."""
-        if not plan or len(plan) != len(self.running):
+        the middle of its prompt goes on with it, and waiting requests are admitted as in `plan()`.
+        A request that reaches its budget with the token under way is left out (it ends when `plan`
+        is committed; the place it leaves is filled one step later).  None when the step cannot be
+        known yet: a running request is not in `plan`, one of them needs the host for its next token
+        (penalties, bias), or the pages are short (the caller then commits `plan` first and plans as
+        usual, which may preempt).  The decoding requests come first, in the order in which `plan`
+        samples for them.  A request that `plan`'s token ends by a stop id has then run one token
+        too far; its pages go back when `plan` is committed, and its row of the step planned here is
+        dropped."""
+        live = [p for p in plan if p.seq in self.running]       # the others ended with the step before `plan`
+        if not live or len(live) != len(self.running):
             return None
-        if self.waiting and len(self.running) < self.max_num_seqs:
-            return None
-        for p in plan:
+        nxt = []
+        for p in live:
             s = p.seq
-            if p.want_last and (s.req.params.adjusts or len(s.tokens) - s.n_prompt + 1 >= s.budget):
+            if not p.want_last:
+                continue
+            if s.req.params.adjusts:
                 return None
-        nxt = [PlannedItem(p.seq, 1, True, ahead=p.take, sampled=True) for p in plan if p.want_last]
+            if len(s.tokens) - s.n_prompt + 1 < s.budget:
+                nxt.append(PlannedItem(s, 1, True, ahead=p.take, sampled=True))
         n_decoders = len(nxt)
+        self._admit()
+        held = {id(p.seq): p.take for p in live}                # tokens that `plan` holds, not yet committed
         left = self.prefill_chunk
-        for p in sorted((p for p in plan if not p.want_last), key=lambda p: p.seq.order):
-            s = p.seq
-            take = min(s.todo() - p.take, left)          # what is left of the prompt behind plan's portion
+        for s in sorted((s for s in self.running if id(s) not in held or not _wants(live, s)), key=lambda s: s.order):
+            ahead = held.get(id(s), 0)
+            take = min(s.todo() - ahead, left)                   # what is left of the prompt behind plan's portion
             if take <= 0:
                 continue
             left -= take
-            nxt.append(PlannedItem(s, take, s.cached + p.take + take == len(s.tokens), ahead=p.take))
+            nxt.append(PlannedItem(s, take, s.cached + ahead + take == len(s.tokens), ahead=ahead))
+        if not nxt:
+            return None
         nxt = self._trim(nxt, n_decoders)
         if not self.cache.can_append([(p.seq.rid, p.take) for p in nxt]):
             return None

@@ -102,7 +102,7 @@ class LLM:
         # A step whose sampled ids are still on the device: (plan, ids).  While they travel to the host
         # the next step is planned and launched already where that is possible (Scheduler.plan_ahead),
         # taking its tokens from the device; the host's work for a step then hides behind the GPU's.
-        pending = None
+        pending = also = None
         try:
             while sched.has_work() or pending is not None:
                 try:
@@ -119,11 +119,16 @@ class LLM:
                     else:
                         plan, sampled = pending
                         ahead = sched.plan_ahead(plan)
-                        ahead_ids = (self._run_step(ahead, host_samplers, device_tokens=sampled.device_ids)
+                        ahead_ids = (self._run_step(ahead, host_samplers, device_tokens=self._ids_for(plan, ahead, sampled))
                                      if ahead else None)
                         ids = sampled.tolist()
-                        pending = (ahead, ahead_ids) if ahead else None
+                        pending = (ahead, ahead_ids) if isinstance(ahead_ids, _SampledIds) else None
+                        if ahead and pending is None:
+                            also = (ahead, ahead_ids)         # a step that samples nothing: committed right behind
                     sched.commit(plan, ids)
+                    if also is not None:
+                        sched.commit(*also)
+                        also = None
                     for f in sched.collect():
                         results[f.request_id] = f
                     steps += 1
@@ -132,7 +137,7 @@ class LLM:
                 except Exception as e:
                     # a failed step fails the requests that were running and frees what they hold; the
                     # queue goes on (crates/rllm-server/src/engine.rs:569-578)
-                    pending = None
+                    pending = also = None
                     sched.fail_running(f"step failed: {type(e).__name__}: {e}")
                     for f in sched.collect():
                         results[f.request_id] = f
@@ -156,6 +161,17 @@ class LLM:
         if self.last_errors:
             raise GenerationError(out)
         return [f.tokens for f in out]
+
+    @staticmethod
+    def _ids_for(plan, ahead, sampled):
+        """The ids that `plan`'s sampler left on the device, in the order of the items of `ahead` that
+        take them (those of `plan`'s requests that go on; one that ends with its token is not among them)."""
+        order = {id(p.seq): j for j, p in enumerate(q for q in plan if q.want_last)}
+        src = [order[id(p.seq)] for p in ahead if p.sampled]
+        ids = sampled.device_ids
+        if src == list(range(len(src))):
+            return ids
+        return ids.index_select(0, torch.tensor(src, dtype=torch.int64, device=ids.device))
 
     def _run_step(self, plan, host_samplers, device_tokens=None):
         """One engine step for the planned items and one sampled id per item that wants its last row:

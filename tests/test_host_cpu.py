@@ -543,13 +543,15 @@ def drive_pipelined(sched, cache, pick, max_steps=10000):
             n_ahead += 1
             # the requests that `plan` samples for decode that token (a placeholder until it is known), first
             # and in `plan`'s order; the others go on with their prompts, whose tokens are known
-            n_dec = sum(p.want_last for p in plan)
-            assert [p.seq for p in ahead[:n_dec]] == [p.seq for p in plan if p.want_last]
+            n_dec = sum(p.sampled for p in ahead)
+            sampled_for = [p.seq for p in plan if p.want_last and p.seq in sched.running]
+            assert [p.seq for p in ahead[:n_dec]] == [q for q in sampled_for if any(a.seq is q for a in ahead[:n_dec])]
             assert all(p.sampled and p.tokens == [0] for p in ahead[:n_dec])
             for p in ahead[n_dec:]:
-                mine = next(q for q in plan if q.seq is p.seq)
-                first = p.seq.cached + mine.take
-                assert not p.sampled and not mine.want_last and p.tokens == p.seq.tokens[first:first + p.take]
+                mine = next((q for q in plan if q.seq is p.seq), None)      # None: admitted with this step
+                first = p.seq.cached + (mine.take if mine else 0)
+                assert not p.sampled and (mine is None or not mine.want_last)
+                assert p.tokens == p.seq.tokens[first:first + p.take]
             if len(ahead) > n_dec:
                 drive_pipelined.mixed += 1
             for p in ahead:
