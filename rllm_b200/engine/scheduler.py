@@ -225,14 +225,17 @@ class Scheduler:
         the middle of its prompt goes on with it, and waiting requests are admitted as in `plan()`.
         A request that reaches its budget with the token under way is left out (it ends when `plan`
         is committed; the place it leaves is filled one step later).  None when the step cannot be
-        known yet: a running request is not in `plan`, one of them needs the host for its next token
+        known yet: a decoding request is not in `plan`, one of them needs the host for its next token
         (penalties, bias), or the pages are short (the caller then commits `plan` first and plans as
         usual, which may preempt).  The decoding requests come first, in the order in which `plan`
         samples for them.  A request that `plan`'s token ends by a stop id has then run one token
         too far; its pages go back when `plan` is committed, and its row of the step planned here is
         dropped."""
         live = [p for p in plan if p.seq in self.running]       # the others ended with the step before `plan`
-        if not live or len(live) != len(self.running):
+        in_plan = {id(p.seq) for p in live}
+        # a running request that `plan` left out waits for its share of the prompt budget: it is as the
+        # host knows it; one that decodes would have to be in `plan`
+        if not live or any(id(s) not in in_plan and s.decoding() for s in self.running):
             return None
         nxt = []
         for p in live:
