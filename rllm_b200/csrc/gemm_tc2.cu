@@ -23,6 +23,13 @@
 //   SwiGLU: the leader's half of B holds 128 gate rows, the peer's the 128 up rows of the same
 //   index, so that a thread finds gate and up of an output column in its own accumulator row.
 //
+// A fourth epilogue (T2_EPI_QKV) ends the fused q/k/v projection of a prompt step: a thread owns a
+// token's row of the tile, 256 columns = whole heads (head size 64 or 128), and does for each head
+// what qk_norm_rope_store (elementwise.cu) does in a kernel of its own: RMSNorm over the head with
+// the q or k norm weight, rotate-half rotary with the (cos, sin) of the token's angles, queries out
+// as bfloat16, keys and values into their page of the cache.  The float32 projection never goes
+// to memory.
+//
 // The last, partial wave: when the tiles left over after the full waves would keep at most half (a
 // quarter) of the pairs busy, each of them is cut into two (four) slices of columns (MMAs of N = 128
 // or 64), so that the wave takes half (a quarter) of a tile's time; a product with fewer tiles than
@@ -42,7 +49,7 @@
 #define T2_KH 2                                  // blocks of 64 along K per stage (one barrier round, 4 * T2_KH MMAs)
 #define T2_STAGE_BYTES (2 * T2_KH * T2_HALF_BYTES)   // per CTA: T2_KH A tiles, then T2_KH tiles of its half of B
 
-enum { T2_EPI_STORE = 0, T2_EPI_ACCUM = 1, T2_EPI_SWIGLU = 2 };
+enum { T2_EPI_STORE = 0, T2_EPI_ACCUM = 1, T2_EPI_SWIGLU = 2, T2_EPI_QKV = 3 };
 enum { T2_ERR_FULL = 1, T2_ERR_EMPTY = 2, T2_ERR_ACC = 3 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -121,6 +128,18 @@ template <> __device__ __forceinline__ void t2_store_row32<bf16>(bf16* dst, cons
     }
 }
 
+struct T2Qkv {
+    bf16* q_out;                 // [M, H * hd]
+    bf16* k_cache;               // [pages, K, bs, hd]
+    bf16* v_cache;
+    const int* slots;            // [M]: page * bs + offset of the token's place, < 0: keep nothing
+    const float2* cs_table;      // [M, hd / 2] (cos, sin), null: no rotation
+    const float* q_norm_w;       // [hd], null: no norm
+    const float* k_norm_w;
+    int H, K, bs, write_kv, n_slots;
+    float eps;
+};
+
 struct T2Maps {
     CUtensorMap a;          // boxes of 64 x 128 rows
     CUtensorMap b[3];       // boxes of 64 x 128, 64 and 32 rows: a CTA's half of a whole, half and quarter B tile
@@ -139,10 +158,10 @@ __device__ __forceinline__ void t2_item(int item, int head, int tail_log2, int& 
 // grid (2 * pairs), clusters of two along x (a kernel with cta_group::2 instructions is refused with
 // "invalid cluster size" when its clusters are not even along x): CTAs 2p and 2p + 1 are pair p,
 // which takes tiles p, p + pairs, ... (m fastest, as in gemm_tc.cu).
-template <int EPI, typename TC, int STAGES>
+template <int EPI, typename TC, int STAGES, int HD = 128>
 __global__ void __launch_bounds__(T2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ T2Maps maps, TC* __restrict__ C, int ldc, int M, int N, int K,
-                int up_row_offset, int* __restrict__ err, int tail_tiles, int tail_log2) {
+                int up_row_offset, int* __restrict__ err, int tail_tiles, int tail_log2, const T2Qkv qk) {
     constexpr int BN_OUT = (EPI == T2_EPI_SWIGLU) ? T2_BN / 2 : T2_BN;      // output columns per tile
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -276,6 +295,74 @@ gemm_tc2_kernel(const __grid_constant__ T2Maps maps, TC* __restrict__ C, int ldc
             tc_fence_after();
             if (first && item + n_pairs >= total_items) { pdl_launch_dependents(); first = false; }
             const uint32_t taddr = tmem_base + buf * T2_BN + ((uint32_t)(quarter * 32) << 16);
+            if constexpr (EPI == T2_EPI_QKV) {
+                // this thread's token: its place in the cache and its angles
+                const bool row_ok = gm < M;
+                int slot = row_ok ? qk.slots[gm] : -1;
+                if (slot >= qk.n_slots) {
+                    atomicExch(err, RLLM_ERR_SLOT);
+                    slot = -1;
+                }
+                const float2* cs = (qk.cs_table && row_ok) ? qk.cs_table + (size_t)gm * (HD / 2) : nullptr;
+#pragma unroll 1
+                for (int hh = 0; hh < T2_BN / HD; ++hh) {
+                    const int head = n0 / HD + hh;
+                    float v[HD];
+#pragma unroll
+                    for (int c = 0; c < HD / 32; ++c)
+                        tmem_ld32(taddr + hh * HD + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * c]));
+                    tmem_ld_wait();
+                    if (hh == T2_BN / HD - 1) {                  // all of this warp's TMEM reads of the tile are done
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[buf], 0));
+                    }
+                    if (!row_ok || head >= qk.H + 2 * qk.K) continue;
+                    const int kind = head < qk.H ? 0 : (head < qk.H + qk.K ? 1 : 2);
+                    bf16* dst = nullptr;
+                    if (kind == 0) {
+                        dst = qk.q_out + ((size_t)gm * qk.H + head) * HD;
+                    } else if (slot >= 0 && qk.write_kv) {
+                        const int kvh = kind == 1 ? head - qk.H : head - qk.H - qk.K;
+                        dst = (kind == 1 ? qk.k_cache : qk.v_cache) +
+                              (((size_t)(slot / qk.bs) * qk.K + kvh) * qk.bs + (slot % qk.bs)) * HD;
+                    }
+                    if (!dst) continue;
+                    const float* nw = kind == 0 ? qk.q_norm_w : (kind == 1 ? qk.k_norm_w : nullptr);
+                    float rs = 1.f;
+                    if (nw) {
+                        float ss = 0.f;
+#pragma unroll
+                        for (int i = 0; i < HD; ++i) ss += v[i] * v[i];
+                        rs = 1.0f / sqrtf(ss / (float)HD + qk.eps);
+                    }
+#pragma unroll
+                    for (int i = 0; i < HD / 2; i += 2) {
+                        float4 c4 = make_float4(1.f, 0.f, 1.f, 0.f);
+                        if (cs && kind != 2) c4 = *reinterpret_cast<const float4*>(cs + i);      // two (cos, sin) pairs
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            float a = v[i + e], b = v[i + e + HD / 2];
+                            if (nw) { a = a * rs * __ldg(nw + i + e); b = b * rs * __ldg(nw + i + e + HD / 2); }
+                            if (kind != 2) {
+                                const float cx = e ? c4.z : c4.x, cy = e ? c4.w : c4.y;
+                                const float a2 = a * cx - b * cy, b2 = a * cy + b * cx;
+                                a = a2; b = b2;
+                            }
+                            v[i + e] = a; v[i + e + HD / 2] = b;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < HD / 8; ++j) {
+                        uint4 u;
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                        u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
+                        u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
+                        reinterpret_cast<uint4*>(dst)[j] = u;
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int c0 = 0; c0 < cols_out; c0 += 32) {
                 uint32_t r[32];
@@ -319,6 +406,7 @@ gemm_tc2_kernel(const __grid_constant__ T2Maps maps, TC* __restrict__ C, int ldc
                     t2_store_row32<TC>(dst, v, n_valid);
                 }
             }
+            }
         }
     }
     __syncwarp();          // the lanes that had no role meet the elected one: the barriers below want whole warps
@@ -342,11 +430,12 @@ static int t2_make_tmap(CUtensorMap* map, const void* base, int rows, int cols, 
     return r == CUDA_SUCCESS ? 0 : 30000 + (int)r;
 }
 
-template <int EPI, typename TC, int STAGES>
-static int launch_tc2(const T2Maps& maps, void* C, int ldc, int M, int N, int K, int up, int* err, cudaStream_t stream) {
+template <int EPI, typename TC, int STAGES, int HD = 128>
+static int launch_tc2(const T2Maps& maps, void* C, int ldc, int M, int N, int K, int up, int* err, cudaStream_t stream,
+                      const T2Qkv& qk = T2Qkv()) {
     constexpr int BN_OUT = (EPI == T2_EPI_SWIGLU) ? T2_BN / 2 : T2_BN;
     constexpr size_t smem = (size_t)STAGES * T2_STAGE_BYTES + 1024;
-    auto kern = gemm_tc2_kernel<EPI, TC, STAGES>;
+    auto kern = gemm_tc2_kernel<EPI, TC, STAGES, HD>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -365,13 +454,14 @@ static int launch_tc2(const T2Maps& maps, void* C, int ldc, int M, int N, int K,
     const int all_pairs = n_sm / 2;
     const int rem = tiles % all_pairs;
     int tail_log2 = 0;
-    if (rem > 0 && rem * 4 <= all_pairs) tail_log2 = 2;
+    if (EPI == T2_EPI_QKV) tail_log2 = 0;                      // whole heads: a tile is not cut
+    else if (rem > 0 && rem * 4 <= all_pairs) tail_log2 = 2;
     else if (rem > 0 && rem * 2 <= all_pairs) tail_log2 = 1;
     const int tail_tiles = tail_log2 ? rem : 0;
     const int items = tiles - tail_tiles + (tail_tiles << tail_log2);
     const int pairs = items < all_pairs ? items : all_pairs;
     return rllm_launch_clusters(kern, dim3(2 * pairs), dim3(T2_THREADS), smem, stream, dim3(2, 1, 1), maps, (TC*)C, ldc,
-                                M, N, K, up, err, tail_tiles, tail_log2);
+                                M, N, K, up, err, tail_tiles, tail_log2, qk);
 }
 
 // C[M,N] (+)= A[M,K] . B[N,K]^T with two SMs per 256 x 256 tile.  Arguments, epilogues and return
@@ -403,7 +493,38 @@ RLLM_API int rllm_gemm_tc2(const void* A, const void* B, void* C, int c_dtype, i
     return (int)cudaErrorInvalidValue;
 }
 
+// The fused q/k/v projection of a prompt step with the q/k norm, the rotary encoding and the cache
+// write in its epilogue: A [M, Kdim] rows, W [(H + 2 Kh) * hd, Kdim] the stacked projections (q heads,
+// k heads, v heads), head size 64 or 128, bfloat16 queries and cache.  cs_table [M, hd / 2] float2
+// (cos, sin) or null; q_norm_w, k_norm_w [hd] float32 or null; slots [M].
+RLLM_API int rllm_qkv_tc2(const void* A, const void* W, int M, int Kdim, int lda, int ldw, void* q_out, void* k_cache,
+                          void* v_cache, const int* slots, const void* cs_table, const float* q_norm_w,
+                          const float* k_norm_w, int H, int Kh, int hd, int bs, float eps, int write_kv,
+                          long long n_slots, int* err, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    const int N = (H + 2 * Kh) * hd;
+    if (Kdim <= 0 || (Kdim & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || !err ||
+        (hd != 64 && hd != 128) || H <= 0 || Kh <= 0 || bs <= 0 || !slots || !q_out || !k_cache || !v_cache ||
+        ((uintptr_t)q_out & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)cs_table & 15))
+        return (int)cudaErrorInvalidValue;
+    T2Maps maps;
+    int st = t2_make_tmap(&maps.a, A, M, Kdim, lda);
+    if (st) return st;
+    for (int i = 0; i < 3; ++i) {
+        st = t2_make_tmap(&maps.b[i], W, N, Kdim, ldw, 128 >> i);
+        if (st) return st;
+    }
+    T2Qkv qk;
+    qk.q_out = (bf16*)q_out; qk.k_cache = (bf16*)k_cache; qk.v_cache = (bf16*)v_cache; qk.slots = slots;
+    qk.cs_table = (const float2*)cs_table; qk.q_norm_w = q_norm_w; qk.k_norm_w = k_norm_w;
+    qk.H = H; qk.K = Kh; qk.bs = bs; qk.write_kv = write_kv;
+    qk.n_slots = (int)(n_slots > 0x7fffffffLL ? 0x7fffffffLL : n_slots); qk.eps = eps;
+    if (hd == 128) return launch_tc2<T2_EPI_QKV, bf16, 3, 128>(maps, nullptr, 0, M, N, Kdim, 0, err, stream, qk);
+    return launch_tc2<T2_EPI_QKV, bf16, 3, 64>(maps, nullptr, 0, M, N, Kdim, 0, err, stream, qk);
+}
+
 TC_DEFINE_WAIT_CONTROLS(rllm_tc2)
 
 // the packed-argument forms (common.cuh) for the host runtime's replay of recorded launches
 RLLM_PACKED(rllm_gemm_tc2)
+RLLM_PACKED(rllm_qkv_tc2)

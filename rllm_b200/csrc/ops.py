@@ -596,6 +596,50 @@ def gemm_tc2(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
     return out
 
 
+# From this many rows on the fused projection beats the library product followed by the q/k norm + rotary
+# kernel (us, library + kernel / fused; 8B sizes: 1,024 rows 46.5 / 52.6, 2,048 rows 90.2 / 78.1, 4,096 rows
+# 180.8 / 147.5; 0.6B sizes: 1,024 rows 23.0 / 24.1, 2,048 rows 35.3 / 32.8; 32B sizes: 2,048 rows 170.7 / 152.6)
+QKV_FUSED_MIN_ROWS = 2048
+USE_QKV_FUSED = os.environ.get("RLLM_B200_NO_QKV_FUSED", "0") in ("", "0")
+
+
+def can_fuse_qkv(h, w_qkv, hd: int, q_out, k_cache) -> bool:
+    """Whether qkv_norm_rope_store_fused takes this step: a prompt step of many rows, bfloat16
+    throughout, head size 64 or 128."""
+    return (USE_QKV_FUSED and isinstance(h, torch.Tensor) and h.shape[0] >= QKV_FUSED_MIN_ROWS and hd in (64, 128)
+            and _tc_ok(h, w_qkv) and q_out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+            and q_out.is_contiguous() and q_out.data_ptr() % 16 == 0)
+
+
+def qkv_norm_rope_store_fused(h, w_qkv, q_norm_w, k_norm_w, cs_table, slots, q_out, k_cache, v_cache, H, K, hd,
+                              block_size, eps, write_kv=True):
+    """q_out, caches <- norm / rotary / store of h . w_qkv^T, in one kernel: the two-SM tcgen05 product
+    with qk_norm_rope_store's work in its epilogue (gemm_tc2.cu); the float32 projection is never
+    written.  Arguments as qk_norm_rope_store with a table of angles (or None)."""
+    _need_cuda(h, w_qkv, q_out, k_cache, v_cache, slots)
+    n = h.shape[0]
+    if not _tc_ok(h, w_qkv) or hd not in (64, 128) or w_qkv.shape[0] != (H + 2 * K) * hd:
+        raise KernelError("qkv_norm_rope_store_fused needs bfloat16 operands with 16-byte aligned rows, head size 64 "
+                          "or 128 and the stacked q, k, v projections")
+    assert q_out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16
+    assert q_out.shape == (n, H * hd) and q_out.is_contiguous() and slots.dtype == torch.int32 and slots.numel() >= n
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape[-1] == hd
+    if cs_table is not None:
+        assert cs_table.dtype == torch.float32 and cs_table.numel() >= n * hd and cs_table.is_contiguous()
+    for nw in (q_norm_w, k_norm_w):
+        assert nw is None or (nw.dtype == torch.float32 and nw.numel() == hd and nw.is_contiguous())
+    n_slots = k_cache.numel() // (K * hd)
+    st = _lib("tc2").rllm_qkv_tc2(
+        _ptr(h), _ptr(w_qkv), c_int(n), c_int(h.shape[1]), c_int(h.stride(0)), c_int(w_qkv.stride(0)), _ptr(q_out),
+        _ptr(k_cache), _ptr(v_cache), _ptr(slots), _ptr(cs_table), _ptr(q_norm_w), _ptr(k_norm_w), c_int(H), c_int(K),
+        c_int(hd), c_int(block_size), c_float(eps), c_int(1 if write_kv else 0), c_longlong(n_slots),
+        _ptr(error_word(h.device)), _stream())
+    if st >= 30000:
+        raise KernelError(f"qkv_norm_rope_store_fused: tensor map encoding failed (CUresult {st - 30000})")
+    _check(st, "qkv_norm_rope_store_fused")
+    return q_out
+
+
 def tc_swap_splits(n_tiles: int, k: int, swiglu: bool = False, n_sm: int = 148) -> int:
     """Number of K splits (CTAs of a cluster) for the swapped tcgen05 product, a power of two up to
     8 (clusters of 3, 5, 6, 7 CTAs schedule badly) that leaves every CTA at least 4 blocks of 64

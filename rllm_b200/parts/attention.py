@@ -74,9 +74,16 @@ class Attention(Mixer):
         norm that follows and the rows come back as ops.NormedRows (needs `residual`)."""
         n = h.shape[0]
         dt = self.runtime.dtype
-        qkv = ops.linear(h, self.w_qkv, out_dtype=torch.float32)
-        q = torch.empty((n, self.H * self.hd), dtype=dt, device=qkv.device)
-        if position is not None and hasattr(position, "apply_and_store"):
+        q = torch.empty((n, self.H * self.hd), dtype=dt, device=self.w_qkv.device)
+        whole = getattr(position, "project_and_store", None)
+        if whole is not None and whole(h, self.w_qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, ctx, cache, q,
+                                       self.H, self.K, self.hd):
+            qkv = None                            # the position part did the projection too
+        else:
+            qkv = ops.linear(h, self.w_qkv, out_dtype=torch.float32)
+        if qkv is None:
+            pass
+        elif position is not None and hasattr(position, "apply_and_store"):
             # the position part does it all: q/k norm, its own encoding, queries out, keys and values stored
             position.apply_and_store(qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, ctx, cache, q,
                                      self.H, self.K, self.hd)

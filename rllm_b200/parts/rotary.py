@@ -18,6 +18,11 @@ layers of the pass can share).  Any scheme can be written this way, with
 kernels of its own or on top of ``ops.qk_norm_rope_store`` (which, without a table, norms and
 stores without rotating).
 
+``project_and_store(h, w_qkv, ...same arguments...) -> bool`` (optional): as apply_and_store, but the
+part is given the rows before the fused projection and the projection's matrix, and may do the
+projection too (one kernel with the norm, the encoding and the cache write in its epilogue); it
+returns False when it does not take the step.
+
 ``table()``: for schemes of the form "rotate pairs (i, i + head_dim/2) by position * table[i]":
 the float32 vector of head_dim/2 entries that the fused kernel takes; the mixer then calls the
 kernel itself.  This part offers both.
@@ -47,14 +52,29 @@ class RotaryNeox(Part):
     def table(self):
         return self.inv_freq
 
-    def apply_and_store(self, qkv, q_norm_w, k_norm_w, eps, ctx, cache, q_out, H, K, head_dim):
+    def _angles(self, ctx):
+        """(cos, sin) of the step's tokens: the same in every layer with this table, so once per pass."""
         from ..csrc import ops
-        # the angles of the step's tokens are the same in every layer with this table: once per pass
         key = ("rotary_neox", self.head_dim, self.theta)
         table = ctx.scratch.get(key)
         if table is None:
             with ops.untraced():                  # once per pass, not once per layer that replays this one
                 table = ctx.scratch[key] = ops.rope_table(ctx.positions, self.inv_freq)
+        return table
+
+    def apply_and_store(self, qkv, q_norm_w, k_norm_w, eps, ctx, cache, q_out, H, K, head_dim):
+        from ..csrc import ops
         return ops.qk_norm_rope_store(qkv, q_norm_w, k_norm_w, None, ctx.positions, cache.slots, q_out,
                                       cache.k, cache.v, H, K, head_dim, cache.block_size, eps, write_kv=cache.write,
-                                      cs_table=table)
+                                      cs_table=self._angles(ctx))
+
+    def project_and_store(self, h, w_qkv, q_norm_w, k_norm_w, eps, ctx, cache, q_out, H, K, head_dim) -> bool:
+        """Optional third form of a position part's interface: the part also does the q/k/v projection
+        h . w_qkv^T itself, so that it can be one kernel with what follows it.  Returns False when it
+        does not take the step (the mixer then projects and calls apply_and_store)."""
+        from ..csrc import ops
+        if not ops.can_fuse_qkv(h, w_qkv, head_dim, q_out, cache.k):
+            return False
+        ops.qkv_norm_rope_store_fused(h, w_qkv, q_norm_w, k_norm_w, self._angles(ctx), cache.slots, q_out, cache.k,
+                                      cache.v, H, K, head_dim, cache.block_size, eps, write_kv=cache.write)
+        return True

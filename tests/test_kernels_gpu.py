@@ -135,6 +135,49 @@ def test_qk_norm_rope_store_many_tokens(hd, H, K):
     o.check_device_errors()
 
 
+@pytest.mark.parametrize("hd,H,K,d,n", [(128, 8, 2, 512, 300), (64, 6, 3, 256, 1100), (128, 5, 1, 192, 257), (128, 32, 8, 1024, 1024)])
+def test_qkv_norm_rope_store_fused(hd, H, K, d, n):
+    """The q/k/v projection with the q/k norm, the rotary encoding and the cache write in the epilogue of
+    the two-SM product, against the product followed by the kernel that does those steps alone."""
+    o = ops()
+    bs, theta, eps = 16, 1e6, 1e-6
+    pages = -(-n // bs) + 2
+    g = torch.Generator().manual_seed(31)
+    h = rnd(n, d, seed=32, dtype=torch.bfloat16).to(DEV)
+    w = rnd((H + 2 * K) * hd, d, seed=33, scale=0.05, dtype=torch.bfloat16).to(DEV)
+    qw, kw = (1 + 0.1 * rnd(hd, seed=34)).to(DEV), (1 + 0.1 * rnd(hd, seed=35)).to(DEV)
+    positions = torch.randint(0, 9000, (n,), generator=g, dtype=torch.int32).to(DEV)
+    slots = torch.randperm(pages * bs, generator=g)[:n].to(torch.int32)
+    slots[7] = -1                                     # a token whose keys are not kept
+    slots = slots.to(DEV)
+    inv = (1.0 / torch.pow(torch.tensor(theta), torch.arange(0, hd, 2).float() / hd)).to(DEV)
+    table = o.rope_table(positions, inv)
+    outs = []
+    for fused in (False, True):
+        kc = torch.zeros(pages, K, bs, hd, dtype=torch.bfloat16, device=DEV)
+        vc = torch.zeros_like(kc)
+        q = torch.full((n, H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        if fused:
+            o.qkv_norm_rope_store_fused(h, w, qw, kw, table, slots, q, kc, vc, H, K, hd, bs, eps)
+        else:
+            qkv = o.linear(h, w, out_dtype=torch.float32)
+            o.qk_norm_rope_store(qkv, qw, kw, None, positions, slots, q, kc, vc, H, K, hd, bs, eps, cs_table=table)
+        outs.append((q.float().cpu(), kc.float().cpu(), vc.float().cpu()))
+    o.check_device_errors()
+    for name, x, y in zip("qkv", outs[1], outs[0]):
+        assert not torch.isnan(x).any()
+        assert rel_err(x, y) < 1e-2, name             # one bfloat16 rounding of values that differ in the last float32 bits
+        assert float((x - y).abs().mean() / y.abs().mean()) < 2e-3, name
+    # without norm weights and without a table: the plain projection, rounded
+    kc = torch.zeros(pages, K, bs, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = torch.empty(n, H * hd, dtype=torch.bfloat16, device=DEV)
+    o.qkv_norm_rope_store_fused(h, w, None, None, None, slots, q, kc, vc, H, K, hd, bs, eps)
+    ref = (h.float() @ w.float().t())[:, :H * hd]
+    assert rel_err(q.float().cpu(), ref.cpu()) < 1e-2
+    o.check_device_errors()
+
+
 def paged_case(hd, H, K, bs, lens, q_lens, seed, dtype, window=0, spike=False):
     """Builds a scattered paged cache for requests of `lens` tokens whose last `q_lens` tokens are
     the step's queries; returns kernel inputs and the plain reference output."""

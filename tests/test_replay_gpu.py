@@ -434,7 +434,21 @@ def test_long_context(long_dirs, dtype):
     refs = {"a": reference(long_dirs[dtype], dtype, toks)}
     eng = make_engine(long_dirs[dtype], dtype, max_tokens=3072 + 64, max_requests=2)
     places = sorted(set(range(0, n, 37)) | {1, 63, 64, 127, 128, 699, 700, 701, 2047, 2048, 2943, 2944, 2999, 3000})
-    out = helpers.run_steps(eng, [{"entries": [{"id": "a", "tokens": toks, "want": places}], "end": ["a"]}])
+    from rllm_b200.csrc import ops as _ops
+    fused_calls, real_fused = [0], _ops.qkv_norm_rope_store_fused
+
+    def spy_fused(*a, **k):
+        fused_calls[0] += 1
+        return real_fused(*a, **k)
+
+    _ops.qkv_norm_rope_store_fused = spy_fused
+    try:
+        out = helpers.run_steps(eng, [{"entries": [{"id": "a", "tokens": toks, "want": places}], "end": ["a"]}])
+    finally:
+        _ops.qkv_norm_rope_store_fused = real_fused
+    # the whole prompt in one step: in bfloat16 the q/k/v projection runs with the norm, the rotary
+    # encoding and the cache write in its epilogue (both layers, one of them with a window)
+    assert fused_calls[0] == (2 if dtype == "bfloat16" else 0)
     check_long(out, toks, long_dirs[dtype], dtype, refs, "long context, whole")
     # and bit for bit the same when run again, on other pages (the reference's prefill_is_deterministic,
     # crates/rllm-model/tests/common/gpu.rs:42-67): a race between the kernels' roles shows here first
