@@ -305,14 +305,14 @@ gemm_tc2_kernel(const __grid_constant__ T2Maps maps, TC* __restrict__ C, int ldc
                 }
                 const float2* cs = (qk.cs_table && row_ok) ? qk.cs_table + (size_t)gm * (HD / 2) : nullptr;
 #pragma unroll 1
-                for (int hh = 0; hh < T2_BN / HD; ++hh) {
+                for (int hh = 0; hh < cols_out / HD; ++hh) {
                     const int head = n0 / HD + hh;
                     float v[HD];
 #pragma unroll
                     for (int c = 0; c < HD / 32; ++c)
                         tmem_ld32(taddr + hh * HD + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&v[32 * c]));
                     tmem_ld_wait();
-                    if (hh == T2_BN / HD - 1) {                  // all of this warp's TMEM reads of the tile are done
+                    if (hh == cols_out / HD - 1) {               // all of this warp's TMEM reads of the item are done
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[buf], 0));
@@ -454,8 +454,8 @@ static int launch_tc2(const T2Maps& maps, void* C, int ldc, int M, int N, int K,
     const int all_pairs = n_sm / 2;
     const int rem = tiles % all_pairs;
     int tail_log2 = 0;
-    if (EPI == T2_EPI_QKV) tail_log2 = 0;                      // whole heads: a tile is not cut
-    else if (rem > 0 && rem * 4 <= all_pairs) tail_log2 = 2;
+    const int max_log2 = EPI == T2_EPI_QKV ? (HD == 64 ? 2 : 1) : 2;       // a slice holds whole heads
+    if (rem > 0 && rem * 4 <= all_pairs && max_log2 >= 2) tail_log2 = 2;
     else if (rem > 0 && rem * 2 <= all_pairs) tail_log2 = 1;
     const int tail_tiles = tail_log2 ? rem : 0;
     const int items = tiles - tail_tiles + (tail_tiles << tail_log2);

@@ -596,10 +596,10 @@ def gemm_tc2(a, w, out, epilogue=EPI_STORE, up_row_offset=0):
     return out
 
 
-# From this many rows on the fused projection beats the library product followed by the q/k norm + rotary
-# kernel (us, library + kernel / fused; 8B sizes: 1,024 rows 46.5 / 52.6, 2,048 rows 90.2 / 78.1, 4,096 rows
-# 180.8 / 147.5; 0.6B sizes: 1,024 rows 23.0 / 24.1, 2,048 rows 35.3 / 32.8; 32B sizes: 2,048 rows 170.7 / 152.6)
-QKV_FUSED_MIN_ROWS = 2048
+# From this many rows on the fused projection is at least as fast as the library product followed by the q/k
+# norm + rotary kernel (us, library + kernel / fused; 8B sizes: 1,024 rows 46.6 / 46.1, 1,536 rows 64.4 / 58.2,
+# 2,048 rows 90.1 / 78.1; 0.6B sizes: 512 rows 10.9 / 12.5, 1,024 rows 20.8 / 19.0; 32B sizes: 2,048 rows 170 / 147)
+QKV_FUSED_MIN_ROWS = 1024
 USE_QKV_FUSED = os.environ.get("RLLM_B200_NO_QKV_FUSED", "0") in ("", "0")
 
 
