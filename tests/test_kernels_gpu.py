@@ -168,6 +168,12 @@ def test_qkv_norm_rope_store_fused(hd, H, K, d, n):
         assert not torch.isnan(x).any()
         assert rel_err(x, y) < 1e-2, name             # one bfloat16 rounding of values that differ in the last float32 bits
         assert float((x - y).abs().mean() / y.abs().mean()) < 2e-3, name
+    # a layer that reads another layer's cache writes none of its own: the queries only
+    kc = torch.zeros(pages, K, bs, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = torch.empty(n, H * hd, dtype=torch.bfloat16, device=DEV)
+    o.qkv_norm_rope_store_fused(h, w, qw, kw, table, slots, q, kc, vc, H, K, hd, bs, eps, write_kv=False)
+    assert torch.equal(q.float().cpu(), outs[1][0]) and float(kc.abs().max()) == 0.0 and float(vc.abs().max()) == 0.0
     # without norm weights and without a table: the plain projection, rounded
     kc = torch.zeros(pages, K, bs, hd, dtype=torch.bfloat16, device=DEV)
     vc = torch.zeros_like(kc)
